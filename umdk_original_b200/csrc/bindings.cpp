@@ -1,0 +1,611 @@
+// PyTorch binding layer: the six ops of the reference's `umdk_cam_op_lib`
+// (pybind/pybind.cpp:13-42, same names, same positional order) registered three ways like the
+// reference does -- schema (TORCH_LIBRARY), device implementation (CUDA key where the reference
+// uses PrivateUse1), Meta implementation for shape inference where shapes are not data dependent
+// (pybind/fused_deep_moe.cpp:87-122) and an Autograd-key wrapper that runs the op without
+// recording a graph (pybind/fused_deep_moe.cpp:152-217 returns empty grads) -- plus the explicit
+// symmetric `Buffer` object that replaces the HCCL group name / SHMEM heap pointer.
+//
+// `group_ep` / `groupEp` names a registered Buffer, `extInfo` is a registered Buffer's integer id.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+#include <torch/library.h>
+
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+
+#include "runtime/cam_runtime.h"
+
+namespace {
+
+#define CAM_ASSERT(cond, ...) TORCH_CHECK(cond, "umdk_cam_op_lib: ", __VA_ARGS__)
+#define CAM_RT(call) TORCH_CHECK((call) == 0, "umdk_cam_op_lib: ", cam_last_error())
+
+class Buffer;
+std::mutex g_reg_mutex;
+std::map<std::string, Buffer*> g_by_name;
+std::map<int64_t, Buffer*> g_by_id;
+int64_t g_next_id = 1;
+int g_phase_mask = 15;  // all phases; the single-GPU virtual-rank harness narrows it
+
+class Buffer {
+public:
+    Buffer(int64_t device, int64_t rank, int64_t num_ranks, int64_t num_experts, int64_t max_tokens, int64_t hidden,
+           int64_t topk, int64_t capacity, int64_t ll_max_tokens) {
+        CAM_RT(cam_layout_compute(&layout_, static_cast<int>(num_ranks), static_cast<int>(num_experts),
+                                  static_cast<int>(max_tokens), static_cast<int>(hidden), static_cast<int>(topk),
+                                  static_cast<int>(capacity), static_cast<int>(ll_max_tokens)));
+        buf_ = cam_buffer_create(static_cast<int>(device), static_cast<int>(rank), static_cast<int>(num_ranks), &layout_);
+        TORCH_CHECK(buf_ != nullptr, "umdk_cam_op_lib: ", cam_last_error());
+        std::lock_guard<std::mutex> g(g_reg_mutex);
+        id_ = g_next_id++;
+        g_by_id[id_] = this;
+    }
+    ~Buffer() { destroy(); }
+    void destroy() {
+        if (buf_ == nullptr) return;
+        {
+            std::lock_guard<std::mutex> g(g_reg_mutex);
+            g_by_id.erase(id_);
+            if (!name_.empty()) g_by_name.erase(name_);
+        }
+        ll_src_ = at::Tensor();
+        ll_total_ = at::Tensor();
+        cam_buffer_destroy(buf_);
+        buf_ = nullptr;
+    }
+    void register_name(const std::string& name) {
+        std::lock_guard<std::mutex> g(g_reg_mutex);
+        if (!name_.empty()) g_by_name.erase(name_);
+        name_ = name;
+        g_by_name[name] = this;
+    }
+    int64_t id() const { return id_; }
+    std::string name() const { return name_; }
+    py::bytes ipc_handle() {
+        char h[CAM_IPC_HANDLE_BYTES];
+        CAM_RT(cam_buffer_ipc_handle(buf_, h));
+        return py::bytes(h, CAM_IPC_HANDLE_BYTES);
+    }
+    void open_ipc_peers(const std::vector<std::string>& handles) {
+        CAM_ASSERT(static_cast<int>(handles.size()) == cam_buffer_num_ranks(buf_), "need one IPC handle per rank");
+        std::string all;
+        for (auto& h : handles) {
+            CAM_ASSERT(h.size() == CAM_IPC_HANDLE_BYTES, "bad IPC handle size");
+            all += h;
+        }
+        CAM_RT(cam_buffer_open_ipc_peers(buf_, all.data()));
+    }
+    void set_local_peers(const std::vector<Buffer*>& peers) {
+        std::vector<CamBuffer*> raw;
+        for (auto* p : peers) raw.push_back(p->buf_);
+        CAM_ASSERT(static_cast<int>(raw.size()) == cam_buffer_num_ranks(buf_), "need one peer per rank");
+        CAM_RT(cam_buffer_set_local_peers(buf_, raw.data()));
+    }
+    void reset() { CAM_RT(cam_buffer_reset(buf_, stream())); }
+    void set_timeout_ms(double ms) { cam_buffer_set_timeout_ms(buf_, ms); }
+    void set_debug_drop_flags(bool on) { cam_buffer_set_debug_drop_flags(buf_, on ? 1 : 0); }
+    std::tuple<int64_t, int64_t, int64_t, int64_t, std::string> poll_status() {
+        CamStatus st;
+        CAM_RT(cam_buffer_poll_status(buf_, stream(), &st));
+        return {st.code, st.who, st.detail, st.block, cam_status_string(st.code)};
+    }
+    int64_t total_bytes() const { return static_cast<int64_t>(layout_.total_bytes); }
+    int64_t capacity() const { return layout_.capacity; }
+
+    cudaStream_t stream() const { return at::cuda::getCurrentCUDAStream(cam_buffer_device(buf_)).stream(); }
+    c10::Device device() const { return c10::Device(c10::kCUDA, static_cast<c10::DeviceIndex>(cam_buffer_device(buf_))); }
+    at::Tensor view(void* ptr, at::IntArrayRef sizes, at::ScalarType dt) const {
+        return at::from_blob(ptr, sizes, at::TensorOptions().dtype(dt).device(device()));
+    }
+    at::Tensor recv_x(int64_t rows, int64_t h, int64_t quant_mode) const {
+        auto* base = static_cast<uint8_t*>(cam_buffer_base(buf_));
+        const at::ScalarType dt = quant_mode == 0 ? at::kBFloat16 : quant_mode == 2 ? at::kChar : at::kFloat8_e4m3fn;
+        return view(base + layout_.off_recv_x, {rows, h}, dt);
+    }
+    at::Tensor recv_scales(int64_t rows, int64_t n) const {
+        auto* base = static_cast<uint8_t*>(cam_buffer_base(buf_));
+        return view(base + layout_.off_recv_scales, {rows, n}, at::kFloat);
+    }
+    at::Tensor recv_src(int64_t rows) const {
+        auto* base = static_cast<uint8_t*>(cam_buffer_base(buf_));
+        return view(base + layout_.off_recv_src, {rows * 3}, at::kInt);
+    }
+    at::Tensor recv_count(int64_t n) const { return view(cam_buffer_recv_count(buf_), {n}, at::kInt); }
+    at::Tensor expert_offsets(int64_t n) const { return view(cam_buffer_expert_offsets(buf_), {n}, at::kInt); }
+    at::Tensor num_recv_per_expert(int64_t n) const { return view(cam_buffer_num_recv_per_expert(buf_), {n}, at::kLong); }
+    at::Tensor total_recv() const { return view(cam_buffer_total_recv(buf_), {1}, at::kInt); }
+    at::Tensor send_row(int64_t n) const { return view(cam_buffer_send_row(buf_), {n}, at::kInt); }
+    at::Tensor num_tokens_per_expert(int64_t n) const { return view(cam_buffer_num_tokens_per_expert(buf_), {n}, at::kInt); }
+    at::Tensor act_q(int64_t rows, int64_t cols) const { return view(cam_buffer_act_q(buf_), {rows, cols}, at::kFloat8_e4m3fn); }
+    at::Tensor act_s(int64_t rows, int64_t cols) const { return view(cam_buffer_act_s(buf_), {rows, cols}, at::kFloat); }
+
+    CamBuffer* raw() const { return buf_; }
+    const CamLayout& layout() const { return layout_; }
+    int rank() const { return cam_buffer_rank(buf_); }
+    int num_ranks() const { return cam_buffer_num_ranks(buf_); }
+    // state that low-latency dispatch leaves for the matching combine
+    at::Tensor ll_src_, ll_total_;
+
+private:
+    CamBuffer* buf_ = nullptr;
+    CamLayout layout_{};
+    int64_t id_ = 0;
+    std::string name_;
+};
+
+Buffer* buffer_by_name(c10::string_view name) {
+    std::lock_guard<std::mutex> g(g_reg_mutex);
+    auto it = g_by_name.find(std::string(name));
+    CAM_ASSERT(it != g_by_name.end(), "no Buffer is registered under the group name '", std::string(name),
+               "' (create a Buffer and call register_name first)");
+    return it->second;
+}
+Buffer* buffer_by_id(int64_t id) {
+    std::lock_guard<std::mutex> g(g_reg_mutex);
+    auto it = g_by_id.find(id);
+    CAM_ASSERT(it != g_by_id.end(), "extInfo ", id, " is not the id of a live Buffer");
+    return it->second;
+}
+
+int idx_kind(const at::Tensor& t, const char* what) {
+    CAM_ASSERT(t.scalar_type() == at::kLong || t.scalar_type() == at::kInt, what, " must be int64 or int32");
+    return t.scalar_type() == at::kLong ? 1 : 0;
+}
+void check_cuda_contig(const at::Tensor& t, const char* what) {
+    CAM_ASSERT(t.is_cuda(), what, " must be a CUDA tensor");
+    CAM_ASSERT(t.is_contiguous(), what, " must be contiguous");
+}
+
+// --------------------------------------------------------------------------------------------
+// get_dispatch_layout  (pybind/get_dispatch_layout.cpp:25-55)
+// --------------------------------------------------------------------------------------------
+std::tuple<at::Tensor, at::Tensor, at::Tensor> get_dispatch_layout_cuda(const at::Tensor& topk_idx,
+                                                                        int64_t num_experts, int64_t num_ranks) {
+    CAM_ASSERT(topk_idx.dim() == 2, "topk_idx must be 2-D [tokens, topk]");
+    check_cuda_contig(topk_idx, "topk_idx");
+    const int is64 = idx_kind(topk_idx, "topk_idx");
+    c10::cuda::CUDAGuard guard(topk_idx.device());
+    const int64_t T = topk_idx.size(0), K = topk_idx.size(1);
+    auto opts = topk_idx.options().dtype(at::kInt);
+    at::Tensor per_rank = at::zeros({num_ranks}, opts);
+    at::Tensor per_expert = at::zeros({num_experts}, opts);
+    at::Tensor in_rank = at::zeros({T, num_ranks}, topk_idx.options().dtype(at::kBool));
+    CAM_RT(cam_get_dispatch_layout(topk_idx.data_ptr(), is64, static_cast<int>(T), static_cast<int>(K),
+                                   static_cast<int>(num_experts), static_cast<int>(num_ranks),
+                                   per_rank.data_ptr<int>(), per_expert.data_ptr<int>(),
+                                   reinterpret_cast<uint8_t*>(in_rank.data_ptr<bool>()),
+                                   at::cuda::getCurrentCUDAStream().stream()));
+    return {per_rank, per_expert, in_rank};
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> get_dispatch_layout_meta(const at::Tensor& topk_idx,
+                                                                        int64_t num_experts, int64_t num_ranks) {
+    auto opts = topk_idx.options().dtype(at::kInt);
+    return {at::empty({num_ranks}, opts), at::empty({num_experts}, opts),
+            at::empty({topk_idx.size(0), num_ranks}, topk_idx.options().dtype(at::kBool))};
+}
+
+// --------------------------------------------------------------------------------------------
+// moe_dispatch_prefill  (pybind/moe_dispatch_prefill.cpp:26-192)
+// --------------------------------------------------------------------------------------------
+std::vector<at::Tensor> dispatch_prefill_impl(const at::Tensor& x, const at::Tensor& topk_idx,
+                                              const at::Tensor& topk_weights, int64_t num_worst_tokens,
+                                              c10::string_view group_ep, int64_t rank, int64_t num_ranks,
+                                              int64_t quant_mode, int64_t num_experts) {
+    Buffer* b = buffer_by_name(group_ep);
+    CAM_ASSERT(x.dim() == 2 && topk_idx.dim() == 2, "x must be [tokens, hidden] and topk_idx [tokens, topk]");
+    CAM_ASSERT(x.scalar_type() == at::kBFloat16, "x must be bfloat16");
+    check_cuda_contig(x, "x");
+    check_cuda_contig(topk_idx, "topk_idx");
+    CAM_ASSERT(topk_weights.sizes() == topk_idx.sizes(), "topk_weights must match topk_idx");
+    CAM_ASSERT(rank == b->rank() && num_ranks == b->num_ranks(), "rank/num_ranks do not match the Buffer of group '",
+               std::string(group_ep), "'");
+    CAM_ASSERT(x.size(0) == topk_idx.size(0), "x and topk_idx disagree on the token count");
+    const int is64 = idx_kind(topk_idx, "topk_idx");
+    c10::cuda::CUDAGuard guard(x.device());
+    const int64_t T = x.size(0), h = x.size(1), K = topk_idx.size(1);
+    const int64_t E = num_experts > 0 ? num_experts : b->layout().num_experts, El = E / num_ranks;
+    CAM_RT(cam_dispatch_normal(b->raw(), x.data_ptr(), topk_idx.data_ptr(), is64, static_cast<int>(T),
+                               static_cast<int>(K), static_cast<int>(h), static_cast<int>(E),
+                               static_cast<int>(quant_mode), g_phase_mask & 7, b->stream()));
+    int64_t rows = num_worst_tokens;
+    at::Tensor per_expert = b->num_recv_per_expert(El);
+    if (num_worst_tokens <= 0) {
+        // exact-size outputs need the row count on the host: one 4-byte copy (the reference syncs twice)
+        rows = b->total_recv().cpu().item<int>();
+        per_expert = per_expert.cpu();
+    }
+    CAM_ASSERT(rows <= b->capacity(), "num_worst_tokens exceeds the Buffer capacity");
+    const int64_t nscale = quant_mode == 3 ? h / 128 : (quant_mode == 2 ? 1 : 0);
+    at::Tensor scales = nscale > 0 ? b->recv_scales(rows, nscale) : at::empty({0}, x.options().dtype(at::kFloat));
+    return {b->recv_x(rows, h, quant_mode), b->recv_src(rows), b->recv_count(E), per_expert, scales};
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> moe_dispatch_prefill_cuda(
+    const at::Tensor& x, const at::Tensor& topk_idx, const at::Tensor& topk_weights,
+    const at::Tensor& num_tokens_per_rank, const at::Tensor& is_token_in_rank,
+    const at::Tensor& num_tokens_per_expert, int64_t num_worst_tokens, c10::string_view group_ep, int64_t rank,
+    int64_t num_ranks) {
+    (void)num_tokens_per_rank; (void)is_token_in_rank;  // the layout is recomputed on the device
+    auto r = dispatch_prefill_impl(x, topk_idx, topk_weights, num_worst_tokens, group_ep, rank, num_ranks, 0,
+                                   num_tokens_per_expert.numel());
+    return {r[0], r[1], r[2], r[3]};
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> moe_dispatch_prefill_quant_cuda(
+    const at::Tensor& x, const at::Tensor& topk_idx, const at::Tensor& topk_weights, int64_t num_worst_tokens,
+    c10::string_view group_ep, int64_t rank, int64_t num_ranks, int64_t quant_mode) {
+    auto r = dispatch_prefill_impl(x, topk_idx, topk_weights, num_worst_tokens, group_ep, rank, num_ranks, quant_mode, 0);
+    return {r[0], r[1], r[2], r[3], r[4]};
+}
+
+// --------------------------------------------------------------------------------------------
+// moe_combine_prefill  (pybind/moe_combine_prefill.cpp:26-74)
+// --------------------------------------------------------------------------------------------
+at::Tensor moe_combine_prefill_cuda(const at::Tensor& x, const at::Tensor& topk_idx, const at::Tensor& topk_weights,
+                                    const at::Tensor& src_idx, const at::Tensor& send_head,
+                                    c10::string_view group_ep, int64_t rank, int64_t num_ranks) {
+    Buffer* b = buffer_by_name(group_ep);
+    CAM_ASSERT(x.dim() == 2 && x.scalar_type() == at::kBFloat16, "x must be a 2-D bfloat16 tensor of expert outputs");
+    check_cuda_contig(x, "x");
+    check_cuda_contig(topk_idx, "topk_idx");
+    check_cuda_contig(src_idx, "src_idx");
+    CAM_ASSERT(src_idx.scalar_type() == at::kInt && src_idx.numel() >= x.size(0) * 3, "src_idx must hold 3 int32 per row of x");
+    CAM_ASSERT(topk_weights.scalar_type() == at::kFloat && topk_weights.sizes() == topk_idx.sizes(),
+               "topk_weights must be float32 with the shape of topk_idx");
+    CAM_ASSERT(rank == b->rank() && num_ranks == b->num_ranks(), "rank/num_ranks do not match the Buffer");
+    const int is64 = idx_kind(topk_idx, "topk_idx");
+    c10::cuda::CUDAGuard guard(x.device());
+    const int64_t T = topk_idx.size(0), K = topk_idx.size(1), h = x.size(1);
+    const int64_t E = send_head.numel();
+    at::Tensor w = topk_weights.contiguous();
+    at::Tensor out = at::empty({T, h}, x.options());
+    // rows actually present: the smaller of x's rows and the device-side count of the last dispatch
+    at::Tensor total = at::minimum(b->total_recv(), at::full({1}, x.size(0), b->total_recv().options()));
+    CAM_RT(cam_combine(b->raw(), x.data_ptr(), src_idx.data_ptr<int>(), total.data_ptr<int>(), topk_idx.data_ptr(),
+                       is64, w.data_ptr<float>(), out.data_ptr(), static_cast<int>(T), static_cast<int>(K),
+                       static_cast<int>(h), static_cast<int>(E), 0, (g_phase_mask & 7) & (CAM_PHASE_SEND | CAM_PHASE_RECV),
+                       b->stream()));
+    return out;
+}
+
+// --------------------------------------------------------------------------------------------
+// moe_dispatch_shmem / moe_combine_shmem  (pybind/moe_dispatch_shmem.cpp:27-153, moe_combine_shmem.cpp:27-85)
+// --------------------------------------------------------------------------------------------
+std::vector<at::Tensor> moe_dispatch_shmem_cuda(const at::Tensor& x, const at::Tensor& expertIds,
+                                                const c10::optional<at::Tensor>& scales,
+                                                const c10::optional<at::Tensor>& xActiveMask, int64_t epWorldSize,
+                                                int64_t epRankId, int64_t moeExpertNum, int64_t tpWorldSize,
+                                                int64_t tpRankId, int64_t expertShardType, int64_t sharedExpertNum,
+                                                int64_t sharedExpertRankNum, int64_t quantMode, int64_t globalBS,
+                                                int64_t expertTokenNumsType, int64_t extInfo) {
+    (void)tpRankId; (void)expertShardType; (void)globalBS; (void)sharedExpertNum;
+    Buffer* b = buffer_by_id(extInfo);
+    CAM_ASSERT(x.dim() == 2 && expertIds.dim() == 2, "x must be [bs, h] and expertIds [bs, k]");
+    CAM_ASSERT(x.scalar_type() == at::kBFloat16, "x must be bfloat16");
+    check_cuda_contig(x, "x");
+    check_cuda_contig(expertIds, "expertIds");
+    CAM_ASSERT(epWorldSize == b->num_ranks() && epRankId == b->rank(), "epWorldSize/epRankId do not match the Buffer");
+    CAM_ASSERT(tpWorldSize <= 1, "tpWorldSize > 1 is not supported by this build");
+    CAM_ASSERT(sharedExpertRankNum == 0, "shared-expert ranks are not supported by this build");
+    CAM_ASSERT(quantMode != 1, "static quantisation (quantMode 1) is rejected, as in the reference");
+    const int is64 = idx_kind(expertIds, "expertIds");
+    c10::cuda::CUDAGuard guard(x.device());
+    const int64_t T = x.size(0), h = x.size(1), K = expertIds.size(1);
+    const int64_t El = moeExpertNum / epWorldSize;
+    const int64_t A = std::max<int64_t>(1, T * epWorldSize * std::min<int64_t>(El, K));
+    int64_t active = T;
+    if (xActiveMask.has_value() && xActiveMask->defined()) active = xActiveMask->to(at::kLong).sum().item<int64_t>();
+    const float* smooth = nullptr;
+    at::Tensor smooth_t;
+    if (scales.has_value() && scales->defined() && quantMode == 2) {
+        smooth_t = scales->to(at::kFloat).contiguous();
+        CAM_ASSERT(smooth_t.dim() == 2 && smooth_t.size(0) >= moeExpertNum && smooth_t.size(1) == h,
+                   "scales must be [>= moeExpertNum, h]");
+        smooth = smooth_t.data_ptr<float>();
+    }
+    const at::ScalarType xdt = quantMode == 0 ? at::kBFloat16 : quantMode == 2 ? at::kChar : at::kFloat8_e4m3fn;
+    const int64_t nscale = quantMode == 3 ? h / 128 : 1;
+    at::Tensor expandX = at::empty({A, h}, x.options().dtype(xdt));
+    at::Tensor dynScales = quantMode == 3 ? at::empty({A, nscale}, x.options().dtype(at::kFloat))
+                                          : at::empty({A}, x.options().dtype(at::kFloat));
+    at::Tensor expandIdx = at::empty({T * K}, x.options().dtype(at::kInt));
+    at::Tensor expandSrc = at::empty({A, 3}, x.options().dtype(at::kInt));
+    at::Tensor tokenNums = at::empty({El}, x.options().dtype(at::kLong));
+    at::Tensor epSend = at::empty({epWorldSize * El}, x.options().dtype(at::kInt));
+    at::Tensor tpSend = at::zeros({std::max<int64_t>(tpWorldSize, 1)}, x.options().dtype(at::kInt));
+    at::Tensor total = at::zeros({1}, x.options().dtype(at::kInt));
+    CAM_RT(cam_dispatch_ll(b->raw(), x.data_ptr(), expertIds.data_ptr(), is64, smooth, static_cast<int>(T),
+                           static_cast<int>(K), static_cast<int>(h), static_cast<int>(moeExpertNum),
+                           static_cast<int>(active), static_cast<int>(quantMode), static_cast<int>(expertTokenNumsType),
+                           expandX.data_ptr(), dynScales.data_ptr<float>(), expandIdx.data_ptr<int>(),
+                           expandSrc.data_ptr<int>(), tokenNums.data_ptr<int64_t>(), epSend.data_ptr<int>(),
+                           total.data_ptr<int>(), (g_phase_mask & 7) & (CAM_PHASE_SEND | CAM_PHASE_RECV), b->stream()));
+    b->ll_src_ = expandSrc;
+    b->ll_total_ = total;
+    return {expandX, dynScales, expandIdx, tokenNums, epSend, tpSend};
+}
+
+std::vector<at::Tensor> moe_dispatch_shmem_meta(const at::Tensor& x, const at::Tensor& expertIds,
+                                                const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&,
+                                                int64_t epWorldSize, int64_t, int64_t moeExpertNum,
+                                                int64_t tpWorldSize, int64_t, int64_t, int64_t, int64_t,
+                                                int64_t quantMode, int64_t, int64_t, int64_t) {
+    const int64_t T = x.size(0), h = x.size(1), K = expertIds.size(1), El = moeExpertNum / epWorldSize;
+    const int64_t A = std::max<int64_t>(1, T * epWorldSize * std::min<int64_t>(El, K));
+    const at::ScalarType xdt = quantMode == 0 ? at::kBFloat16 : quantMode == 2 ? at::kChar : at::kFloat8_e4m3fn;
+    return {at::empty({A, h}, x.options().dtype(xdt)),
+            quantMode == 3 ? at::empty({A, h / 128}, x.options().dtype(at::kFloat)) : at::empty({A}, x.options().dtype(at::kFloat)),
+            at::empty({T * K}, x.options().dtype(at::kInt)), at::empty({El}, x.options().dtype(at::kLong)),
+            at::empty({epWorldSize * El}, x.options().dtype(at::kInt)),
+            at::empty({std::max<int64_t>(tpWorldSize, 1)}, x.options().dtype(at::kInt))};
+}
+
+at::Tensor moe_combine_shmem_cuda(const at::Tensor& expandX, const at::Tensor& expertIds, const at::Tensor& expandIdx,
+                                  const at::Tensor& epSendCounts, const at::Tensor& expertScales,
+                                  const c10::optional<at::Tensor>& tpSendCounts,
+                                  const c10::optional<at::Tensor>& xActiveMask,
+                                  const c10::optional<at::Tensor>& activationScale,
+                                  const c10::optional<at::Tensor>& weightScale,
+                                  const c10::optional<at::Tensor>& groupList,
+                                  const c10::optional<at::Tensor>& expandScales, int64_t epWorldSize, int64_t epRankId,
+                                  int64_t moeExpertNum, int64_t tpWorldSize, int64_t tpRankId, int64_t expertShardType,
+                                  int64_t sharedExpertNum, int64_t sharedExpertRankNum, int64_t globalBS,
+                                  int64_t commQuantMode, int64_t extInfo, int64_t outDtype, int64_t groupListType) {
+    (void)expandIdx; (void)epSendCounts; (void)tpSendCounts; (void)xActiveMask; (void)activationScale;
+    (void)weightScale; (void)groupList; (void)expandScales; (void)tpRankId; (void)expertShardType;
+    (void)sharedExpertNum; (void)globalBS; (void)outDtype; (void)groupListType;
+    Buffer* b = buffer_by_id(extInfo);
+    CAM_ASSERT(expandX.dim() == 2 && expandX.scalar_type() == at::kBFloat16, "expandX must be 2-D bfloat16");
+    check_cuda_contig(expandX, "expandX");
+    check_cuda_contig(expertIds, "expertIds");
+    CAM_ASSERT(epWorldSize == b->num_ranks() && epRankId == b->rank(), "epWorldSize/epRankId do not match the Buffer");
+    CAM_ASSERT(tpWorldSize <= 1 && sharedExpertRankNum == 0, "tp > 1 and shared-expert ranks are not supported");
+    CAM_ASSERT(commQuantMode == 0, "commQuantMode must be 0 in this build");
+    CAM_ASSERT(b->ll_src_.defined(), "moe_combine_shmem needs a preceding moe_dispatch_shmem on the same Buffer");
+    CAM_ASSERT(expertScales.scalar_type() == at::kFloat, "expertScales must be float32");
+    const int is64 = idx_kind(expertIds, "expertIds");
+    c10::cuda::CUDAGuard guard(expandX.device());
+    const int64_t T = expertIds.size(0), K = expertIds.size(1), h = expandX.size(1);
+    at::Tensor w = expertScales.contiguous();
+    at::Tensor out = at::empty({T, h}, expandX.options());
+    CAM_RT(cam_combine(b->raw(), expandX.data_ptr(), b->ll_src_.data_ptr<int>(), b->ll_total_.data_ptr<int>(),
+                       expertIds.data_ptr(), is64, w.data_ptr<float>(), out.data_ptr(), static_cast<int>(T),
+                       static_cast<int>(K), static_cast<int>(h), static_cast<int>(moeExpertNum), 1,
+                       (g_phase_mask & 7) & (CAM_PHASE_SEND | CAM_PHASE_RECV), b->stream()));
+    return out;
+}
+
+at::Tensor moe_combine_shmem_meta(const at::Tensor& expandX, const at::Tensor& expertIds, const at::Tensor&,
+                                  const at::Tensor&, const at::Tensor&, const c10::optional<at::Tensor>&,
+                                  const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&,
+                                  const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&,
+                                  const c10::optional<at::Tensor>&, int64_t, int64_t, int64_t, int64_t, int64_t,
+                                  int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t) {
+    return at::empty({expertIds.size(0), expandX.size(1)}, expandX.options());
+}
+
+// --------------------------------------------------------------------------------------------
+// fused_deep_moe  (pybind/fused_deep_moe.cpp:26-79).  quantMode 3 = block-scaled fp8 weights:
+// gmm1PermutedWeight [E_l, 2I, h] e4m3 (gate rows first) with scales [E_l, 2I/128, h/128],
+// gmm2Weight [E_l, h, I] e4m3 with scales [E_l, h/128, I/128]; a list of E_l per-expert tensors
+// is stacked once and cached by the Python layer before it reaches this function.
+// --------------------------------------------------------------------------------------------
+std::vector<at::Tensor> fused_deep_moe_cuda(const at::Tensor& x, const at::Tensor& expertIds,
+                                            at::TensorList gmm1PermutedWeight, at::TensorList gmm1PermutedWeightScale,
+                                            at::TensorList gmm2Weight, at::TensorList gmm2WeightScale,
+                                            const at::Tensor& expertScales,
+                                            const c10::optional<at::Tensor>& expertSmoothScales,
+                                            const c10::optional<at::Tensor>& xActiveMask, c10::string_view groupEp,
+                                            int64_t epRankSize, int64_t epRankId, int64_t moeExpertNum,
+                                            int64_t sharedExpertNum, int64_t sharedExpertRankNum, int64_t quantMode,
+                                            int64_t globalBs) {
+    (void)expertSmoothScales; (void)sharedExpertNum; (void)globalBs;
+    Buffer* b = buffer_by_name(groupEp);
+    CAM_ASSERT(x.dim() == 2 && expertIds.dim() == 2, "x must be [bs, h] and expertIds [bs, k]");
+    CAM_ASSERT(x.scalar_type() == at::kBFloat16, "x must be bfloat16");
+    check_cuda_contig(x, "x");
+    check_cuda_contig(expertIds, "expertIds");
+    CAM_ASSERT(epRankSize == b->num_ranks() && epRankId == b->rank(), "epRankSize/epRankId do not match the Buffer");
+    CAM_ASSERT(sharedExpertRankNum == 0, "shared-expert ranks are not supported by this build");
+    CAM_ASSERT(quantMode == 3, "this entry point runs the block-scaled fp8 path (quantMode 3); "
+               "int8 W8A8 weights are converted by umdk_original_b200.models before the call");
+    CAM_ASSERT(gmm1PermutedWeight.size() == 1 && gmm2Weight.size() == 1 && gmm1PermutedWeightScale.size() == 1 &&
+                   gmm2WeightScale.size() == 1,
+               "stack per-expert tensor lists into one tensor per argument first");
+    const at::Tensor& w1 = gmm1PermutedWeight[0];
+    const at::Tensor& s1 = gmm1PermutedWeightScale[0];
+    const at::Tensor& w2 = gmm2Weight[0];
+    const at::Tensor& s2 = gmm2WeightScale[0];
+    const int64_t T = x.size(0), h = x.size(1), K = expertIds.size(1), El = moeExpertNum / epRankSize;
+    CAM_ASSERT(w1.dim() == 3 && w1.size(0) == El && w1.size(2) == h && w1.size(1) % 256 == 0,
+               "gmm1PermutedWeight must be [E_local, 2I, h] with 2I a multiple of 256");
+    const int64_t I = w1.size(1) / 2;
+    CAM_ASSERT(w2.dim() == 3 && w2.size(0) == El && w2.size(1) == h && w2.size(2) == I, "gmm2Weight must be [E_local, h, I]");
+    CAM_ASSERT(w1.scalar_type() == at::kFloat8_e4m3fn && w2.scalar_type() == at::kFloat8_e4m3fn, "weights must be float8_e4m3fn");
+    CAM_ASSERT(s1.scalar_type() == at::kFloat && s1.numel() == El * (2 * I / 128) * (h / 128), "gmm1 scale must be [E_local, 2I/128, h/128] float32");
+    CAM_ASSERT(s2.scalar_type() == at::kFloat && s2.numel() == El * (h / 128) * (I / 128), "gmm2 scale must be [E_local, h/128, I/128] float32");
+    for (const at::Tensor* t : {&w1, &s1, &w2, &s2}) check_cuda_contig(*t, "weight/scale");
+    CAM_ASSERT(expertScales.scalar_type() == at::kFloat, "expertScales must be float32");
+    const int is64 = idx_kind(expertIds, "expertIds");
+    c10::cuda::CUDAGuard guard(x.device());
+    at::Tensor ids = expertIds;
+    if (xActiveMask.has_value() && xActiveMask->defined()) {
+        // prefix mask: tokens past the active count do not take part (GMM1.h:647-678)
+        const int64_t active = xActiveMask->to(at::kLong).sum().item<int64_t>();
+        ids = expertIds.clone();
+        if (active < T) ids.slice(0, active, T).fill_(-1);
+    }
+    at::Tensor w = expertScales.contiguous();
+    at::Tensor out = at::empty({T, h}, x.options());
+    at::Tensor nums = at::zeros({El}, x.options().dtype(at::kLong));
+    CAM_RT(cam_fused_moe_fp8(b->raw(), x.data_ptr(), ids.data_ptr(), is64, w.data_ptr<float>(), w1.data_ptr(),
+                             s1.data_ptr<float>(), w2.data_ptr(), s2.data_ptr<float>(), out.data_ptr(),
+                             nums.data_ptr<int64_t>(), static_cast<int>(T), static_cast<int>(K), static_cast<int>(h),
+                             static_cast<int>(I), static_cast<int>(moeExpertNum), g_phase_mask, b->stream()));
+    return {out, nums};
+}
+
+std::vector<at::Tensor> fused_deep_moe_meta(const at::Tensor& x, const at::Tensor&, at::TensorList, at::TensorList,
+                                            at::TensorList, at::TensorList, const at::Tensor&,
+                                            const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&,
+                                            c10::string_view, int64_t epRankSize, int64_t epRankId, int64_t moeExpertNum,
+                                            int64_t, int64_t sharedExpertRankNum, int64_t, int64_t) {
+    const int64_t local = (epRankId < sharedExpertRankNum) ? 1 : moeExpertNum / (epRankSize - sharedExpertRankNum);
+    return {at::empty_like(x), at::empty({local}, x.options().dtype(at::kLong))};
+}
+
+// Stand-alone grouped GEMM (mode 0) for tests and for engines that only want the expert MLP.
+at::Tensor grouped_gemm_fp8_cuda(const at::Tensor& a_q, const at::Tensor& a_s, const at::Tensor& w_q,
+                                 const at::Tensor& w_s, const at::Tensor& expert_offsets) {
+    check_cuda_contig(a_q, "a_q");
+    check_cuda_contig(a_s, "a_s");
+    check_cuda_contig(w_q, "w_q");
+    check_cuda_contig(w_s, "w_s");
+    check_cuda_contig(expert_offsets, "expert_offsets");
+    CAM_ASSERT(a_q.dim() == 2 && w_q.dim() == 3 && a_q.size(1) == w_q.size(2), "a_q [M, K], w_q [E, N, K]");
+    CAM_ASSERT(a_q.scalar_type() == at::kFloat8_e4m3fn && w_q.scalar_type() == at::kFloat8_e4m3fn, "operands must be float8_e4m3fn");
+    CAM_ASSERT(expert_offsets.scalar_type() == at::kInt && expert_offsets.numel() == w_q.size(0) + 1, "expert_offsets must be int32 [E+1]");
+    const int64_t M = a_q.size(0), Kd = a_q.size(1), E = w_q.size(0), N = w_q.size(1);
+    CAM_ASSERT(a_s.scalar_type() == at::kFloat && a_s.numel() == M * (Kd / 128), "a_s must be float32 [M, K/128]");
+    CAM_ASSERT(w_s.scalar_type() == at::kFloat && w_s.numel() == E * (N / 128) * (Kd / 128), "w_s must be float32 [E, N/128, K/128]");
+    c10::cuda::CUDAGuard guard(a_q.device());
+    at::Tensor out = at::empty({M, N}, a_q.options().dtype(at::kBFloat16));
+    CAM_RT(cam_grouped_gemm_fp8(nullptr, a_q.data_ptr(), a_s.data_ptr<float>(), static_cast<int>(M), w_q.data_ptr(),
+                                w_s.data_ptr<float>(), expert_offsets.data_ptr<int>(), static_cast<int>(E),
+                                static_cast<int>(N), static_cast<int>(Kd), 0, out.data_ptr(), nullptr, nullptr, nullptr,
+                                1, 0, at::cuda::getCurrentCUDAStream().stream()));
+    return out;
+}
+
+// GEMM1 flavour stand-alone: returns (act_q [M, I] e4m3, act_s [M, I/128]).
+std::tuple<at::Tensor, at::Tensor> grouped_gemm_fp8_swiglu_cuda(const at::Tensor& a_q, const at::Tensor& a_s,
+                                                                const at::Tensor& w_q, const at::Tensor& w_s,
+                                                                const at::Tensor& expert_offsets) {
+    check_cuda_contig(a_q, "a_q");
+    check_cuda_contig(a_s, "a_s");
+    check_cuda_contig(w_q, "w_q");
+    check_cuda_contig(w_s, "w_s");
+    const int64_t M = a_q.size(0), Kd = a_q.size(1), E = w_q.size(0), N = w_q.size(1);
+    CAM_ASSERT(N % 256 == 0 && a_q.size(1) == w_q.size(2), "w_q must be [E, 2I, K] with 2I a multiple of 256");
+    c10::cuda::CUDAGuard guard(a_q.device());
+    at::Tensor q = at::zeros({M, N / 2}, a_q.options());
+    at::Tensor s = at::zeros({M, N / 2 / 128}, a_s.options());
+    CAM_RT(cam_grouped_gemm_fp8(nullptr, a_q.data_ptr(), a_s.data_ptr<float>(), static_cast<int>(M), w_q.data_ptr(),
+                                w_s.data_ptr<float>(), expert_offsets.data_ptr<int>(), static_cast<int>(E),
+                                static_cast<int>(N), static_cast<int>(Kd), 1, nullptr, q.data_ptr(), s.data_ptr<float>(),
+                                nullptr, 1, 0, at::cuda::getCurrentCUDAStream().stream()));
+    return {q, s};
+}
+
+// Autograd-key wrapper: runs below autograd, outputs carry no graph (inference-only op).
+std::vector<at::Tensor> fused_deep_moe_autograd(const at::Tensor& x, const at::Tensor& ids, at::TensorList a,
+                                                at::TensorList b2, at::TensorList c, at::TensorList d,
+                                                const at::Tensor& es, const c10::optional<at::Tensor>& sm,
+                                                const c10::optional<at::Tensor>& mask, c10::string_view g, int64_t i0,
+                                                int64_t i1, int64_t i2, int64_t i3, int64_t i4, int64_t i5, int64_t i6) {
+    at::AutoDispatchBelowADInplaceOrView guard;
+    static auto op = c10::Dispatcher::singleton().findSchemaOrThrow("umdk_cam_op_lib::fused_deep_moe", "")
+                         .typed<std::vector<at::Tensor>(const at::Tensor&, const at::Tensor&, at::TensorList, at::TensorList,
+                                                        at::TensorList, at::TensorList, const at::Tensor&,
+                                                        const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&,
+                                                        c10::string_view, int64_t, int64_t, int64_t, int64_t, int64_t,
+                                                        int64_t, int64_t)>();
+    return op.call(x, ids, a, b2, c, d, es, sm, mask, g, i0, i1, i2, i3, i4, i5, i6);
+}
+
+}  // namespace
+
+TORCH_LIBRARY(umdk_cam_op_lib, m) {
+    m.def("fused_deep_moe(Tensor x, Tensor expertIds, Tensor[] gmm1PermutedWeight, Tensor[] gmm1PermutedWeightScale, "
+          "Tensor[] gmm2Weight, Tensor[] gmm2WeightScale, Tensor expertScales, Tensor? expertSmoothScales, "
+          "Tensor? xActiveMask, str groupEp, int epRankSize, int epRankId, int moeExpertNum, int sharedExpertNum, "
+          "int sharedExpertRankNum, int quantMode, int globalBs) -> Tensor[]");
+    m.def("get_dispatch_layout(Tensor topk_idx, int num_experts, int num_ranks) -> (Tensor, Tensor, Tensor)");
+    m.def("moe_dispatch_prefill(Tensor x, Tensor topk_idx, Tensor topk_weights, Tensor num_tokens_per_rank, "
+          "Tensor is_token_in_rank, Tensor num_tokens_per_expert, int num_worst_tokens, str group_ep, int rank, "
+          "int num_ranks) -> (Tensor, Tensor, Tensor, Tensor)");
+    m.def("moe_combine_prefill(Tensor x, Tensor topk_idx, Tensor topk_weights, Tensor src_idx, Tensor send_head, "
+          "str group_ep, int rank, int num_ranks) -> Tensor");
+    m.def("moe_dispatch_shmem(Tensor x, Tensor expertIds, Tensor? scales, Tensor? xActiveMask, int epWorldSize, "
+          "int epRankId, int moeExpertNum, int tpWorldSize, int tpRankId, int expertShardType, int sharedExpertNum, "
+          "int sharedExpertRankNum, int quantMode, int globalBS, int expertTokenNumsType, int extInfo) -> Tensor[]");
+    m.def("moe_combine_shmem(Tensor expandX, Tensor expertIds, Tensor expandIdx, Tensor epSendCounts, "
+          "Tensor expertScales, Tensor? tpSendCounts, Tensor? xActiveMask, Tensor? activationScale, "
+          "Tensor? weightScale, Tensor? groupList, Tensor? expandScales, int epWorldSize, int epRankId, "
+          "int moeExpertNum, int tpWorldSize, int tpRankId, int expertShardType, int sharedExpertNum, "
+          "int sharedExpertRankNum, int globalBS, int commQuantMode, int extInfo, int outDtype, int groupListType) "
+          "-> Tensor");
+    // additions of this library (no counterpart schema in the reference)
+    m.def("moe_dispatch_prefill_quant(Tensor x, Tensor topk_idx, Tensor topk_weights, int num_worst_tokens, "
+          "str group_ep, int rank, int num_ranks, int quant_mode) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
+    m.def("grouped_gemm_fp8(Tensor a_q, Tensor a_s, Tensor w_q, Tensor w_s, Tensor expert_offsets) -> Tensor");
+    m.def("grouped_gemm_fp8_swiglu(Tensor a_q, Tensor a_s, Tensor w_q, Tensor w_s, Tensor expert_offsets) -> (Tensor, Tensor)");
+}
+
+TORCH_LIBRARY_IMPL(umdk_cam_op_lib, CUDA, m) {
+    m.impl("fused_deep_moe", &fused_deep_moe_cuda);
+    m.impl("get_dispatch_layout", &get_dispatch_layout_cuda);
+    m.impl("moe_dispatch_prefill", &moe_dispatch_prefill_cuda);
+    m.impl("moe_combine_prefill", &moe_combine_prefill_cuda);
+    m.impl("moe_dispatch_shmem", &moe_dispatch_shmem_cuda);
+    m.impl("moe_combine_shmem", &moe_combine_shmem_cuda);
+    m.impl("moe_dispatch_prefill_quant", &moe_dispatch_prefill_quant_cuda);
+    m.impl("grouped_gemm_fp8", &grouped_gemm_fp8_cuda);
+    m.impl("grouped_gemm_fp8_swiglu", &grouped_gemm_fp8_swiglu_cuda);
+}
+
+TORCH_LIBRARY_IMPL(umdk_cam_op_lib, Meta, m) {
+    m.impl("fused_deep_moe", &fused_deep_moe_meta);
+    m.impl("get_dispatch_layout", &get_dispatch_layout_meta);
+    m.impl("moe_dispatch_shmem", &moe_dispatch_shmem_meta);
+    m.impl("moe_combine_shmem", &moe_combine_shmem_meta);
+}
+
+TORCH_LIBRARY_IMPL(umdk_cam_op_lib, Autograd, m) {
+    m.impl("fused_deep_moe", &fused_deep_moe_autograd);
+    m.impl("get_dispatch_layout", torch::autograd::autogradNotImplementedFallback());
+    m.impl("moe_dispatch_prefill", torch::autograd::autogradNotImplementedFallback());
+    m.impl("moe_combine_prefill", torch::autograd::autogradNotImplementedFallback());
+    m.impl("moe_dispatch_shmem", torch::autograd::autogradNotImplementedFallback());
+    m.impl("moe_combine_shmem", torch::autograd::autogradNotImplementedFallback());
+}
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    m.doc() = "umdk_cam_op_lib for B200: symmetric Buffer + op registrations";
+    py::class_<Buffer>(m, "Buffer")
+        .def(py::init<int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t>(),
+             py::arg("device"), py::arg("rank"), py::arg("num_ranks"), py::arg("num_experts"), py::arg("max_tokens"),
+             py::arg("hidden"), py::arg("topk"), py::arg("capacity"), py::arg("ll_max_tokens") = 0)
+        .def("destroy", &Buffer::destroy)
+        .def("register_name", &Buffer::register_name)
+        .def_property_readonly("id", &Buffer::id)
+        .def_property_readonly("name", &Buffer::name)
+        .def_property_readonly("total_bytes", &Buffer::total_bytes)
+        .def_property_readonly("capacity", &Buffer::capacity)
+        .def("ipc_handle", &Buffer::ipc_handle)
+        .def("open_ipc_peers", &Buffer::open_ipc_peers)
+        .def("set_local_peers", &Buffer::set_local_peers)
+        .def("reset", &Buffer::reset)
+        .def("set_timeout_ms", &Buffer::set_timeout_ms)
+        .def("set_debug_drop_flags", &Buffer::set_debug_drop_flags)
+        .def("poll_status", &Buffer::poll_status)
+        .def("recv_x", &Buffer::recv_x)
+        .def("recv_scales", &Buffer::recv_scales)
+        .def("recv_src", &Buffer::recv_src)
+        .def("recv_count", &Buffer::recv_count)
+        .def("expert_offsets", &Buffer::expert_offsets)
+        .def("num_recv_per_expert", &Buffer::num_recv_per_expert)
+        .def("total_recv", &Buffer::total_recv)
+        .def("send_row", &Buffer::send_row)
+        .def("num_tokens_per_expert", &Buffer::num_tokens_per_expert)
+        .def("act_q", &Buffer::act_q)
+        .def("act_s", &Buffer::act_s);
+    m.def("set_phase_mask", [](int mask) { g_phase_mask = mask; });
+    m.def("get_phase_mask", []() { return g_phase_mask; });
+    m.def("status_string", [](int code) { return std::string(cam_status_string(code)); });
+}

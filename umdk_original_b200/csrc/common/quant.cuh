@@ -1,0 +1,98 @@
+// Warp-level row quantisation used by the dispatch kernels.
+//   fp8 1x128 : inv = 448 / max(amax_blk, 1e-4);  q = e4m3_rn_sat(x * inv);  scale = max(amax_blk, 1e-4) / 448
+//   int8 token: inv = 127 / (amax_row + 1e-12);   q = rint(x * inv);         scale = 1 / inv
+// The int8 form follows the per-token dynamic quantisation of the reference's dispatch kernels
+// (moe_dispatch_normal.h:289-315); the fp8 form is the DeepSeek-style block scaling.
+#pragma once
+#include "ptx.cuh"
+
+namespace cam {
+
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+    // cvt packs (hi, lo) -> the first source lands in the upper byte.
+    uint16_t lo, hi;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+    return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
+__device__ __forceinline__ float e4m3_to_float(uint8_t v) {
+    __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(v), __NV_E4M3);
+    return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+// One warp quantises one bf16 row of `h` elements (h % 256 == 0 handled fast, h % 128 == 0 in
+// general) to e4m3 with 1x128 scales.  Output goes to the warp's staging area in shared memory:
+// `q` (h bytes, 16-byte aligned) and `s` (h/128 floats).
+__device__ __forceinline__ void warp_quant_fp8_1x128(const __nv_bfloat16* __restrict__ row, int h,
+                                                     uint8_t* q, float* s) {
+    const uint32_t lane = lane_id();
+    // Each lane owns 8 consecutive elements per step; 16 lanes cover one 128-element block.
+    for (int base = 0; base < h; base += 256) {
+        const int col = base + static_cast<int>(lane) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        const bool in = col < h;
+        if (in) v = ld_nc_v4(row + col);
+        float f[8] = {bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y),
+                      bf16_lo(v.z), bf16_hi(v.z), bf16_lo(v.w), bf16_hi(v.w)};
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+#pragma unroll
+        for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+        const float a = fmaxf(amax, 1e-4f);
+        const float inv = 448.f / a;
+        if (in) {
+            uint2 o2;
+            o2.x = pack_e4m3x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+            o2.y = pack_e4m3x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+            *reinterpret_cast<uint2*>(q + col) = o2;
+            if ((lane & 15u) == 0u) s[col >> 7] = a / 448.f;
+        }
+    }
+}
+
+// One warp quantises one bf16 row to int8 with a single dynamic scale.  `q` holds h bytes,
+// s[0] receives the dequantisation scale.
+// `smooth` (optional, h floats) multiplies the row element-wise first (moe_dispatch_shmem.h:693-733).
+__device__ __forceinline__ void warp_quant_int8_token(const __nv_bfloat16* __restrict__ row, int h,
+                                                      uint8_t* q, float* s,
+                                                      const float* __restrict__ smooth = nullptr) {
+    const uint32_t lane = lane_id();
+    float amax = 0.f;
+    for (int col = static_cast<int>(lane) * 8; col < h; col += 256) {
+        uint4 v = ld_nc_v4(row + col);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float m0 = smooth ? smooth[col + 2 * i] : 1.f, m1 = smooth ? smooth[col + 2 * i + 1] : 1.f;
+            amax = fmaxf(amax, fabsf(bf16_lo(w[i]) * m0));
+            amax = fmaxf(amax, fabsf(bf16_hi(w[i]) * m1));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    const float inv = 127.f / (amax + 1e-12f);
+    for (int col = static_cast<int>(lane) * 8; col < h; col += 256) {
+        uint4 v = ld_nc_v4(row + col);  // second read hits L1/L2
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t out[2] = {0u, 0u};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float m0 = smooth ? smooth[col + 2 * i] : 1.f, m1 = smooth ? smooth[col + 2 * i + 1] : 1.f;
+            int a = __float2int_rn(bf16_lo(w[i]) * m0 * inv);
+            int b = __float2int_rn(bf16_hi(w[i]) * m1 * inv);
+            a = max(-127, min(127, a));
+            b = max(-127, min(127, b));
+            const uint32_t two = (static_cast<uint32_t>(a) & 0xFFu) | ((static_cast<uint32_t>(b) & 0xFFu) << 8);
+            out[i >> 1] |= two << ((i & 1) * 16);
+        }
+        *reinterpret_cast<uint2*>(q + col) = make_uint2(out[0], out[1]);
+    }
+    if (lane == 0) s[0] = 1.f / inv;
+}
+
+}  // namespace cam

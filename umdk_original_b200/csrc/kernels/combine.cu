@@ -1,0 +1,167 @@
+// Combine for sm_100a: every expert-output row is pushed with P2P stores into the (token, k)
+// slot of its origin rank, a per-source completion flag follows, and the origin fuses the
+// top-k weighted sum in fp32 (k order) with a round-to-nearest bf16 store.
+//
+// Same data flow as the reference's moe_combine_normal
+// (ascend_kernels/moe_combine_normal/op_kernel/moe_combine_normal.h:211-374) and, with the row
+// table that low-latency dispatch keeps, as moe_combine_shmem (moe_combine_shmem.h:919-930);
+// the per-(token,k) float flags summed by a vector reduce become one integer epoch flag per
+// source rank, raised once by the last CTA of the sender.  Pairs whose expert id is negative
+// are skipped instead of waited for.
+#include "../common/cam_types.h"
+#include "../common/ptx.cuh"
+#include "../common/quant.cuh"
+#include "launch.h"
+
+namespace cam {
+
+constexpr int kCombThreads = 512;
+constexpr int kCombWarps = kCombThreads / 32;
+
+__device__ __forceinline__ void comb_record_status(CamStatus* st, int code, int who, int detail) {
+    if (atomicCAS(&st->code, 0, code) == 0) {
+        st->who = who;
+        st->detail = detail;
+        st->block = static_cast<int>(blockIdx.x);
+    }
+}
+
+__device__ __forceinline__ int comb_expert_id(const void* idx, int is_i64, size_t i) {
+    return is_i64 ? static_cast<int>(reinterpret_cast<const long long*>(idx)[i])
+                  : reinterpret_cast<const int*>(idx)[i];
+}
+
+__device__ __forceinline__ void fma_bf16x8(float (&acc)[8], const uint4& v, float w) {
+    acc[0] = fmaf(w, bf16_lo(v.x), acc[0]);
+    acc[1] = fmaf(w, bf16_hi(v.x), acc[1]);
+    acc[2] = fmaf(w, bf16_lo(v.y), acc[2]);
+    acc[3] = fmaf(w, bf16_hi(v.y), acc[3]);
+    acc[4] = fmaf(w, bf16_lo(v.z), acc[4]);
+    acc[5] = fmaf(w, bf16_hi(v.z), acc[5]);
+    acc[6] = fmaf(w, bf16_lo(v.w), acc[6]);
+    acc[7] = fmaf(w, bf16_hi(v.w), acc[7]);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+}
+
+__global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineParams p) {
+    __shared__ uint32_t s_abort;
+    __shared__ float s_w[kCombWarps][CAM_MAX_TOPK];
+    const int tid = static_cast<int>(threadIdx.x);
+    const int warp = tid >> 5;
+    const uint32_t lane = lane_id();
+    const int nb = static_cast<int>(gridDim.x);
+    const int gwarp = static_cast<int>(blockIdx.x) * kCombWarps + warp;
+    const int nwarps = nb * kCombWarps;
+    const int row_bytes = p.h * 2;
+    if (tid == 0) s_abort = 0u;
+    __syncthreads();
+
+    // ------------------------------------------------------------------ SEND
+    if (p.phase_mask & CAM_PHASE_SEND) {
+        const int n = p.total_rows[0];
+        for (int i = gwarp; i < n; i += nwarps) {
+            const int src = p.row_src[static_cast<size_t>(i) * 3 + 0];
+            const int t = p.row_src[static_cast<size_t>(i) * 3 + 1];
+            const int k = p.row_src[static_cast<size_t>(i) * 3 + 2];
+            if (src < 0 || src >= p.R || t < 0 || k < 0 || k >= p.K) continue;  // defensive: never store out of range
+            const uint8_t* s = reinterpret_cast<const uint8_t*>(p.y) + static_cast<size_t>(i) * row_bytes;
+            uint8_t* d = p.peer_base[src] + p.off_combine_buf +
+                         (static_cast<size_t>(t) * p.K + k) * static_cast<size_t>(row_bytes);
+            int o = static_cast<int>(lane) * 16;
+            for (; o + 3 * 512 < row_bytes; o += 4 * 512) {
+                const uint4 a = ld_nc_v4(s + o), b4 = ld_nc_v4(s + o + 512), c = ld_nc_v4(s + o + 1024),
+                            e = ld_nc_v4(s + o + 1536);
+                st_na_v4(d + o, a);
+                st_na_v4(d + o + 512, b4);
+                st_na_v4(d + o + 1024, c);
+                st_na_v4(d + o + 1536, e);
+            }
+            for (; o < row_bytes; o += 512) st_na_v4(d + o, ld_nc_v4(s + o));
+        }
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence_system();
+            const unsigned int old = atomicAdd(p.done_ctr, 1u);
+            if (old == static_cast<unsigned int>(nb - 1)) {
+                p.done_ctr[0] = 0u;
+                __threadfence_system();
+                if (p.dbg_drop_flags == 0) {
+                    for (int d = 0; d < p.R; ++d)
+                        st_release_sys_u32(
+                            reinterpret_cast<uint32_t*>(p.peer_base[d] + p.off_combine_flag) + p.rank, p.epoch);
+                }
+            }
+        }
+    }
+
+    // ------------------------------------------------------------------ RECV
+    if (p.phase_mask & CAM_PHASE_RECV) {
+        uint8_t* const my_base = p.peer_base[p.rank];
+        if (tid < p.R) {
+            const uint32_t* f = reinterpret_cast<const uint32_t*>(my_base + p.off_combine_flag) + tid;
+            if (!wait_flag_eq_sys(f, p.epoch, p.timeout_ns)) {
+                comb_record_status(p.status, CAM_ERR_TIMEOUT_COMBINE_FLAG, tid,
+                                   static_cast<int>(ld_acquire_sys_u32(f)));
+                s_abort = 1u;
+            }
+        }
+        __syncthreads();
+        if (s_abort) return;
+
+        const uint8_t* buf = my_base + p.off_combine_buf;
+        for (int t = gwarp; t < p.T; t += nwarps) {
+            bool pair_ok = false;
+            if (lane < static_cast<uint32_t>(p.K)) {
+                const int id = comb_expert_id(p.topk_idx, p.idx_is_i64, static_cast<size_t>(t) * p.K + lane);
+                s_w[warp][lane] = p.topk_weights[static_cast<size_t>(t) * p.K + lane];
+                pair_ok = (id >= 0 && id < p.E);
+            }
+            const uint32_t valid = __ballot_sync(0xFFFFFFFFu, pair_ok);  // bit k: pair (t, k) has a row
+            __syncwarp();
+            const uint8_t* trow = buf + static_cast<size_t>(t) * p.K * row_bytes;
+            uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) + static_cast<size_t>(t) * row_bytes;
+            for (int o = static_cast<int>(lane) * 16; o < row_bytes; o += 512) {
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                for (int k0 = 0; k0 < p.K; k0 += 8) {
+                    uint4 v[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int k = k0 + j;
+                        const bool ok = (k < p.K) && ((valid >> k) & 1u);
+                        v[j] = ok ? ld_cg_v4(trow + static_cast<size_t>(k) * row_bytes + o) : make_uint4(0, 0, 0, 0);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int k = k0 + j;
+                        if (k < p.K && ((valid >> k) & 1u)) fma_bf16x8(acc, v[j], s_w[warp][k]);
+                    }
+                }
+                uint4 r;
+                r.x = pack_bf16x2(acc[0], acc[1]);
+                r.y = pack_bf16x2(acc[2], acc[3]);
+                r.z = pack_bf16x2(acc[4], acc[5]);
+                r.w = pack_bf16x2(acc[6], acc[7]);
+                st_na_v4(orow + o, r);
+            }
+            __syncwarp();
+        }
+    }
+}
+
+}  // namespace cam
+
+extern "C" int cam_combine_max_grid(int device) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return -1;
+    return sms;
+}
+
+extern "C" int cam_launch_combine(const cam::CombineParams* p, int grid, cudaStream_t stream) {
+    void* args[] = {const_cast<cam::CombineParams*>(p)};
+    return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(cam::combine_kernel), dim3(grid),
+                                                        dim3(cam::kCombThreads), args, 0, stream));
+}

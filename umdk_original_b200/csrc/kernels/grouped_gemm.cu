@@ -1,0 +1,365 @@
+// Grouped (per-expert, ragged-M) block-scaled fp8 GEMM for sm_100a, written directly on
+// tcgen05 / TMEM / TMA, with three epilogues:
+//   mode 0  dequantised bf16 tile to a local [rows, N] tensor (stand-alone grouped GEMM)
+//   mode 1  GEMM1 of the MoE MLP: SiLU(gate) * up on the fp32 accumulators, then 1x128 fp8
+//           re-quantisation -> feeds GEMM2 without an extra pass over memory
+//   mode 2  GEMM2: bf16 tile pushed with P2P stores straight into the (token, k) combine slot
+//           of the token's origin rank; the last CTA raises this rank's combine flag in every
+//           peer, so the combine transfer overlaps the tensor-core tiles
+//
+// It stands where the reference has its two CATLASS-based kernels
+// GroupedMatmulSliceMPerTokenDequantSwigluQuant (fused_deep_moe/gemm/kernel/
+// grouped_matmul_slice_m_per_token_dequant_swiglu_quant_multistage_workspace.h:355-1718) and
+// GroupedMatmulSliceMPerTokenDequant (..._dequant_multistage_workspace.h:24-378), the SwiGLU
+// epilogue (epilogue/block/block_epilogue_per_token_dequant_swiglu.h:236-272: first half of N is
+// the gate) and the combine-send epilogue (block_epilogue_per_token_dequant.hpp:531-570).
+//
+// Tile: 128 rows x 256 columns x 128 K per pipeline stage.  The 256 columns are two 128-row
+// B boxes, which for mode 1 are the gate rows [n, n+128) and the up rows [I+n, I+n+128) of the
+// same expert, so one thread owns matching gate/up columns.
+// Scaling: activations carry one fp32 scale per (row, 128 K), weights one per (128 N, 128 K).
+// Each 128-K block is multiplied into a fresh TMEM accumulator (two TMEM stages of 256 columns)
+// and promoted into fp32 registers by the epilogue warps while the tensor core works on the
+// next block.
+//
+// Warp roles (384 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 4..11 = epilogue (warp w reads TMEM lanes 32*(w%4).., column half (w-4)/4).
+// Every mbarrier wait is bounded; a role that gives up sets a shared abort word that releases
+// the others, a status word is recorded and the CTA frees its TMEM and returns.
+#include "../common/cam_types.h"
+#include "../common/ptx.cuh"
+#include "../common/quant.cuh"
+#include "launch.h"
+
+namespace cam {
+
+constexpr int BM = 128, BN = 256, BK = 128, kStages = 4;
+constexpr int kATile = BM * BK;            // 16 KiB
+constexpr int kBTile = BN * BK;            // 32 KiB
+constexpr int kStageBytes = kATile + kBTile;
+constexpr int kGemmThreads = 384;
+constexpr int kEpiThreads = 256;
+constexpr int kSmemCtrl = 2048;
+constexpr int kGemmSmem = kStages * kStageBytes + kSmemCtrl + 1024;  // +1024 alignment slack
+constexpr uint32_t kTmemCols = 512;
+
+struct TileWalker {
+    const int* off;
+    int num_experts, n_tiles;
+    int e, base;
+    __device__ TileWalker(const int* o, int ne, int nt) : off(o), num_experts(ne), n_tiles(nt), e(0), base(0) {}
+    // Maps a linear tile index (monotonically increasing across calls) to its expert and tile.
+    __device__ bool locate(int tile, int& e_out, int& mt, int& nt, int& row0, int& rows) {
+        while (e < num_experts) {
+            const int first = __ldg(off + e);
+            const int cnt = __ldg(off + e + 1) - first;
+            const int tiles = ((cnt + BM - 1) / BM) * n_tiles;
+            if (tile < base + tiles) {
+                const int local = tile - base;
+                mt = local / n_tiles;
+                nt = local - mt * n_tiles;
+                row0 = first + mt * BM;
+                rows = min(BM, cnt - mt * BM);
+                e_out = e;
+                return true;
+            }
+            base += tiles;
+            ++e;
+        }
+        return false;
+    }
+};
+
+__device__ __forceinline__ void gemm_record_status(CamStatus* st, int code, int who, int detail) {
+    if (atomicCAS(&st->code, 0, code) == 0) {
+        st->who = who;
+        st->detail = detail;
+        st->block = static_cast<int>(blockIdx.x);
+    }
+}
+
+// tcgen05.wait::ld that also names the destination registers, so no use of them can be
+// scheduled ahead of the wait.
+__device__ __forceinline__ void tc_wait_ld_regs(uint32_t (&v)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]),
+                   "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]),
+                   "+r"(v[14]), "+r"(v[15]), "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]),
+                   "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]), "+r"(v[24]), "+r"(v[25]),
+                   "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+                 :
+                 : "memory");
+}
+
+template <int OFF>
+__device__ __forceinline__ void promote32(float (&acc)[128], const uint32_t (&v)[32], float s) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) acc[OFF + j] = fmaf(s, __uint_as_float(v[j]), acc[OFF + j]);
+}
+
+__device__ __forceinline__ uint4 pack_bf16x8(float a0, float a1, float a2, float a3, float a4, float a5,
+                                             float a6, float a7) {
+    uint4 r;
+    __nv_bfloat162 t0 = __floats2bfloat162_rn(a0, a1);
+    __nv_bfloat162 t1 = __floats2bfloat162_rn(a2, a3);
+    __nv_bfloat162 t2 = __floats2bfloat162_rn(a4, a5);
+    __nv_bfloat162 t3 = __floats2bfloat162_rn(a6, a7);
+    r.x = *reinterpret_cast<uint32_t*>(&t0);
+    r.y = *reinterpret_cast<uint32_t*>(&t1);
+    r.z = *reinterpret_cast<uint32_t*>(&t2);
+    r.w = *reinterpret_cast<uint32_t*>(&t3);
+    return r;
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const GroupedGemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* ctrl = smem + kStages * kStageBytes;
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(ctrl);
+    uint64_t* bar_empty = bar_full + kStages;
+    uint64_t* bar_tfull = bar_empty + kStages;
+    uint64_t* bar_tempty = bar_tfull + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    float* s_amax = reinterpret_cast<float*>(ctrl + 256);  // [2 parities][2 halves][128 rows]
+
+    const int warp = static_cast<int>(threadIdx.x) >> 5;
+    const uint32_t lane = lane_id();
+    const int kblocks = p.k_dim / BK;
+    const int n_tiles = (p.mode == 1) ? (p.n_dim / 2) / 128 : (p.n_dim + BN - 1) / BN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&bar_tfull[a], 1);
+            mbar_init(&bar_tempty[a], kEpiThreads / 32);
+        }
+        *abort_flag = 0u;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 4) {
+        reg_dealloc<40>();
+        if (warp == 0 && lane == 0) {
+            // ------------------------------------------------------------ TMA producer
+            prefetch_tensormap(&tmap_a);
+            prefetch_tensormap(&tmap_b);
+            TileWalker w(p.expert_offsets, p.num_experts, n_tiles);
+            uint32_t it = 0;
+            int e, mt, nt, row0, rows;
+            bool ok = true;
+            for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
+                 tile += static_cast<int>(gridDim.x)) {
+                const int brow_lo = e * p.n_dim + ((p.mode == 1) ? nt * 128 : nt * BN);
+                const int brow_hi = (p.mode == 1) ? (e * p.n_dim + p.n_dim / 2 + nt * 128) : (brow_lo + 128);
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    if (!mbar_wait_bounded(&bar_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                    uint8_t* sa = smem + s * kStageBytes;
+                    mbar_arrive_expect_tx(&bar_full[s], kStageBytes);
+                    tma_load_2d(sa, &tmap_a, &bar_full[s], kb * BK, row0);
+                    tma_load_2d(sa + kATile, &tmap_b, &bar_full[s], kb * BK, brow_lo);
+                    tma_load_2d(sa + kATile + kBTile / 2, &tmap_b, &bar_full[s], kb * BK, brow_hi);
+                }
+            }
+            if (!ok) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 0, static_cast<int>(it));
+        } else if (warp == 1 && lane == 0) {
+            // ------------------------------------------------------------ MMA issuer
+            constexpr uint32_t idesc = umma_idesc(BM, BN, /*c=f32*/ 1u, /*e4m3*/ 0u);
+            TileWalker w(p.expert_offsets, p.num_experts, n_tiles);
+            uint32_t it = 0;
+            int e, mt, nt, row0, rows;
+            bool ok = true;
+            for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
+                 tile += static_cast<int>(gridDim.x)) {
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    const uint32_t a = it & 1u, aph = (it >> 1) & 1u;
+                    if (!mbar_wait_bounded(&bar_tempty[a], aph ^ 1u, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait_bounded(&bar_full[s], ph, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_u32(smem + s * kStageBytes);
+                    const uint64_t adesc = umma_desc_k_sw128(sa);
+                    const uint64_t bdesc = umma_desc_k_sw128(sa + kATile);
+                    const uint32_t d = tmem_base + a * BN;
+#pragma unroll
+                    for (int k = 0; k < BK / 32; ++k)  // advance 32 bytes (= 2 x 16) along K inside the swizzle atom
+                        tc_mma_f8(d, adesc + 2u * k, bdesc + 2u * k, idesc, k > 0 ? 1u : 0u);
+                    tc_commit(&bar_empty[s]);  // smem stage reusable once these MMAs retire
+                    tc_commit(&bar_tfull[a]);  // accumulator stage ready for the epilogue
+                }
+            }
+            if (!ok) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 1, static_cast<int>(it));
+        }
+    } else {
+        reg_alloc<232>();
+        // ---------------------------------------------------------------- epilogue warps
+        const int ew = warp - 4;
+        const int q = warp & 3;   // TMEM lane quarter this warp may read
+        const int ch = ew >> 2;   // which 64-column half of each 128-column block
+        const int r = q * 32 + static_cast<int>(lane);
+        const int kbs = kblocks;  // scales per row of A
+        const int nblk = p.n_dim / 128;
+        TileWalker w(p.expert_offsets, p.num_experts, n_tiles);
+        uint32_t it = 0;
+        uint32_t tile_parity = 0;
+        int e, mt, nt, row0, rows;
+        bool ok = true;
+        for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
+             tile += static_cast<int>(gridDim.x), tile_parity ^= 1u) {
+            const bool valid = r < rows;
+            const int grow = row0 + (valid ? r : 0);
+            const float* as = p.a_scales + static_cast<size_t>(grow) * kbs;
+            int nb_lo, nb_hi;
+            if (p.mode == 1) { nb_lo = nt; nb_hi = nblk / 2 + nt; }
+            else { nb_lo = 2 * nt; nb_hi = min(2 * nt + 1, nblk - 1); }
+            const float* bs_lo = p.b_scales + (static_cast<size_t>(e) * nblk + nb_lo) * kbs;
+            const float* bs_hi = p.b_scales + (static_cast<size_t>(e) * nblk + nb_hi) * kbs;
+
+            float acc[128];
+#pragma unroll
+            for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+
+            float sa_next = __ldg(as), wl_next = __ldg(bs_lo), wh_next = __ldg(bs_hi);
+            for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                const float s_lo = sa_next * wl_next, s_hi = sa_next * wh_next;
+                if (kb + 1 < kblocks) {
+                    sa_next = __ldg(as + kb + 1);
+                    wl_next = __ldg(bs_lo + kb + 1);
+                    wh_next = __ldg(bs_hi + kb + 1);
+                }
+                const uint32_t a = it & 1u, aph = (it >> 1) & 1u;
+                if (!mbar_wait_bounded(&bar_tfull[a], aph, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * BN + ch * 64;
+                uint32_t v0[32], v1[32];
+                tmem_ld_32x32b_x32(t0, v0);
+                tc_wait_ld_regs(v0);
+                tmem_ld_32x32b_x32(t0 + 32, v1);
+                promote32<0>(acc, v0, s_lo);
+                tc_wait_ld_regs(v1);
+                tmem_ld_32x32b_x32(t0 + 128, v0);
+                promote32<32>(acc, v1, s_lo);
+                tc_wait_ld_regs(v0);
+                tmem_ld_32x32b_x32(t0 + 160, v1);
+                promote32<64>(acc, v0, s_hi);
+                tc_wait_ld_regs(v1);
+                // all TMEM reads of this stage are done: hand it back to the MMA issuer
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_tempty[a]);
+                promote32<96>(acc, v1, s_hi);
+            }
+            if (!ok) break;
+
+            if (p.mode == 1) {
+                // SwiGLU on matching gate/up columns, then 1x128 fp8 requantisation of the row block.
+                const int ia = p.n_dim / 2;
+                float amax = 0.f;
+#pragma unroll
+                for (int j = 0; j < 64; ++j) {
+                    const float g = acc[j];
+                    const float act = (g / (1.f + expf(-g))) * acc[64 + j];
+                    acc[j] = act;
+                    amax = fmaxf(amax, fabsf(act));
+                }
+                float* xch = s_amax + tile_parity * 256;
+                xch[ch * 128 + r] = amax;
+                named_bar_sync(1, kEpiThreads);
+                amax = fmaxf(xch[r], xch[128 + r]);
+                const float a_cl = fmaxf(amax, 1e-4f);
+                const float inv = 448.f / a_cl;
+                if (valid) {
+                    uint8_t* dst = p.act_q + static_cast<size_t>(grow) * ia + nt * 128 + ch * 64;
+#pragma unroll
+                    for (int j = 0; j < 64; j += 16) {
+                        uint4 o;
+                        o.x = pack_e4m3x4(acc[j + 0] * inv, acc[j + 1] * inv, acc[j + 2] * inv, acc[j + 3] * inv);
+                        o.y = pack_e4m3x4(acc[j + 4] * inv, acc[j + 5] * inv, acc[j + 6] * inv, acc[j + 7] * inv);
+                        o.z = pack_e4m3x4(acc[j + 8] * inv, acc[j + 9] * inv, acc[j + 10] * inv, acc[j + 11] * inv);
+                        o.w = pack_e4m3x4(acc[j + 12] * inv, acc[j + 13] * inv, acc[j + 14] * inv, acc[j + 15] * inv);
+                        *reinterpret_cast<uint4*>(dst + j) = o;
+                    }
+                    if (ch == 0) p.act_s[static_cast<size_t>(grow) * (ia / 128) + nt] = a_cl / 448.f;
+                }
+            } else {
+                // bf16 tile, either to the local output or straight to the origin rank's combine slot
+                __nv_bfloat16* orow = nullptr;
+                if (valid) {
+                    if (p.mode == 0) {
+                        orow = p.out + static_cast<size_t>(grow) * p.n_dim;
+                    } else {
+                        const int src = p.row_src[static_cast<size_t>(grow) * 3 + 0];
+                        const int tok = p.row_src[static_cast<size_t>(grow) * 3 + 1];
+                        const int kk = p.row_src[static_cast<size_t>(grow) * 3 + 2];
+                        if (src >= 0 && src < p.num_ranks && tok >= 0 && kk >= 0 && kk < p.topk)
+                            orow = reinterpret_cast<__nv_bfloat16*>(p.peer_base[src] + p.off_combine_buf) +
+                                   (static_cast<size_t>(tok) * p.topk + kk) * static_cast<size_t>(p.n_dim);
+                    }
+                }
+                if (orow != nullptr) {
+                    const int c_lo = nt * BN + ch * 64;
+                    const int c_hi = c_lo + 128;
+                    if (c_lo < p.n_dim) {
+#pragma unroll
+                        for (int j = 0; j < 64; j += 8) st_na_v4(orow + c_lo + j, pack_bf16x8(acc[j], acc[j + 1], acc[j + 2], acc[j + 3], acc[j + 4],
+                                                                   acc[j + 5], acc[j + 6], acc[j + 7]));
+                    }
+                    if (c_hi < p.n_dim) {
+#pragma unroll
+                        for (int j = 0; j < 64; j += 8) st_na_v4(orow + c_hi + j, pack_bf16x8(acc[64 + j], acc[65 + j], acc[66 + j], acc[67 + j], acc[68 + j],
+                                                                   acc[69 + j], acc[70 + j], acc[71 + j]));
+                    }
+                }
+            }
+        }
+        if (!ok) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 2, static_cast<int>(it));
+    }
+
+    // ------------------------------------------------------------------ teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+    if (p.mode == 2 && threadIdx.x == 0) {
+        __threadfence_system();
+        const unsigned int old = atomicAdd(p.done_ctr, 1u);
+        if (old == gridDim.x - 1) {
+            p.done_ctr[0] = 0u;
+            __threadfence_system();
+            if (p.dbg_drop_flags == 0) {
+                for (int d = 0; d < p.num_ranks; ++d)
+                    st_release_sys_u32(reinterpret_cast<uint32_t*>(p.peer_base[d] + p.off_combine_flag) + p.rank,
+                                       p.epoch);
+            }
+        }
+    }
+}
+
+}  // namespace cam
+
+extern "C" int cam_grouped_gemm_smem_bytes(void) { return cam::kGemmSmem; }
+
+extern "C" int cam_launch_grouped_gemm_fp8(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
+                                           const CUtensorMap* tmap_b, int grid, cudaStream_t stream) {
+    cudaError_t e = cudaFuncSetAttribute(cam::grouped_gemm_fp8_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, cam::kGemmSmem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cam::grouped_gemm_fp8_kernel<<<grid, cam::kGemmThreads, cam::kGemmSmem, stream>>>(*tmap_a, *tmap_b, *p);
+    return static_cast<int>(cudaGetLastError());
+}

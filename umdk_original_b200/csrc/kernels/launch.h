@@ -1,0 +1,128 @@
+// Parameter blocks and C-ABI launchers of every kernel in the library.  The launchers take raw
+// device pointers only, so they can be driven from the torch bindings, from the C runtime or
+// straight from ctypes.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "../common/cam_types.h"
+
+namespace cam {
+
+struct DispatchNormalParams {
+    const __nv_bfloat16* x;  // [T, h]
+    const void* topk_idx;    // [T, K] int64 or int32, ids outside [0, E) are skipped
+    int idx_is_i64;
+    int T, K, h, E, R, rank;
+    int quant_mode;  // CamQuantMode
+    int capacity;    // rows of every rank's receive buffer
+    uint32_t epoch;  // per-buffer call counter; flags carry it, count matrix ping-pongs on its parity
+    uint64_t timeout_ns;
+    int phase_mask;      // CamPhase bits
+    int dbg_drop_flags;  // host-side fault injection: this rank withholds its flags
+    uint8_t* const* peer_base;  // [R] base of every rank's symmetric allocation (device array)
+    uint64_t off_count_flag, off_data_flag, off_count_matrix, off_recv_x, off_recv_scales, off_recv_src;
+    // local workspace / outputs
+    int* cta_hist;                  // [grid, E]
+    int* slot_in_expert;            // [T*K]
+    int* send_row;                  // [T*K] row at the destination, -1 when skipped
+    int* recv_count;                // [E_local*R] inclusive cumsum (expert major, source minor)
+    int* expert_offsets;            // [E_local+1]
+    int64_t* num_recv_per_expert;   // [E_local]
+    int* total_recv;                // [1]
+    int* num_tokens_per_expert_out; // [E] optional (may be null)
+    unsigned int* done_ctr;         // [1], self-resetting
+    CamStatus* status;
+};
+
+struct CombineParams {
+    const __nv_bfloat16* y;   // [N, h] expert outputs in receive order (SEND phase)
+    const int* row_src;       // [N, 3] (src rank, src token, src k)
+    const int* total_rows;    // [1] device-side N
+    const void* topk_idx;     // [T, K] of this rank's own tokens (RECV phase)
+    int idx_is_i64;
+    const float* topk_weights;  // [T, K]
+    __nv_bfloat16* out;         // [T, h]
+    int T, K, h, E, R, rank;
+    uint32_t epoch;
+    uint64_t timeout_ns;
+    int phase_mask;
+    int dbg_drop_flags;
+    uint8_t* const* peer_base;
+    uint64_t off_combine_buf, off_combine_flag;
+    unsigned int* done_ctr;
+    CamStatus* status;
+};
+
+struct DispatchLLParams {
+    const __nv_bfloat16* x;  // [T, h]
+    const void* expert_ids;  // [T, K]
+    int idx_is_i64;
+    const float* smooth;     // optional [E, h] smooth scales (may be null)
+    int T, K, h, E, R, rank;
+    int active_tokens;       // tokens [0, active_tokens) take part (x_active_mask prefix count)
+    int quant_mode;
+    int max_tokens;          // slab depth per (src, local expert) cell
+    int count_type;          // 1 = per-expert counts, 0 = cumulative
+    uint32_t epoch;
+    uint64_t timeout_ns;
+    int phase_mask;
+    int dbg_drop_flags;
+    uint8_t* const* peer_base;
+    uint64_t off_ll_cells, off_ll_x, off_ll_scales, off_ll_meta;
+    // outputs (local)
+    uint8_t* expand_x;        // [A, row_bytes]
+    float* expand_scales;     // [A, nscale]
+    int* expand_idx;          // [T*K] slot of every pair inside its (src, expert) cell
+    int* expand_src;          // [A, 3] (src rank, src token, src k) of every packed row
+    int64_t* expert_token_nums;  // [E_local]
+    int* ep_send_counts;      // [E_local*R] inclusive cumsum
+    int* total_rows;          // [1]
+    CamStatus* status;
+};
+
+// Grouped GEMM  D[rows of expert e] = A[rows of expert e] * B[e]^T  with block-scaled fp8.
+struct GroupedGemmParams {
+    const int* expert_offsets;  // [E_local+1] first row of every expert in A (device memory)
+    int num_experts;            // E_local
+    int n_dim;                  // output columns per expert (2I for gemm1, h for gemm2)
+    int k_dim;                  // reduction length
+    int a_rows;                 // rows covered by the A tensor map
+    const float* a_scales;      // [a_rows, k_dim/128] row major
+    const float* b_scales;      // [E_local, n_dim/128, k_dim/128]
+    int mode;                   // 0: plain bf16 out, 1: SwiGLU + fp8 requant, 2: bf16 out pushed to combine slots
+    // mode 0
+    __nv_bfloat16* out;         // [a_rows, n_dim]
+    // mode 1
+    uint8_t* act_q;             // [a_rows, n_dim/2] e4m3
+    float* act_s;               // [a_rows, n_dim/2/128]
+    // mode 2
+    const int* row_src;         // [a_rows, 3]
+    uint8_t* const* peer_base;
+    uint64_t off_combine_buf, off_combine_flag;
+    int topk, num_ranks, rank;
+    uint32_t epoch;
+    int dbg_drop_flags;
+    unsigned int* done_ctr;
+    CamStatus* status;
+};
+
+}  // namespace cam
+
+extern "C" {
+int cam_dispatch_normal_smem_bytes(int h, int quant_mode);
+int cam_dispatch_normal_max_grid(int device, int h, int quant_mode);
+int cam_launch_dispatch_normal(const cam::DispatchNormalParams* p, int grid, cudaStream_t stream);
+int cam_launch_layout(const void* topk_idx, int idx_is_i64, int T, int K, int E, int R,
+                      int* num_tokens_per_rank, int* num_tokens_per_expert, uint8_t* is_token_in_rank,
+                      cudaStream_t stream);
+int cam_combine_max_grid(int device);
+int cam_launch_combine(const cam::CombineParams* p, int grid, cudaStream_t stream);
+int cam_dispatch_ll_smem_bytes(int h, int quant_mode, int T, int K);
+int cam_dispatch_ll_max_grid(int device, int h, int quant_mode, int T, int K);
+int cam_launch_dispatch_ll(const cam::DispatchLLParams* p, int grid, cudaStream_t stream);
+int cam_launch_grouped_gemm_fp8(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
+                                const CUtensorMap* tmap_b, int grid, cudaStream_t stream);
+int cam_grouped_gemm_smem_bytes(void);
+}

@@ -1,0 +1,621 @@
+// Host runtime: symmetric buffers over CUDA IPC, peer tables, epochs, status, TMA descriptors and
+// the host halves of the ops.  Argument checks mirror the reference's tiling-time validation
+// (moe_dispatch_normal_tiling.cc:88-108, moe_dispatch_shmem_tiling.cpp:83-92,
+// fused_deep_moe_tiling.cpp:49-58) with limits that fit one NVSwitch domain.
+#include "cam_runtime.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "../kernels/launch.h"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return -1;
+}
+
+#define CAM_CUDA(call)                                                                      \
+    do {                                                                                    \
+        cudaError_t e__ = (call);                                                           \
+        if (e__ != cudaSuccess) return fail("%s failed: %s", #call, cudaGetErrorString(e__)); \
+    } while (0)
+
+#define CAM_CHECK(cond, ...)                   \
+    do {                                       \
+        if (!(cond)) return fail(__VA_ARGS__); \
+    } while (0)
+
+uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+struct CamBuffer {
+    int device = 0, rank = 0, num_ranks = 1;
+    CamLayout layout{};
+    uint8_t* base = nullptr;             // own symmetric allocation
+    std::vector<uint8_t*> peer_ptr;      // host copy of the peer table
+    std::vector<bool> peer_is_ipc;
+    uint8_t** d_peer_table = nullptr;    // device copy
+    // workspace (local)
+    int grid_dispatch = 0, grid_combine = 0, num_sms = 0;
+    int* cta_hist = nullptr;
+    int* slot_in_expert = nullptr;
+    int* send_row = nullptr;
+    int* recv_count = nullptr;
+    int* expert_offsets = nullptr;
+    int64_t* num_recv_per_expert = nullptr;
+    int* total_recv = nullptr;
+    int* num_tokens_per_expert = nullptr;
+    unsigned int* done_ctr = nullptr;  // [4]: dispatch, combine, gemm, spare
+    CamStatus* d_status = nullptr;
+    CamStatus* h_status = nullptr;  // pinned
+    uint8_t* act_q = nullptr;       // [capacity, hidden] scratch between the two GEMMs (sized for I <= hidden)
+    float* act_s = nullptr;
+    uint32_t epoch_dispatch = 0, epoch_combine = 0, epoch_ll = 0, epoch_ll_combine = 0;
+    uint64_t timeout_ns = 10ull * 1000ull * 1000ull * 1000ull;
+    int dbg_drop_flags = 0;
+    std::map<std::tuple<const void*, uint64_t, uint64_t>, CUtensorMap> tmap_cache;
+};
+
+extern "C" const char* cam_last_error(void) { return g_last_error.c_str(); }
+
+extern "C" const char* cam_status_string(int code) {
+    switch (code) {
+        case CAM_OK: return "ok";
+        case CAM_ERR_TIMEOUT_COUNT_FLAG: return "timeout waiting for a peer's per-expert counts";
+        case CAM_ERR_TIMEOUT_DATA_FLAG: return "timeout waiting for a peer's dispatch completion flag";
+        case CAM_ERR_TIMEOUT_COMBINE_FLAG: return "timeout waiting for a peer's combine completion flag";
+        case CAM_ERR_RECV_OVERFLOW: return "rows routed to one rank or cell exceed the buffer capacity";
+        case CAM_ERR_TIMEOUT_PIPELINE: return "timeout inside the GEMM pipeline (mbarrier wait)";
+        case CAM_ERR_TIMEOUT_LL_CELL: return "timeout waiting for a low-latency count cell";
+        case CAM_ERR_TIMEOUT_BARRIER: return "timeout in the cross-rank barrier";
+        case CAM_ERR_BAD_INDEX: return "index out of range recorded by a device-side check";
+        default: return "unknown status";
+    }
+}
+
+extern "C" int cam_layout_compute(CamLayout* L, int R, int E, int max_tokens, int hidden, int topk, int capacity,
+                                  int ll_max_tokens) {
+    CAM_CHECK(L != nullptr, "layout: null output");
+    CAM_CHECK(R >= 1 && R <= CAM_MAX_RANKS, "layout: num_ranks %d outside [1, %d]", R, CAM_MAX_RANKS);
+    CAM_CHECK(E >= R && E <= CAM_MAX_EXPERTS && E % R == 0, "layout: num_experts %d must be a multiple of num_ranks %d and <= %d",
+              E, R, CAM_MAX_EXPERTS);
+    CAM_CHECK(topk >= 1 && topk <= CAM_MAX_TOPK, "layout: topk %d outside [1, %d]", topk, CAM_MAX_TOPK);
+    CAM_CHECK(hidden >= 128 && hidden % 128 == 0 && hidden <= 16384, "layout: hidden %d must be a multiple of 128 in [128, 16384]", hidden);
+    CAM_CHECK(max_tokens >= 1 && capacity >= 1 && ll_max_tokens >= 0, "layout: bad token counts");
+    memset(L, 0, sizeof(*L));
+    L->num_ranks = R;
+    L->num_experts = E;
+    L->max_tokens = max_tokens;
+    L->hidden = hidden;
+    L->topk = topk;
+    L->capacity = capacity;
+    L->ll_max_tokens = ll_max_tokens;
+    uint64_t off = 0;
+    auto take = [&](uint64_t bytes) {
+        uint64_t o = off;
+        off = align_up(off + bytes, 1024);
+        return o;
+    };
+    L->off_count_flag = take(sizeof(uint32_t) * CAM_MAX_RANKS);
+    L->off_data_flag = take(sizeof(uint32_t) * CAM_MAX_RANKS);
+    L->off_combine_flag = take(sizeof(uint32_t) * CAM_MAX_RANKS);
+    L->off_barrier_flag = take(sizeof(uint32_t) * CAM_MAX_RANKS);
+    L->off_ll_combine_flag = take(sizeof(uint32_t) * CAM_MAX_RANKS);
+    L->off_count_matrix = take(sizeof(int32_t) * 2ull * R * E);
+    L->off_ll_cells = take(sizeof(uint64_t) * 2ull * E);
+    const uint64_t ctrl_end = off;
+    (void)ctrl_end;
+    L->off_recv_x = take(static_cast<uint64_t>(capacity) * hidden * 2);
+    L->off_recv_scales = take(static_cast<uint64_t>(capacity) * (hidden / 128) * 4);
+    L->off_recv_src = take(static_cast<uint64_t>(capacity) * 3 * 4);
+    L->off_combine_buf = take(static_cast<uint64_t>(max_tokens) * topk * hidden * 2);
+    if (ll_max_tokens > 0) {
+        const uint64_t cells = 2ull * E;
+        L->off_ll_x = take(cells * ll_max_tokens * hidden * 2);
+        L->off_ll_scales = take(cells * ll_max_tokens * (hidden / 128) * 4);
+        L->off_ll_meta = take(cells * ll_max_tokens * 2 * 4);
+        L->off_ll_combine_buf = take(static_cast<uint64_t>(ll_max_tokens) * topk * hidden * 2);
+    }
+    L->total_bytes = off;
+    return 0;
+}
+
+extern "C" CamBuffer* cam_buffer_create(int device, int rank, int num_ranks, const CamLayout* layout) {
+    auto bad = [](const char* what, cudaError_t e) -> CamBuffer* {
+        fail("%s failed: %s", what, cudaGetErrorString(e));
+        return nullptr;
+    };
+    if (layout == nullptr || layout->num_ranks != num_ranks || rank < 0 || rank >= num_ranks) {
+        fail("buffer_create: bad rank/layout");
+        return nullptr;
+    }
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return bad("cudaSetDevice", e);
+    CamBuffer* b = new CamBuffer();
+    b->device = device;
+    b->rank = rank;
+    b->num_ranks = num_ranks;
+    b->layout = *layout;
+    const int E = layout->num_experts, R = num_ranks;
+    if ((e = cudaDeviceGetAttribute(&b->num_sms, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess) {
+        delete b;
+        return bad("cudaDeviceGetAttribute", e);
+    }
+    if ((e = cudaMalloc(&b->base, layout->total_bytes)) != cudaSuccess) {
+        delete b;
+        return bad("cudaMalloc(symmetric region)", e);
+    }
+    // control words (everything before recv_x) start at zero
+    cudaMemset(b->base, 0, layout->off_recv_x);
+    b->peer_ptr.assign(R, nullptr);
+    b->peer_is_ipc.assign(R, false);
+    b->peer_ptr[rank] = b->base;
+    const size_t pairs = static_cast<size_t>(layout->max_tokens > layout->ll_max_tokens ? layout->max_tokens
+                                                                                        : layout->ll_max_tokens) *
+                         layout->topk;
+    bool ok = true;
+    ok &= cudaMalloc(&b->d_peer_table, sizeof(uint8_t*) * R) == cudaSuccess;
+    ok &= cudaMalloc(&b->cta_hist, sizeof(int) * static_cast<size_t>(b->num_sms) * E) == cudaSuccess;
+    ok &= cudaMalloc(&b->slot_in_expert, sizeof(int) * pairs) == cudaSuccess;
+    ok &= cudaMalloc(&b->send_row, sizeof(int) * pairs) == cudaSuccess;
+    ok &= cudaMalloc(&b->recv_count, sizeof(int) * E) == cudaSuccess;
+    ok &= cudaMalloc(&b->expert_offsets, sizeof(int) * (E + 1)) == cudaSuccess;
+    ok &= cudaMalloc(&b->num_recv_per_expert, sizeof(int64_t) * E) == cudaSuccess;
+    ok &= cudaMalloc(&b->total_recv, sizeof(int) * 4) == cudaSuccess;
+    ok &= cudaMalloc(&b->num_tokens_per_expert, sizeof(int) * E) == cudaSuccess;
+    ok &= cudaMalloc(&b->done_ctr, sizeof(unsigned int) * 4) == cudaSuccess;
+    ok &= cudaMalloc(&b->d_status, sizeof(CamStatus)) == cudaSuccess;
+    ok &= cudaMallocHost(&b->h_status, sizeof(CamStatus)) == cudaSuccess;
+    ok &= cudaMalloc(&b->act_q, static_cast<size_t>(layout->capacity) * layout->hidden) == cudaSuccess;
+    ok &= cudaMalloc(&b->act_s, static_cast<size_t>(layout->capacity) * (layout->hidden / 128) * 4) == cudaSuccess;
+    if (!ok) {
+        fail("buffer_create: workspace allocation failed: %s", cudaGetErrorString(cudaGetLastError()));
+        cam_buffer_destroy(b);
+        return nullptr;
+    }
+    cudaMemset(b->done_ctr, 0, sizeof(unsigned int) * 4);
+    cudaMemset(b->d_status, 0, sizeof(CamStatus));
+    cudaMemset(b->total_recv, 0, sizeof(int) * 4);
+    cudaMemset(b->expert_offsets, 0, sizeof(int) * (E + 1));
+    memset(b->h_status, 0, sizeof(CamStatus));
+    cudaMemcpy(b->d_peer_table, b->peer_ptr.data(), sizeof(uint8_t*) * R, cudaMemcpyHostToDevice);
+    cudaDeviceSynchronize();
+    return b;
+}
+
+extern "C" int cam_buffer_destroy(CamBuffer* b) {
+    if (b == nullptr) return 0;
+    cudaSetDevice(b->device);
+    cudaDeviceSynchronize();
+    for (int r = 0; r < b->num_ranks; ++r)
+        if (r != b->rank && b->peer_is_ipc[r] && b->peer_ptr[r] != nullptr) cudaIpcCloseMemHandle(b->peer_ptr[r]);
+    void* frees[] = {b->base, b->d_peer_table, b->cta_hist, b->slot_in_expert, b->send_row, b->recv_count,
+                     b->expert_offsets, b->num_recv_per_expert, b->total_recv, b->num_tokens_per_expert,
+                     b->done_ctr, b->d_status, b->act_q, b->act_s};
+    for (void* p : frees)
+        if (p != nullptr) cudaFree(p);
+    if (b->h_status != nullptr) cudaFreeHost(b->h_status);
+    delete b;
+    return 0;
+}
+
+extern "C" int cam_buffer_ipc_handle(CamBuffer* b, void* out_handle) {
+    CAM_CHECK(b != nullptr && out_handle != nullptr, "ipc_handle: null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == CAM_IPC_HANDLE_BYTES, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    CAM_CUDA(cudaSetDevice(b->device));
+    CAM_CUDA(cudaIpcGetMemHandle(&h, b->base));
+    memcpy(out_handle, &h, sizeof(h));
+    return 0;
+}
+
+static int upload_peer_table(CamBuffer* b) {
+    for (int r = 0; r < b->num_ranks; ++r) CAM_CHECK(b->peer_ptr[r] != nullptr, "peer %d has no mapping", r);
+    CAM_CUDA(cudaMemcpy(b->d_peer_table, b->peer_ptr.data(), sizeof(uint8_t*) * b->num_ranks, cudaMemcpyHostToDevice));
+    return 0;
+}
+
+extern "C" int cam_buffer_open_ipc_peers(CamBuffer* b, const void* handles) {
+    CAM_CHECK(b != nullptr && handles != nullptr, "open_ipc_peers: null argument");
+    CAM_CUDA(cudaSetDevice(b->device));
+    const uint8_t* hp = static_cast<const uint8_t*>(handles);
+    for (int r = 0; r < b->num_ranks; ++r) {
+        if (r == b->rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, hp + static_cast<size_t>(r) * CAM_IPC_HANDLE_BYTES, sizeof(h));
+        void* p = nullptr;
+        CAM_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        b->peer_ptr[r] = static_cast<uint8_t*>(p);
+        b->peer_is_ipc[r] = true;
+    }
+    return upload_peer_table(b);
+}
+
+extern "C" int cam_buffer_set_local_peers(CamBuffer* b, CamBuffer* const* peers) {
+    CAM_CHECK(b != nullptr && peers != nullptr, "set_local_peers: null argument");
+    CAM_CUDA(cudaSetDevice(b->device));
+    for (int r = 0; r < b->num_ranks; ++r) {
+        CAM_CHECK(peers[r] != nullptr && peers[r]->device == b->device && peers[r]->rank == r &&
+                      peers[r]->layout.total_bytes == b->layout.total_bytes,
+                  "set_local_peers: peer %d is not a matching buffer on the same device", r);
+        b->peer_ptr[r] = peers[r]->base;
+        b->peer_is_ipc[r] = false;
+    }
+    return upload_peer_table(b);
+}
+
+extern "C" int cam_buffer_reset(CamBuffer* b, cudaStream_t stream) {
+    CAM_CHECK(b != nullptr, "reset: null buffer");
+    CAM_CUDA(cudaSetDevice(b->device));
+    CAM_CUDA(cudaMemsetAsync(b->base, 0, b->layout.off_recv_x, stream));
+    CAM_CUDA(cudaMemsetAsync(b->done_ctr, 0, sizeof(unsigned int) * 4, stream));
+    CAM_CUDA(cudaMemsetAsync(b->d_status, 0, sizeof(CamStatus), stream));
+    CAM_CUDA(cudaStreamSynchronize(stream));
+    b->epoch_dispatch = b->epoch_combine = b->epoch_ll = b->epoch_ll_combine = 0;
+    return 0;
+}
+
+extern "C" void* cam_buffer_base(CamBuffer* b) { return b ? b->base : nullptr; }
+extern "C" const CamLayout* cam_buffer_layout(CamBuffer* b) { return b ? &b->layout : nullptr; }
+extern "C" int cam_buffer_rank(CamBuffer* b) { return b ? b->rank : -1; }
+extern "C" int cam_buffer_num_ranks(CamBuffer* b) { return b ? b->num_ranks : -1; }
+extern "C" int cam_buffer_device(CamBuffer* b) { return b ? b->device : -1; }
+extern "C" void cam_buffer_set_timeout_ms(CamBuffer* b, double ms) {
+    if (b != nullptr && ms > 0) b->timeout_ns = static_cast<uint64_t>(ms * 1e6);
+}
+extern "C" void cam_buffer_set_debug_drop_flags(CamBuffer* b, int on) {
+    if (b != nullptr) b->dbg_drop_flags = on ? 1 : 0;
+}
+extern "C" int* cam_buffer_recv_count(CamBuffer* b) { return b->recv_count; }
+extern "C" int* cam_buffer_expert_offsets(CamBuffer* b) { return b->expert_offsets; }
+extern "C" int64_t* cam_buffer_num_recv_per_expert(CamBuffer* b) { return b->num_recv_per_expert; }
+extern "C" int* cam_buffer_total_recv(CamBuffer* b) { return b->total_recv; }
+extern "C" int* cam_buffer_send_row(CamBuffer* b) { return b->send_row; }
+extern "C" int* cam_buffer_num_tokens_per_expert(CamBuffer* b) { return b->num_tokens_per_expert; }
+extern "C" uint8_t* cam_buffer_act_q(CamBuffer* b) { return b->act_q; }
+extern "C" float* cam_buffer_act_s(CamBuffer* b) { return b->act_s; }
+
+extern "C" int cam_buffer_poll_status(CamBuffer* b, cudaStream_t stream, CamStatus* out) {
+    CAM_CHECK(b != nullptr && out != nullptr, "poll_status: null argument");
+    CAM_CUDA(cudaSetDevice(b->device));
+    CAM_CUDA(cudaMemcpyAsync(b->h_status, b->d_status, sizeof(CamStatus), cudaMemcpyDeviceToHost, stream));
+    CAM_CUDA(cudaStreamSynchronize(stream));
+    *out = *b->h_status;
+    if (out->code != CAM_OK) {
+        CAM_CUDA(cudaMemsetAsync(b->d_status, 0, sizeof(CamStatus), stream));
+        CAM_CUDA(cudaMemsetAsync(b->done_ctr, 0, sizeof(unsigned int) * 4, stream));
+        CAM_CUDA(cudaStreamSynchronize(stream));
+    }
+    return 0;
+}
+
+extern "C" int cam_get_dispatch_layout(const void* topk_idx, int idx_is_i64, int T, int K, int E, int R,
+                                       int* num_tokens_per_rank, int* num_tokens_per_expert,
+                                       uint8_t* is_token_in_rank, cudaStream_t stream) {
+    CAM_CHECK(R >= 1 && R <= CAM_MAX_RANKS, "get_dispatch_layout: num_ranks %d outside [1, %d]", R, CAM_MAX_RANKS);
+    CAM_CHECK(E >= R && E <= CAM_MAX_EXPERTS && E % R == 0, "get_dispatch_layout: num_experts %d vs num_ranks %d", E, R);
+    CAM_CHECK(K >= 1 && K <= CAM_MAX_TOPK, "get_dispatch_layout: topk %d outside [1, %d]", K, CAM_MAX_TOPK);
+    CAM_CHECK(T >= 0, "get_dispatch_layout: negative token count");
+    const int rc = cam_launch_layout(topk_idx, idx_is_i64, T, K, E, R, num_tokens_per_rank, num_tokens_per_expert,
+                                     is_token_in_rank, stream);
+    CAM_CHECK(rc == 0, "layout kernel launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    return 0;
+}
+
+static int check_common(const CamBuffer* b, int T, int K, int h, int E, const char* op) {
+    CAM_CHECK(b != nullptr, "%s: null buffer", op);
+    const CamLayout& L = b->layout;
+    CAM_CHECK(E >= b->num_ranks && E <= L.num_experts && E % b->num_ranks == 0,
+              "%s: num_experts %d must be a multiple of num_ranks %d and <= %d (buffer)", op, E, b->num_ranks, L.num_experts);
+    CAM_CHECK(K >= 1 && K <= L.topk, "%s: topk %d outside [1, %d (buffer)]", op, K, L.topk);
+    CAM_CHECK(h >= 128 && h <= L.hidden && h % 128 == 0, "%s: hidden %d must be a multiple of 128 and <= %d (buffer)", op, h, L.hidden);
+    CAM_CHECK(T >= 0, "%s: negative token count", op);
+    return 0;
+}
+
+extern "C" int cam_dispatch_normal(CamBuffer* b, const void* x, const void* topk_idx, int idx_is_i64, int T, int K,
+                                   int h, int E, int quant_mode, int phase_mask, cudaStream_t stream) {
+    if (check_common(b, T, K, h, E, "dispatch_normal") != 0) return -1;
+    CAM_CHECK(T <= b->layout.max_tokens, "dispatch_normal: %d tokens exceed the buffer's max_tokens %d", T, b->layout.max_tokens);
+    CAM_CHECK(quant_mode == CAM_QUANT_NONE || quant_mode == CAM_QUANT_INT8_TOKEN || quant_mode == CAM_QUANT_FP8_1x128,
+              "dispatch_normal: quant_mode %d is not one of 0 (bf16), 2 (int8 per token), 3 (fp8 1x128)", quant_mode);
+    CAM_CUDA(cudaSetDevice(b->device));
+    if (phase_mask & CAM_PHASE_COUNT) ++b->epoch_dispatch;
+    cam::DispatchNormalParams p{};
+    p.x = static_cast<const __nv_bfloat16*>(x);
+    p.topk_idx = topk_idx;
+    p.idx_is_i64 = idx_is_i64;
+    p.T = T; p.K = K; p.h = h; p.E = E; p.R = b->num_ranks; p.rank = b->rank;
+    p.quant_mode = quant_mode;
+    p.capacity = b->layout.capacity;
+    p.epoch = b->epoch_dispatch;
+    p.timeout_ns = b->timeout_ns;
+    p.phase_mask = phase_mask;
+    p.dbg_drop_flags = b->dbg_drop_flags;
+    p.peer_base = b->d_peer_table;
+    p.off_count_flag = b->layout.off_count_flag;
+    p.off_data_flag = b->layout.off_data_flag;
+    p.off_count_matrix = b->layout.off_count_matrix;
+    p.off_recv_x = b->layout.off_recv_x;
+    p.off_recv_scales = b->layout.off_recv_scales;
+    p.off_recv_src = b->layout.off_recv_src;
+    p.cta_hist = b->cta_hist;
+    p.slot_in_expert = b->slot_in_expert;
+    p.send_row = b->send_row;
+    p.recv_count = b->recv_count;
+    p.expert_offsets = b->expert_offsets;
+    p.num_recv_per_expert = b->num_recv_per_expert;
+    p.total_recv = b->total_recv;
+    p.num_tokens_per_expert_out = b->num_tokens_per_expert;
+    p.done_ctr = b->done_ctr + 0;
+    p.status = b->d_status;
+    // The count matrix is laid out for layout.num_experts; a call with fewer experts still uses
+    // stride E because every rank of the call passes the same E.
+    int grid = b->num_sms;  // fixed per device so that the COUNT and SEND phases agree on token chunks
+    const int rc = cam_launch_dispatch_normal(&p, grid, stream);
+    CAM_CHECK(rc == 0, "dispatch_normal launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    return 0;
+}
+
+extern "C" int cam_combine(CamBuffer* b, const void* y, const int* row_src, const int* total_rows,
+                           const void* topk_idx, int idx_is_i64, const float* topk_weights, void* out, int T, int K,
+                           int h, int E, int low_latency, int phase_mask, cudaStream_t stream) {
+    if (check_common(b, T, K, h, E, "combine") != 0) return -1;
+    const int maxT = low_latency ? b->layout.ll_max_tokens : b->layout.max_tokens;
+    CAM_CHECK(T <= maxT, "combine: %d tokens exceed the buffer's limit %d", T, maxT);
+    CAM_CHECK(K == b->layout.topk || true, "combine");
+    CAM_CUDA(cudaSetDevice(b->device));
+    uint32_t& epoch = low_latency ? b->epoch_ll_combine : b->epoch_combine;
+    if (phase_mask & CAM_PHASE_SEND) ++epoch;
+    cam::CombineParams p{};
+    p.y = static_cast<const __nv_bfloat16*>(y);
+    p.row_src = row_src;
+    p.total_rows = total_rows;
+    p.topk_idx = topk_idx;
+    p.idx_is_i64 = idx_is_i64;
+    p.topk_weights = topk_weights;
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.T = T; p.K = K; p.h = h; p.E = E; p.R = b->num_ranks; p.rank = b->rank;
+    p.epoch = epoch;
+    p.timeout_ns = b->timeout_ns;
+    p.phase_mask = phase_mask;
+    p.dbg_drop_flags = b->dbg_drop_flags;
+    p.peer_base = b->d_peer_table;
+    p.off_combine_buf = low_latency ? b->layout.off_ll_combine_buf : b->layout.off_combine_buf;
+    p.off_combine_flag = low_latency ? b->layout.off_ll_combine_flag : b->layout.off_combine_flag;
+    p.done_ctr = b->done_ctr + 1;
+    p.status = b->d_status;
+    const int rc = cam_launch_combine(&p, b->num_sms, stream);
+    CAM_CHECK(rc == 0, "combine launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    return 0;
+}
+
+extern "C" int cam_dispatch_ll(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,
+                               const float* smooth, int T, int K, int h, int E, int active_tokens, int quant_mode,
+                               int count_type, void* expand_x, float* expand_scales, int* expand_idx,
+                               int* expand_src, int64_t* expert_token_nums, int* ep_send_counts, int* total_rows,
+                               int phase_mask, cudaStream_t stream) {
+    if (check_common(b, T, K, h, E, "dispatch_ll") != 0) return -1;
+    CAM_CHECK(b->layout.ll_max_tokens > 0, "dispatch_ll: the buffer was created without low-latency regions");
+    CAM_CHECK(T <= b->layout.ll_max_tokens, "dispatch_ll: %d tokens exceed ll_max_tokens %d", T, b->layout.ll_max_tokens);
+    CAM_CHECK(E == b->layout.num_experts, "dispatch_ll: num_experts %d must equal the buffer's %d", E, b->layout.num_experts);
+    CAM_CHECK(quant_mode == CAM_QUANT_NONE || quant_mode == CAM_QUANT_INT8_TOKEN || quant_mode == CAM_QUANT_FP8_1x128,
+              "dispatch_ll: quant_mode %d is not one of 0, 2, 3 (static quantisation, mode 1, is not supported)", quant_mode);
+    CAM_CHECK(count_type == 0 || count_type == 1, "dispatch_ll: expertTokenNumsType must be 0 (cumulative) or 1 (counts)");
+    CAM_CUDA(cudaSetDevice(b->device));
+    if (phase_mask & CAM_PHASE_SEND) ++b->epoch_ll;
+    cam::DispatchLLParams p{};
+    p.x = static_cast<const __nv_bfloat16*>(x);
+    p.expert_ids = expert_ids;
+    p.idx_is_i64 = idx_is_i64;
+    p.smooth = smooth;
+    p.T = T; p.K = K; p.h = h; p.E = E; p.R = b->num_ranks; p.rank = b->rank;
+    p.active_tokens = active_tokens < 0 ? T : active_tokens;
+    p.quant_mode = quant_mode;
+    p.max_tokens = b->layout.ll_max_tokens;
+    p.count_type = count_type;
+    p.epoch = b->epoch_ll;
+    p.timeout_ns = b->timeout_ns;
+    p.phase_mask = phase_mask;
+    p.dbg_drop_flags = b->dbg_drop_flags;
+    p.peer_base = b->d_peer_table;
+    p.off_ll_cells = b->layout.off_ll_cells;
+    p.off_ll_x = b->layout.off_ll_x;
+    p.off_ll_scales = b->layout.off_ll_scales;
+    p.off_ll_meta = b->layout.off_ll_meta;
+    p.expand_x = static_cast<uint8_t*>(expand_x);
+    p.expand_scales = expand_scales;
+    p.expand_idx = expand_idx;
+    p.expand_src = expand_src;
+    p.expert_token_nums = expert_token_nums;
+    p.ep_send_counts = ep_send_counts;
+    p.total_rows = total_rows;
+    p.status = b->d_status;
+    int grid = cam_dispatch_ll_max_grid(b->device, h, quant_mode, T, K);
+    CAM_CHECK(grid > 0, "dispatch_ll: kernel does not fit (shared memory for T=%d K=%d h=%d)", T, K, h);
+    if (grid > E) grid = E;
+    const int rc = cam_launch_dispatch_ll(&p, grid, stream);
+    CAM_CHECK(rc == 0, "dispatch_ll launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// TMA descriptors
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// 2-D byte tensor [rows, inner] with row pitch == inner, boxes of 128 bytes x 128 rows, 128-byte swizzle.
+static int make_tmap(CamBuffer* cache_owner, CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows) {
+    if (cache_owner != nullptr) {
+        auto it = cache_owner->tmap_cache.find(std::make_tuple(base, inner, rows));
+        if (it != cache_owner->tmap_cache.end()) {
+            *out = it->second;
+            return 0;
+        }
+    }
+    EncodeTiledFn fn = get_encode_fn();
+    CAM_CHECK(fn != nullptr, "cuTensorMapEncodeTiled is not available from the driver");
+    CAM_CHECK((reinterpret_cast<uintptr_t>(base) & 15u) == 0, "tensor map base %p is not 16-byte aligned", base);
+    CAM_CHECK(inner % 16 == 0 && inner >= 128, "tensor map inner extent %llu must be a multiple of 16 and >= 128",
+              static_cast<unsigned long long>(inner));
+    CAM_CHECK(rows >= 1, "tensor map needs at least one row");
+    cuuint64_t dims[2] = {inner, rows};
+    cuuint64_t strides[1] = {inner};
+    cuuint32_t box[2] = {128, 128};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CAM_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+    if (cache_owner != nullptr) {
+        if (cache_owner->tmap_cache.size() > 64) cache_owner->tmap_cache.clear();
+        cache_owner->tmap_cache[std::make_tuple(base, inner, rows)] = *out;
+    }
+    return 0;
+}
+
+extern "C" int cam_grouped_gemm_fp8(CamBuffer* b, const void* a_q, const float* a_scales, int a_rows,
+                                    const void* w_q, const float* w_scales, const int* expert_offsets,
+                                    int num_experts, int n_dim, int k_dim, int mode, void* out_bf16, void* act_q,
+                                    float* act_s, const int* row_src, int topk, int low_latency,
+                                    cudaStream_t stream) {
+    CAM_CHECK(a_q && a_scales && w_q && w_scales && expert_offsets, "grouped_gemm: null operand");
+    CAM_CHECK(num_experts >= 1 && a_rows >= 1, "grouped_gemm: empty problem");
+    CAM_CHECK(k_dim >= 128 && k_dim % 128 == 0, "grouped_gemm: K %d must be a multiple of 128", k_dim);
+    CAM_CHECK(mode >= 0 && mode <= 2, "grouped_gemm: mode %d", mode);
+    if (mode == 1) {
+        CAM_CHECK(n_dim % 256 == 0, "grouped_gemm: gate+up width %d must be a multiple of 256", n_dim);
+        CAM_CHECK(act_q && act_s, "grouped_gemm: mode 1 needs act_q / act_s");
+    } else {
+        CAM_CHECK(n_dim % 128 == 0, "grouped_gemm: N %d must be a multiple of 128", n_dim);
+    }
+    if (mode == 0) CAM_CHECK(out_bf16 != nullptr, "grouped_gemm: mode 0 needs an output");
+    if (mode == 2) CAM_CHECK(b != nullptr && row_src != nullptr && topk >= 1, "grouped_gemm: mode 2 needs a buffer, row_src and topk");
+    CAM_CHECK(static_cast<uint64_t>(num_experts) * n_dim < (1ull << 31), "grouped_gemm: weight rows overflow");
+    int device = 0;
+    if (b != nullptr) {
+        CAM_CUDA(cudaSetDevice(b->device));
+        device = b->device;
+    } else {
+        CAM_CUDA(cudaGetDevice(&device));
+    }
+    CUtensorMap ta, tb;
+    if (make_tmap(b, &ta, a_q, static_cast<uint64_t>(k_dim), static_cast<uint64_t>(a_rows)) != 0) return -1;
+    if (make_tmap(b, &tb, w_q, static_cast<uint64_t>(k_dim), static_cast<uint64_t>(num_experts) * n_dim) != 0) return -1;
+    cam::GroupedGemmParams p{};
+    p.expert_offsets = expert_offsets;
+    p.num_experts = num_experts;
+    p.n_dim = n_dim;
+    p.k_dim = k_dim;
+    p.a_rows = a_rows;
+    p.a_scales = a_scales;
+    p.b_scales = w_scales;
+    p.mode = mode;
+    p.out = static_cast<__nv_bfloat16*>(out_bf16);
+    p.act_q = static_cast<uint8_t*>(act_q);
+    p.act_s = act_s;
+    p.row_src = row_src;
+    static CamStatus* s_fallback_status = nullptr;
+    static unsigned int* s_fallback_ctr = nullptr;
+    if (b != nullptr) {
+        p.peer_base = b->d_peer_table;
+        p.off_combine_buf = low_latency ? b->layout.off_ll_combine_buf : b->layout.off_combine_buf;
+        p.off_combine_flag = low_latency ? b->layout.off_ll_combine_flag : b->layout.off_combine_flag;
+        p.num_ranks = b->num_ranks;
+        p.rank = b->rank;
+        p.dbg_drop_flags = b->dbg_drop_flags;
+        p.done_ctr = b->done_ctr + 2;
+        p.status = b->d_status;
+        if (mode == 2) {
+            uint32_t& epoch = low_latency ? b->epoch_ll_combine : b->epoch_combine;
+            ++epoch;
+            p.epoch = epoch;
+        }
+    } else {
+        if (s_fallback_status == nullptr) {
+            CAM_CUDA(cudaMalloc(&s_fallback_status, sizeof(CamStatus)));
+            CAM_CUDA(cudaMemset(s_fallback_status, 0, sizeof(CamStatus)));
+            CAM_CUDA(cudaMalloc(&s_fallback_ctr, sizeof(unsigned int)));
+            CAM_CUDA(cudaMemset(s_fallback_ctr, 0, sizeof(unsigned int)));
+        }
+        p.status = s_fallback_status;
+        p.done_ctr = s_fallback_ctr;
+    }
+    p.topk = topk;
+    int sms = 0;
+    CAM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    const int rc = cam_launch_grouped_gemm_fp8(&p, &ta, &tb, sms, stream);
+    CAM_CHECK(rc == 0, "grouped_gemm launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    return 0;
+}
+
+extern "C" int cam_fused_moe_fp8(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,
+                                 const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
+                                 const float* w2_s, void* out, int64_t* expert_token_nums, int T, int K, int h,
+                                 int inter, int E, int phase_mask, cudaStream_t stream) {
+    if (check_common(b, T, K, h, E, "fused_moe_fp8") != 0) return -1;
+    CAM_CHECK(inter >= 128 && inter % 128 == 0 && inter <= b->layout.hidden,
+              "fused_moe_fp8: intermediate size %d must be a multiple of 128 and <= the buffer's hidden %d", inter, b->layout.hidden);
+    CAM_CHECK(w1_q && w1_s && w2_q && w2_s && topk_weights && out, "fused_moe_fp8: null operand");
+    const int El = E / b->num_ranks;
+    const CamLayout& L = b->layout;
+    const int disp_mask = phase_mask & CAM_PHASE_ALL;
+    if (disp_mask) {
+        if (cam_dispatch_normal(b, x, expert_ids, idx_is_i64, T, K, h, E, CAM_QUANT_FP8_1x128, disp_mask, stream) != 0)
+            return -1;
+    }
+    if (phase_mask & CAM_PHASE_RECV) {
+        const uint8_t* recv_x = b->base + L.off_recv_x;
+        const float* recv_s = reinterpret_cast<const float*>(b->base + L.off_recv_scales);
+        const int* recv_src = reinterpret_cast<const int*>(b->base + L.off_recv_src);
+        if (cam_grouped_gemm_fp8(b, recv_x, recv_s, L.capacity, w1_q, w1_s, b->expert_offsets, El, 2 * inter, h, 1,
+                                 nullptr, b->act_q, b->act_s, nullptr, K, 0, stream) != 0)
+            return -1;
+        if (cam_grouped_gemm_fp8(b, b->act_q, b->act_s, L.capacity, w2_q, w2_s, b->expert_offsets, El, h, inter, 2,
+                                 nullptr, nullptr, nullptr, recv_src, K, 0, stream) != 0)
+            return -1;
+        if (expert_token_nums != nullptr)
+            CAM_CUDA(cudaMemcpyAsync(expert_token_nums, b->num_recv_per_expert, sizeof(int64_t) * El,
+                                     cudaMemcpyDeviceToDevice, stream));
+    }
+    if (phase_mask & 8) {
+        if (cam_combine(b, nullptr, nullptr, nullptr, expert_ids, idx_is_i64, topk_weights, out, T, K, h, E, 0,
+                        CAM_PHASE_RECV, stream) != 0)
+            return -1;
+    }
+    return 0;
+}

@@ -1,0 +1,97 @@
+// C ABI of the host runtime: symmetric buffers, peer tables, epochs, status words and the
+// host-side halves of every op (argument validation, workspace carving, launches).
+//
+// The reference has no explicit buffer object: its kernels find peer "windows" through HCCL's
+// HcclOpResParam (ascend_kernels/utils/op_kernel/moe_distribute_base.h:123-173) and keep the
+// ping-pong state inside the window itself (moe_dispatch_normal.h:217-229).  Here that state is
+// an explicit CamBuffer: one symmetric allocation per rank, a device table of every peer's base
+// address, per-op epoch counters and a status word that bounded device waits report into.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+#include "../common/cam_types.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CamBuffer CamBuffer;
+
+#define CAM_IPC_HANDLE_BYTES 64
+
+const char* cam_last_error(void);
+const char* cam_status_string(int code);
+
+int cam_layout_compute(CamLayout* out, int num_ranks, int num_experts, int max_tokens, int hidden, int topk,
+                       int capacity, int ll_max_tokens);
+
+// Creates the symmetric allocation (cudaMalloc, so that it can be exported with CUDA IPC), the
+// local workspace and the status word on `device`.  Returns NULL on failure.
+CamBuffer* cam_buffer_create(int device, int rank, int num_ranks, const CamLayout* layout);
+int cam_buffer_destroy(CamBuffer* b);
+int cam_buffer_ipc_handle(CamBuffer* b, void* out_handle /* CAM_IPC_HANDLE_BYTES */);
+// Multi-process: open every peer's IPC handle (handles = num_ranks * 64 bytes, own slot ignored).
+int cam_buffer_open_ipc_peers(CamBuffer* b, const void* handles);
+// Single-process virtual ranks: every rank is a CamBuffer of this process on the same device.
+int cam_buffer_set_local_peers(CamBuffer* b, CamBuffer* const* peers);
+int cam_buffer_reset(CamBuffer* b, cudaStream_t stream);
+void* cam_buffer_base(CamBuffer* b);
+const CamLayout* cam_buffer_layout(CamBuffer* b);
+int cam_buffer_rank(CamBuffer* b);
+int cam_buffer_num_ranks(CamBuffer* b);
+int cam_buffer_device(CamBuffer* b);
+void cam_buffer_set_timeout_ms(CamBuffer* b, double ms);
+void cam_buffer_set_debug_drop_flags(CamBuffer* b, int on);
+// Copies the device status word (after synchronising `stream`) into *out and clears it on the device.
+int cam_buffer_poll_status(CamBuffer* b, cudaStream_t stream, CamStatus* out);
+// Device pointers of the results that normal dispatch leaves in the buffer's workspace.
+int* cam_buffer_recv_count(CamBuffer* b);
+int* cam_buffer_expert_offsets(CamBuffer* b);
+int64_t* cam_buffer_num_recv_per_expert(CamBuffer* b);
+int* cam_buffer_total_recv(CamBuffer* b);
+int* cam_buffer_send_row(CamBuffer* b);
+int* cam_buffer_num_tokens_per_expert(CamBuffer* b);
+uint8_t* cam_buffer_act_q(CamBuffer* b);
+float* cam_buffer_act_s(CamBuffer* b);
+
+// get_dispatch_layout: outputs must be zero-initialised by the caller.
+int cam_get_dispatch_layout(const void* topk_idx, int idx_is_i64, int T, int K, int E, int R,
+                            int* num_tokens_per_rank, int* num_tokens_per_expert, uint8_t* is_token_in_rank,
+                            cudaStream_t stream);
+
+// Normal-mode dispatch.  Rows land in the symmetric buffer's recv_x / recv_scales / recv_src
+// regions of their destination; counts land in this buffer's workspace.
+int cam_dispatch_normal(CamBuffer* b, const void* x_bf16, const void* topk_idx, int idx_is_i64, int T, int K,
+                        int h, int E, int quant_mode, int phase_mask, cudaStream_t stream);
+
+// Combine (push + flag + weighted reduce).  `y` rows follow `row_src` ([N,3] device ints), N is
+// read on the device from `total_rows`.  low_latency selects the low-latency slot/flag regions.
+int cam_combine(CamBuffer* b, const void* y_bf16, const int* row_src, const int* total_rows, const void* topk_idx,
+                int idx_is_i64, const float* topk_weights, void* out_bf16, int T, int K, int h, int E,
+                int low_latency, int phase_mask, cudaStream_t stream);
+
+int cam_dispatch_ll(CamBuffer* b, const void* x_bf16, const void* expert_ids, int idx_is_i64, const float* smooth,
+                    int T, int K, int h, int E, int active_tokens, int quant_mode, int count_type,
+                    void* expand_x, float* expand_scales, int* expand_idx, int* expand_src,
+                    int64_t* expert_token_nums, int* ep_send_counts, int* total_rows, int phase_mask,
+                    cudaStream_t stream);
+
+// Grouped block-scaled fp8 GEMM (see kernels/grouped_gemm.cu for the modes).  For mode 2 `b`
+// must be non-NULL: rows are pushed into the combine slots of their origin ranks and this rank's
+// combine flag is raised (that call plays the SEND phase of combine).
+int cam_grouped_gemm_fp8(CamBuffer* b, const void* a_q, const float* a_scales, int a_rows, const void* w_q,
+                         const float* w_scales, const int* expert_offsets, int num_experts, int n_dim, int k_dim,
+                         int mode, void* out_bf16, void* act_q, float* act_s, const int* row_src, int topk,
+                         int low_latency, cudaStream_t stream);
+
+// Whole fp8 MoE layer on the normal-mode path:
+// dispatch (fp8 1x128) -> GEMM1 + SwiGLU + requant -> GEMM2 with combine-send epilogue -> reduce.
+int cam_fused_moe_fp8(CamBuffer* b, const void* x_bf16, const void* expert_ids, int idx_is_i64,
+                      const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
+                      const float* w2_s, void* out_bf16, int64_t* expert_token_nums, int T, int K, int h,
+                      int inter, int E, int phase_mask, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,164 @@
+"""CPU plumbing on gloo (world_size 2): the op surface end to end, checked against the oracle.
+Covers the first benchmark configuration: 128 tokens/rank, hidden 1024, 8 experts top-2, SwiGLU
+with intermediate 512, against a single-process dense MoE with seed 0."""
+import pytest
+import torch
+
+from conftest import run_gloo
+
+pytestmark = pytest.mark.multi_process_test
+
+
+def _make_inputs(seed, world, t, h, e, k, dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    xs = [torch.randn(t, h, generator=g).to(dtype) for _ in range(world)]
+    logits = [torch.randn(t, e, generator=g) for _ in range(world)]
+    return xs, logits, g
+
+
+def _config1_rank(rank, world):
+    import torch
+    import umdk_original_b200 as u
+    from umdk_original_b200.models import topk_softmax
+    from umdk_original_b200.ops import reference as ref
+    t, h, e, k, inter = 128, 1024, 8, 2, 512
+    xs, logits, g = _make_inputs(0, world, t, h, e, k)
+    w1 = torch.randn(e, 2 * inter, h, generator=g) * 0.02
+    w2 = torch.randn(e, h, inter, generator=g) * 0.02
+    buf = u.Buffer(None, u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k), name="cfg1",
+                   device=torch.device("cpu"))
+    idx, wt = topk_softmax(logits[rank], k)
+    el = e // world
+    lo = rank * el
+    out, nums = torch.ops.umdk_cam_op_lib.fused_deep_moe(
+        xs[rank], idx, [w1[lo:lo + el]], [torch.empty(0)], [w2[lo:lo + el]], [torch.empty(0)], wt, None, None,
+        "cfg1", world, rank, e, 0, 0, 0, 0)
+    dense = ref.dense_moe_fp32(xs[rank], idx, wt, w1, w2)
+    # tokens per local expert counted over all ranks' routing
+    want = torch.zeros(el, dtype=torch.int64)
+    for r in range(world):
+        ir, _ = topk_softmax(logits[r], k)
+        for le in range(el):
+            want[le] += int((ir == lo + le).sum())
+    return float((out - dense).abs().max()), nums.tolist(), want.tolist()
+
+
+def test_config1_dense_equivalence():
+    res = run_gloo(_config1_rank, 2)
+    assert len(res) == 2
+    for r, (st, val) in res.items():
+        assert st == "ok", val
+        err, nums, want = val
+        assert err < 1e-4, f"rank {r}: max abs err {err}"
+        assert nums == want
+
+
+def _dispatch_combine_rank(rank, world, quant_mode):
+    import torch
+    import umdk_original_b200 as u
+    from umdk_original_b200.ops import reference as ref
+    t, h, e, k = 40, 256, 8, 3
+    g = torch.Generator().manual_seed(5)
+    xs = [torch.randn(t, h, generator=g).to(torch.bfloat16) for _ in range(world)]
+    topk = [torch.randint(-1, e, (t, k), generator=g) for _ in range(world)]
+    wts = [torch.rand(t, k, generator=g) for _ in range(world)]
+    buf = u.Buffer(None, u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k), name="dc", device=torch.device("cpu"))
+    ops = torch.ops.umdk_cam_op_lib
+    nr, ne, inr = ops.get_dispatch_layout(topk[rank], e, world)
+    rx, src, cnt, per_e, rs = ops.moe_dispatch_prefill_quant(xs[rank], topk[rank], wts[rank], 0, "dc", rank, world, quant_mode)
+    plan = ref.plan_dispatch(topk, e)[rank]
+    assert torch.equal(src.reshape(-1, 3), plan.src)
+    assert torch.equal(cnt, plan.recv_count)
+    assert torch.equal(per_e, plan.per_expert)
+    rows = torch.stack([xs[s][tt] for s, tt, _ in plan.src.tolist()]) if plan.src.shape[0] else rx
+    if quant_mode == 0:
+        assert torch.equal(rx, rows)
+        y = rx
+    else:
+        q, s = ref.quant_fp8_1x128(rows)
+        assert torch.equal(rx.view(torch.uint8), q.view(torch.uint8)) and torch.equal(rs, s)
+        y = ref.dequant_fp8_1x128(rx, rs).to(torch.bfloat16)
+    out = ops.moe_combine_prefill(y, topk[rank], wts[rank], src, cnt, "dc", rank, world)
+    pair_rows = y.new_zeros(t, k, h)
+    idx = topk[rank]
+    xin = xs[rank] if quant_mode == 0 else ref.dequant_fp8_1x128(*ref.quant_fp8_1x128(xs[rank])).to(torch.bfloat16)
+    for kk in range(k):
+        pair_rows[:, kk] = xin
+    want = ref.combine_reference(pair_rows, idx, wts[rank], e)
+    return float((out.float() - want.float()).abs().max())
+
+
+@pytest.mark.parametrize("quant_mode", [0, 3])
+def test_dispatch_combine_contract(quant_mode):
+    res = run_gloo(_dispatch_combine_rank, 2, args=(quant_mode,))
+    assert len(res) == 2
+    for r, (st, val) in res.items():
+        assert st == "ok", val
+        assert val == 0.0
+
+
+def _ll_rank(rank, world):
+    import torch
+    import umdk_original_b200 as u
+    from umdk_original_b200.ops import reference as ref
+    t, h, e, k = 16, 128, 4, 2
+    g = torch.Generator().manual_seed(9)
+    xs = [torch.randn(t, h, generator=g).to(torch.bfloat16) for _ in range(world)]
+    topk = [torch.randint(0, e, (t, k), generator=g).to(torch.int32) for _ in range(world)]
+    wts = [torch.rand(t, k, generator=g) for _ in range(world)]
+    buf = u.Buffer(None, u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, ll_max_tokens=t), name="ll",
+                   device=torch.device("cpu"))
+    ops = torch.ops.umdk_cam_op_lib
+    mask = torch.zeros(t, dtype=torch.bool)
+    mask[:12] = True
+    outs = ops.moe_dispatch_shmem(xs[rank], topk[rank], None, mask, world, rank, e, 1, 0, 0, 0, 0, 0, 0, 1, buf.handle)
+    expand, dyn, eidx, nums, ep_cnt, tp_cnt = outs
+    masked = [tk.clone() for tk in topk]
+    for m in masked:
+        m[12:] = -1
+    plan = ref.plan_dispatch(masked, e)[rank]
+    n = plan.src.shape[0]
+    assert expand.shape[0] == t * world * min(e // world, k)
+    assert torch.equal(ep_cnt, plan.recv_count) and torch.equal(nums, plan.per_expert)
+    assert torch.equal(eidx, ref.slots_in_expert(topk[rank], e, 12))
+    rows = torch.stack([xs[s][tt] for s, tt, _ in plan.src.tolist()])
+    assert torch.equal(expand[:n], rows)
+    out = ops.moe_combine_shmem(expand, topk[rank], eidx, ep_cnt, wts[rank], None, mask, None, None, None, None,
+                                world, rank, e, 1, 0, 0, 0, 0, 0, 0, buf.handle, 0, 0)
+    pair_rows = xs[rank].unsqueeze(1).expand(t, k, h).contiguous()
+    want = ref.combine_reference(pair_rows, masked[rank], wts[rank], e)
+    return float((out.float() - want.float()).abs().max())
+
+
+def test_low_latency_ops_with_active_mask():
+    res = run_gloo(_ll_rank, 2)
+    assert len(res) == 2
+    for r, (st, val) in res.items():
+        assert st == "ok", val
+        assert val == 0.0
+
+
+def _fault_rank(rank, world):
+    """Rank 1 raises before its dispatch; rank 0 must get MoeCommTimeout, not hang."""
+    import torch
+    import umdk_original_b200 as u
+    t, h, e, k = 8, 128, 4, 2
+    buf = u.Buffer(None, u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k), name="flt", device=torch.device("cpu"))
+    x = torch.randn(t, h).to(torch.bfloat16)
+    idx = torch.randint(0, e, (t, k))
+    w = torch.rand(t, k)
+    if rank == 1:
+        buf.inject_drop_flags(True)
+    try:
+        torch.ops.umdk_cam_op_lib.moe_dispatch_prefill_quant(x, idx, w, 0, "flt", rank, world, 0)
+    except u.MoeCommTimeout as e2:
+        return "timeout:" + str(e2.code)
+    return "completed"
+
+
+def test_fault_injection_rank_withholds_dispatch():
+    res = run_gloo(_fault_rank, 2, timeout_s=8)
+    assert len(res) == 2
+    for r, (st, val) in res.items():
+        assert st == "ok", val
+        assert val.startswith("timeout"), f"rank {r}: {val}"

@@ -1,0 +1,205 @@
+"""GPU tests of the communication kernels: layout, normal dispatch/combine, low-latency
+dispatch/combine.  Multi-rank protocols run as R virtual ranks on one GPU, phase by phase, so no
+launch ever waits for another launch.  Every check is against the CPU oracle."""
+import pytest
+import torch
+
+import umdk_original_b200 as u
+from umdk_original_b200.ops import reference as ref
+from umdk_original_b200.parallel import PHASE_COUNT, PHASE_RECV, PHASE_SEND, run_virtual
+
+pytestmark = pytest.mark.gpu
+ops = torch.ops.umdk_cam_op_lib
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+@pytest.mark.parametrize("dtype", [torch.int64, torch.int32])
+def test_layout_kernel(dtype):
+    g = torch.Generator().manual_seed(0)
+    idx = torch.randint(-1, 64, (777, 8), generator=g).to(dtype)
+    got = ops.get_dispatch_layout(idx.to(_dev()), 64, 8)
+    want = ref.get_dispatch_layout(idx, 64, 8)
+    for a, b in zip(got, want):
+        assert torch.equal(a.cpu(), b)
+
+
+def _inputs(world, t, h, e, k, seed, lo=-1):
+    g = torch.Generator().manual_seed(seed)
+    xs = [torch.randn(t, h, generator=g).to(torch.bfloat16) for _ in range(world)]
+    topk = [torch.randint(lo, e, (t, k), generator=g) for _ in range(world)]
+    wts = [torch.rand(t, k, generator=g) for _ in range(world)]
+    return xs, topk, wts
+
+
+@pytest.mark.parametrize("world,quant_mode", [(1, 0), (1, 3), (2, 3), (4, 0), (4, 2), (8, 3)])
+def test_dispatch_combine_normal(world, quant_mode):
+    t, h, e, k = 61, 512, 16, 4
+    xs, topk, wts = _inputs(world, t, h, e, k, seed=world * 10 + quant_mode)
+    cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, timeout_ms=2000.0)
+    bufs = u.Buffer.virtual(world, cfg, _dev(), name=f"n{world}q{quant_mode}_")
+    dx = [x.to(_dev()) for x in xs]
+    dk = [x.to(_dev()) for x in topk]
+    dw = [x.to(_dev()) for x in wts]
+
+    def disp(r):
+        return ops.moe_dispatch_prefill_quant(dx[r], dk[r], dw[r], 0, bufs[r].name, r, world, quant_mode)
+
+    res = run_virtual(disp, world, masks=(PHASE_COUNT, PHASE_SEND, PHASE_RECV))
+    plans = ref.plan_dispatch(topk, e)
+    ys = []
+    for r in range(world):
+        bufs[r].check()
+        rx, src, cnt, per_e, rs = res[r]
+        plan = plans[r]
+        assert torch.equal(src.cpu().reshape(-1, 3), plan.src)
+        assert torch.equal(cnt.cpu(), plan.recv_count)
+        assert torch.equal(per_e.cpu(), plan.per_expert)
+        rows = torch.stack([xs[s][tt] for s, tt, _ in plan.src.tolist()])
+        if quant_mode == 0:
+            assert torch.equal(rx.cpu(), rows)
+            ys.append(rx.clone())
+        elif quant_mode == 3:
+            q, s = ref.quant_fp8_1x128(rows)
+            assert torch.equal(rs.cpu(), s)
+            assert torch.equal(rx.cpu().view(torch.uint8), q.view(torch.uint8))
+            ys.append(ref.dequant_fp8_1x128(rx.cpu(), rs.cpu()).to(torch.bfloat16).to(_dev()))
+        else:
+            q, s = ref.quant_int8_token(rows)
+            assert torch.allclose(rs.cpu().reshape(-1), s, rtol=1e-6)
+            assert (rx.cpu().int() - q.int()).abs().max() <= 1
+            ys.append((rx.float() * rs).to(torch.bfloat16))
+
+    def comb(r):
+        rx, src, cnt, per_e, rs = res[r]
+        return ops.moe_combine_prefill(ys[r], dk[r], dw[r], src, cnt, bufs[r].name, r, world)
+
+    outs = run_virtual(comb, world, masks=(PHASE_SEND, PHASE_RECV))
+    for r in range(world):
+        bufs[r].check()
+        if quant_mode == 0:
+            xin = xs[r]
+        elif quant_mode == 3:
+            xin = ref.dequant_fp8_1x128(*ref.quant_fp8_1x128(xs[r])).to(torch.bfloat16)
+        else:
+            q, s = ref.quant_int8_token(xs[r])
+            xin = (q.float() * s.unsqueeze(-1)).to(torch.bfloat16)
+        want = ref.combine_reference(xin.unsqueeze(1).expand(t, k, h).contiguous(), topk[r], wts[r], e)
+        tol = 0.0 if quant_mode != 2 else 0.1
+        assert (outs[r].cpu().float() - want.float()).abs().max() <= tol
+    for b in bufs:
+        b.destroy()
+
+
+def test_dispatch_padded_mode_no_host_sync():
+    t, h, e, k = 32, 256, 8, 2
+    xs, topk, wts = _inputs(1, t, h, e, k, seed=3, lo=0)
+    cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, timeout_ms=2000.0)
+    buf = u.Buffer(None, cfg, name="pad", device=_dev(), rank=0, num_ranks=1)
+    rx, src, cnt, per_e, rs = ops.moe_dispatch_prefill_quant(xs[0].to(_dev()), topk[0].to(_dev()), wts[0].to(_dev()),
+                                                              t * k, "pad", 0, 1, 3)
+    assert rx.shape[0] == t * k and per_e.is_cuda
+    assert int(per_e.sum()) == t * k
+    buf.check()
+    buf.destroy()
+
+
+@pytest.mark.parametrize("world,quant_mode", [(1, 3), (2, 0), (4, 3), (4, 2)])
+def test_low_latency_dispatch_combine(world, quant_mode):
+    t, h, e, k = 24, 256, 8, 2
+    xs, topk, wts = _inputs(world, t, h, e, k, seed=40 + world, lo=-1)
+    topk = [x.to(torch.int32) for x in topk]
+    cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, ll_max_tokens=t, timeout_ms=2000.0)
+    bufs = u.Buffer.virtual(world, cfg, _dev(), name=f"l{world}q{quant_mode}_")
+    dx = [x.to(_dev()) for x in xs]
+    dk = [x.to(_dev()) for x in topk]
+    dw = [x.to(_dev()) for x in wts]
+    active = t - 5
+    mask = torch.zeros(t, dtype=torch.bool, device=_dev())
+    mask[:active] = True
+
+    def disp(r):
+        return ops.moe_dispatch_shmem(dx[r], dk[r], None, mask, world, r, e, 1, 0, 0, 0, 0, quant_mode, 0, 1,
+                                      bufs[r].handle)
+
+    res = run_virtual(disp, world, masks=(PHASE_SEND, PHASE_RECV))
+    masked = [x.clone() for x in topk]
+    for m in masked:
+        m[active:] = -1
+    plans = ref.plan_dispatch(masked, e)
+    ys = []
+    for r in range(world):
+        bufs[r].check()
+        expand, dyn, eidx, nums, ep_cnt, tp_cnt = res[r]
+        plan = plans[r]
+        n = plan.src.shape[0]
+        assert expand.shape[0] == t * world * min(e // world, k)
+        assert torch.equal(ep_cnt.cpu(), plan.recv_count)
+        assert torch.equal(nums.cpu(), plan.per_expert)
+        assert torch.equal(eidx.cpu(), ref.slots_in_expert(topk[r], e, active))
+        rows = torch.stack([xs[s][tt] for s, tt, _ in plan.src.tolist()]) if n else None
+        if n and quant_mode == 0:
+            assert torch.equal(expand[:n].cpu(), rows)
+        elif n and quant_mode == 3:
+            q, s = ref.quant_fp8_1x128(rows)
+            assert torch.equal(expand[:n].cpu().view(torch.uint8), q.view(torch.uint8))
+            assert torch.equal(dyn[:n].cpu(), s)
+        elif n:
+            q, s = ref.quant_int8_token(rows)
+            assert (expand[:n].cpu().int() - q.int()).abs().max() <= 1
+        y = torch.zeros(expand.shape[0], h, dtype=torch.bfloat16, device=_dev())
+        if n:
+            y[:n] = rows.to(_dev())
+        ys.append(y)
+
+    def comb(r):
+        expand, dyn, eidx, nums, ep_cnt, tp_cnt = res[r]
+        return ops.moe_combine_shmem(ys[r], dk[r], eidx, ep_cnt, dw[r], None, mask, None, None, None, None, world, r, e,
+                                     1, 0, 0, 0, 0, 0, 0, bufs[r].handle, 0, 0)
+
+    # the combine of virtual rank r must use rank r's own dispatch state, which the Buffer keeps
+    outs = run_virtual(comb, world, masks=(PHASE_SEND, PHASE_RECV))
+    for r in range(world):
+        bufs[r].check()
+        want = ref.combine_reference(xs[r].unsqueeze(1).expand(t, k, h).contiguous(), masked[r], wts[r], e)
+        assert (outs[r].cpu().float() - want.float()).abs().max() == 0.0
+    for b in bufs:
+        b.destroy()
+
+
+def test_bounded_wait_reports_timeout_and_buffer_recovers():
+    """Rank 1 withholds its flags (host-side injection); rank 0's wait runs out after 50 ms, the
+    kernel returns a status record, and after reset() the same buffers work again."""
+    world, t, h, e, k = 2, 16, 256, 4, 2
+    xs, topk, wts = _inputs(world, t, h, e, k, seed=77, lo=0)
+    cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, timeout_ms=50.0)
+    bufs = u.Buffer.virtual(world, cfg, _dev(), name="to_")
+    dx = [x.to(_dev()) for x in xs]
+    dk = [x.to(_dev()) for x in topk]
+    dw = [x.to(_dev()) for x in wts]
+
+    def disp(r):
+        return ops.moe_dispatch_prefill_quant(dx[r], dk[r], dw[r], t * k * world, bufs[r].name, r, world, 0)
+
+    bufs[1].inject_drop_flags(True)
+    run_virtual(disp, world, masks=(PHASE_COUNT, PHASE_SEND))
+    with pytest.raises(u.MoeCommTimeout) as ei:
+        bufs[0].check()
+    assert ei.value.code == 1 and ei.value.who == 1
+    bufs[1].inject_drop_flags(False)
+    for b in bufs:
+        try:
+            b.check()
+        except u.CamError:
+            pass
+        b.reset()
+    res = run_virtual(disp, world, masks=(PHASE_COUNT, PHASE_SEND, PHASE_RECV))
+    plans = ref.plan_dispatch(topk, e)
+    for r in range(world):
+        bufs[r].check()
+        n = plans[r].src.shape[0]
+        assert torch.equal(res[r][1].cpu().reshape(-1, 3)[:n], plans[r].src)
+    for b in bufs:
+        b.destroy()

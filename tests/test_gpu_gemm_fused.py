@@ -1,0 +1,118 @@
+"""GPU tests of the tcgen05 grouped GEMM and of the fused MoE layer, against the fp32 oracle."""
+import pytest
+import torch
+
+import umdk_original_b200 as u
+from umdk_original_b200.models import ExpertWeights
+from umdk_original_b200.ops import reference as ref
+from umdk_original_b200.parallel import run_virtual
+
+pytestmark = pytest.mark.gpu
+ops = torch.ops.umdk_cam_op_lib
+DEV = torch.device("cuda", 0)
+
+
+def _ragged_problem(counts, n, k, seed):
+    g = torch.Generator().manual_seed(seed)
+    m = sum(counts)
+    a = torch.randn(m, k, generator=g)
+    w = torch.randn(len(counts), n, k, generator=g) * 0.05
+    aq, a_s = ref.quant_fp8_1x128(a)
+    wq, w_s = ref.quant_fp8_128x128(w)
+    off = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32)
+    return aq, a_s, wq, w_s, off
+
+
+@pytest.mark.parametrize("counts,n,k", [([128], 256, 128), ([128], 256, 512), ([5, 0, 130, 257], 512, 384),
+                                         ([300, 1, 77], 384, 256)])
+def test_grouped_gemm_plain(counts, n, k):
+    aq, a_s, wq, w_s, off = _ragged_problem(counts, n, k, seed=len(counts) * 7 + n)
+    got = ops.grouped_gemm_fp8(aq.to(DEV), a_s.to(DEV), wq.to(DEV), w_s.to(DEV), off.to(DEV)).cpu().float()
+    want = ops.grouped_gemm_fp8(aq, a_s, wq, w_s, off).float()  # CPU oracle
+    torch.cuda.synchronize()
+    err = (got - want).abs().max().item()
+    assert err <= 2e-2 * want.abs().max().item() + 1e-3, f"max err {err}, scale {want.abs().max().item()}"
+
+
+@pytest.mark.parametrize("counts,inter,k", [([128], 128, 256), ([70, 200, 0, 3], 256, 384)])
+def test_grouped_gemm_swiglu_requant(counts, inter, k):
+    aq, a_s, wq, w_s, off = _ragged_problem(counts, 2 * inter, k, seed=inter + k)
+    q, s = ops.grouped_gemm_fp8_swiglu(aq.to(DEV), a_s.to(DEV), wq.to(DEV), w_s.to(DEV), off.to(DEV))
+    qc, sc = ops.grouped_gemm_fp8_swiglu(aq, a_s, wq, w_s, off)
+    got = ref.dequant_fp8_1x128(q.cpu(), s.cpu())
+    want = ref.dequant_fp8_1x128(qc, sc)
+    scale = want.abs().max().item()
+    # one e4m3 step (2^-3 relative) where a value sits on a rounding boundary
+    assert (got - want).abs().max().item() <= 0.14 * scale + 1e-4
+    assert (got - want).abs().mean().item() <= 0.01 * scale + 1e-5
+    assert torch.allclose(s.cpu(), sc, rtol=2e-2, atol=1e-6)
+
+
+def _fused_case(world, t, h, inter, e, k, seed, lo=0):
+    g = torch.Generator().manual_seed(seed)
+    xs = [torch.randn(t, h, generator=g).to(torch.bfloat16) for _ in range(world)]
+    topk = [torch.stack([torch.randperm(e, generator=g)[:k] for _ in range(t)]) for _ in range(world)]
+    if lo < 0:
+        for tk in topk:
+            tk[::7, 0] = -1
+    wts = [torch.softmax(torch.randn(t, k, generator=g), -1) for _ in range(world)]
+    w1 = torch.randn(e, 2 * inter, h, generator=g) * 0.05
+    w2 = torch.randn(e, h, inter, generator=g) * 0.05
+    w1q, s1 = ref.quant_fp8_128x128(w1)
+    w2q, s2 = ref.quant_fp8_128x128(w2)
+    return xs, topk, wts, (w1q, s1, w2q, s2)
+
+
+@pytest.mark.parametrize("world,lo", [(1, 0), (1, -1), (2, 0), (4, -1)])
+def test_fused_moe_fp8(world, lo):
+    t, h, inter, e, k = 48, 512, 256, 8, 2
+    xs, topk, wts, (w1q, s1, w2q, s2) = _fused_case(world, t, h, inter, e, k, seed=100 + world, lo=lo)
+    cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, timeout_ms=3000.0)
+    bufs = u.Buffer.virtual(world, cfg, DEV, name=f"f{world}_{-lo}_")
+    el = e // world
+    local = [ExpertWeights(w1q[r * el:(r + 1) * el].contiguous(), s1[r * el:(r + 1) * el].contiguous(),
+                           w2q[r * el:(r + 1) * el].contiguous(), s2[r * el:(r + 1) * el].contiguous()).to(DEV)
+             for r in range(world)]
+    dx = [x.to(DEV) for x in xs]
+    dk = [x.to(DEV) for x in topk]
+    dw = [x.to(DEV) for x in wts]
+
+    def step(r):
+        w = local[r]
+        return ops.fused_deep_moe(dx[r], dk[r], [w.w1], [w.s1], [w.w2], [w.s2], dw[r], None, None, bufs[r].name, world, r,
+                                  e, 0, 0, 3, 0)
+
+    res = run_virtual(step, world)
+    total_counts = torch.zeros(e, dtype=torch.int64)
+    for r in range(world):
+        bufs[r].check()
+        want, counts = ref.fused_moe_fp8_reference(xs[r], topk[r], wts[r], w1q, s1, w2q, s2)
+        total_counts += counts
+        got = res[r][0].cpu().float()
+        scale = want.float().abs().max().item()
+        err = (got - want.float()).abs().max().item()
+        assert err <= 0.06 * scale + 1e-3, f"rank {r}: max err {err} vs scale {scale}"
+    for r in range(world):
+        assert torch.equal(res[r][1].cpu(), total_counts[r * el:(r + 1) * el])
+    for b in bufs:
+        b.destroy()
+
+
+def test_fused_moe_x_active_mask():
+    t, h, inter, e, k = 32, 256, 128, 4, 2
+    xs, topk, wts, (w1q, s1, w2q, s2) = _fused_case(1, t, h, inter, e, k, seed=5)
+    cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, timeout_ms=3000.0)
+    buf = u.Buffer(None, cfg, name="mask", device=DEV, rank=0, num_ranks=1)
+    w = ExpertWeights(w1q, s1, w2q, s2).to(DEV)
+    mask = torch.zeros(t, dtype=torch.bool, device=DEV)
+    mask[:20] = True
+    out, nums = ops.fused_deep_moe(xs[0].to(DEV), topk[0].to(DEV), [w.w1], [w.s1], [w.w2], [w.s2], wts[0].to(DEV), None,
+                                   mask, "mask", 1, 0, e, 0, 0, 3, 0)
+    buf.check()
+    masked = topk[0].clone()
+    masked[20:] = -1
+    want, counts = ref.fused_moe_fp8_reference(xs[0], masked, wts[0], w1q, s1, w2q, s2)
+    assert torch.equal(nums.cpu(), counts)
+    assert (out.cpu().float() - want.float()).abs().max() <= 0.06 * want.float().abs().max() + 1e-3
+    assert (out[20:].float().abs().max() == 0)
+    buf.destroy()

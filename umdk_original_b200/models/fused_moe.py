@@ -1,0 +1,119 @@
+"""``FusedMoE``: an expert-parallel MoE layer on top of ``fused_deep_moe``.
+
+What a user of the reference writes by hand around ``torch.ops.umdk_cam_op_lib.fused_deep_moe``
+(the FusionOp class of test/cam/ut/fused_deep_moe/test_fused_deep_moe.py:199-267): keep the
+local experts' quantised weights, route, call the op.  ``MoEStepRunner`` adds the host side of a
+serving step: inputs arrive in pinned host memory, are copied to the device on a side stream
+while the previous step computes, and a small result record is read back.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from ..ops import cam_ops
+from ..parallel.buffer import Buffer
+from ..utils.config import CamConfig
+from .configs import MoEConfig
+from .router import route
+from .weights import ExpertWeights, random_fp8_experts
+
+
+class FusedMoE(torch.nn.Module):
+    def __init__(self, cfg: MoEConfig, buffer: Buffer, weights: Optional[ExpertWeights] = None, seed: int = 0,
+                 gate_weight: Optional[torch.Tensor] = None):
+        super().__init__()
+        self.cfg, self.buffer = cfg, buffer
+        self.rank, self.num_ranks = buffer.rank, buffer.num_ranks
+        assert cfg.num_experts % self.num_ranks == 0
+        self.num_local = cfg.num_experts // self.num_ranks
+        dev = buffer.device
+        if weights is None:
+            weights = random_fp8_experts(self.num_local, cfg.hidden, cfg.intermediate, device=dev,
+                                         seed=seed * 1000 + self.rank)
+        self.weights = weights.to(dev)
+        if gate_weight is None:
+            g = torch.Generator(device="cpu")
+            g.manual_seed(seed + 17)
+            gate_weight = torch.randn(cfg.num_experts, cfg.hidden, generator=g) * 0.02
+        self.register_buffer("gate_weight", gate_weight.to(dev, torch.bfloat16))
+
+    def route(self, x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        logits = x @ self.gate_weight.t()
+        return route(logits, self.cfg.topk, self.cfg.num_groups, self.cfg.topk_groups)
+
+    def forward(self, x: torch.Tensor, topk_idx: Optional[torch.Tensor] = None,
+                topk_weights: Optional[torch.Tensor] = None, x_active_mask: Optional[torch.Tensor] = None):
+        """x [T, h] bf16 -> (out [T, h] bf16, tokens per local expert [E_l] int64)."""
+        if topk_idx is None:
+            topk_idx, topk_weights = self.route(x)
+        w = self.weights
+        out, nums = cam_ops.ops.fused_deep_moe(
+            x, topk_idx, [w.w1], [w.s1], [w.w2], [w.s2], topk_weights.float(), None, x_active_mask,
+            self.buffer.name, self.num_ranks, self.rank, self.cfg.num_experts, 0, 0, 3, 0)
+        return out, nums
+
+
+class MoEStepRunner:
+    """End-to-end step: pinned host inputs -> H2D -> FusedMoE -> D2H of a result record.
+
+    Two device input slots alternate; the copy of step i+1 runs on a side stream while step i
+    computes.  The record read back each step is the per-expert token count plus the sum of the
+    output in fp32 (a checksum a caller can log); ``h2d_bytes`` / ``d2h_bytes`` are what moves."""
+
+    def __init__(self, layer: FusedMoE, tokens: int):
+        self.layer = layer
+        cfg, dev = layer.cfg, layer.buffer.device
+        self.copy_stream = torch.cuda.Stream(device=dev)
+        self.slots = []
+        for _ in range(2):
+            self.slots.append({
+                "x": torch.empty(tokens, cfg.hidden, dtype=torch.bfloat16, device=dev),
+                "idx": torch.empty(tokens, cfg.topk, dtype=torch.int64, device=dev),
+                "w": torch.empty(tokens, cfg.topk, dtype=torch.float32, device=dev),
+                "ready": torch.cuda.Event(), "free": torch.cuda.Event(),
+            })
+        self.result_dev = torch.zeros(layer.num_local + 1, dtype=torch.float32, device=dev)
+        self.result_host = torch.zeros(layer.num_local + 1, dtype=torch.float32).pin_memory()
+        self.h2d_bytes = tokens * (cfg.hidden * 2 + cfg.topk * 8 + cfg.topk * 4)
+        self.d2h_bytes = (layer.num_local + 1) * 4
+        self._step = 0
+        self._staged = None
+
+    def stage(self, x_host: torch.Tensor, idx_host: torch.Tensor, w_host: torch.Tensor) -> None:
+        """Starts the host->device copy of the next step's inputs (pinned tensors)."""
+        slot = self.slots[self._step % 2]
+        with torch.cuda.stream(self.copy_stream):
+            self.copy_stream.wait_event(slot["free"])
+            slot["x"].copy_(x_host, non_blocking=True)
+            slot["idx"].copy_(idx_host, non_blocking=True)
+            slot["w"].copy_(w_host, non_blocking=True)
+            slot["ready"].record(self.copy_stream)
+        self._staged = slot
+
+    def run(self) -> torch.Tensor:
+        """Runs the staged step and returns the host result record (synchronises)."""
+        slot = self._staged
+        cur = torch.cuda.current_stream()
+        cur.wait_event(slot["ready"])
+        out, nums = self.layer(slot["x"], slot["idx"], slot["w"])
+        slot["free"].record(cur)
+        self.result_dev[:-1] = nums.float()
+        self.result_dev[-1] = out.sum(dtype=torch.float32)
+        self.result_host.copy_(self.result_dev, non_blocking=True)
+        self._step += 1
+        self.last_out = out
+        return self.result_host
+
+    def finish(self) -> torch.Tensor:
+        torch.cuda.current_stream().synchronize()
+        return self.result_host
+
+
+def make_buffer_for(cfg: MoEConfig, group=None, tokens: Optional[int] = None, capacity_factor: float = 0.0,
+                    ll_max_tokens: int = 0, name: Optional[str] = None, device=None, timeout_ms: float = 10000.0) -> Buffer:
+    cam_cfg = CamConfig(num_experts=cfg.num_experts, max_tokens=tokens or cfg.tokens_per_rank, hidden=cfg.hidden,
+                        topk=cfg.topk, capacity_factor=capacity_factor, ll_max_tokens=ll_max_tokens,
+                        timeout_ms=timeout_ms)
+    return Buffer(group, cam_cfg, name=name, device=device)

@@ -1,0 +1,195 @@
+"""``Buffer``: the registered symmetric memory every op works on.
+
+The reference has no such object: peers' "windows" come from the HCCL group named by
+``group_ep`` (pybind/fused_deep_moe.cpp:65-77) or from the Ascend-SHMEM heap pointer passed as
+``extInfo`` (pybind/moe_dispatch_shmem.cpp:143-150), and the ping-pong state hides inside the
+window.  Here one Buffer per rank owns
+
+* one symmetric allocation, exported with CUDA IPC and mapped into every peer of the group
+  (bootstrap over the caller's ``torch.distributed`` group: NCCL or gloo, never in the hot path);
+* a device table of every peer's base address, per-op epoch counters and a status word;
+* a name (what ops take as ``group_ep`` / ``groupEp``) and an integer id (``extInfo``).
+
+On CPU tensors the same class wraps a gloo group, so the op surface is identical.
+``Buffer.virtual`` builds R buffers on ONE GPU whose peer tables point at each other; with
+``phases()`` the ops then run phase by phase over all virtual ranks, which exercises the whole
+multi-rank protocol without any launch waiting for another launch.
+"""
+from __future__ import annotations
+
+import contextlib
+from typing import Iterator, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from ..ops import cam_ops
+from ..utils.config import CamConfig
+from ..utils.errors import raise_for_status
+from ..utils.log import get_logger
+from . import registry
+from .gloo_backend import CpuGroup
+
+log = get_logger("umdk_cam.buffer")
+
+PHASE_COUNT, PHASE_SEND, PHASE_RECV, PHASE_FINAL = 1, 2, 4, 8
+PHASE_ALL = 15
+_AUTO = [0]
+
+
+class Buffer:
+    def __init__(self, group=None, config: Optional[CamConfig] = None, *, name: Optional[str] = None,
+                 device: Optional[torch.device] = None, rank: Optional[int] = None, num_ranks: Optional[int] = None,
+                 _connect: bool = True):
+        self.config = config or CamConfig.from_env()
+        self.group = group
+        if rank is None:
+            rank = dist.get_rank(group) if dist.is_available() and dist.is_initialized() else 0
+        if num_ranks is None:
+            num_ranks = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+        self.rank, self.num_ranks = int(rank), int(num_ranks)
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        self.device = torch.device(device)
+        _AUTO[0] += 1
+        self.name = name or f"umdk_cam_group_{_AUTO[0]}"
+        self._native = None
+        self._cpu: Optional[CpuGroup] = None
+        cfg = self.config
+        if cfg.num_experts % self.num_ranks != 0:
+            raise ValueError(f"num_experts {cfg.num_experts} must be a multiple of num_ranks {self.num_ranks}")
+        self.capacity = cfg.resolve_capacity(self.num_ranks)
+        if self.device.type == "cuda":
+            C = cam_ops.native_module()
+            self._native = C.Buffer(self.device.index or 0, self.rank, self.num_ranks, cfg.num_experts, cfg.max_tokens,
+                                    cfg.hidden, cfg.topk, self.capacity, cfg.ll_max_tokens)
+            self._native.set_timeout_ms(cfg.timeout_ms)
+            self._native.register_name(self.name)
+            self.handle = int(self._native.id)
+            if _connect:
+                self._connect_ipc()
+        else:
+            self._cpu = CpuGroup(group, self.rank, self.num_ranks, cfg.num_experts)
+            self.handle = registry.register(self._cpu, self.name)
+        log.info("Buffer %s rank %d/%d on %s: %.1f MiB symmetric", self.name, self.rank, self.num_ranks, self.device,
+                 self.total_bytes / 2 ** 20)
+
+    # ------------------------------------------------------------------ construction helpers
+    def _connect_ipc(self) -> None:
+        if self.num_ranks == 1:
+            self._native.set_local_peers([self._native])
+            return
+        handles: List[Optional[bytes]] = [None] * self.num_ranks
+        dist.all_gather_object(handles, self._native.ipc_handle(), group=self.group)
+        self._native.open_ipc_peers([bytes(h) for h in handles])
+        dist.barrier(group=self.group)
+
+    @classmethod
+    def virtual(cls, num_ranks: int, config: CamConfig, device: Optional[torch.device] = None,
+                name: str = "virt") -> List["Buffer"]:
+        """R ranks as R buffers of this process on one GPU (peer tables point at each other)."""
+        device = device or torch.device("cuda", torch.cuda.current_device())
+        bufs = [cls(None, config, name=f"{name}{r}", device=device, rank=r, num_ranks=num_ranks, _connect=False)
+                for r in range(num_ranks)]
+        natives = [b._native for b in bufs]
+        for b in bufs:
+            b._native.set_local_peers(natives)
+        return bufs
+
+    @staticmethod
+    def get_size_hint(config: CamConfig, num_ranks: int) -> int:
+        """Bytes of symmetric memory a Buffer of this configuration allocates per rank."""
+        cap = config.resolve_capacity(num_ranks)
+        h, e, k = config.hidden, config.num_experts, config.topk
+        total = 5 * 4 * 72 + 8 * num_ranks * e + 16 * e
+        total += cap * h * 2 + cap * (h // 128) * 4 + cap * 12 + config.max_tokens * k * h * 2
+        if config.ll_max_tokens:
+            cells = 2 * e
+            total += cells * config.ll_max_tokens * (h * 2 + (h // 128) * 4 + 8) + config.ll_max_tokens * k * h * 2
+        return int(total + 16 * 1024)
+
+    # ------------------------------------------------------------------ properties / state
+    @property
+    def total_bytes(self) -> int:
+        return int(self._native.total_bytes) if self._native is not None else 0
+
+    @property
+    def native(self):
+        return self._native
+
+    @property
+    def cpu_group(self) -> Optional[CpuGroup]:
+        return self._cpu
+
+    def check(self) -> None:
+        """Synchronises the current stream, reads the device status word and raises on an error."""
+        if self._native is None:
+            return
+        code, who, detail, block, text = self._native.poll_status()
+        raise_for_status(code, who, detail, block, text)
+
+    def reset(self) -> None:
+        """Zeroes flags and epochs after an error (every surviving rank must call it).  Handles and
+        tensors returned by earlier dispatch calls are void afterwards."""
+        if self._native is not None:
+            self._native.reset()
+        elif self._cpu is not None:
+            self._cpu.ll_src = None
+            self._cpu.last_src = None
+
+    def set_timeout_ms(self, ms: float) -> None:
+        if self._native is not None:
+            self._native.set_timeout_ms(ms)
+
+    def inject_drop_flags(self, on: bool = True) -> None:
+        """Host-side fault injection: this rank withholds its completion flags / its next send."""
+        if self._native is not None:
+            self._native.set_debug_drop_flags(on)
+        else:
+            self._cpu.drop_next_send = on
+
+    def stats(self) -> dict:
+        if self._cpu is not None:
+            return dict(self._cpu.stats)
+        el = self.config.num_experts // self.num_ranks
+        return {"total_recv": int(self._native.total_recv().item()),
+                "recv_per_expert": self._native.num_recv_per_expert(el).tolist(),
+                "symmetric_bytes": self.total_bytes}
+
+    def destroy(self) -> None:
+        if self._native is not None:
+            self._native.destroy()
+            self._native = None
+        if self._cpu is not None:
+            registry.unregister(self._cpu)
+            self._cpu = None
+
+    def __del__(self):  # pragma: no cover - best effort
+        try:
+            self.destroy()
+        except Exception:  # noqa: BLE001
+            pass
+
+
+@contextlib.contextmanager
+def phases(mask: int) -> Iterator[None]:
+    """Restricts the CUDA ops to the given phases (virtual-rank harness); restores all phases."""
+    C = cam_ops.native_module()
+    old = C.get_phase_mask()
+    C.set_phase_mask(mask)
+    try:
+        yield
+    finally:
+        C.set_phase_mask(old)
+
+
+def run_virtual(fn, num_ranks: int, masks: Sequence[int] = (PHASE_COUNT, PHASE_SEND, PHASE_RECV, PHASE_FINAL)):
+    """Calls ``fn(rank)`` for every virtual rank once per phase and returns the results of the last
+    phase.  ``fn`` issues the same op call(s) each time; the phase mask decides what the kernels do."""
+    out = [None] * num_ranks
+    for m in masks:
+        with phases(m):
+            for r in range(num_ranks):
+                out[r] = fn(r)
+    torch.cuda.synchronize()
+    return out

@@ -124,7 +124,8 @@ def test_low_latency_dispatch_combine(world, quant_mode):
         return ops.moe_dispatch_shmem(dx[r], dk[r], None, mask, world, r, e, 1, 0, 0, 0, 0, quant_mode, 0, 1,
                                       bufs[r].handle)
 
-    res = run_virtual(disp, world, masks=(PHASE_SEND, PHASE_RECV))
+    both = run_virtual(disp, world, masks=(PHASE_SEND, PHASE_RECV), return_all=True)
+    res = both[PHASE_RECV]
     masked = [x.clone() for x in topk]
     for m in masked:
         m[active:] = -1
@@ -138,6 +139,7 @@ def test_low_latency_dispatch_combine(world, quant_mode):
         assert expand.shape[0] == t * world * min(e // world, k)
         assert torch.equal(ep_cnt.cpu(), plan.recv_count)
         assert torch.equal(nums.cpu(), plan.per_expert)
+        eidx = both[PHASE_SEND][r][2]  # expandIdx is produced by the send phase
         assert torch.equal(eidx.cpu(), ref.slots_in_expert(topk[r], e, active))
         rows = torch.stack([xs[s][tt] for s, tt, _ in plan.src.tolist()]) if n else None
         if n and quant_mode == 0:

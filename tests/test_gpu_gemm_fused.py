@@ -5,7 +5,7 @@ import torch
 import umdk_original_b200 as u
 from umdk_original_b200.models import ExpertWeights
 from umdk_original_b200.ops import reference as ref
-from umdk_original_b200.parallel import run_virtual
+from umdk_original_b200.parallel import PHASE_FINAL, PHASE_RECV, run_virtual
 
 pytestmark = pytest.mark.gpu
 ops = torch.ops.umdk_cam_op_lib
@@ -82,7 +82,8 @@ def test_fused_moe_fp8(world, lo):
         return ops.fused_deep_moe(dx[r], dk[r], [w.w1], [w.s1], [w.w2], [w.s2], dw[r], None, None, bufs[r].name, world, r,
                                   e, 0, 0, 3, 0)
 
-    res = run_virtual(step, world)
+    every = run_virtual(step, world, return_all=True)
+    res = every[PHASE_FINAL]
     total_counts = torch.zeros(e, dtype=torch.int64)
     for r in range(world):
         bufs[r].check()
@@ -93,7 +94,7 @@ def test_fused_moe_fp8(world, lo):
         err = (got - want.float()).abs().max().item()
         assert err <= 0.06 * scale + 1e-3, f"rank {r}: max err {err} vs scale {scale}"
     for r in range(world):
-        assert torch.equal(res[r][1].cpu(), total_counts[r * el:(r + 1) * el])
+        assert torch.equal(every[PHASE_RECV][r][1].cpu(), total_counts[r * el:(r + 1) * el])
     for b in bufs:
         b.destroy()
 

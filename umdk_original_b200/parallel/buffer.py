@@ -183,13 +183,18 @@ def phases(mask: int) -> Iterator[None]:
         C.set_phase_mask(old)
 
 
-def run_virtual(fn, num_ranks: int, masks: Sequence[int] = (PHASE_COUNT, PHASE_SEND, PHASE_RECV, PHASE_FINAL)):
+def run_virtual(fn, num_ranks: int, masks: Sequence[int] = (PHASE_COUNT, PHASE_SEND, PHASE_RECV, PHASE_FINAL),
+                return_all: bool = False):
     """Calls ``fn(rank)`` for every virtual rank once per phase and returns the results of the last
-    phase.  ``fn`` issues the same op call(s) each time; the phase mask decides what the kernels do."""
+    phase (with ``return_all`` a dict phase -> results, since an op allocates fresh outputs on every
+    call and fills each of them in one particular phase).  ``fn`` issues the same op call(s) each
+    time; the phase mask decides what the kernels do."""
     out = [None] * num_ranks
+    every = {}
     for m in masks:
         with phases(m):
             for r in range(num_ranks):
                 out[r] = fn(r)
+        every[m] = list(out)
     torch.cuda.synchronize()
-    return out
+    return every if return_all else out

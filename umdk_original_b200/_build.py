@@ -36,6 +36,7 @@ KERNEL_SOURCES = [
     "kernels/combine.cu",
     "kernels/dispatch_ll.cu",
     "kernels/grouped_gemm.cu",
+    "kernels/dispatch_noalloc.cu",
     "runtime/cam_runtime.cpp",
 ]
 

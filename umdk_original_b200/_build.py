@@ -48,12 +48,24 @@ def _nvcc() -> str:
     return "nvcc"
 
 
-def _run(cmd: list[str]) -> None:
+def _run(cmd: list[str]) -> str:
     proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if proc.returncode != 0:
         raise RuntimeError("command failed: " + " ".join(cmd) + "\n" + proc.stdout)
     if os.environ.get("UMDK_BUILD_VERBOSE"):
         sys.stdout.write(proc.stdout)
+    return proc.stdout
+
+
+def _check_gemm_registers(ptxas_log: str, src: Path) -> None:
+    """The grouped GEMM re-partitions registers with setmaxnreg against the per-thread count the
+    CTA is launched with; that count must be the kLaunchRegs constant of the source, or the
+    kernel would wait for registers that never come."""
+    import re
+    want = int(re.search(r"kLaunchRegs\s*=\s*(\d+)", src.read_text()).group(1))
+    got = [int(m) for m in re.findall(r"Used (\d+) registers", ptxas_log)]
+    if not got or any(g != want for g in got):
+        raise RuntimeError(f"{src.name}: ptxas reports {got} registers but kLaunchRegs is {want}")
 
 
 def _deps_digest(extra: str = "") -> str:
@@ -98,8 +110,10 @@ def build_kernels(force: bool = False, debug: bool = False) -> Path:
             jobs.append((cmd, src, obj))
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
-            list(ex.map(lambda j: _run(j[0]), jobs))
-        for _, src, obj in jobs:
+            logs = list(ex.map(lambda j: _run(j[0]), jobs))
+        for (_, src, obj), log in zip(jobs, logs):
+            if src.name == "grouped_gemm.cu":
+                _check_gemm_registers(log, src)
             _mark(src, obj, stamp)
     so = LIB / "libumdk_cam.so"
     if jobs or force or not so.exists():

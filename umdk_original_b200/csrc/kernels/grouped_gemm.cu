@@ -22,8 +22,9 @@
 // and promoted into fp32 registers by the epilogue warps while the tensor core works on the
 // next block.
 //
-// Warp roles (384 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
-// warps 4..11 = epilogue (warp w reads TMEM lanes 32*(w%4).., column half (w-4)/4).
+// Warp roles (640 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 4..19 = epilogue (warp w reads TMEM lanes 32*(w%4).., 32-column quarter (w-4)/4 of each
+// 128-column block; four epilogue warps per scheduler hide the TMEM load latency).
 // Every mbarrier wait is bounded; a role that gives up sets a shared abort word that releases
 // the others, a status word is recorded and the CTA frees its TMEM and returns.
 #include "../common/cam_types.h"
@@ -37,11 +38,18 @@ constexpr int BM = 128, BN = 256, BK = 128, kStages = 4;
 constexpr int kATile = BM * BK;            // 16 KiB
 constexpr int kBTile = BN * BK;            // 32 KiB
 constexpr int kStageBytes = kATile + kBTile;
-constexpr int kGemmThreads = 384;
-constexpr int kEpiThreads = 256;
-constexpr int kSmemCtrl = 2048;
+constexpr int kGemmThreads = 640;   // 4 control warps + 16 epilogue warps
+constexpr int kEpiThreads = 512;
+constexpr int kSmemCtrl = 8192;
 constexpr int kGemmSmem = kStages * kStageBytes + kSmemCtrl + 1024;  // +1024 alignment slack
 constexpr uint32_t kTmemCols = 512;
+// Register re-partitioning (setmaxnreg).  The CTA is launched with kLaunchRegs per thread (what
+// ptxas reports for __launch_bounds__(640, 1)); the control warp-group gives registers back and
+// the four epilogue warp-groups take them.  setmaxnreg.inc blocks until the CTA's pool has the
+// registers, without any time limit, so the budget below must hold exactly.
+constexpr uint32_t kLaunchRegs = 96, kCtrlRegs = 32, kEpiRegs = 112;
+static_assert(128 * kCtrlRegs + kEpiThreads * kEpiRegs <= kLaunchRegs * kGemmThreads,
+              "setmaxnreg budget exceeds the registers the CTA owns: the kernel would hang");
 
 struct TileWalker {
     const int* off;
@@ -91,12 +99,6 @@ __device__ __forceinline__ void tc_wait_ld_regs(uint32_t (&v)[32]) {
                  : "memory");
 }
 
-template <int OFF>
-__device__ __forceinline__ void promote32(float (&acc)[128], const uint32_t (&v)[32], float s) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) acc[OFF + j] = fmaf(s, __uint_as_float(v[j]), acc[OFF + j]);
-}
-
 __device__ __forceinline__ uint4 pack_bf16x8(float a0, float a1, float a2, float a3, float a4, float a5,
                                              float a6, float a7) {
     uint4 r;
@@ -123,7 +125,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     uint64_t* bar_tempty = bar_tfull + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    float* s_amax = reinterpret_cast<float*>(ctrl + 256);  // [2 parities][2 halves][128 rows]
+    float* s_amax = reinterpret_cast<float*>(ctrl + 256);  // [2 parities][4 column quarters][128 rows]
 
     const int warp = static_cast<int>(threadIdx.x) >> 5;
     const uint32_t lane = lane_id();
@@ -152,7 +154,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp < 4) {
-        reg_dealloc<40>();
+        reg_dealloc<kCtrlRegs>();
         if (warp == 0 && lane == 0) {
             // ------------------------------------------------------------ TMA producer
             prefetch_tensormap(&tmap_a);
@@ -205,11 +207,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             if (!ok) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 1, static_cast<int>(it));
         }
     } else {
-        reg_alloc<232>();
+        reg_alloc<kEpiRegs>();
         // ---------------------------------------------------------------- epilogue warps
         const int ew = warp - 4;
         const int q = warp & 3;   // TMEM lane quarter this warp may read
-        const int ch = ew >> 2;   // which 64-column half of each 128-column block
+        const int cq = ew >> 2;   // which 32-column quarter of each 128-column block
         const int r = q * 32 + static_cast<int>(lane);
         const int kbs = kblocks;  // scales per row of A
         const int nblk = p.n_dim / 128;
@@ -229,39 +231,39 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             const float* bs_lo = p.b_scales + (static_cast<size_t>(e) * nblk + nb_lo) * kbs;
             const float* bs_hi = p.b_scales + (static_cast<size_t>(e) * nblk + nb_hi) * kbs;
 
-            float acc[128];
+            float acc[64];  // [0,32): columns cq*32.. of the first 128-column block, [32,64): same of the second
 #pragma unroll
-            for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+            for (int j = 0; j < 64; ++j) acc[j] = 0.f;
 
-            float sa_next = __ldg(as), wl_next = __ldg(bs_lo), wh_next = __ldg(bs_hi);
+            // scales are fetched two K-blocks ahead of their use
+            float sa0 = __ldg(as), wl0 = __ldg(bs_lo), wh0 = __ldg(bs_hi);
+            float sa1 = sa0, wl1 = wl0, wh1 = wh0;
+            if (kblocks > 1) { sa1 = __ldg(as + 1); wl1 = __ldg(bs_lo + 1); wh1 = __ldg(bs_hi + 1); }
             for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                const float s_lo = sa_next * wl_next, s_hi = sa_next * wh_next;
-                if (kb + 1 < kblocks) {
-                    sa_next = __ldg(as + kb + 1);
-                    wl_next = __ldg(bs_lo + kb + 1);
-                    wh_next = __ldg(bs_hi + kb + 1);
+                const float s_lo = sa0 * wl0, s_hi = sa0 * wh0;
+                sa0 = sa1; wl0 = wl1; wh0 = wh1;
+                if (kb + 2 < kblocks) {
+                    sa1 = __ldg(as + kb + 2);
+                    wl1 = __ldg(bs_lo + kb + 2);
+                    wh1 = __ldg(bs_hi + kb + 2);
                 }
                 const uint32_t a = it & 1u, aph = (it >> 1) & 1u;
                 if (!mbar_wait_bounded(&bar_tfull[a], aph, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
-                const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * BN + ch * 64;
-                uint32_t v0[32], v1[32];
-                tmem_ld_32x32b_x32(t0, v0);
-                tc_wait_ld_regs(v0);
-                tmem_ld_32x32b_x32(t0 + 32, v1);
-                promote32<0>(acc, v0, s_lo);
-                tc_wait_ld_regs(v1);
-                tmem_ld_32x32b_x32(t0 + 128, v0);
-                promote32<32>(acc, v1, s_lo);
-                tc_wait_ld_regs(v0);
-                tmem_ld_32x32b_x32(t0 + 160, v1);
-                promote32<64>(acc, v0, s_hi);
-                tc_wait_ld_regs(v1);
+                const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * BN + cq * 32;
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(t0, v);
+                tc_wait_ld_regs(v);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) acc[j] = fmaf(s_lo, __uint_as_float(v[j]), acc[j]);
+                tmem_ld_32x32b_x32(t0 + 128, v);
+                tc_wait_ld_regs(v);
                 // all TMEM reads of this stage are done: hand it back to the MMA issuer
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bar_tempty[a]);
-                promote32<96>(acc, v1, s_hi);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(s_hi, __uint_as_float(v[j]), acc[32 + j]);
             }
             if (!ok) break;
 
@@ -270,22 +272,22 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 const int ia = p.n_dim / 2;
                 float amax = 0.f;
 #pragma unroll
-                for (int j = 0; j < 64; ++j) {
+                for (int j = 0; j < 32; ++j) {
                     const float g = acc[j];
-                    const float act = (g / (1.f + expf(-g))) * acc[64 + j];
+                    const float act = (g / (1.f + expf(-g))) * acc[32 + j];
                     acc[j] = act;
                     amax = fmaxf(amax, fabsf(act));
                 }
-                float* xch = s_amax + tile_parity * 256;
-                xch[ch * 128 + r] = amax;
+                float* xch = s_amax + tile_parity * 512;
+                xch[cq * 128 + r] = amax;
                 named_bar_sync(1, kEpiThreads);
-                amax = fmaxf(xch[r], xch[128 + r]);
+                amax = fmaxf(fmaxf(xch[r], xch[128 + r]), fmaxf(xch[256 + r], xch[384 + r]));
                 const float a_cl = fmaxf(amax, 1e-4f);
                 const float inv = 448.f / a_cl;
                 if (valid) {
-                    uint8_t* dst = p.act_q + static_cast<size_t>(grow) * ia + nt * 128 + ch * 64;
+                    uint8_t* dst = p.act_q + static_cast<size_t>(grow) * ia + nt * 128 + cq * 32;
 #pragma unroll
-                    for (int j = 0; j < 64; j += 16) {
+                    for (int j = 0; j < 32; j += 16) {
                         uint4 o;
                         o.x = pack_e4m3x4(acc[j + 0] * inv, acc[j + 1] * inv, acc[j + 2] * inv, acc[j + 3] * inv);
                         o.y = pack_e4m3x4(acc[j + 4] * inv, acc[j + 5] * inv, acc[j + 6] * inv, acc[j + 7] * inv);
@@ -293,7 +295,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                         o.w = pack_e4m3x4(acc[j + 12] * inv, acc[j + 13] * inv, acc[j + 14] * inv, acc[j + 15] * inv);
                         *reinterpret_cast<uint4*>(dst + j) = o;
                     }
-                    if (ch == 0) p.act_s[static_cast<size_t>(grow) * (ia / 128) + nt] = a_cl / 448.f;
+                    if (cq == 0) p.act_s[static_cast<size_t>(grow) * (ia / 128) + nt] = a_cl / 448.f;
                 }
             } else {
                 // bf16 tile, either to the local output or straight to the origin rank's combine slot
@@ -311,17 +313,19 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     }
                 }
                 if (orow != nullptr) {
-                    const int c_lo = nt * BN + ch * 64;
+                    const int c_lo = nt * BN + cq * 32;
                     const int c_hi = c_lo + 128;
                     if (c_lo < p.n_dim) {
 #pragma unroll
-                        for (int j = 0; j < 64; j += 8) st_na_v4(orow + c_lo + j, pack_bf16x8(acc[j], acc[j + 1], acc[j + 2], acc[j + 3], acc[j + 4],
-                                                                   acc[j + 5], acc[j + 6], acc[j + 7]));
+                        for (int j = 0; j < 32; j += 8)
+                            st_na_v4(orow + c_lo + j, pack_bf16x8(acc[j], acc[j + 1], acc[j + 2], acc[j + 3], acc[j + 4],
+                                                                  acc[j + 5], acc[j + 6], acc[j + 7]));
                     }
                     if (c_hi < p.n_dim) {
 #pragma unroll
-                        for (int j = 0; j < 64; j += 8) st_na_v4(orow + c_hi + j, pack_bf16x8(acc[64 + j], acc[65 + j], acc[66 + j], acc[67 + j], acc[68 + j],
-                                                                   acc[69 + j], acc[70 + j], acc[71 + j]));
+                        for (int j = 0; j < 32; j += 8)
+                            st_na_v4(orow + c_hi + j, pack_bf16x8(acc[32 + j], acc[33 + j], acc[34 + j], acc[35 + j],
+                                                                  acc[36 + j], acc[37 + j], acc[38 + j], acc[39 + j]));
                     }
                 }
             }

@@ -12,43 +12,56 @@ ops = torch.ops.umdk_cam_op_lib
 DEV = torch.device("cuda", 0)
 
 
-def _ragged_problem(counts, n, k, seed):
+def _ragged_problem(counts, n, k, seed, ue8m0=False):
     g = torch.Generator().manual_seed(seed)
     m = sum(counts)
-    a = torch.randn(m, k, generator=g)
+    # rows and weight blocks of very different magnitude, so that a misplaced scale factor shows
+    a = torch.randn(m, k, generator=g) * torch.exp(torch.randn(m, 1, generator=g) * 2.0)
     w = torch.randn(len(counts), n, k, generator=g) * 0.05
-    aq, a_s = ref.quant_fp8_1x128(a)
-    wq, w_s = ref.quant_fp8_128x128(w)
+    w = w * torch.exp(torch.randn(len(counts), n // 128, 1, k // 128, 1, generator=g)).expand(
+        -1, -1, 128, -1, 128).reshape(len(counts), n, k)
+    aq, a_s = ref.quant_fp8_1x128(a, ue8m0)
+    wq, w_s = ref.quant_fp8_128x128(w, ue8m0)
     off = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32)
     return aq, a_s, wq, w_s, off
 
 
+@pytest.mark.parametrize("ue8m0", [False, True])
 @pytest.mark.parametrize("counts,n,k", [([128], 256, 128), ([128], 256, 512), ([5, 0, 130, 257], 512, 384),
-                                         ([300, 1, 77], 384, 256)])
-def test_grouped_gemm_plain(counts, n, k):
-    aq, a_s, wq, w_s, off = _ragged_problem(counts, n, k, seed=len(counts) * 7 + n)
-    got = ops.grouped_gemm_fp8(aq.to(DEV), a_s.to(DEV), wq.to(DEV), w_s.to(DEV), off.to(DEV)).cpu().float()
+                                         ([300, 1, 77], 384, 256), ([40, 512, 129], 512, 1024)])
+def test_grouped_gemm_plain(counts, n, k, ue8m0):
+    aq, a_s, wq, w_s, off = _ragged_problem(counts, n, k, seed=len(counts) * 7 + n, ue8m0=ue8m0)
+    got = ops.grouped_gemm_fp8(aq.to(DEV), a_s.to(DEV), wq.to(DEV), w_s.to(DEV), off.to(DEV), ue8m0).cpu().float()
     want = ops.grouped_gemm_fp8(aq, a_s, wq, w_s, off).float()  # CPU oracle
     torch.cuda.synchronize()
-    err = (got - want).abs().max().item()
-    assert err <= 2e-2 * want.abs().max().item() + 1e-3, f"max err {err}, scale {want.abs().max().item()}"
+    # per-row tolerance: rows differ in magnitude by orders
+    row_scale = want.abs().amax(dim=1, keepdim=True)
+    err = ((got - want).abs() / (row_scale + 1e-6)).max().item()
+    assert err <= 2e-2, f"max row-relative err {err}"
 
 
+@pytest.mark.parametrize("ue8m0", [False, True])
 @pytest.mark.parametrize("counts,inter,k", [([128], 128, 256), ([70, 200, 0, 3], 256, 384)])
-def test_grouped_gemm_swiglu_requant(counts, inter, k):
-    aq, a_s, wq, w_s, off = _ragged_problem(counts, 2 * inter, k, seed=inter + k)
-    q, s = ops.grouped_gemm_fp8_swiglu(aq.to(DEV), a_s.to(DEV), wq.to(DEV), w_s.to(DEV), off.to(DEV))
-    qc, sc = ops.grouped_gemm_fp8_swiglu(aq, a_s, wq, w_s, off)
+def test_grouped_gemm_swiglu_requant(counts, inter, k, ue8m0):
+    aq, a_s, wq, w_s, off = _ragged_problem(counts, 2 * inter, k, seed=inter + k, ue8m0=ue8m0)
+    q, s = ops.grouped_gemm_fp8_swiglu(aq.to(DEV), a_s.to(DEV), wq.to(DEV), w_s.to(DEV), off.to(DEV), ue8m0)
+    qc, sc = ops.grouped_gemm_fp8_swiglu(aq, a_s, wq, w_s, off, ue8m0)
     got = ref.dequant_fp8_1x128(q.cpu(), s.cpu())
     want = ref.dequant_fp8_1x128(qc, sc)
-    scale = want.abs().max().item()
+    row_scale = want.abs().amax(dim=1, keepdim=True) + 1e-6
     # one e4m3 step (2^-3 relative) where a value sits on a rounding boundary
-    assert (got - want).abs().max().item() <= 0.14 * scale + 1e-4
-    assert (got - want).abs().mean().item() <= 0.01 * scale + 1e-5
-    assert torch.allclose(s.cpu(), sc, rtol=2e-2, atol=1e-6)
+    assert ((got - want).abs() / row_scale).max().item() <= 0.14
+    assert ((got - want).abs() / row_scale).mean().item() <= 0.01
+    if ue8m0:
+        assert ref.is_power_of_two(s.cpu()[: sum(counts)])
+        # a block whose amax/448 sits within rounding of a power of two may land one step apart
+        ratio = s.cpu()[: sum(counts)] / sc[: sum(counts)]
+        assert ((ratio == 1.0) | (ratio == 2.0) | (ratio == 0.5)).all() and (ratio == 1.0).float().mean() > 0.98
+    else:
+        assert torch.allclose(s.cpu(), sc, rtol=2e-2, atol=1e-6)
 
 
-def _fused_case(world, t, h, inter, e, k, seed, lo=0):
+def _fused_case(world, t, h, inter, e, k, seed, lo=0, ue8m0=False):
     g = torch.Generator().manual_seed(seed)
     xs = [torch.randn(t, h, generator=g).to(torch.bfloat16) for _ in range(world)]
     topk = [torch.stack([torch.randperm(e, generator=g)[:k] for _ in range(t)]) for _ in range(world)]
@@ -58,17 +71,18 @@ def _fused_case(world, t, h, inter, e, k, seed, lo=0):
     wts = [torch.softmax(torch.randn(t, k, generator=g), -1) for _ in range(world)]
     w1 = torch.randn(e, 2 * inter, h, generator=g) * 0.05
     w2 = torch.randn(e, h, inter, generator=g) * 0.05
-    w1q, s1 = ref.quant_fp8_128x128(w1)
-    w2q, s2 = ref.quant_fp8_128x128(w2)
+    w1q, s1 = ref.quant_fp8_128x128(w1, ue8m0)
+    w2q, s2 = ref.quant_fp8_128x128(w2, ue8m0)
     return xs, topk, wts, (w1q, s1, w2q, s2)
 
 
+@pytest.mark.parametrize("ue8m0", [False, True])
 @pytest.mark.parametrize("world,lo", [(1, 0), (1, -1), (2, 0), (4, -1)])
-def test_fused_moe_fp8(world, lo):
+def test_fused_moe_fp8(world, lo, ue8m0):
     t, h, inter, e, k = 48, 512, 256, 8, 2
-    xs, topk, wts, (w1q, s1, w2q, s2) = _fused_case(world, t, h, inter, e, k, seed=100 + world, lo=lo)
+    xs, topk, wts, (w1q, s1, w2q, s2) = _fused_case(world, t, h, inter, e, k, seed=100 + world, lo=lo, ue8m0=ue8m0)
     cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, timeout_ms=3000.0)
-    bufs = u.Buffer.virtual(world, cfg, DEV, name=f"f{world}_{-lo}_")
+    bufs = u.Buffer.virtual(world, cfg, DEV, name=f"f{world}_{-lo}_{int(ue8m0)}_")
     el = e // world
     local = [ExpertWeights(w1q[r * el:(r + 1) * el].contiguous(), s1[r * el:(r + 1) * el].contiguous(),
                            w2q[r * el:(r + 1) * el].contiguous(), s2[r * el:(r + 1) * el].contiguous()).to(DEV)
@@ -80,14 +94,14 @@ def test_fused_moe_fp8(world, lo):
     def step(r):
         w = local[r]
         return ops.fused_deep_moe(dx[r], dk[r], [w.w1], [w.s1], [w.w2], [w.s2], dw[r], None, None, bufs[r].name, world, r,
-                                  e, 0, 0, 3, 0)
+                                  e, 0, 0, 4 if ue8m0 else 3, 0)
 
     every = run_virtual(step, world, return_all=True)
     res = every[PHASE_FINAL]
     total_counts = torch.zeros(e, dtype=torch.int64)
     for r in range(world):
         bufs[r].check()
-        want, counts = ref.fused_moe_fp8_reference(xs[r], topk[r], wts[r], w1q, s1, w2q, s2)
+        want, counts = ref.fused_moe_fp8_reference(xs[r], topk[r], wts[r], w1q, s1, w2q, s2, ue8m0=ue8m0)
         total_counts += counts
         got = res[r][0].cpu().float()
         scale = want.float().abs().max().item()

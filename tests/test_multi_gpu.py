@@ -64,6 +64,19 @@ def _case(rank, world):
     assert err <= 0.06 * want.float().abs().max().item() + 1e-3, err
     assert torch.equal(nums.cpu(), plan.per_expert)
     report["fused_err"] = err
+    # the same layer with power-of-two scales: tensor-core block-scaled GEMMs (quantMode 4)
+    p1q, p1s = ref.quant_fp8_128x128(ref.dequant_fp8_128x128(w1q, s1), True)
+    p2q, p2s = ref.quant_fp8_128x128(ref.dequant_fp8_128x128(w2q, s2), True)
+    pw = ExpertWeights(p1q[sl].contiguous(), p1s[sl].contiguous(), p2q[sl].contiguous(), p2s[sl].contiguous()).to(dev)
+    for _ in range(2):
+        out, nums = ops.fused_deep_moe(x, idx, [pw.w1], [pw.s1], [pw.w2], [pw.s2], w, None, None, "mg", world, rank, e,
+                                       0, 0, 4, 0)
+        buf.check()
+    want, _ = ref.fused_moe_fp8_reference(xs[rank], topk[rank], wts[rank], p1q, p1s, p2q, p2s, ue8m0=True)
+    err = (out.cpu().float() - want.float()).abs().max().item()
+    assert err <= 0.06 * want.float().abs().max().item() + 1e-3, err
+    assert torch.equal(nums.cpu(), plan.per_expert)
+    report["fused_mx_err"] = err
     # low-latency pair
     idx32 = idx.to(torch.int32)
     for _ in range(3):

@@ -220,7 +220,7 @@ std::vector<at::Tensor> dispatch_prefill_impl(const at::Tensor& x, const at::Ten
         per_expert = per_expert.cpu();
     }
     CAM_ASSERT(rows <= b->capacity(), "num_worst_tokens exceeds the Buffer capacity");
-    const int64_t nscale = quant_mode == 3 ? h / 128 : (quant_mode == 2 ? 1 : 0);
+    const int64_t nscale = (quant_mode == 3 || quant_mode == 4) ? h / 128 : (quant_mode == 2 ? 1 : 0);
     at::Tensor scales = nscale > 0 ? b->recv_scales(rows, nscale) : at::empty({0}, x.options().dtype(at::kFloat));
     return {b->recv_x(rows, h, quant_mode), b->recv_src(rows), b->recv_count(E), per_expert, scales};
 }
@@ -309,9 +309,10 @@ std::vector<at::Tensor> moe_dispatch_shmem_cuda(const at::Tensor& x, const at::T
         smooth = smooth_t.data_ptr<float>();
     }
     const at::ScalarType xdt = quantMode == 0 ? at::kBFloat16 : quantMode == 2 ? at::kChar : at::kFloat8_e4m3fn;
-    const int64_t nscale = quantMode == 3 ? h / 128 : 1;
+    const bool fp8 = quantMode == 3 || quantMode == 4;
+    const int64_t nscale = fp8 ? h / 128 : 1;
     at::Tensor expandX = at::empty({A, h}, x.options().dtype(xdt));
-    at::Tensor dynScales = quantMode == 3 ? at::empty({A, nscale}, x.options().dtype(at::kFloat))
+    at::Tensor dynScales = fp8 ? at::empty({A, nscale}, x.options().dtype(at::kFloat))
                                           : at::empty({A}, x.options().dtype(at::kFloat));
     at::Tensor expandIdx = at::empty({T * K}, x.options().dtype(at::kInt));
     at::Tensor expandSrc = at::empty({A, 3}, x.options().dtype(at::kInt));
@@ -339,7 +340,8 @@ std::vector<at::Tensor> moe_dispatch_shmem_meta(const at::Tensor& x, const at::T
     const int64_t A = std::max<int64_t>(1, T * epWorldSize * std::min<int64_t>(El, K));
     const at::ScalarType xdt = quantMode == 0 ? at::kBFloat16 : quantMode == 2 ? at::kChar : at::kFloat8_e4m3fn;
     return {at::empty({A, h}, x.options().dtype(xdt)),
-            quantMode == 3 ? at::empty({A, h / 128}, x.options().dtype(at::kFloat)) : at::empty({A}, x.options().dtype(at::kFloat)),
+            (quantMode == 3 || quantMode == 4) ? at::empty({A, h / 128}, x.options().dtype(at::kFloat))
+                                               : at::empty({A}, x.options().dtype(at::kFloat)),
             at::empty({T * K}, x.options().dtype(at::kInt)), at::empty({El}, x.options().dtype(at::kLong)),
             at::empty({epWorldSize * El}, x.options().dtype(at::kInt)),
             at::empty({std::max<int64_t>(tpWorldSize, 1)}, x.options().dtype(at::kInt))};
@@ -390,7 +392,8 @@ at::Tensor moe_combine_shmem_meta(const at::Tensor& expandX, const at::Tensor& e
 }
 
 // --------------------------------------------------------------------------------------------
-// fused_deep_moe  (pybind/fused_deep_moe.cpp:26-79).  quantMode 3 = block-scaled fp8 weights:
+// fused_deep_moe  (pybind/fused_deep_moe.cpp:26-79).  quantMode 3 = block-scaled fp8 weights with
+// arbitrary fp32 scales, quantMode 4 = the same layout with power-of-two scales (tensor-core block scaling):
 // gmm1PermutedWeight [E_l, 2I, h] e4m3 (gate rows first) with scales [E_l, 2I/128, h/128],
 // gmm2Weight [E_l, h, I] e4m3 with scales [E_l, h/128, I/128]; a list of E_l per-expert tensors
 // is stacked once and cached by the Python layer before it reaches this function.
@@ -412,8 +415,8 @@ std::vector<at::Tensor> fused_deep_moe_cuda(const at::Tensor& x, const at::Tenso
     check_cuda_contig(expertIds, "expertIds");
     CAM_ASSERT(epRankSize == b->num_ranks() && epRankId == b->rank(), "epRankSize/epRankId do not match the Buffer");
     CAM_ASSERT(sharedExpertRankNum == 0, "shared-expert ranks are not supported by this build");
-    CAM_ASSERT(quantMode == 3, "this entry point runs the block-scaled fp8 path (quantMode 3); "
-               "int8 W8A8 weights are converted by umdk_original_b200.models before the call");
+    CAM_ASSERT(quantMode == 3 || quantMode == 4, "this entry point runs the block-scaled fp8 paths (quantMode 3: fp32 "
+               "scales, 4: power-of-two scales); int8 W8A8 weights are converted by umdk_original_b200.models first");
     CAM_ASSERT(gmm1PermutedWeight.size() == 1 && gmm2Weight.size() == 1 && gmm1PermutedWeightScale.size() == 1 &&
                    gmm2WeightScale.size() == 1,
                "stack per-expert tensor lists into one tensor per argument first");
@@ -443,10 +446,11 @@ std::vector<at::Tensor> fused_deep_moe_cuda(const at::Tensor& x, const at::Tenso
     at::Tensor w = expertScales.contiguous();
     at::Tensor out = at::empty({T, h}, x.options());
     at::Tensor nums = at::zeros({El}, x.options().dtype(at::kLong));
-    CAM_RT(cam_fused_moe_fp8(b->raw(), x.data_ptr(), ids.data_ptr(), is64, w.data_ptr<float>(), w1.data_ptr(),
-                             s1.data_ptr<float>(), w2.data_ptr(), s2.data_ptr<float>(), out.data_ptr(),
-                             nums.data_ptr<int64_t>(), static_cast<int>(T), static_cast<int>(K), static_cast<int>(h),
-                             static_cast<int>(I), static_cast<int>(moeExpertNum), g_phase_mask, b->stream()));
+    auto fused = quantMode == 4 ? &cam_fused_moe_mxfp8 : &cam_fused_moe_fp8;
+    CAM_RT(fused(b->raw(), x.data_ptr(), ids.data_ptr(), is64, w.data_ptr<float>(), w1.data_ptr(), s1.data_ptr<float>(),
+                 w2.data_ptr(), s2.data_ptr<float>(), out.data_ptr(), nums.data_ptr<int64_t>(), static_cast<int>(T),
+                 static_cast<int>(K), static_cast<int>(h), static_cast<int>(I), static_cast<int>(moeExpertNum),
+                 g_phase_mask, b->stream()));
     return {out, nums};
 }
 
@@ -461,7 +465,7 @@ std::vector<at::Tensor> fused_deep_moe_meta(const at::Tensor& x, const at::Tenso
 
 // Stand-alone grouped GEMM (mode 0) for tests and for engines that only want the expert MLP.
 at::Tensor grouped_gemm_fp8_cuda(const at::Tensor& a_q, const at::Tensor& a_s, const at::Tensor& w_q,
-                                 const at::Tensor& w_s, const at::Tensor& expert_offsets) {
+                                 const at::Tensor& w_s, const at::Tensor& expert_offsets, bool ue8m0) {
     check_cuda_contig(a_q, "a_q");
     check_cuda_contig(a_s, "a_s");
     check_cuda_contig(w_q, "w_q");
@@ -475,17 +479,18 @@ at::Tensor grouped_gemm_fp8_cuda(const at::Tensor& a_q, const at::Tensor& a_s, c
     CAM_ASSERT(w_s.scalar_type() == at::kFloat && w_s.numel() == E * (N / 128) * (Kd / 128), "w_s must be float32 [E, N/128, K/128]");
     c10::cuda::CUDAGuard guard(a_q.device());
     at::Tensor out = at::empty({M, N}, a_q.options().dtype(at::kBFloat16));
-    CAM_RT(cam_grouped_gemm_fp8(nullptr, a_q.data_ptr(), a_s.data_ptr<float>(), static_cast<int>(M), w_q.data_ptr(),
-                                w_s.data_ptr<float>(), expert_offsets.data_ptr<int>(), static_cast<int>(E),
-                                static_cast<int>(N), static_cast<int>(Kd), 0, out.data_ptr(), nullptr, nullptr, nullptr,
-                                1, 0, at::cuda::getCurrentCUDAStream().stream()));
+    auto gemm = ue8m0 ? &cam_grouped_gemm_mxfp8 : &cam_grouped_gemm_fp8;
+    CAM_RT(gemm(nullptr, a_q.data_ptr(), a_s.data_ptr<float>(), static_cast<int>(M), w_q.data_ptr(),
+                w_s.data_ptr<float>(), expert_offsets.data_ptr<int>(), static_cast<int>(E), static_cast<int>(N),
+                static_cast<int>(Kd), 0, out.data_ptr(), nullptr, nullptr, nullptr, 1, 0,
+                at::cuda::getCurrentCUDAStream().stream()));
     return out;
 }
 
 // GEMM1 flavour stand-alone: returns (act_q [M, I] e4m3, act_s [M, I/128]).
 std::tuple<at::Tensor, at::Tensor> grouped_gemm_fp8_swiglu_cuda(const at::Tensor& a_q, const at::Tensor& a_s,
                                                                 const at::Tensor& w_q, const at::Tensor& w_s,
-                                                                const at::Tensor& expert_offsets) {
+                                                                const at::Tensor& expert_offsets, bool ue8m0) {
     check_cuda_contig(a_q, "a_q");
     check_cuda_contig(a_s, "a_s");
     check_cuda_contig(w_q, "w_q");
@@ -495,10 +500,11 @@ std::tuple<at::Tensor, at::Tensor> grouped_gemm_fp8_swiglu_cuda(const at::Tensor
     c10::cuda::CUDAGuard guard(a_q.device());
     at::Tensor q = at::zeros({M, N / 2}, a_q.options());
     at::Tensor s = at::zeros({M, N / 2 / 128}, a_s.options());
-    CAM_RT(cam_grouped_gemm_fp8(nullptr, a_q.data_ptr(), a_s.data_ptr<float>(), static_cast<int>(M), w_q.data_ptr(),
-                                w_s.data_ptr<float>(), expert_offsets.data_ptr<int>(), static_cast<int>(E),
-                                static_cast<int>(N), static_cast<int>(Kd), 1, nullptr, q.data_ptr(), s.data_ptr<float>(),
-                                nullptr, 1, 0, at::cuda::getCurrentCUDAStream().stream()));
+    auto gemm = ue8m0 ? &cam_grouped_gemm_mxfp8 : &cam_grouped_gemm_fp8;
+    CAM_RT(gemm(nullptr, a_q.data_ptr(), a_s.data_ptr<float>(), static_cast<int>(M), w_q.data_ptr(),
+                w_s.data_ptr<float>(), expert_offsets.data_ptr<int>(), static_cast<int>(E), static_cast<int>(N),
+                static_cast<int>(Kd), 1, nullptr, q.data_ptr(), s.data_ptr<float>(), nullptr, 1, 0,
+                at::cuda::getCurrentCUDAStream().stream()));
     return {q, s};
 }
 
@@ -543,8 +549,10 @@ TORCH_LIBRARY(umdk_cam_op_lib, m) {
     // additions of this library (no counterpart schema in the reference)
     m.def("moe_dispatch_prefill_quant(Tensor x, Tensor topk_idx, Tensor topk_weights, int num_worst_tokens, "
           "str group_ep, int rank, int num_ranks, int quant_mode) -> (Tensor, Tensor, Tensor, Tensor, Tensor)");
-    m.def("grouped_gemm_fp8(Tensor a_q, Tensor a_s, Tensor w_q, Tensor w_s, Tensor expert_offsets) -> Tensor");
-    m.def("grouped_gemm_fp8_swiglu(Tensor a_q, Tensor a_s, Tensor w_q, Tensor w_s, Tensor expert_offsets) -> (Tensor, Tensor)");
+    m.def("grouped_gemm_fp8(Tensor a_q, Tensor a_s, Tensor w_q, Tensor w_s, Tensor expert_offsets, "
+          "bool ue8m0=False) -> Tensor");
+    m.def("grouped_gemm_fp8_swiglu(Tensor a_q, Tensor a_s, Tensor w_q, Tensor w_s, Tensor expert_offsets, "
+          "bool ue8m0=False) -> (Tensor, Tensor)");
 }
 
 TORCH_LIBRARY_IMPL(umdk_cam_op_lib, CUDA, m) {

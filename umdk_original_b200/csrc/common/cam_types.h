@@ -34,11 +34,14 @@ enum CamQuantMode {
     CAM_QUANT_NONE = 0,        // rows travel as bf16
     CAM_QUANT_INT8_TOKEN = 2,  // per-token dynamic int8 + one fp32 scale per row
     CAM_QUANT_FP8_1x128 = 3,   // e4m3 + one fp32 scale per 128 contiguous hidden elements
+    CAM_QUANT_FP8_1x128_UE8M0 = 4,  // same layout, scales rounded up to powers of two (tensor-core block scaling)
 };
 
 // Phases of the comm kernels.  A real multi-GPU call runs all phases in one launch.  The
 // single-GPU "virtual rank" test mode launches phase by phase for all ranks in turn, so no
 // launch ever waits for a launch that has not run yet.
+#define CAM_QUANT_IS_FP8(q) ((q) == CAM_QUANT_FP8_1x128 || (q) == CAM_QUANT_FP8_1x128_UE8M0)
+
 enum CamPhase {
     CAM_PHASE_COUNT = 1,  // dispatch: histogram, slots, count all-gather
     CAM_PHASE_SEND = 2,   // dispatch: wait counts, push rows, raise data flags / combine: push rows

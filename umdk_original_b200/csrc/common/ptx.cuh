@@ -257,6 +257,39 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// D[tmem] (+)= (A[smem] * sfa) * (B[smem] * sfb): e4m3 operands with one UE8M0 (power-of-two)
+// scale per 32 K-elements of every A row and every B row, applied by the tensor core itself.
+// The scale factors live in TMEM (see tmem_st_32x32b_x4 for their layout).
+__device__ __forceinline__ void tc_mma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate, uint32_t sfa_tmem,
+                                            uint32_t sfb_tmem) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
+// Block-scaled instruction descriptor (kind::mxf8f6f4): e4m3 x e4m3, both K-major, UE8M0 scales,
+// scale-factor byte 0 of every 32-bit scale column for A and for B.
+//   b_sf_id [4,6), a_format [7,10), b_format [10,13), n_dim = N>>3 at [17,23),
+//   scale_format [23] (1 = E8M0), m_dim = M>>4 at [24,29), a_sf_id [29,31).
+__host__ __device__ constexpr uint32_t umma_idesc_mxf8(uint32_t m, uint32_t n) {
+    return ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24);
+}
+// Register -> TMEM stores: thread i of the warp writes N consecutive 32-bit columns of lane
+// (lane base + i).  A warp may only touch the 32 lanes of its own quarter (warp id % 4).
+__device__ __forceinline__ void tmem_st_32x32b_x4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c,
+                                                  uint32_t d) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};" ::"r"(taddr), "r"(a),
+                 "r"(b), "r"(c), "r"(d)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }

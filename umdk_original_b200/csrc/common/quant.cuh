@@ -1,5 +1,6 @@
 // Warp-level row quantisation used by the dispatch kernels.
 //   fp8 1x128 : inv = 448 / max(amax_blk, 1e-4);  q = e4m3_rn_sat(x * inv);  scale = max(amax_blk, 1e-4) / 448
+//   fp8 1x128 with power-of-two scales: scale = 2^ceil(log2(max(amax_blk, 1e-4) / 448)), inv = 1 / scale
 //   int8 token: inv = 127 / (amax_row + 1e-12);   q = rint(x * inv);         scale = 1 / inv
 // The int8 form follows the per-token dynamic quantisation of the reference's dispatch kernels
 // (moe_dispatch_normal.h:289-315); the fp8 form is the DeepSeek-style block scaling.
@@ -24,9 +25,21 @@ __device__ __forceinline__ float e4m3_to_float(uint8_t v) {
     return __half2float(*reinterpret_cast<__half*>(&h));
 }
 
+// Power-of-two ("UE8M0") block scale: the smallest 2^k >= amax / 448, and its exact reciprocal.
+// The tensor core's block-scaled MMA takes only the exponent byte of a scale, so scales meant for
+// it must be exact powers of two.  amax is clamped to 1e-4 first, like the fp32-scale form.
+__device__ __forceinline__ void ue8m0_scale(float amax, float& scale, float& inv) {
+    const uint32_t b = __float_as_uint(__fdiv_rn(fmaxf(amax, 1e-4f), 448.f));
+    const uint32_t e = (b >> 23) + ((b & 0x7FFFFFu) ? 1u : 0u);
+    scale = __uint_as_float(e << 23);
+    inv = __uint_as_float((254u - e) << 23);
+}
+
 // One warp quantises one bf16 row of `h` elements (h % 256 == 0 handled fast, h % 128 == 0 in
-// general) to e4m3 with 1x128 scales.  Output goes to the warp's staging area in shared memory:
-// `q` (h bytes, 16-byte aligned) and `s` (h/128 floats).
+// general) to e4m3 with 1x128 scales (arbitrary fp32 scales, or powers of two when UE8M0).
+// Output goes to the warp's staging area in shared memory: `q` (h bytes, 16-byte aligned) and
+// `s` (h/128 floats).
+template <bool UE8M0 = false>
 __device__ __forceinline__ void warp_quant_fp8_1x128(const __nv_bfloat16* __restrict__ row, int h,
                                                      uint8_t* q, float* s) {
     const uint32_t lane = lane_id();
@@ -43,14 +56,20 @@ __device__ __forceinline__ void warp_quant_fp8_1x128(const __nv_bfloat16* __rest
         for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
 #pragma unroll
         for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-        const float a = fmaxf(amax, 1e-4f);
-        const float inv = 448.f / a;
+        float sc, inv;
+        if (UE8M0) {
+            ue8m0_scale(amax, sc, inv);
+        } else {
+            const float a = fmaxf(amax, 1e-4f);
+            inv = 448.f / a;
+            sc = a / 448.f;
+        }
         if (in) {
             uint2 o2;
             o2.x = pack_e4m3x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
             o2.y = pack_e4m3x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
             *reinterpret_cast<uint2*>(q + col) = o2;
-            if ((lane & 15u) == 0u) s[col >> 7] = a / 448.f;
+            if ((lane & 15u) == 0u) s[col >> 7] = sc;
         }
     }
 }

@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
     const int E = p.E, R = p.R, K = p.K, El = p.E / p.R;
     const int npairs = p.T * K;
     const int parity = static_cast<int>(p.epoch & 1u);
-    const int nscale = (p.quant_mode == CAM_QUANT_FP8_1x128) ? (p.h >> 7)
+    const int nscale = CAM_QUANT_IS_FP8(p.quant_mode) ? (p.h >> 7)
                        : (p.quant_mode == CAM_QUANT_INT8_TOKEN) ? 1 : 0;
     const int row_bytes = (p.quant_mode == CAM_QUANT_NONE) ? p.h * 2 : p.h;
     const size_t cell_rows = static_cast<size_t>(p.max_tokens);
@@ -117,7 +117,9 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
                         st_na_v4(dst + o, ld_nc_v4(src + o));
                 } else {
                     if (p.quant_mode == CAM_QUANT_FP8_1x128)
-                        warp_quant_fp8_1x128(xrow, p.h, stage_q, stage_s);
+                        warp_quant_fp8_1x128<false>(xrow, p.h, stage_q, stage_s);
+                    else if (p.quant_mode == CAM_QUANT_FP8_1x128_UE8M0)
+                        warp_quant_fp8_1x128<true>(xrow, p.h, stage_q, stage_s);
                     else
                         warp_quant_int8_token(xrow, p.h, stage_q, stage_s,
                                               p.smooth ? p.smooth + static_cast<size_t>(e) * p.h : nullptr);
@@ -222,7 +224,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
 }  // namespace cam
 
 extern "C" int cam_dispatch_ll_smem_bytes(int h, int quant_mode, int T, int K) {
-    const int nscale = (quant_mode == CAM_QUANT_FP8_1x128) ? h / 128 : (quant_mode == CAM_QUANT_INT8_TOKEN) ? 1 : 0;
+    const int nscale = CAM_QUANT_IS_FP8(quant_mode) ? h / 128 : (quant_mode == CAM_QUANT_INT8_TOKEN) ? 1 : 0;
     const int stage = (quant_mode == CAM_QUANT_NONE) ? 0 : ((h + nscale * 4 + 15) & ~15);
     return ((T * K * 8 + 15) & ~15) + cam::kLLWarps * stage;
 }

@@ -187,7 +187,7 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
         // row, its scales and its (src rank, token, k) triple to every destination.
         const int warp = tid >> 5;
         const uint32_t lane = lane_id();
-        const int nscale = (p.quant_mode == CAM_QUANT_FP8_1x128) ? (p.h >> 7)
+        const int nscale = CAM_QUANT_IS_FP8(p.quant_mode) ? (p.h >> 7)
                            : (p.quant_mode == CAM_QUANT_INT8_TOKEN) ? 1 : 0;
         const int row_bytes = (p.quant_mode == CAM_QUANT_NONE) ? p.h * 2 : p.h;
         const int stage_bytes = (p.quant_mode == CAM_QUANT_NONE) ? 0 : ((p.h + nscale * 4 + 15) & ~15);
@@ -197,7 +197,9 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
         for (int t = t0 + warp; t < t1; t += kDispWarps) {
             const __nv_bfloat16* xrow = p.x + static_cast<size_t>(t) * p.h;
             if (p.quant_mode == CAM_QUANT_FP8_1x128) {
-                warp_quant_fp8_1x128(xrow, p.h, stage_q, stage_s);
+                warp_quant_fp8_1x128<false>(xrow, p.h, stage_q, stage_s);
+            } else if (p.quant_mode == CAM_QUANT_FP8_1x128_UE8M0) {
+                warp_quant_fp8_1x128<true>(xrow, p.h, stage_q, stage_s);
             } else if (p.quant_mode == CAM_QUANT_INT8_TOKEN) {
                 warp_quant_int8_token(xrow, p.h, stage_q, stage_s);
             }
@@ -301,7 +303,7 @@ __global__ void layout_kernel(const void* topk_idx, int idx_is_i64, int T, int K
 // ----------------------------------------------------------------------------------------
 extern "C" int cam_dispatch_normal_smem_bytes(int h, int quant_mode) {
     if (quant_mode == CAM_QUANT_NONE) return 0;
-    const int nscale = (quant_mode == CAM_QUANT_FP8_1x128) ? h / 128 : 1;
+    const int nscale = CAM_QUANT_IS_FP8(quant_mode) ? h / 128 : 1;
     return cam::kDispWarps * ((h + nscale * 4 + 15) & ~15);
 }
 

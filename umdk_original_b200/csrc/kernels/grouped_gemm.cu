@@ -27,17 +27,10 @@
 // 128-column block; four epilogue warps per scheduler hide the TMEM load latency).
 // Every mbarrier wait is bounded; a role that gives up sets a shared abort word that releases
 // the others, a status word is recorded and the CTA frees its TMEM and returns.
-#include "../common/cam_types.h"
-#include "../common/ptx.cuh"
-#include "../common/quant.cuh"
-#include "launch.h"
+#include "gemm_common.cuh"
 
 namespace cam {
 
-constexpr int BM = 128, BN = 256, BK = 128, kStages = 4;
-constexpr int kATile = BM * BK;            // 16 KiB
-constexpr int kBTile = BN * BK;            // 32 KiB
-constexpr int kStageBytes = kATile + kBTile;
 constexpr int kGemmThreads = 640;   // 4 control warps + 16 epilogue warps
 constexpr int kEpiThreads = 512;
 constexpr int kSmemCtrl = 8192;
@@ -50,68 +43,6 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kLaunchRegs = 96, kCtrlRegs = 32, kEpiRegs = 112;
 static_assert(128 * kCtrlRegs + kEpiThreads * kEpiRegs <= kLaunchRegs * kGemmThreads,
               "setmaxnreg budget exceeds the registers the CTA owns: the kernel would hang");
-
-struct TileWalker {
-    const int* off;
-    int num_experts, n_tiles;
-    int e, base;
-    __device__ TileWalker(const int* o, int ne, int nt) : off(o), num_experts(ne), n_tiles(nt), e(0), base(0) {}
-    // Maps a linear tile index (monotonically increasing across calls) to its expert and tile.
-    __device__ bool locate(int tile, int& e_out, int& mt, int& nt, int& row0, int& rows) {
-        while (e < num_experts) {
-            const int first = __ldg(off + e);
-            const int cnt = __ldg(off + e + 1) - first;
-            const int tiles = ((cnt + BM - 1) / BM) * n_tiles;
-            if (tile < base + tiles) {
-                const int local = tile - base;
-                mt = local / n_tiles;
-                nt = local - mt * n_tiles;
-                row0 = first + mt * BM;
-                rows = min(BM, cnt - mt * BM);
-                e_out = e;
-                return true;
-            }
-            base += tiles;
-            ++e;
-        }
-        return false;
-    }
-};
-
-__device__ __forceinline__ void gemm_record_status(CamStatus* st, int code, int who, int detail) {
-    if (atomicCAS(&st->code, 0, code) == 0) {
-        st->who = who;
-        st->detail = detail;
-        st->block = static_cast<int>(blockIdx.x);
-    }
-}
-
-// tcgen05.wait::ld that also names the destination registers, so no use of them can be
-// scheduled ahead of the wait.
-__device__ __forceinline__ void tc_wait_ld_regs(uint32_t (&v)[32]) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]),
-                   "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]),
-                   "+r"(v[14]), "+r"(v[15]), "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]),
-                   "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]), "+r"(v[24]), "+r"(v[25]),
-                   "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
-                 :
-                 : "memory");
-}
-
-__device__ __forceinline__ uint4 pack_bf16x8(float a0, float a1, float a2, float a3, float a4, float a5,
-                                             float a6, float a7) {
-    uint4 r;
-    __nv_bfloat162 t0 = __floats2bfloat162_rn(a0, a1);
-    __nv_bfloat162 t1 = __floats2bfloat162_rn(a2, a3);
-    __nv_bfloat162 t2 = __floats2bfloat162_rn(a4, a5);
-    __nv_bfloat162 t3 = __floats2bfloat162_rn(a6, a7);
-    r.x = *reinterpret_cast<uint32_t*>(&t0);
-    r.y = *reinterpret_cast<uint32_t*>(&t1);
-    r.z = *reinterpret_cast<uint32_t*>(&t2);
-    r.w = *reinterpret_cast<uint32_t*>(&t3);
-    return r;
-}
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,

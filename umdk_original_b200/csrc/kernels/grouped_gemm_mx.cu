@@ -1,0 +1,342 @@
+// Grouped (per-expert, ragged-M) fp8 GEMM for sm_100a whose block scaling is done by the tensor
+// core: tcgen05.mma kind::mxf8f6f4.block_scale multiplies every 32-element K-slice of an A row
+// and of a B row by a UE8M0 (power-of-two) scale factor held in tensor memory, so the whole
+// reduction accumulates in ONE TMEM tile and the epilogue runs once per output tile instead of
+// once per 128-K block.  It is the fast path of the expert MLP; the kernel in grouped_gemm.cu
+// keeps arbitrary fp32 scales by promoting every K-block in registers and is about 2x slower.
+//
+// Contract: a_scales [rows, K/128] and b_scales [E, N/128, K/128] are fp32 numbers that are exact
+// powers of two (what quantisation with `ue8m0` scale rounding produces); only their exponent
+// byte is used.  Same three epilogues as grouped_gemm.cu (mode 0 bf16 tile, mode 1 SwiGLU + 1x128
+// fp8 requantisation with power-of-two scales, mode 2 bf16 rows pushed into the combine slots of
+// the origin ranks), same role in the layer as the reference's two CATLASS kernels
+// (fused_deep_moe/gemm/kernel/grouped_matmul_slice_m_per_token_dequant_swiglu_quant_multistage_
+// workspace.h:355-1718 and ..._dequant_multistage_workspace.h:24-378): there the per-token and
+// per-channel scales are applied by vector cores after an int32 cube GEMM
+// (epilogue/block/block_epilogue_per_token_dequant_swiglu.h:236-272).
+//
+// Tile 128 x 256 x 128 per pipeline stage, four stages of shared memory fed by TMA.
+// Tensor memory (512 columns): accumulator in columns [0, 256); scale factors of pipeline stage
+// s in columns [256 + 16 s, 256 + 16 s + 12): 4 columns for the 128 A rows (row m sits in lane
+// m % 32, column m / 32, replicated in the four 32-lane quarters), 8 columns for the 256 B rows.
+// Each 32-bit scale column holds the scale bytes of 4 consecutive 32-element K-slices; with 1x128
+// scaling the four bytes are equal, so every MMA of a stage uses byte 0.
+//
+// Warp roles (768 threads): warp 0 lane 0 = TMA producer, warp 1 lane 0 = MMA issuer (warp 1 owns
+// the TMEM allocation), warps 4..7 = scale-factor writers (one per TMEM lane quarter: they load
+// the fp32 scales two K-blocks ahead, take the exponent bytes and tcgen05.st them), warps 8..23 =
+// epilogue (warp w drains lanes 32 (w % 4).., 32-column quarter (w - 8) / 4 of each 128-column
+// half into registers, hands the accumulator back, then does the math and the stores while the
+// tensor core already works on the next tile).
+// Every mbarrier wait is bounded; a role that gives up sets a shared abort word that releases
+// the others, a status word is recorded and the CTA frees its TMEM and returns.
+#include "gemm_common.cuh"
+
+namespace cam {
+
+constexpr int kMxThreads = 768;
+constexpr int kMxEpiThreads = 512;
+constexpr int kMxSfWarp0 = 4, kMxEpiWarp0 = 8;
+constexpr int kMxSmemCtrl = 8192;
+constexpr int kMxSmem = kStages * kStageBytes + kMxSmemCtrl + 1024;  // +1024 alignment slack
+constexpr uint32_t kMxTmemCols = 512;
+constexpr uint32_t kMxSfCol0 = 256, kMxSfStride = 16;
+// Register re-partitioning (setmaxnreg): the CTA is launched with kMxLaunchRegs per thread (what
+// ptxas reports for this kernel); the control and scale-factor warp-groups give registers back
+// and the four epilogue warp-groups take them.  setmaxnreg.inc waits for the CTA's pool without
+// any time limit, so the sum below must not exceed what the CTA owns.
+constexpr uint32_t kMxLaunchRegs = 80, kMxCtrlRegs = 32, kMxSfRegs = 56, kMxEpiRegs = 96;
+static_assert(128 * kMxCtrlRegs + 128 * kMxSfRegs + kMxEpiThreads * kMxEpiRegs <= kMxLaunchRegs * kMxThreads,
+              "setmaxnreg budget exceeds the registers the CTA owns: the kernel would hang");
+
+__device__ __forceinline__ uint32_t ue8m0_word(float scale) {
+    return ((__float_as_uint(scale) >> 23) & 0xFFu) * 0x01010101u;
+}
+
+__global__ void __launch_bounds__(kMxThreads, 1)
+grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                          const GroupedGemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* ctrl = smem + kStages * kStageBytes;
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(ctrl);   // TMA bytes of a stage have landed
+    uint64_t* bar_sf = bar_full + kStages;                    // scale factors of a stage are in TMEM
+    uint64_t* bar_empty = bar_sf + kStages;                   // the MMAs that read a stage have retired
+    uint64_t* bar_tfull = bar_empty + kStages;                // accumulator of a tile is complete
+    uint64_t* bar_tempty = bar_tfull + 1;                     // accumulator has been drained
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 1);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    float* s_amax = reinterpret_cast<float*>(ctrl + 256);  // [2 parities][4 column quarters][128 rows]
+
+    const int warp = static_cast<int>(threadIdx.x) >> 5;
+    const uint32_t lane = lane_id();
+    const int kblocks = p.k_dim / BK;
+    const int n_tiles = (p.mode == 1) ? (p.n_dim / 2) / 128 : (p.n_dim + BN - 1) / BN;
+    const int nblk = p.n_dim / 128;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_sf[s], 4);
+            mbar_init(&bar_empty[s], 1);
+        }
+        mbar_init(bar_tfull, 1);
+        mbar_init(bar_tempty, kMxEpiThreads / 32);
+        *abort_flag = 0u;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, kMxTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < kMxSfWarp0) {
+        reg_dealloc<kMxCtrlRegs>();
+        if (warp == 0 && lane == 0) {
+            // ------------------------------------------------------------ TMA producer
+            prefetch_tensormap(&tmap_a);
+            prefetch_tensormap(&tmap_b);
+            TileWalker w(p.expert_offsets, p.num_experts, n_tiles);
+            uint32_t it = 0;
+            int e, mt, nt, row0, rows;
+            bool ok = true;
+            for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
+                 tile += static_cast<int>(gridDim.x)) {
+                const int brow_lo = e * p.n_dim + ((p.mode == 1) ? nt * 128 : nt * BN);
+                const int brow_hi = (p.mode == 1) ? (e * p.n_dim + p.n_dim / 2 + nt * 128) : (brow_lo + 128);
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    if (!mbar_wait_bounded(&bar_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                    uint8_t* sa = smem + s * kStageBytes;
+                    mbar_arrive_expect_tx(&bar_full[s], kStageBytes);
+                    tma_load_2d(sa, &tmap_a, &bar_full[s], kb * BK, row0);
+                    tma_load_2d(sa + kATile, &tmap_b, &bar_full[s], kb * BK, brow_lo);
+                    tma_load_2d(sa + kATile + kBTile / 2, &tmap_b, &bar_full[s], kb * BK, brow_hi);
+                }
+            }
+            if (!ok) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 0, static_cast<int>(it));
+        } else if (warp == 1 && lane == 0) {
+            // ------------------------------------------------------------ MMA issuer
+            constexpr uint32_t idesc = umma_idesc_mxf8(BM, BN);
+            TileWalker w(p.expert_offsets, p.num_experts, n_tiles);
+            uint32_t it = 0, tcount = 0;
+            int e, mt, nt, row0, rows;
+            bool ok = true;
+            for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
+                 tile += static_cast<int>(gridDim.x), ++tcount) {
+                // the epilogue must have drained the previous tile before its columns are overwritten
+                if (!mbar_wait_bounded(bar_tempty, (tcount & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    if (!mbar_wait_bounded(&bar_sf[s], ph, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait_bounded(&bar_full[s], ph, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_u32(smem + s * kStageBytes);
+                    const uint64_t adesc = umma_desc_k_sw128(sa);
+                    const uint64_t bdesc = umma_desc_k_sw128(sa + kATile);
+                    const uint32_t sfa = tmem_base + kMxSfCol0 + s * kMxSfStride;
+                    const uint32_t sfb = sfa + 4u;
+#pragma unroll
+                    for (int k = 0; k < BK / 32; ++k)  // 32 bytes (= 2 x 16) further along K inside the swizzle atom
+                        tc_mma_mxf8(tmem_base, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) ? 1u : 0u, sfa, sfb);
+                    tc_commit(&bar_empty[s]);  // stage (smem and scale columns) reusable once these MMAs retire
+                }
+                if (!ok) break;
+                tc_commit(bar_tfull);  // accumulator complete once every MMA of the tile has retired
+            }
+            if (!ok) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 1, static_cast<int>(it));
+        }
+    } else if (warp < kMxEpiWarp0) {
+        reg_dealloc<kMxSfRegs>();
+        // ---------------------------------------------------------------- scale-factor writers
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        TileWalker w(p.expert_offsets, p.num_experts, n_tiles);
+        uint32_t it = 0;
+        int e, mt, nt, row0, rows;
+        bool ok = true;
+        for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
+             tile += static_cast<int>(gridDim.x)) {
+            const float* as[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int r = min(row0 + 32 * j + static_cast<int>(lane), p.a_rows - 1);
+                as[j] = p.a_scales + static_cast<size_t>(r) * kblocks;
+            }
+            int nb_lo, nb_hi;
+            if (p.mode == 1) { nb_lo = nt; nb_hi = nblk / 2 + nt; }
+            else { nb_lo = 2 * nt; nb_hi = min(2 * nt + 1, nblk - 1); }
+            const float* bs_lo = p.b_scales + (static_cast<size_t>(e) * nblk + nb_lo) * kblocks;
+            const float* bs_hi = p.b_scales + (static_cast<size_t>(e) * nblk + nb_hi) * kblocks;
+            // scales are fetched two K-blocks ahead of their use
+            float c[6], n1[6];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) c[j] = __ldg(as[j]);
+            c[4] = __ldg(bs_lo); c[5] = __ldg(bs_hi);
+#pragma unroll
+            for (int j = 0; j < 6; ++j) n1[j] = c[j];
+            if (kblocks > 1) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) n1[j] = __ldg(as[j] + 1);
+                n1[4] = __ldg(bs_lo + 1); n1[5] = __ldg(bs_hi + 1);
+            }
+            for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                uint32_t wd[6];
+#pragma unroll
+                for (int j = 0; j < 6; ++j) { wd[j] = ue8m0_word(c[j]); c[j] = n1[j]; }
+                if (kb + 2 < kblocks) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) n1[j] = __ldg(as[j] + kb + 2);
+                    n1[4] = __ldg(bs_lo + kb + 2); n1[5] = __ldg(bs_hi + kb + 2);
+                }
+                const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                const bool got = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, abort_flag);
+                if (!__all_sync(0xFFFFFFFFu, got)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t col = tmem_base + lane_base + kMxSfCol0 + s * kMxSfStride;
+                tmem_st_32x32b_x4(col, wd[0], wd[1], wd[2], wd[3]);
+                tmem_st_32x32b_x4(col + 4u, wd[4], wd[4], wd[4], wd[4]);
+                tmem_st_32x32b_x4(col + 8u, wd[5], wd[5], wd[5], wd[5]);
+                tc_wait_st();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_sf[s]);
+            }
+        }
+        if (!ok && lane == 0) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 3, static_cast<int>(it));
+    } else {
+        reg_alloc<kMxEpiRegs>();
+        // ---------------------------------------------------------------- epilogue warps
+        const int ew = warp - kMxEpiWarp0;
+        const int q = warp & 3;   // TMEM lane quarter this warp may read
+        const int cq = ew >> 2;   // which 32-column quarter of each 128-column half
+        const int r = q * 32 + static_cast<int>(lane);
+        TileWalker w(p.expert_offsets, p.num_experts, n_tiles);
+        uint32_t tcount = 0;
+        int e, mt, nt, row0, rows;
+        bool ok = true;
+        for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
+             tile += static_cast<int>(gridDim.x), ++tcount) {
+            const bool valid = r < rows;
+            const int grow = row0 + (valid ? r : 0);
+            if (!mbar_wait_bounded(bar_tfull, tcount & 1u, abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + cq * 32;
+            uint32_t v0[32], v1[32];  // columns cq*32.. of the first 128-column half, same of the second
+            tmem_ld_32x32b_x32(t0, v0);
+            tmem_ld_32x32b_x32(t0 + 128, v1);
+            tc_wait_ld_regs(v0);
+            tc_wait_ld_regs(v1);
+            // the tile now lives in registers: hand the accumulator back to the MMA issuer
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty);
+
+            if (p.mode == 1) {
+                // SwiGLU on matching gate/up columns, then 1x128 fp8 requantisation (power-of-two scale).
+                const int ia = p.n_dim / 2;
+                float act[32];
+                float amax = 0.f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float g = __uint_as_float(v0[j]);
+                    act[j] = (g / (1.f + expf(-g))) * __uint_as_float(v1[j]);
+                    amax = fmaxf(amax, fabsf(act[j]));
+                }
+                float* xch = s_amax + (tcount & 1u) * 512;
+                xch[cq * 128 + r] = amax;
+                named_bar_sync(1, kMxEpiThreads);
+                amax = fmaxf(fmaxf(xch[r], xch[128 + r]), fmaxf(xch[256 + r], xch[384 + r]));
+                float scale, inv;
+                ue8m0_scale(amax, scale, inv);
+                if (valid) {
+                    uint8_t* dst = p.act_q + static_cast<size_t>(grow) * ia + nt * 128 + cq * 32;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 16) {
+                        uint4 o;
+                        o.x = pack_e4m3x4(act[j + 0] * inv, act[j + 1] * inv, act[j + 2] * inv, act[j + 3] * inv);
+                        o.y = pack_e4m3x4(act[j + 4] * inv, act[j + 5] * inv, act[j + 6] * inv, act[j + 7] * inv);
+                        o.z = pack_e4m3x4(act[j + 8] * inv, act[j + 9] * inv, act[j + 10] * inv, act[j + 11] * inv);
+                        o.w = pack_e4m3x4(act[j + 12] * inv, act[j + 13] * inv, act[j + 14] * inv, act[j + 15] * inv);
+                        *reinterpret_cast<uint4*>(dst + j) = o;
+                    }
+                    if (cq == 0) p.act_s[static_cast<size_t>(grow) * (ia / 128) + nt] = scale;
+                }
+            } else {
+                // bf16 tile, either to the local output or straight to the origin rank's combine slot
+                __nv_bfloat16* orow = nullptr;
+                if (valid) {
+                    if (p.mode == 0) {
+                        orow = p.out + static_cast<size_t>(grow) * p.n_dim;
+                    } else {
+                        const int src = p.row_src[static_cast<size_t>(grow) * 3 + 0];
+                        const int tok = p.row_src[static_cast<size_t>(grow) * 3 + 1];
+                        const int kk = p.row_src[static_cast<size_t>(grow) * 3 + 2];
+                        if (src >= 0 && src < p.num_ranks && tok >= 0 && kk >= 0 && kk < p.topk)
+                            orow = reinterpret_cast<__nv_bfloat16*>(p.peer_base[src] + p.off_combine_buf) +
+                                   (static_cast<size_t>(tok) * p.topk + kk) * static_cast<size_t>(p.n_dim);
+                    }
+                }
+                if (orow != nullptr) {
+                    const int c_lo = nt * BN + cq * 32;
+                    const int c_hi = c_lo + 128;
+                    if (c_lo < p.n_dim) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8)
+                            st_na_v4(orow + c_lo + j,
+                                     pack_bf16x8(__uint_as_float(v0[j]), __uint_as_float(v0[j + 1]), __uint_as_float(v0[j + 2]),
+                                                 __uint_as_float(v0[j + 3]), __uint_as_float(v0[j + 4]), __uint_as_float(v0[j + 5]),
+                                                 __uint_as_float(v0[j + 6]), __uint_as_float(v0[j + 7])));
+                    }
+                    if (c_hi < p.n_dim) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8)
+                            st_na_v4(orow + c_hi + j,
+                                     pack_bf16x8(__uint_as_float(v1[j]), __uint_as_float(v1[j + 1]), __uint_as_float(v1[j + 2]),
+                                                 __uint_as_float(v1[j + 3]), __uint_as_float(v1[j + 4]), __uint_as_float(v1[j + 5]),
+                                                 __uint_as_float(v1[j + 6]), __uint_as_float(v1[j + 7])));
+                    }
+                }
+            }
+        }
+        if (!ok) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 2, static_cast<int>(tcount));
+    }
+
+    // ------------------------------------------------------------------ teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kMxTmemCols);
+    }
+    if (p.mode == 2 && threadIdx.x == 0) {
+        __threadfence_system();
+        const unsigned int old = atomicAdd(p.done_ctr, 1u);
+        if (old == gridDim.x - 1) {
+            p.done_ctr[0] = 0u;
+            __threadfence_system();
+            if (p.dbg_drop_flags == 0) {
+                for (int d = 0; d < p.num_ranks; ++d)
+                    st_release_sys_u32(reinterpret_cast<uint32_t*>(p.peer_base[d] + p.off_combine_flag) + p.rank,
+                                       p.epoch);
+            }
+        }
+    }
+}
+
+}  // namespace cam
+
+extern "C" int cam_grouped_gemm_mx_smem_bytes(void) { return cam::kMxSmem; }
+
+extern "C" int cam_launch_grouped_gemm_mxfp8(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
+                                             const CUtensorMap* tmap_b, int grid, cudaStream_t stream) {
+    cudaError_t e = cudaFuncSetAttribute(cam::grouped_gemm_mxfp8_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, cam::kMxSmem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cam::grouped_gemm_mxfp8_kernel<<<grid, cam::kMxThreads, cam::kMxSmem, stream>>>(*tmap_a, *tmap_b, *p);
+    return static_cast<int>(cudaGetLastError());
+}

@@ -336,8 +336,9 @@ extern "C" int cam_dispatch_normal(CamBuffer* b, const void* x, const void* topk
                                    int h, int E, int quant_mode, int phase_mask, cudaStream_t stream) {
     if (check_common(b, T, K, h, E, "dispatch_normal") != 0) return -1;
     CAM_CHECK(T <= b->layout.max_tokens, "dispatch_normal: %d tokens exceed the buffer's max_tokens %d", T, b->layout.max_tokens);
-    CAM_CHECK(quant_mode == CAM_QUANT_NONE || quant_mode == CAM_QUANT_INT8_TOKEN || quant_mode == CAM_QUANT_FP8_1x128,
-              "dispatch_normal: quant_mode %d is not one of 0 (bf16), 2 (int8 per token), 3 (fp8 1x128)", quant_mode);
+    CAM_CHECK(quant_mode == CAM_QUANT_NONE || quant_mode == CAM_QUANT_INT8_TOKEN || CAM_QUANT_IS_FP8(quant_mode),
+              "dispatch_normal: quant_mode %d is not one of 0 (bf16), 2 (int8 per token), 3 (fp8 1x128), "
+              "4 (fp8 1x128, power-of-two scales)", quant_mode);
     CAM_CUDA(cudaSetDevice(b->device));
     if (phase_mask & CAM_PHASE_COUNT) ++b->epoch_dispatch;
     cam::DispatchNormalParams p{};
@@ -418,8 +419,8 @@ extern "C" int cam_dispatch_ll(CamBuffer* b, const void* x, const void* expert_i
     CAM_CHECK(b->layout.ll_max_tokens > 0, "dispatch_ll: the buffer was created without low-latency regions");
     CAM_CHECK(T <= b->layout.ll_max_tokens, "dispatch_ll: %d tokens exceed ll_max_tokens %d", T, b->layout.ll_max_tokens);
     CAM_CHECK(E == b->layout.num_experts, "dispatch_ll: num_experts %d must equal the buffer's %d", E, b->layout.num_experts);
-    CAM_CHECK(quant_mode == CAM_QUANT_NONE || quant_mode == CAM_QUANT_INT8_TOKEN || quant_mode == CAM_QUANT_FP8_1x128,
-              "dispatch_ll: quant_mode %d is not one of 0, 2, 3 (static quantisation, mode 1, is not supported)", quant_mode);
+    CAM_CHECK(quant_mode == CAM_QUANT_NONE || quant_mode == CAM_QUANT_INT8_TOKEN || CAM_QUANT_IS_FP8(quant_mode),
+              "dispatch_ll: quant_mode %d is not one of 0, 2, 3, 4 (static quantisation, mode 1, is not supported)", quant_mode);
     CAM_CHECK(count_type == 0 || count_type == 1, "dispatch_ll: expertTokenNumsType must be 0 (cumulative) or 1 (counts)");
     CAM_CUDA(cudaSetDevice(b->device));
     if (phase_mask & CAM_PHASE_SEND) ++b->epoch_ll;
@@ -508,11 +509,10 @@ static int make_tmap(CamBuffer* cache_owner, CUtensorMap* out, const void* base,
     return 0;
 }
 
-extern "C" int cam_grouped_gemm_fp8(CamBuffer* b, const void* a_q, const float* a_scales, int a_rows,
-                                    const void* w_q, const float* w_scales, const int* expert_offsets,
-                                    int num_experts, int n_dim, int k_dim, int mode, void* out_bf16, void* act_q,
-                                    float* act_s, const int* row_src, int topk, int low_latency,
-                                    cudaStream_t stream) {
+static int grouped_gemm_impl(CamBuffer* b, const void* a_q, const float* a_scales, int a_rows, const void* w_q,
+                             const float* w_scales, const int* expert_offsets, int num_experts, int n_dim, int k_dim,
+                             int mode, void* out_bf16, void* act_q, float* act_s, const int* row_src, int topk,
+                             int low_latency, bool ue8m0, cudaStream_t stream) {
     CAM_CHECK(a_q && a_scales && w_q && w_scales && expert_offsets, "grouped_gemm: null operand");
     CAM_CHECK(num_experts >= 1 && a_rows >= 1, "grouped_gemm: empty problem");
     CAM_CHECK(k_dim >= 128 && k_dim % 128 == 0, "grouped_gemm: K %d must be a multiple of 128", k_dim);
@@ -578,15 +578,34 @@ extern "C" int cam_grouped_gemm_fp8(CamBuffer* b, const void* a_q, const float* 
     p.topk = topk;
     int sms = 0;
     CAM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-    const int rc = cam_launch_grouped_gemm_fp8(&p, &ta, &tb, sms, stream);
+    const int rc = ue8m0 ? cam_launch_grouped_gemm_mxfp8(&p, &ta, &tb, sms, stream)
+                         : cam_launch_grouped_gemm_fp8(&p, &ta, &tb, sms, stream);
     CAM_CHECK(rc == 0, "grouped_gemm launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
     return 0;
 }
 
-extern "C" int cam_fused_moe_fp8(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,
-                                 const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
-                                 const float* w2_s, void* out, int64_t* expert_token_nums, int T, int K, int h,
-                                 int inter, int E, int phase_mask, cudaStream_t stream) {
+extern "C" int cam_grouped_gemm_fp8(CamBuffer* b, const void* a_q, const float* a_scales, int a_rows,
+                                    const void* w_q, const float* w_scales, const int* expert_offsets,
+                                    int num_experts, int n_dim, int k_dim, int mode, void* out_bf16, void* act_q,
+                                    float* act_s, const int* row_src, int topk, int low_latency,
+                                    cudaStream_t stream) {
+    return grouped_gemm_impl(b, a_q, a_scales, a_rows, w_q, w_scales, expert_offsets, num_experts, n_dim, k_dim, mode,
+                             out_bf16, act_q, act_s, row_src, topk, low_latency, false, stream);
+}
+
+extern "C" int cam_grouped_gemm_mxfp8(CamBuffer* b, const void* a_q, const float* a_scales, int a_rows,
+                                      const void* w_q, const float* w_scales, const int* expert_offsets,
+                                      int num_experts, int n_dim, int k_dim, int mode, void* out_bf16, void* act_q,
+                                      float* act_s, const int* row_src, int topk, int low_latency,
+                                      cudaStream_t stream) {
+    return grouped_gemm_impl(b, a_q, a_scales, a_rows, w_q, w_scales, expert_offsets, num_experts, n_dim, k_dim, mode,
+                             out_bf16, act_q, act_s, row_src, topk, low_latency, true, stream);
+}
+
+static int fused_moe_impl(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,
+                          const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
+                          const float* w2_s, void* out, int64_t* expert_token_nums, int T, int K, int h, int inter,
+                          int E, int phase_mask, bool ue8m0, cudaStream_t stream) {
     if (check_common(b, T, K, h, E, "fused_moe_fp8") != 0) return -1;
     CAM_CHECK(inter >= 128 && inter % 128 == 0 && inter <= b->layout.hidden,
               "fused_moe_fp8: intermediate size %d must be a multiple of 128 and <= the buffer's hidden %d", inter, b->layout.hidden);
@@ -595,18 +614,19 @@ extern "C" int cam_fused_moe_fp8(CamBuffer* b, const void* x, const void* expert
     const CamLayout& L = b->layout;
     const int disp_mask = phase_mask & CAM_PHASE_ALL;
     if (disp_mask) {
-        if (cam_dispatch_normal(b, x, expert_ids, idx_is_i64, T, K, h, E, CAM_QUANT_FP8_1x128, disp_mask, stream) != 0)
+        if (cam_dispatch_normal(b, x, expert_ids, idx_is_i64, T, K, h, E,
+                                ue8m0 ? CAM_QUANT_FP8_1x128_UE8M0 : CAM_QUANT_FP8_1x128, disp_mask, stream) != 0)
             return -1;
     }
     if (phase_mask & CAM_PHASE_RECV) {
         const uint8_t* recv_x = b->base + L.off_recv_x;
         const float* recv_s = reinterpret_cast<const float*>(b->base + L.off_recv_scales);
         const int* recv_src = reinterpret_cast<const int*>(b->base + L.off_recv_src);
-        if (cam_grouped_gemm_fp8(b, recv_x, recv_s, L.capacity, w1_q, w1_s, b->expert_offsets, El, 2 * inter, h, 1,
-                                 nullptr, b->act_q, b->act_s, nullptr, K, 0, stream) != 0)
+        if (grouped_gemm_impl(b, recv_x, recv_s, L.capacity, w1_q, w1_s, b->expert_offsets, El, 2 * inter, h, 1,
+                              nullptr, b->act_q, b->act_s, nullptr, K, 0, ue8m0, stream) != 0)
             return -1;
-        if (cam_grouped_gemm_fp8(b, b->act_q, b->act_s, L.capacity, w2_q, w2_s, b->expert_offsets, El, h, inter, 2,
-                                 nullptr, nullptr, nullptr, recv_src, K, 0, stream) != 0)
+        if (grouped_gemm_impl(b, b->act_q, b->act_s, L.capacity, w2_q, w2_s, b->expert_offsets, El, h, inter, 2,
+                              nullptr, nullptr, nullptr, recv_src, K, 0, ue8m0, stream) != 0)
             return -1;
         if (expert_token_nums != nullptr)
             CAM_CUDA(cudaMemcpyAsync(expert_token_nums, b->num_recv_per_expert, sizeof(int64_t) * El,
@@ -618,4 +638,20 @@ extern "C" int cam_fused_moe_fp8(CamBuffer* b, const void* x, const void* expert
             return -1;
     }
     return 0;
+}
+
+extern "C" int cam_fused_moe_fp8(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,
+                                 const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
+                                 const float* w2_s, void* out, int64_t* expert_token_nums, int T, int K, int h,
+                                 int inter, int E, int phase_mask, cudaStream_t stream) {
+    return fused_moe_impl(b, x, expert_ids, idx_is_i64, topk_weights, w1_q, w1_s, w2_q, w2_s, out, expert_token_nums,
+                          T, K, h, inter, E, phase_mask, false, stream);
+}
+
+extern "C" int cam_fused_moe_mxfp8(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,
+                                   const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
+                                   const float* w2_s, void* out, int64_t* expert_token_nums, int T, int K, int h,
+                                   int inter, int E, int phase_mask, cudaStream_t stream) {
+    return fused_moe_impl(b, x, expert_ids, idx_is_i64, topk_weights, w1_q, w1_s, w2_q, w2_s, out, expert_token_nums,
+                          T, K, h, inter, E, phase_mask, true, stream);
 }

@@ -85,12 +85,26 @@ int cam_grouped_gemm_fp8(CamBuffer* b, const void* a_q, const float* a_scales, i
                          int mode, void* out_bf16, void* act_q, float* act_s, const int* row_src, int topk,
                          int low_latency, cudaStream_t stream);
 
+// Same, with the tensor core's own block scaling (kernels/grouped_gemm_mx.cu): every scale must be an
+// exact power of two; mode 1 emits power-of-two activation scales.
+int cam_grouped_gemm_mxfp8(CamBuffer* b, const void* a_q, const float* a_scales, int a_rows, const void* w_q,
+                           const float* w_scales, const int* expert_offsets, int num_experts, int n_dim, int k_dim,
+                           int mode, void* out_bf16, void* act_q, float* act_s, const int* row_src, int topk,
+                           int low_latency, cudaStream_t stream);
+
 // Whole fp8 MoE layer on the normal-mode path:
 // dispatch (fp8 1x128) -> GEMM1 + SwiGLU + requant -> GEMM2 with combine-send epilogue -> reduce.
 int cam_fused_moe_fp8(CamBuffer* b, const void* x_bf16, const void* expert_ids, int idx_is_i64,
                       const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
                       const float* w2_s, void* out_bf16, int64_t* expert_token_nums, int T, int K, int h,
                       int inter, int E, int phase_mask, cudaStream_t stream);
+
+// Same layer with power-of-two scales end to end: dispatch quantises with UE8M0 scale rounding, the
+// weights' 128x128 scales must be powers of two, both GEMMs run on the block-scaled tensor-core path.
+int cam_fused_moe_mxfp8(CamBuffer* b, const void* x_bf16, const void* expert_ids, int idx_is_i64,
+                        const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
+                        const float* w2_s, void* out_bf16, int64_t* expert_token_nums, int T, int K, int h,
+                        int inter, int E, int phase_mask, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

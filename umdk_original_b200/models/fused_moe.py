@@ -33,6 +33,8 @@ class FusedMoE(torch.nn.Module):
             weights = random_fp8_experts(self.num_local, cfg.hidden, cfg.intermediate, device=dev,
                                          seed=seed * 1000 + self.rank)
         self.weights = weights.to(dev)
+        # 4: power-of-two scales -> tcgen05 block-scaled GEMMs; 3: arbitrary fp32 scales
+        self.quant_mode = 4 if self.weights.power_of_two_scales else 3
         if gate_weight is None:
             g = torch.Generator(device="cpu")
             g.manual_seed(seed + 17)
@@ -51,7 +53,7 @@ class FusedMoE(torch.nn.Module):
         w = self.weights
         out, nums = cam_ops.ops.fused_deep_moe(
             x, topk_idx, [w.w1], [w.s1], [w.w2], [w.s2], topk_weights.float(), None, x_active_mask,
-            self.buffer.name, self.num_ranks, self.rank, self.cfg.num_experts, 0, 0, 3, 0)
+            self.buffer.name, self.num_ranks, self.rank, self.cfg.num_experts, 0, 0, self.quant_mode, 0)
         return out, nums
 
 

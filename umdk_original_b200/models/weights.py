@@ -30,6 +30,12 @@ class ExpertWeights:
         return ExpertWeights(self.w1.to(device), self.s1.to(device), self.w2.to(device), self.s2.to(device))
 
     @property
+    def power_of_two_scales(self) -> bool:
+        """True when both scale tensors hold exact powers of two: the layer then runs the
+        tensor-core block-scaled path (``quantMode=4``)."""
+        return ref.is_power_of_two(self.s1) and ref.is_power_of_two(self.s2)
+
+    @property
     def num_local_experts(self) -> int:
         return self.w1.shape[0]
 
@@ -37,31 +43,33 @@ class ExpertWeights:
         return sum(t.numel() * t.element_size() for t in (self.w1, self.s1, self.w2, self.s2))
 
 
-def quantize_fp8_block(w: torch.Tensor, chunk: int = 8) -> Tuple[torch.Tensor, torch.Tensor]:
-    """[E, N, K] float -> (e4m3, fp32 128x128 scales); processed in expert chunks to bound memory."""
+def quantize_fp8_block(w: torch.Tensor, chunk: int = 8, ue8m0: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    """[E, N, K] float -> (e4m3, fp32 128x128 scales); processed in expert chunks to bound memory.
+    ``ue8m0`` rounds the scales up to powers of two (needed by the tensor-core block-scaled path)."""
     qs, ss = [], []
     for i in range(0, w.shape[0], chunk):
-        q, s = ref.quant_fp8_128x128(w[i:i + chunk])
+        q, s = ref.quant_fp8_128x128(w[i:i + chunk], ue8m0)
         qs.append(q)
         ss.append(s)
     return torch.cat(qs), torch.cat(ss)
 
 
 def random_fp8_experts(num_local: int, hidden: int, inter: int, device="cpu", std: float = 0.02, seed: int = 0,
-                       chunk: int = 4) -> ExpertWeights:
-    """Random-init N(0, std) experts, quantised to e4m3 with 128x128 block scales, generated on
-    `device` in chunks so that 256 DeepSeek-sized experts never exist in fp32 at once."""
+                       chunk: int = 4, ue8m0: bool = True) -> ExpertWeights:
+    """Random-init N(0, std) experts, quantised to e4m3 with 128x128 block scales (powers of two
+    unless ``ue8m0=False``), generated on `device` in chunks so that 256 DeepSeek-sized experts
+    never exist in fp32 at once."""
     g = torch.Generator(device=device)
     g.manual_seed(seed)
     w1q, s1, w2q, s2 = [], [], [], []
     for i in range(0, num_local, chunk):
         n = min(chunk, num_local - i)
         a = torch.randn(n, 2 * inter, hidden, device=device, generator=g) * std
-        q, s = ref.quant_fp8_128x128(a)
+        q, s = ref.quant_fp8_128x128(a, ue8m0)
         w1q.append(q)
         s1.append(s)
         b = torch.randn(n, hidden, inter, device=device, generator=g) * std
-        q, s = ref.quant_fp8_128x128(b)
+        q, s = ref.quant_fp8_128x128(b, ue8m0)
         w2q.append(q)
         s2.append(s)
         del a, b
@@ -80,18 +88,19 @@ def random_w8a8_experts(num_local: int, hidden: int, inter: int, device="cpu", s
     return w1, s1, w2, s2
 
 
-def from_reference_w8a8(w1: torch.Tensor, s1: torch.Tensor, w2: torch.Tensor, s2: torch.Tensor) -> ExpertWeights:
+def from_reference_w8a8(w1: torch.Tensor, s1: torch.Tensor, w2: torch.Tensor, s2: torch.Tensor,
+                        ue8m0: bool = True) -> ExpertWeights:
     """Reference-format int8 W8A8 weights (w1 [E,h,2I] + s1 [E,2I], w2 [E,I,h] + s2 [E,h]) to the
     block-scaled fp8 form the tensor-core path computes in: dequantise per output channel, then
     requantise per 128x128 block."""
     qs1, ss1, qs2, ss2 = [], [], [], []
     for e in range(w1.shape[0]):
         a = w1[e].t().float() * s1[e].float().unsqueeze(-1)   # [2I, h]
-        q, s = ref.quant_fp8_128x128(a)
+        q, s = ref.quant_fp8_128x128(a, ue8m0)
         qs1.append(q)
         ss1.append(s)
         b = w2[e].t().float() * s2[e].float().unsqueeze(-1)   # [h, I]
-        q, s = ref.quant_fp8_128x128(b)
+        q, s = ref.quant_fp8_128x128(b, ue8m0)
         qs2.append(q)
         ss2.append(s)
     return ExpertWeights(torch.stack(qs1), torch.stack(ss1), torch.stack(qs2), torch.stack(ss2))

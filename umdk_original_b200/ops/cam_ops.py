@@ -47,8 +47,10 @@ SCHEMAS = [
     "-> Tensor",
     "moe_dispatch_prefill_quant(Tensor x, Tensor topk_idx, Tensor topk_weights, int num_worst_tokens, "
     "str group_ep, int rank, int num_ranks, int quant_mode) -> (Tensor, Tensor, Tensor, Tensor, Tensor)",
-    "grouped_gemm_fp8(Tensor a_q, Tensor a_s, Tensor w_q, Tensor w_s, Tensor expert_offsets) -> Tensor",
-    "grouped_gemm_fp8_swiglu(Tensor a_q, Tensor a_s, Tensor w_q, Tensor w_s, Tensor expert_offsets) -> (Tensor, Tensor)",
+    "grouped_gemm_fp8(Tensor a_q, Tensor a_s, Tensor w_q, Tensor w_s, Tensor expert_offsets, "
+    "bool ue8m0=False) -> Tensor",
+    "grouped_gemm_fp8_swiglu(Tensor a_q, Tensor a_s, Tensor w_q, Tensor w_s, Tensor expert_offsets, "
+    "bool ue8m0=False) -> (Tensor, Tensor)",
 ]
 
 if _C is None:
@@ -143,7 +145,7 @@ def _moe_dispatch_shmem_cpu(x, expertIds, scales, xActiveMask, epWorldSize, epRa
         expand = torch.cat([rx.view(torch.uint8), torch.zeros((pad, rx.shape[1]), dtype=torch.uint8)]).view(ref.FP8)
     else:
         expand = torch.cat([rx, rx.new_zeros((pad, rx.shape[1]))])
-    if quantMode == 3:
+    if quantMode in (3, 4):
         dyn = torch.cat([rs, rs.new_zeros((pad, rs.shape[1]))])
     elif quantMode == 2:
         dyn = torch.cat([rs.reshape(-1), rs.new_zeros(pad)])
@@ -188,14 +190,15 @@ def _fused_deep_moe_cpu(x, expertIds, gmm1PermutedWeight, gmm1PermutedWeightScal
     if active is not None:
         ids = expertIds.clone()
         ids[active:] = -1
-    if w1.dtype == ref.FP8:  # block-scaled fp8 (quantMode 3)
-        rx, rs, src, cnt, per_e, _ = be.dispatch(g, x, ids, 3)
+    if w1.dtype == ref.FP8:  # block-scaled fp8 (quantMode 3; 4 = power-of-two scales)
+        po2 = quantMode == 4
+        rx, rs, src, cnt, per_e, _ = be.dispatch(g, x, ids, 4 if po2 else 3)
         y = torch.zeros(rx.shape[0], x.shape[1], dtype=torch.bfloat16)
         off = torch.cat([torch.zeros(1, dtype=torch.long), per_e.cumsum(0)])
         for le in range(el):
             a, b = int(off[le]), int(off[le + 1])
             if b > a:
-                y[a:b] = ref.expert_mlp_fp8(rx[a:b], rs[a:b], w1[le], s1[le], w2[le], s2[le])
+                y[a:b] = ref.expert_mlp_fp8(rx[a:b], rs[a:b], w1[le], s1[le], w2[le], s2[le], ue8m0=po2)
     elif w1.dtype == torch.int8:  # reference layout: w1 [E_l, h, 2I], s1 [E_l, 2I], w2 [E_l, I, h], s2 [E_l, h]
         rx, rs, src, cnt, per_e, _ = be.dispatch(g, x, ids, 0)
         y = torch.zeros(rx.shape[0], x.shape[1], dtype=torch.bfloat16)
@@ -216,7 +219,7 @@ def _fused_deep_moe_cpu(x, expertIds, gmm1PermutedWeight, gmm1PermutedWeightScal
     return [out, per_e.to(torch.int64)]
 
 
-def _grouped_gemm_fp8_cpu(a_q, a_s, w_q, w_s, expert_offsets):
+def _grouped_gemm_fp8_cpu(a_q, a_s, w_q, w_s, expert_offsets, ue8m0=False):
     out = torch.zeros(a_q.shape[0], w_q.shape[1], dtype=torch.bfloat16)
     off = expert_offsets.tolist()
     for e in range(w_q.shape[0]):
@@ -226,7 +229,7 @@ def _grouped_gemm_fp8_cpu(a_q, a_s, w_q, w_s, expert_offsets):
     return out
 
 
-def _grouped_gemm_fp8_swiglu_cpu(a_q, a_s, w_q, w_s, expert_offsets):
+def _grouped_gemm_fp8_swiglu_cpu(a_q, a_s, w_q, w_s, expert_offsets, ue8m0=False):
     i = w_q.shape[1] // 2
     q = torch.zeros(a_q.shape[0], i, dtype=torch.uint8).view(ref.FP8)
     s = torch.zeros(a_q.shape[0], i // 128, dtype=torch.float32)
@@ -236,7 +239,7 @@ def _grouped_gemm_fp8_swiglu_cpu(a_q, a_s, w_q, w_s, expert_offsets):
         if b > a:
             y = ref.dequant_fp8_1x128(a_q[a:b], a_s[a:b]) @ ref.dequant_fp8_128x128(w_q[e], w_s[e]).t()
             act = (y[:, :i] / (1.0 + torch.exp(-y[:, :i]))) * y[:, i:]
-            qq, ss = ref.quant_fp8_1x128(act)
+            qq, ss = ref.quant_fp8_1x128(act, ue8m0)
             q.view(torch.uint8)[a:b] = qq.view(torch.uint8)
             s[a:b] = ss
     return q, s

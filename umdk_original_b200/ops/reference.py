@@ -27,12 +27,30 @@ FP8 = torch.float8_e4m3fn
 # ----------------------------------------------------------------------------------------------
 # Quantisation
 # ----------------------------------------------------------------------------------------------
-def quant_fp8_1x128(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """e4m3 with one fp32 scale per 128 contiguous elements of the last dim."""
+def ue8m0_round_up(scale: torch.Tensor) -> torch.Tensor:
+    """Smallest power of two >= scale (fp32, positive, normal): what a UE8M0 scale factor can hold.
+    Same bit arithmetic as ue8m0_scale() in csrc/common/quant.cuh."""
+    bits = scale.float().contiguous().view(torch.int32)
+    e = (bits >> 23) + ((bits & 0x7FFFFF) != 0).to(torch.int32)
+    return (e << 23).view(torch.float32)
+
+
+def is_power_of_two(scale: torch.Tensor) -> bool:
+    bits = scale.float().contiguous().view(torch.int32)
+    return bool(((bits & 0x7FFFFF) == 0).all()) and bool((scale > 0).all())
+
+
+def quant_fp8_1x128(x: torch.Tensor, ue8m0: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """e4m3 with one fp32 scale per 128 contiguous elements of the last dim.  With ``ue8m0`` the
+    scale is rounded up to a power of two (the form the tensor core's block scaling takes)."""
     n, h = x.shape
     assert h % 128 == 0
     xf = x.float().view(n, h // 128, 128)
     amax = xf.abs().amax(dim=-1).clamp_min(1e-4)
+    if ue8m0:
+        scale = ue8m0_round_up(amax / torch.tensor(FP8_MAX, dtype=torch.float32))
+        q = (xf * (1.0 / scale).unsqueeze(-1)).to(FP8).view(n, h)
+        return q, scale
     inv = (torch.tensor(FP8_MAX, dtype=torch.float32) / amax).unsqueeze(-1)
     q = (xf * inv).to(FP8).view(n, h)
     return q, amax / FP8_MAX
@@ -43,13 +61,16 @@ def dequant_fp8_1x128(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
     return (q.float().view(n, h // 128, 128) * s.float().unsqueeze(-1)).view(n, h)
 
 
-def quant_fp8_128x128(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Weights [..., N, K] -> e4m3 with one fp32 scale per 128x128 block (scale = amax/448)."""
+def quant_fp8_128x128(w: torch.Tensor, ue8m0: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Weights [..., N, K] -> e4m3 with one fp32 scale per 128x128 block (scale = amax/448, rounded
+    up to a power of two with ``ue8m0``)."""
     *lead, n, k = w.shape
     assert n % 128 == 0 and k % 128 == 0
     wf = w.float().reshape(*lead, n // 128, 128, k // 128, 128)
     amax = wf.abs().amax(dim=(-3, -1)).clamp_min(1e-4)  # [..., n/128, k/128]
     scale = amax / FP8_MAX
+    if ue8m0:
+        scale = ue8m0_round_up(scale)
     q = (wf / scale.unsqueeze(-1).unsqueeze(-3)).to(FP8).reshape(*lead, n, k)
     return q, scale
 
@@ -182,7 +203,7 @@ def dense_moe_fp32(x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.
 
 
 def expert_mlp_fp8(xq: torch.Tensor, xs: torch.Tensor, w1q: torch.Tensor, w1s: torch.Tensor, w2q: torch.Tensor,
-                   w2s: torch.Tensor, return_act: bool = False):
+                   w2s: torch.Tensor, return_act: bool = False, ue8m0: bool = False):
     """Block-scaled fp8 expert MLP exactly as the two grouped GEMMs compute it (one expert).
     xq [n,h] e4m3 + xs [n,h/128]; w1q [2I,h] + w1s [2I/128,h/128]; w2q [h,I] + w2s [h/128,I/128].
     Returns bf16 [n,h]."""
@@ -191,7 +212,7 @@ def expert_mlp_fp8(xq: torch.Tensor, xs: torch.Tensor, w1q: torch.Tensor, w1s: t
     i = w1q.shape[0] // 2
     g, u = y[:, :i], y[:, i:]
     a = (g / (1.0 + torch.exp(-g))) * u
-    aq, a_s = quant_fp8_1x128(a)
+    aq, a_s = quant_fp8_1x128(a, ue8m0)
     z = dequant_fp8_1x128(aq, a_s) @ dequant_fp8_128x128(w2q, w2s).t()
     if return_act:
         return z.to(torch.bfloat16), aq, a_s
@@ -199,13 +220,14 @@ def expert_mlp_fp8(xq: torch.Tensor, xs: torch.Tensor, w1q: torch.Tensor, w1s: t
 
 
 def fused_moe_fp8_reference(x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, w1q: torch.Tensor,
-                            w1s: torch.Tensor, w2q: torch.Tensor, w2s: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+                            w1s: torch.Tensor, w2q: torch.Tensor, w2s: torch.Tensor,
+                            ue8m0: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """Whole fp8 MoE layer for one rank's tokens with all experts visible (w*: [E, ...]).
     Returns (out [T,h] bf16, tokens per expert [E] int64)."""
     t, h = x.shape
     k = topk_idx.shape[1]
     e_total = w1q.shape[0]
-    xq, xs = quant_fp8_1x128(x)
+    xq, xs = quant_fp8_1x128(x, ue8m0)
     rows = torch.zeros(t, k, h, dtype=torch.bfloat16)
     counts = torch.zeros(e_total, dtype=torch.int64)
     idx = topk_idx.long()
@@ -214,7 +236,7 @@ def fused_moe_fp8_reference(x: torch.Tensor, topk_idx: torch.Tensor, topk_weight
         counts[e] = tok.numel()
         if tok.numel() == 0:
             continue
-        rows[tok, kk] = expert_mlp_fp8(xq[tok], xs[tok], w1q[e], w1s[e], w2q[e], w2s[e])
+        rows[tok, kk] = expert_mlp_fp8(xq[tok], xs[tok], w1q[e], w1s[e], w2q[e], w2s[e], ue8m0=ue8m0)
     return combine_reference(rows, topk_idx, topk_weights, e_total), counts
 
 

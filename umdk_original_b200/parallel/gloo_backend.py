@@ -83,8 +83,8 @@ def dispatch(g: CpuGroup, x: torch.Tensor, topk_idx: torch.Tensor, quant_mode: i
     tok = pair // k
     rows = x[tok]
     scales = None
-    if quant_mode == 3:
-        rows, scales = ref.quant_fp8_1x128(rows) if rows.numel() else (rows.to(ref.FP8), rows.new_zeros((0, x.shape[1] // 128), dtype=torch.float32))
+    if quant_mode in (3, 4):
+        rows, scales = ref.quant_fp8_1x128(rows, quant_mode == 4) if rows.numel() else (rows.to(ref.FP8), rows.new_zeros((0, x.shape[1] // 128), dtype=torch.float32))
     elif quant_mode == 2:
         if smooth is not None and rows.numel():
             ids = topk_idx.reshape(-1).long()[pair]

@@ -128,6 +128,16 @@ def run_ours(args, cfg, rank, world, local):
     buf.check()
     clock_summary = clocks.summary()
 
+    # per-stage breakdown from a separate, untimed pass (events between the four launches)
+    buf.set_profile(True)
+    parts = []
+    for i in range(5):
+        step(i)
+        parts.append(buf.read_profile())
+        barrier(world)
+    buf.set_profile(False)
+    breakdown = {k: max_over_ranks(sorted(p[k] for p in parts)[len(parts) // 2], world) for k in parts[0]}
+
     e2e = None
     if not args.no_e2e:
         runner = MoEStepRunner(layer, tokens)
@@ -165,6 +175,7 @@ def run_ours(args, cfg, rank, world, local):
             "clocks": {k: clock_summary[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
             "gpu_launches": 4 * args.steps,
             "tflops_per_gpu": cfg.flops_per_token() * tokens / (ms * 1e-3) / 1e12,
+            "stage_ms_max_over_ranks": breakdown,
         }
         if e2e is not None:
             line["e2e"] = e2e

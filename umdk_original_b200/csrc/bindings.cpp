@@ -88,6 +88,12 @@ public:
     void reset() { CAM_RT(cam_buffer_reset(buf_, stream())); }
     void set_timeout_ms(double ms) { cam_buffer_set_timeout_ms(buf_, ms); }
     void set_debug_drop_flags(bool on) { cam_buffer_set_debug_drop_flags(buf_, on ? 1 : 0); }
+    void set_profile(bool on) { CAM_RT(cam_buffer_set_profile(buf_, on ? 1 : 0)); }
+    std::vector<double> read_profile() {
+        float ms[4];
+        CAM_RT(cam_buffer_read_profile(buf_, ms));
+        return {ms[0], ms[1], ms[2], ms[3]};
+    }
     std::tuple<int64_t, int64_t, int64_t, int64_t, std::string> poll_status() {
         CamStatus st;
         CAM_RT(cam_buffer_poll_status(buf_, stream(), &st));
@@ -601,6 +607,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("reset", &Buffer::reset)
         .def("set_timeout_ms", &Buffer::set_timeout_ms)
         .def("set_debug_drop_flags", &Buffer::set_debug_drop_flags)
+        .def("set_profile", &Buffer::set_profile)
+        .def("read_profile", &Buffer::read_profile)
         .def("poll_status", &Buffer::poll_status)
         .def("recv_x", &Buffer::recv_x)
         .def("recv_scales", &Buffer::recv_scales)

@@ -37,8 +37,15 @@ namespace cam {
 constexpr int kMxThreads = 768;
 constexpr int kMxEpiThreads = 512;
 constexpr int kMxSfWarp0 = 4, kMxEpiWarp0 = 8;
-constexpr int kMxSmemCtrl = 8192;
-constexpr int kMxSmem = kStages * kStageBytes + kMxSmemCtrl + 1024;  // +1024 alignment slack
+// Shared memory: 4 pipeline stages | bf16 staging of half an output tile (128 rows x 256 bytes,
+// rows 272 bytes apart so that 16-byte stores of neighbouring rows fall into different banks; the
+// per-row amax exchange of the SwiGLU epilogue uses the same bytes) | barriers.  232448 bytes, the
+// whole 227 KiB a CTA can have, so the dynamic segment must start on a 1024-byte boundary.
+constexpr int kMxStgPitch = 272;
+constexpr int kMxStgBytes = BM * kMxStgPitch;  // 34816
+constexpr int kMxSmemCtrl = 1024;
+constexpr int kMxSmem = kStages * kStageBytes + kMxStgBytes + kMxSmemCtrl;
+static_assert(kMxSmem <= 232448, "exceeds the shared memory of one CTA");
 constexpr uint32_t kMxTmemCols = 512;
 constexpr uint32_t kMxSfCol0 = 256, kMxSfStride = 16;
 // Register re-partitioning (setmaxnreg): the CTA is launched with kMxLaunchRegs per thread (what
@@ -56,9 +63,13 @@ __device__ __forceinline__ uint32_t ue8m0_word(float scale) {
 __global__ void __launch_bounds__(kMxThreads, 1)
 grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                           const GroupedGemmParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* ctrl = smem + kStages * kStageBytes;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if (smem_u32(smem) & 1023u) {  // swizzled TMA tiles need it; nothing has been set up yet, so just leave
+        if (threadIdx.x == 0) gemm_record_status(p.status, CAM_ERR_BAD_INDEX, 4, static_cast<int>(smem_u32(smem) & 1023u));
+        return;
+    }
+    uint8_t* stg = smem + kStages * kStageBytes;
+    uint8_t* ctrl = stg + kMxStgBytes;
     uint64_t* bar_full = reinterpret_cast<uint64_t*>(ctrl);   // TMA bytes of a stage have landed
     uint64_t* bar_sf = bar_full + kStages;                    // scale factors of a stage are in TMEM
     uint64_t* bar_empty = bar_sf + kStages;                   // the MMAs that read a stage have retired
@@ -66,7 +77,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     uint64_t* bar_tempty = bar_tfull + 1;                     // accumulator has been drained
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    float* s_amax = reinterpret_cast<float*>(ctrl + 256);  // [2 parities][4 column quarters][128 rows]
+    float* s_amax = reinterpret_cast<float*>(stg);  // mode 1 only: [2 parities][4 column quarters][128 rows]
 
     const int warp = static_cast<int>(threadIdx.x) >> 5;
     const uint32_t lane = lane_id();
@@ -281,28 +292,32 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                                    (static_cast<size_t>(tok) * p.topk + kk) * static_cast<size_t>(p.n_dim);
                     }
                 }
-                if (orow != nullptr) {
-                    const int c_lo = nt * BN + cq * 32;
-                    const int c_hi = c_lo + 128;
-                    if (c_lo < p.n_dim) {
+                // Half a tile (128 columns) at a time goes through shared memory as bf16, and every row
+                // leaves as ONE 256-byte bulk copy (local or over NVLink) instead of 16-byte stores
+                // scattered over 32 rows.  The thread of column quarter 0 issues its row's copy.
+                uint8_t* srow = stg + r * kMxStgPitch;
+                auto push_half = [&](const uint32_t (&v)[32], int c0) {
+                    if (cq == 0) bulk_wait_group_read<0>();  // the previous copies have read the staging area
+                    named_bar_sync(1, kMxEpiThreads);
 #pragma unroll
-                        for (int j = 0; j < 32; j += 8)
-                            st_na_v4(orow + c_lo + j,
-                                     pack_bf16x8(__uint_as_float(v0[j]), __uint_as_float(v0[j + 1]), __uint_as_float(v0[j + 2]),
-                                                 __uint_as_float(v0[j + 3]), __uint_as_float(v0[j + 4]), __uint_as_float(v0[j + 5]),
-                                                 __uint_as_float(v0[j + 6]), __uint_as_float(v0[j + 7])));
+                    for (int j = 0; j < 32; j += 8)
+                        *reinterpret_cast<uint4*>(srow + cq * 64 + j * 2) =
+                            pack_bf16x8(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                                        __uint_as_float(v[j + 3]), __uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]),
+                                        __uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                    fence_proxy_async_smem();
+                    named_bar_sync(1, kMxEpiThreads);
+                    if (cq == 0) {
+                        if (orow != nullptr) bulk_store_s2g(orow + c0, srow, 256);
+                        bulk_commit_group();
                     }
-                    if (c_hi < p.n_dim) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8)
-                            st_na_v4(orow + c_hi + j,
-                                     pack_bf16x8(__uint_as_float(v1[j]), __uint_as_float(v1[j + 1]), __uint_as_float(v1[j + 2]),
-                                                 __uint_as_float(v1[j + 3]), __uint_as_float(v1[j + 4]), __uint_as_float(v1[j + 5]),
-                                                 __uint_as_float(v1[j + 6]), __uint_as_float(v1[j + 7])));
-                    }
-                }
+                };
+                const int c_lo = nt * BN;
+                push_half(v0, c_lo);
+                if (c_lo + 128 < p.n_dim) push_half(v1, c_lo + 128);  // same answer in every thread of the CTA
             }
         }
+        if (cq == 0) bulk_wait_group<0>();  // every row this thread sent has been written
         if (!ok) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 2, static_cast<int>(tcount));
     }
 

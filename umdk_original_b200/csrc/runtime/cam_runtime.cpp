@@ -72,6 +72,10 @@ struct CamBuffer {
     uint32_t epoch_dispatch = 0, epoch_combine = 0, epoch_ll = 0, epoch_ll_combine = 0;
     uint64_t timeout_ns = 10ull * 1000ull * 1000ull * 1000ull;
     int dbg_drop_flags = 0;
+    // per-stage device timing of the fused layer (off by default): events around the four launches
+    bool profile = false;
+    bool profile_valid = false;
+    cudaEvent_t prof_ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     std::map<std::tuple<const void*, uint64_t, uint64_t>, CUtensorMap> tmap_cache;
 };
 
@@ -214,6 +218,8 @@ extern "C" int cam_buffer_destroy(CamBuffer* b) {
     for (void* p : frees)
         if (p != nullptr) cudaFree(p);
     if (b->h_status != nullptr) cudaFreeHost(b->h_status);
+    for (auto e : b->prof_ev)
+        if (e != nullptr) cudaEventDestroy(e);
     delete b;
     return 0;
 }
@@ -281,6 +287,23 @@ extern "C" int cam_buffer_num_ranks(CamBuffer* b) { return b ? b->num_ranks : -1
 extern "C" int cam_buffer_device(CamBuffer* b) { return b ? b->device : -1; }
 extern "C" void cam_buffer_set_timeout_ms(CamBuffer* b, double ms) {
     if (b != nullptr && ms > 0) b->timeout_ns = static_cast<uint64_t>(ms * 1e6);
+}
+extern "C" int cam_buffer_set_profile(CamBuffer* b, int on) {
+    CAM_CHECK(b != nullptr, "set_profile: null buffer");
+    CAM_CUDA(cudaSetDevice(b->device));
+    if (on && b->prof_ev[0] == nullptr)
+        for (auto& e : b->prof_ev) CAM_CUDA(cudaEventCreate(&e));
+    b->profile = on != 0;
+    b->profile_valid = false;
+    return 0;
+}
+extern "C" int cam_buffer_read_profile(CamBuffer* b, float* ms4) {
+    CAM_CHECK(b != nullptr && ms4 != nullptr, "read_profile: null argument");
+    CAM_CHECK(b->profile_valid, "read_profile: no fused layer has run with profiling on");
+    CAM_CUDA(cudaSetDevice(b->device));
+    CAM_CUDA(cudaEventSynchronize(b->prof_ev[4]));
+    for (int i = 0; i < 4; ++i) CAM_CUDA(cudaEventElapsedTime(&ms4[i], b->prof_ev[i], b->prof_ev[i + 1]));
+    return 0;
 }
 extern "C" void cam_buffer_set_debug_drop_flags(CamBuffer* b, int on) {
     if (b != nullptr) b->dbg_drop_flags = on ? 1 : 0;
@@ -613,11 +636,15 @@ static int fused_moe_impl(CamBuffer* b, const void* x, const void* expert_ids, i
     const int El = E / b->num_ranks;
     const CamLayout& L = b->layout;
     const int disp_mask = phase_mask & CAM_PHASE_ALL;
+    const bool prof = b->profile && phase_mask == 15;
+    auto stamp = [&](int i) { if (prof) cudaEventRecord(b->prof_ev[i], stream); };
+    stamp(0);
     if (disp_mask) {
         if (cam_dispatch_normal(b, x, expert_ids, idx_is_i64, T, K, h, E,
                                 ue8m0 ? CAM_QUANT_FP8_1x128_UE8M0 : CAM_QUANT_FP8_1x128, disp_mask, stream) != 0)
             return -1;
     }
+    stamp(1);
     if (phase_mask & CAM_PHASE_RECV) {
         const uint8_t* recv_x = b->base + L.off_recv_x;
         const float* recv_s = reinterpret_cast<const float*>(b->base + L.off_recv_scales);
@@ -625,6 +652,7 @@ static int fused_moe_impl(CamBuffer* b, const void* x, const void* expert_ids, i
         if (grouped_gemm_impl(b, recv_x, recv_s, L.capacity, w1_q, w1_s, b->expert_offsets, El, 2 * inter, h, 1,
                               nullptr, b->act_q, b->act_s, nullptr, K, 0, ue8m0, stream) != 0)
             return -1;
+        stamp(2);
         if (grouped_gemm_impl(b, b->act_q, b->act_s, L.capacity, w2_q, w2_s, b->expert_offsets, El, h, inter, 2,
                               nullptr, nullptr, nullptr, recv_src, K, 0, ue8m0, stream) != 0)
             return -1;
@@ -632,11 +660,14 @@ static int fused_moe_impl(CamBuffer* b, const void* x, const void* expert_ids, i
             CAM_CUDA(cudaMemcpyAsync(expert_token_nums, b->num_recv_per_expert, sizeof(int64_t) * El,
                                      cudaMemcpyDeviceToDevice, stream));
     }
+    stamp(3);
     if (phase_mask & 8) {
         if (cam_combine(b, nullptr, nullptr, nullptr, expert_ids, idx_is_i64, topk_weights, out, T, K, h, E, 0,
                         CAM_PHASE_RECV, stream) != 0)
             return -1;
     }
+    stamp(4);
+    if (prof) b->profile_valid = true;
     return 0;
 }
 

@@ -43,6 +43,11 @@ int cam_buffer_num_ranks(CamBuffer* b);
 int cam_buffer_device(CamBuffer* b);
 void cam_buffer_set_timeout_ms(CamBuffer* b, double ms);
 void cam_buffer_set_debug_drop_flags(CamBuffer* b, int on);
+// Per-stage device timing of the fused layer.  While on, every full fused call records CUDA events
+// around its four launches; read_profile waits for the last one and fills
+// {dispatch, GEMM1, GEMM2 + combine send, combine reduce} in milliseconds.  Off by default.
+int cam_buffer_set_profile(CamBuffer* b, int on);
+int cam_buffer_read_profile(CamBuffer* b, float* ms4);
 // Copies the device status word (after synchronising `stream`) into *out and clears it on the device.
 int cam_buffer_poll_status(CamBuffer* b, cudaStream_t stream, CamStatus* out);
 // Device pointers of the results that normal dispatch leaves in the buffer's workspace.

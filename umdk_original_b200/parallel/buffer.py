@@ -148,6 +148,17 @@ class Buffer:
         else:
             self._cpu.drop_next_send = on
 
+    def set_profile(self, on: bool = True) -> None:
+        """Per-stage device timing of ``fused_deep_moe`` (CUDA events around its four launches)."""
+        if self._native is not None:
+            self._native.set_profile(on)
+
+    def read_profile(self) -> dict:
+        """Milliseconds of the last profiled fused layer: dispatch, GEMM1 (+SwiGLU+requant), GEMM2
+        (+combine send), combine reduce.  Synchronises on the last event."""
+        d, g1, g2, c = self._native.read_profile()
+        return {"dispatch_ms": d, "gemm1_ms": g1, "gemm2_send_ms": g2, "combine_ms": c}
+
     def stats(self) -> dict:
         if self._cpu is not None:
             return dict(self._cpu.stats)

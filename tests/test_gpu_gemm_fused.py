@@ -131,3 +131,36 @@ def test_fused_moe_x_active_mask():
     assert (out.cpu().float() - want.float()).abs().max() <= 0.06 * want.float().abs().max() + 1e-3
     assert (out[20:].float().abs().max() == 0)
     buf.destroy()
+
+
+def test_fused_moe_tensor_list_matches_stacked():
+    """Weights as a list of per-expert tensors (dynamic expert placement) give the stacked result,
+    and replacing one expert's tensor is picked up on the next call."""
+    t, h, inter, e, k = 32, 256, 128, 4, 2
+    xs, topk, wts, (w1q, s1, w2q, s2) = _fused_case(1, t, h, inter, e, k, seed=9, ue8m0=True)
+    cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, timeout_ms=3000.0)
+    buf = u.Buffer(None, cfg, name="tl", device=DEV, rank=0, num_ranks=1)
+    w = ExpertWeights(w1q, s1, w2q, s2).to(DEV)
+    x, ids, sc = xs[0].to(DEV), topk[0].to(DEV), wts[0].to(DEV)
+
+    def call(a, b, c, d):
+        out, nums = ops.fused_deep_moe(x, ids, a, b, c, d, sc, None, None, "tl", 1, 0, e, 0, 0, 4, 0)
+        buf.check()
+        return out.clone(), nums.clone()
+
+    want, n0 = call([w.w1], [w.s1], [w.w2], [w.s2])
+    lists = [list(v.unbind(0)) for v in (w.w1, w.s1, w.w2, w.s2)]
+    lists = [[v.clone() for v in l] for l in lists]
+    got, n1 = call(*lists)
+    assert torch.equal(got, want) and torch.equal(n0, n1)
+    got2, _ = call(*lists)  # cached stack
+    assert torch.equal(got2, want)
+    # swap experts 0 and 1 in the list: the result must change like the stacked form does
+    for l in lists:
+        l[0], l[1] = l[1], l[0]
+    perm = torch.tensor([1, 0, 2, 3], device=DEV)
+    want_sw, _ = call([w.w1[perm].contiguous()], [w.s1[perm].contiguous()], [w.w2[perm].contiguous()],
+                      [w.s2[perm].contiguous()])
+    got_sw, _ = call(*lists)
+    assert torch.equal(got_sw, want_sw)
+    buf.destroy()

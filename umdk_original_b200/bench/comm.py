@@ -70,6 +70,35 @@ def _max(v: float, world: int) -> float:
     return float(t.item())
 
 
+def _time_ops_queued(fns, iters, warmup, world, chunk=50):
+    """Device time with the host kept out of the measurement: every chunk starts with a spin kernel
+    of a few milliseconds, behind which the host enqueues `chunk` iterations with an event after
+    every op; the intervals between events are then pure device time (kernel + waits on peers)."""
+    for _ in range(warmup):
+        for f in fns:
+            f()
+    out = [[] for _ in fns]
+    done = 0
+    while done < iters:
+        n = min(chunk, iters - done)
+        _barrier(world)
+        torch.cuda._sleep(20_000_000)  # about 10 ms of spinning on the device
+        evs = []
+        for _ in range(n):
+            row = [torch.cuda.Event(enable_timing=True) for _ in range(len(fns) + 1)]
+            row[0].record()
+            for i, f in enumerate(fns):
+                f()
+                row[i + 1].record()
+            evs.append(row)
+        torch.cuda.synchronize()
+        for row in evs:
+            for i in range(len(fns)):
+                out[i].append(row[i].elapsed_time(row[i + 1]))
+        done += n
+    return out
+
+
 def _time_ops(fns, iters, warmup, world, flush):
     """fns: list of callables run back to back every iteration; returns per-fn lists of ms."""
     from ..utils.timing import flush_l2
@@ -169,7 +198,12 @@ def run(args):
                 d = state["d"]
                 state["o"] = ops.moe_combine_prefill(y, idx, w, d[1], d[2], "commbench", rank, world)
 
-        t_disp, t_comb = _time_ops([disp, comb], args.iters, args.warmup, world, args.flush)
+        if ll:
+            t_disp, t_comb = _time_ops_queued([disp, comb], args.iters, args.warmup, world)
+            result["timing"] = ("CUDA events after every op, iterations enqueued behind a device spin so that host "
+                                "launch latency is outside the intervals, max over ranks")
+        else:
+            t_disp, t_comb = _time_ops([disp, comb], args.iters, args.warmup, world, args.flush)
         buf.check()
         buf.destroy()
     else:
@@ -217,7 +251,10 @@ def run(args):
             rows[state_b["order"]] = ret
             state_b["o"] = (rows.view(tokens, k, h).float() * w.unsqueeze(-1)).sum(dim=1).to(torch.bfloat16)
 
-        t_disp, t_comb = _time_ops([disp, comb], args.iters, args.warmup, world, args.flush)
+        if ll:
+            t_disp, t_comb = _time_ops_queued([disp, comb], args.iters, args.warmup, world)
+        else:
+            t_disp, t_comb = _time_ops([disp, comb], args.iters, args.warmup, world, args.flush)
 
     hbm = _measured_hbm()
     for name, ts, row_bytes in (("dispatch", t_disp, disp_row_bytes), ("combine", t_comb, comb_row_bytes)):

@@ -136,7 +136,35 @@ public:
     // state that low-latency dispatch leaves for the matching combine
     at::Tensor ll_src_, ll_total_;
 
+    // A weight argument given as a list of per-expert tensors (the reference's "tensor list" form for
+    // dynamic expert placement, fused_deep_moe_tiling.cpp:83-127) is stacked into one [E_local, ...]
+    // tensor, which the kernels' single TMA descriptor needs.  The stacked copy is kept until one
+    // of the list's tensors changes (address or version), so steady-state calls do not copy.
+    at::Tensor stacked(int slot, at::TensorList list) {
+        if (list.size() == 1 && list[0].dim() == 3) return list[0];
+        StackCache& c = stack_cache_[slot];
+        bool same = c.value.defined() && c.ptrs.size() == list.size();
+        for (size_t i = 0; same && i < list.size(); ++i)
+            same = c.ptrs[i] == list[i].data_ptr() && c.versions[i] == list[i]._version();
+        if (!same) {
+            c.value = at::stack(list).contiguous();
+            c.ptrs.clear();
+            c.versions.clear();
+            for (const at::Tensor& t : list) {
+                c.ptrs.push_back(t.data_ptr());
+                c.versions.push_back(t._version());
+            }
+        }
+        return c.value;
+    }
+
 private:
+    struct StackCache {
+        at::Tensor value;
+        std::vector<void*> ptrs;
+        std::vector<int64_t> versions;
+    };
+    StackCache stack_cache_[4];
     CamBuffer* buf_ = nullptr;
     CamLayout layout_{};
     int64_t id_ = 0;
@@ -423,13 +451,15 @@ std::vector<at::Tensor> fused_deep_moe_cuda(const at::Tensor& x, const at::Tenso
     CAM_ASSERT(sharedExpertRankNum == 0, "shared-expert ranks are not supported by this build");
     CAM_ASSERT(quantMode == 3 || quantMode == 4, "this entry point runs the block-scaled fp8 paths (quantMode 3: fp32 "
                "scales, 4: power-of-two scales); int8 W8A8 weights are converted by umdk_original_b200.models first");
-    CAM_ASSERT(gmm1PermutedWeight.size() == 1 && gmm2Weight.size() == 1 && gmm1PermutedWeightScale.size() == 1 &&
-                   gmm2WeightScale.size() == 1,
-               "stack per-expert tensor lists into one tensor per argument first");
-    const at::Tensor& w1 = gmm1PermutedWeight[0];
-    const at::Tensor& s1 = gmm1PermutedWeightScale[0];
-    const at::Tensor& w2 = gmm2Weight[0];
-    const at::Tensor& s2 = gmm2WeightScale[0];
+    CAM_ASSERT(gmm1PermutedWeight.size() >= 1 && gmm2Weight.size() == gmm1PermutedWeight.size() &&
+                   gmm1PermutedWeightScale.size() == gmm1PermutedWeight.size() &&
+                   gmm2WeightScale.size() == gmm1PermutedWeight.size(),
+               "the four weight arguments must be lists of the same length (1 stacked tensor or E_local tensors)");
+    c10::cuda::CUDAGuard wguard(x.device());
+    const at::Tensor w1 = b->stacked(0, gmm1PermutedWeight);
+    const at::Tensor s1 = b->stacked(1, gmm1PermutedWeightScale);
+    const at::Tensor w2 = b->stacked(2, gmm2Weight);
+    const at::Tensor s2 = b->stacked(3, gmm2WeightScale);
     const int64_t T = x.size(0), h = x.size(1), K = expertIds.size(1), El = moeExpertNum / epRankSize;
     CAM_ASSERT(w1.dim() == 3 && w1.size(0) == El && w1.size(2) == h && w1.size(1) % 256 == 0,
                "gmm1PermutedWeight must be [E_local, 2I, h] with 2I a multiple of 256");

@@ -105,6 +105,27 @@ __device__ __forceinline__ void st_na_v2(void* p, const uint2& v) {
                  : "memory");
 }
 
+// One warp copies `bytes` (a multiple of 16) of global memory.  Loads are issued four deep before
+// their stores, so a row costs a few memory latencies instead of one per 512 bytes.  COHERENT
+// selects ld.cg for data that a peer GPU wrote during this kernel.
+template <bool COHERENT>
+__device__ __forceinline__ void warp_copy_row(uint8_t* dst, const uint8_t* src, int bytes, uint32_t lane) {
+    int o = static_cast<int>(lane) * 16;
+    for (; o + 3 * 512 < bytes; o += 4 * 512) {
+        uint4 a, b, c, d;
+        if (COHERENT) {
+            a = ld_cg_v4(src + o); b = ld_cg_v4(src + o + 512); c = ld_cg_v4(src + o + 1024); d = ld_cg_v4(src + o + 1536);
+        } else {
+            a = ld_nc_v4(src + o); b = ld_nc_v4(src + o + 512); c = ld_nc_v4(src + o + 1024); d = ld_nc_v4(src + o + 1536);
+        }
+        st_na_v4(dst + o, a);
+        st_na_v4(dst + o + 512, b);
+        st_na_v4(dst + o + 1024, c);
+        st_na_v4(dst + o + 1536, d);
+    }
+    for (; o < bytes; o += 512) st_na_v4(dst + o, COHERENT ? ld_cg_v4(src + o) : ld_nc_v4(src + o));
+}
+
 // Spin until *p == want (acquire, system scope).  Returns false when the budget runs out.
 __device__ __forceinline__ bool wait_flag_eq_sys(const uint32_t* p, uint32_t want,
                                                  uint64_t timeout_ns) {

@@ -39,37 +39,81 @@ __device__ __forceinline__ void ue8m0_scale(float amax, float& scale, float& inv
 // general) to e4m3 with 1x128 scales (arbitrary fp32 scales, or powers of two when UE8M0).
 // Output goes to the warp's staging area in shared memory: `q` (h bytes, 16-byte aligned) and
 // `s` (h/128 floats).
+// Quantises the 8 bf16 values a lane holds (`v`) as part of a 128-element block spread over 16
+// consecutive lanes; all 32 lanes must call it together.  Returns the packed e4m3 bytes and the
+// block's scale.
+template <bool UE8M0>
+__device__ __forceinline__ uint2 quant8_in_block16(const uint4& v, float& scale) {
+    float f[8] = {bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y),
+                  bf16_lo(v.z), bf16_hi(v.z), bf16_lo(v.w), bf16_hi(v.w)};
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+#pragma unroll
+    for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+    float inv;
+    if (UE8M0) {
+        ue8m0_scale(amax, scale, inv);
+    } else {
+        const float a = fmaxf(amax, 1e-4f);
+        inv = 448.f / a;
+        scale = a / 448.f;
+    }
+    uint2 o2;
+    o2.x = pack_e4m3x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
+    o2.y = pack_e4m3x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
+    return o2;
+}
+
 template <bool UE8M0 = false>
 __device__ __forceinline__ void warp_quant_fp8_1x128(const __nv_bfloat16* __restrict__ row, int h,
                                                      uint8_t* q, float* s) {
     const uint32_t lane = lane_id();
-    // Each lane owns 8 consecutive elements per step; 16 lanes cover one 128-element block.
-    for (int base = 0; base < h; base += 256) {
-        const int col = base + static_cast<int>(lane) * 8;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        const bool in = col < h;
-        if (in) v = ld_nc_v4(row + col);
-        float f[8] = {bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y),
-                      bf16_lo(v.z), bf16_hi(v.z), bf16_lo(v.w), bf16_hi(v.w)};
-        float amax = 0.f;
+    // Each lane owns 8 consecutive elements per step of 256; 16 lanes cover one 128-element block.
+    // The loads of four steps are issued together (the steps are independent), which divides the
+    // number of exposed memory latencies per row by four.
+    for (int base = 0; base < h; base += 1024) {
+        uint4 v[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
-#pragma unroll
-        for (int o = 8; o >= 1; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
-        float sc, inv;
-        if (UE8M0) {
-            ue8m0_scale(amax, sc, inv);
-        } else {
-            const float a = fmaxf(amax, 1e-4f);
-            inv = 448.f / a;
-            sc = a / 448.f;
+        for (int u = 0; u < 4; ++u) {
+            const int c = base + u * 256 + static_cast<int>(lane) * 8;
+            v[u] = (c < h) ? ld_nc_v4(row + c) : make_uint4(0, 0, 0, 0);
         }
-        if (in) {
-            uint2 o2;
-            o2.x = pack_e4m3x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv);
-            o2.y = pack_e4m3x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv);
-            *reinterpret_cast<uint2*>(q + col) = o2;
-            if ((lane & 15u) == 0u) s[col >> 7] = sc;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int c = base + u * 256 + static_cast<int>(lane) * 8;
+            float sc;
+            const uint2 o2 = quant8_in_block16<UE8M0>(v[u], sc);
+            if (c < h) {
+                *reinterpret_cast<uint2*>(q + c) = o2;
+                if ((lane & 15u) == 0u) s[c >> 7] = sc;
+            }
+        }
+    }
+}
+
+// The whole CTA quantises one bf16 row (every thread must call it; no barrier inside): thread i
+// owns elements [8 i, 8 i + 8) of every pass of 8 * blockDim.x elements, so a 7168-element row
+// costs a 512-thread CTA two loads per thread, issued together.
+template <bool UE8M0>
+__device__ __forceinline__ void block_quant_fp8_1x128(const __nv_bfloat16* __restrict__ row, int h,
+                                                      uint8_t* q, float* s) {
+    const int stride = static_cast<int>(blockDim.x) * 8;
+    const int c0 = static_cast<int>(threadIdx.x) * 8;
+    for (int base = 0; base < h; base += 2 * stride) {
+        const int ca = base + c0, cb = base + stride + c0;
+        const uint4 va = (ca < h) ? ld_nc_v4(row + ca) : make_uint4(0, 0, 0, 0);
+        const uint4 vb = (cb < h) ? ld_nc_v4(row + cb) : make_uint4(0, 0, 0, 0);
+        float sa, sb;
+        const uint2 oa = quant8_in_block16<UE8M0>(va, sa);
+        const uint2 ob = quant8_in_block16<UE8M0>(vb, sb);
+        if (ca < h) {
+            *reinterpret_cast<uint2*>(q + ca) = oa;
+            if ((threadIdx.x & 15u) == 0u) s[ca >> 7] = sa;
+        }
+        if (cb < h) {
+            *reinterpret_cast<uint2*>(q + cb) = ob;
+            if ((threadIdx.x & 15u) == 0u) s[cb >> 7] = sb;
         }
     }
 }

@@ -113,7 +113,15 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineP
         if (s_abort) return;
 
         const uint8_t* buf = my_base + p.off_combine_buf;
-        for (int t = gwarp; t < p.T; t += nwarps) {
+        // Work item = (token, slice of the row).  With few tokens (decode) a row is cut into as many
+        // 512-byte-aligned slices as there are warps to spare, so the whole grid takes part.
+        const int chunks = (row_bytes + 511) / 512;
+        const int nsplit = min(chunks, max(1, nwarps / max(p.T, 1)));
+        const int per = (chunks + nsplit - 1) / nsplit;
+        for (int it = gwarp; it < p.T * nsplit; it += nwarps) {
+            const int t = it / nsplit;
+            const int o_begin = (it - t * nsplit) * per * 512;
+            const int o_end = min(row_bytes, o_begin + per * 512);
             bool pair_ok = false;
             if (lane < static_cast<uint32_t>(p.K)) {
                 const int id = comb_expert_id(p.topk_idx, p.idx_is_i64, static_cast<size_t>(t) * p.K + lane);
@@ -124,7 +132,7 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineP
             __syncwarp();
             const uint8_t* trow = buf + static_cast<size_t>(t) * p.K * row_bytes;
             uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) + static_cast<size_t>(t) * row_bytes;
-            for (int o = static_cast<int>(lane) * 16; o < row_bytes; o += 512) {
+            for (int o = o_begin + static_cast<int>(lane) * 16; o < o_end; o += 512) {
                 float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
                 for (int k0 = 0; k0 < p.K; k0 += 8) {
                     uint4 v[8];

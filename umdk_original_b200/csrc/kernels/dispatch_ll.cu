@@ -1,25 +1,32 @@
 // Low-latency (decode) dispatch for sm_100a.  No count exchange precedes the data: every
 // (source rank, local expert) pair owns a fixed slab of `max_tokens` rows in the destination's
-// symmetric memory, so a sender knows the address of every row without asking.  One CTA owns one
-// expert: it finds that expert's (token, k) pairs in scan order, quantises and pushes each row
-// with P2P stores, then publishes {epoch, count} as one 64-bit release store into the
-// destination's cell.  The receive phase waits for its cells, packs the slabs into the
-// contiguous expert-major / source-minor layout that the grouped GEMM consumes and emits the
-// cumulative counts.
+// symmetric memory, so a sender knows the address of every row without asking.
+//
+// SEND  every CTA computes the slot of each (token, k) pair inside its expert (scan order) in
+//       shared memory; then the pairs are spread over ALL warps of the grid, one row per warp at a
+//       time, so a hot expert does not serialise on one CTA: quantise, push the row, its scales
+//       and its (token, k) with P2P stores.  After a grid-wide barrier {epoch, count} goes out as
+//       one 64-bit release store per (destination, local expert) cell.
+// RECV  wait for the cells of all sources, prefix-sum the counts, and pack the slabs into the
+//       contiguous expert-major / source-minor layout that the grouped GEMM consumes, again one
+//       row per warp over the whole grid.
 //
 // Counterpart of the reference's moe_dispatch_shmem kernel
 // (ascend_kernels/moe_dispatch_shmem/op_kernel/moe_dispatch_shmem.h: AlltoAllDispatch 551-652,
 // SetStatus 655-690, WaitDispatch 736-778, LocalWindowCopy 840-933, UpdateTokenNumsOut
 // 1056-1086).  expandIdx keeps the reference meaning: the number of earlier pairs of this rank
 // routed to the same expert.  Float flags summed by a vector reduce become one integer cell.
+#include <cooperative_groups.h>
 #include "../common/cam_types.h"
 #include "../common/ptx.cuh"
 #include "../common/quant.cuh"
 #include "launch.h"
 
+namespace cg = cooperative_groups;
+
 namespace cam {
 
-constexpr int kLLThreads = 256;
+constexpr int kLLThreads = 512;
 constexpr int kLLWarps = kLLThreads / 32;
 
 __device__ __forceinline__ void ll_record_status(CamStatus* st, int code, int who, int detail) {
@@ -37,16 +44,16 @@ __device__ __forceinline__ int ll_expert_id(const void* idx, int is_i64, size_t 
 
 __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const DispatchLLParams p) {
     extern __shared__ __align__(16) uint8_t dyn_smem[];
-    __shared__ int s_warp_cnt[kLLWarps];
-    __shared__ int s_cnt[CAM_MAX_EXPERTS];   // RECV: rows per cell, ordered (local expert, source)
+    __shared__ int s_run[CAM_MAX_EXPERTS];   // SEND: pairs per expert / RECV: rows per cell (local expert, source)
     __shared__ int s_cum[CAM_MAX_EXPERTS];   // RECV: inclusive cumsum in the same order
-    __shared__ int s_running;
     __shared__ uint32_t s_abort;
 
     const int tid = static_cast<int>(threadIdx.x);
     const int warp = tid >> 5;
     const uint32_t lane = lane_id();
     const int nb = static_cast<int>(gridDim.x);
+    const int gwarp = static_cast<int>(blockIdx.x) * kLLWarps + warp;
+    const int nwarps = nb * kLLWarps;
     const int E = p.E, R = p.R, K = p.K, El = p.E / p.R;
     const int npairs = p.T * K;
     const int parity = static_cast<int>(p.epoch & 1u);
@@ -54,9 +61,9 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
                        : (p.quant_mode == CAM_QUANT_INT8_TOKEN) ? 1 : 0;
     const int row_bytes = (p.quant_mode == CAM_QUANT_NONE) ? p.h * 2 : p.h;
     const size_t cell_rows = static_cast<size_t>(p.max_tokens);
-    // dynamic smem: ids [npairs] | list [npairs] | per-warp staging
+    // dynamic smem: ids [npairs] | slots [npairs] | per-warp staging
     int* s_ids = reinterpret_cast<int*>(dyn_smem);
-    int* s_list = s_ids + npairs;
+    int* s_slot = s_ids + npairs;
     const int stage_bytes = (p.quant_mode == CAM_QUANT_NONE) ? 0 : ((p.h + nscale * 4 + 15) & ~15);
     uint8_t* stage0 = dyn_smem + ((static_cast<size_t>(npairs) * 8 + 15) & ~static_cast<size_t>(15));
     uint8_t* stage_q = stage0 + static_cast<size_t>(warp) * stage_bytes;
@@ -70,79 +77,118 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
             int id = ll_expert_id(p.expert_ids, p.idx_is_i64, i);
             if (id < 0 || id >= E || (i / K) >= p.active_tokens) id = -1;
             s_ids[i] = id;
-            if (id < 0 && blockIdx.x == 0) p.expand_idx[i] = -1;
+        }
+        for (int e = tid; e < E; e += kLLThreads) s_run[e] = 0;
+        __syncthreads();
+        // Slot of every pair inside its expert, in scan order: one warp walks the pairs 32 at a time;
+        // lanes with the same expert find each other with match.any, the lowest of them advances the
+        // expert's running count.
+        if (warp == 0) {
+            for (int c = 0; c < npairs; c += 32) {
+                const int i = c + static_cast<int>(lane);
+                const int id = (i < npairs) ? s_ids[i] : -1;
+                const uint32_t peers = __match_any_sync(0xFFFFFFFFu, id);
+                if (id >= 0) {
+                    const int before = __popc(peers & ((1u << lane) - 1u));
+                    s_slot[i] = s_run[id] + before;
+                }
+                __syncwarp();
+                if (id >= 0 && (peers & ((1u << lane) - 1u)) == 0u) s_run[id] += __popc(peers);
+                if (id < 0 && i < npairs) s_slot[i] = -1;
+                __syncwarp();
+            }
         }
         __syncthreads();
-        for (int e = static_cast<int>(blockIdx.x); e < E; e += nb) {
-            // ordered compaction of the pairs routed to expert e
-            if (tid == 0) s_running = 0;
-            __syncthreads();
-            for (int sub = 0; sub < npairs; sub += kLLThreads) {
-                const int i = sub + tid;
-                const bool hit = (i < npairs) && (s_ids[i] == e);
-                const uint32_t m = __ballot_sync(0xFFFFFFFFu, hit);
-                if (lane == 0) s_warp_cnt[warp] = __popc(m);
+        if (blockIdx.x == 0)
+            for (int i = tid; i < npairs; i += kLLThreads) p.expand_idx[i] = s_slot[i];
+
+        if (p.quant_mode != CAM_QUANT_INT8_TOKEN) {
+            // Token-major: the CTA quantises a token once (all threads load together, so a row costs one
+            // memory latency), then its warps push the staged row to the token's K destinations, the row
+            // cut into `parts` pieces so that all warps have work.
+            const int parts = max(1, kLLWarps / K);
+            const int part_bytes = ((row_bytes + parts - 1) / parts + 511) & ~511;
+            const int t_end = min(p.T, p.active_tokens);
+            for (int t = static_cast<int>(blockIdx.x); t < t_end; t += nb) {
+                const __nv_bfloat16* xrow = p.x + static_cast<size_t>(t) * p.h;
+                if (p.quant_mode == CAM_QUANT_FP8_1x128)
+                    block_quant_fp8_1x128<false>(xrow, p.h, stage0, reinterpret_cast<float*>(stage0 + p.h));
+                else if (p.quant_mode == CAM_QUANT_FP8_1x128_UE8M0)
+                    block_quant_fp8_1x128<true>(xrow, p.h, stage0, reinterpret_cast<float*>(stage0 + p.h));
                 __syncthreads();
-                int before = s_running;
-                for (int w2 = 0; w2 < warp; ++w2) before += s_warp_cnt[w2];
-                if (hit) {
-                    const int pos = before + __popc(m & ((1u << lane) - 1u));
-                    s_list[pos] = i;
-                    p.expand_idx[i] = pos;
+                for (int item = warp; item < K * parts; item += kLLWarps) {
+                    const int k = item / parts, part = item - k * parts;
+                    const int i = t * K + k;
+                    const int e = s_ids[i];
+                    const int j = s_slot[i];
+                    if (e < 0 || j >= p.max_tokens) continue;  // skipped pair, or beyond the slab (reported below)
+                    const int d = e / El, le = e - d * El;
+                    const size_t cell = static_cast<size_t>(parity) * E + static_cast<size_t>(p.rank) * El + le;
+                    uint8_t* pb = p.peer_base[d];
+                    uint8_t* dst = pb + p.off_ll_x + (cell * cell_rows + j) * static_cast<size_t>(row_bytes);
+                    const int b0 = part * part_bytes, b1 = min(row_bytes, b0 + part_bytes);
+                    if (p.quant_mode == CAM_QUANT_NONE) {
+                        if (b1 > b0)
+                            warp_copy_row<false>(dst + b0, reinterpret_cast<const uint8_t*>(xrow) + b0, b1 - b0, lane);
+                    } else {
+                        for (int o = b0 + static_cast<int>(lane) * 16; o < b1; o += 512)
+                            st_na_v4(dst + o, *reinterpret_cast<const uint4*>(stage0 + o));
+                        if (part == 0) {
+                            const float* ssrc = reinterpret_cast<const float*>(stage0 + p.h);
+                            float* sdst = reinterpret_cast<float*>(pb + p.off_ll_scales) + (cell * cell_rows + j) * nscale;
+                            for (int o = static_cast<int>(lane); o < nscale; o += 32) sdst[o] = ssrc[o];
+                        }
+                    }
+                    if (part == 0 && lane < 2) {
+                        int* m = reinterpret_cast<int*>(pb + p.off_ll_meta) + (cell * cell_rows + j) * 2;
+                        m[lane] = (lane == 0) ? t : k;
+                    }
                 }
-                __syncthreads();
-                if (tid == 0) {
-                    int tot = 0;
-                    for (int w2 = 0; w2 < kLLWarps; ++w2) tot += s_warp_cnt[w2];
-                    s_running += tot;
-                }
-                __syncthreads();
+                __syncthreads();  // the staged row is overwritten by the next token
             }
-            int cnt = s_running;
-            if (cnt > p.max_tokens) {
-                if (tid == 0) ll_record_status(p.status, CAM_ERR_RECV_OVERFLOW, e, cnt);
-                cnt = p.max_tokens;
-            }
-            const int d = e / El, le = e - d * El;
-            const size_t cell = static_cast<size_t>(parity) * E + static_cast<size_t>(p.rank) * El + le;
-            uint8_t* pb = p.peer_base[d];
-            for (int j = warp; j < cnt; j += kLLWarps) {
-                const int pair = s_list[j];
-                const int t = pair / K, k = pair - t * K;
+        } else {
+            // Per-token int8 with an expert-specific smooth scale: the quantised row depends on the
+            // destination expert, so every (token, k) pair is quantised by the warp that sends it.
+            for (int i = gwarp; i < npairs; i += nwarps) {
+                const int e = s_ids[i];
+                const int j = s_slot[i];
+                if (e < 0 || j >= p.max_tokens) continue;
+                const int t = i / K, k = i - t * K;
+                const int d = e / El, le = e - d * El;
+                const size_t cell = static_cast<size_t>(parity) * E + static_cast<size_t>(p.rank) * El + le;
+                uint8_t* pb = p.peer_base[d];
                 const __nv_bfloat16* xrow = p.x + static_cast<size_t>(t) * p.h;
                 uint8_t* dst = pb + p.off_ll_x + (cell * cell_rows + j) * static_cast<size_t>(row_bytes);
-                if (p.quant_mode == CAM_QUANT_NONE) {
-                    const uint8_t* src = reinterpret_cast<const uint8_t*>(xrow);
-                    for (int o = static_cast<int>(lane) * 16; o < row_bytes; o += 512)
-                        st_na_v4(dst + o, ld_nc_v4(src + o));
-                } else {
-                    if (p.quant_mode == CAM_QUANT_FP8_1x128)
-                        warp_quant_fp8_1x128<false>(xrow, p.h, stage_q, stage_s);
-                    else if (p.quant_mode == CAM_QUANT_FP8_1x128_UE8M0)
-                        warp_quant_fp8_1x128<true>(xrow, p.h, stage_q, stage_s);
-                    else
-                        warp_quant_int8_token(xrow, p.h, stage_q, stage_s,
-                                              p.smooth ? p.smooth + static_cast<size_t>(e) * p.h : nullptr);
-                    __syncwarp();
-                    for (int o = static_cast<int>(lane) * 16; o < row_bytes; o += 512)
-                        st_na_v4(dst + o, *reinterpret_cast<const uint4*>(stage_q + o));
-                    float* sdst = reinterpret_cast<float*>(pb + p.off_ll_scales) + (cell * cell_rows + j) * nscale;
-                    for (int o = static_cast<int>(lane); o < nscale; o += 32) sdst[o] = stage_s[o];
-                    __syncwarp();
-                }
+                warp_quant_int8_token(xrow, p.h, stage_q, stage_s,
+                                      p.smooth ? p.smooth + static_cast<size_t>(e) * p.h : nullptr);
+                __syncwarp();
+                for (int o = static_cast<int>(lane) * 16; o < row_bytes; o += 512)
+                    st_na_v4(dst + o, *reinterpret_cast<const uint4*>(stage_q + o));
+                if (lane == 0)
+                    reinterpret_cast<float*>(pb + p.off_ll_scales)[(cell * cell_rows + j) * nscale] = stage_s[0];
+                __syncwarp();
                 if (lane < 2) {
                     int* m = reinterpret_cast<int*>(pb + p.off_ll_meta) + (cell * cell_rows + j) * 2;
                     m[lane] = (lane == 0) ? t : k;
                 }
             }
-            __syncthreads();
-            if (tid == 0 && p.dbg_drop_flags == 0) {
-                __threadfence_system();
-                st_release_sys_u64(reinterpret_cast<uint64_t*>(pb + p.off_ll_cells) + cell,
-                                   (static_cast<uint64_t>(p.epoch) << 32) | static_cast<uint32_t>(cnt));
-            }
-            __syncthreads();
         }
+        __threadfence_system();   // this thread's rows are visible to every GPU before the barrier
+        cg::this_grid().sync();
+        // Every CTA knows every count; CTA b publishes the cells of experts b, b + grid, ...
+        for (int e = static_cast<int>(blockIdx.x) * kLLThreads + tid; e < E; e += nb * kLLThreads) {
+            int cnt = s_run[e];
+            if (cnt > p.max_tokens) {
+                ll_record_status(p.status, CAM_ERR_RECV_OVERFLOW, e, cnt);
+                cnt = p.max_tokens;
+            }
+            const int d = e / El, le = e - d * El;
+            const size_t cell = static_cast<size_t>(parity) * E + static_cast<size_t>(p.rank) * El + le;
+            if (p.dbg_drop_flags == 0)
+                st_release_sys_u64(reinterpret_cast<uint64_t*>(p.peer_base[d] + p.off_ll_cells) + cell,
+                                   (static_cast<uint64_t>(p.epoch) << 32) | static_cast<uint32_t>(cnt));
+        }
+        __syncthreads();
     }
 
     // ------------------------------------------------------------------ RECV
@@ -167,15 +213,15 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
                     }
                 }
             }
-            s_cnt[o] = static_cast<int>(static_cast<uint32_t>(v));
+            s_run[o] = static_cast<int>(static_cast<uint32_t>(v));
         }
         __syncthreads();
         if (s_abort) return;
-        if (warp == 0) {  // inclusive scan of s_cnt in (local expert, source) order
+        if (warp == 0) {  // inclusive scan of the counts in (local expert, source) order
             const int per = (E + 31) / 32;
             const int lo = static_cast<int>(lane) * per, hi = min(E, lo + per);
             int sum = 0;
-            for (int o = lo; o < hi; ++o) sum += s_cnt[o];
+            for (int o = lo; o < hi; ++o) sum += s_run[o];
             int incl = sum;
 #pragma unroll
             for (int s = 1; s < 32; s <<= 1) {
@@ -183,7 +229,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
                 if (static_cast<int>(lane) >= s) incl += n;
             }
             int run = incl - sum;
-            for (int o = lo; o < hi; ++o) { run += s_cnt[o]; s_cum[o] = run; }
+            for (int o = lo; o < hi; ++o) { run += s_run[o]; s_cum[o] = run; }
         }
         __syncthreads();
         if (blockIdx.x == 0) {
@@ -196,26 +242,29 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
             }
             if (tid == 0) p.total_rows[0] = s_cum[E - 1];
         }
-        // pack the slabs into the contiguous output
-        for (int o = static_cast<int>(blockIdx.x); o < E; o += nb) {
+        // pack the slabs into the contiguous output: output row r belongs to the cell o with
+        // s_cum[o-1] <= r < s_cum[o]
+        const int total = s_cum[E - 1];
+        for (int r = gwarp; r < total; r += nwarps) {
+            int lo = 0, hi = E - 1;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (s_cum[mid] > r) hi = mid; else lo = mid + 1;
+            }
+            const int o = lo;
             const int le = o / R, src = o - le * R;
-            const int n = s_cnt[o];
-            const int start = s_cum[o] - n;
+            const int j = r - (s_cum[o] - s_run[o]);
             const size_t cell = static_cast<size_t>(parity) * E + static_cast<size_t>(src) * El + le;
-            const uint8_t* sx = my_base + p.off_ll_x + cell * cell_rows * row_bytes;
-            const float* ss = reinterpret_cast<const float*>(my_base + p.off_ll_scales) + cell * cell_rows * nscale;
-            const int* sm = reinterpret_cast<const int*>(my_base + p.off_ll_meta) + cell * cell_rows * 2;
-            for (int j = warp; j < n; j += kLLWarps) {
-                const uint8_t* s = sx + static_cast<size_t>(j) * row_bytes;
-                uint8_t* dx = p.expand_x + static_cast<size_t>(start + j) * row_bytes;
-                for (int b = static_cast<int>(lane) * 16; b < row_bytes; b += 512) st_na_v4(dx + b, ld_cg_v4(s + b));
-                for (int b = static_cast<int>(lane); b < nscale; b += 32)
-                    p.expand_scales[static_cast<size_t>(start + j) * nscale + b] =
-                        __ldcg(ss + static_cast<size_t>(j) * nscale + b);
-                if (lane < 3) {
-                    const int v = (lane == 0) ? src : __ldcg(sm + static_cast<size_t>(j) * 2 + (lane - 1));
-                    p.expand_src[static_cast<size_t>(start + j) * 3 + lane] = v;
-                }
+            const uint8_t* s = my_base + p.off_ll_x + (cell * cell_rows + j) * static_cast<size_t>(row_bytes);
+            uint8_t* dx = p.expand_x + static_cast<size_t>(r) * row_bytes;
+            warp_copy_row<true>(dx, s, row_bytes, lane);
+            const float* ss = reinterpret_cast<const float*>(my_base + p.off_ll_scales) + (cell * cell_rows + j) * nscale;
+            for (int b = static_cast<int>(lane); b < nscale; b += 32)
+                p.expand_scales[static_cast<size_t>(r) * nscale + b] = __ldcg(ss + b);
+            if (lane < 3) {
+                const int* sm = reinterpret_cast<const int*>(my_base + p.off_ll_meta) + (cell * cell_rows + j) * 2;
+                const int v = (lane == 0) ? src : __ldcg(sm + (lane - 1));
+                p.expand_src[static_cast<size_t>(r) * 3 + lane] = v;
             }
         }
     }
@@ -242,7 +291,8 @@ extern "C" int cam_dispatch_ll_max_grid(int device, int h, int quant_mode, int T
 
 extern "C" int cam_launch_dispatch_ll(const cam::DispatchLLParams* p, int grid, cudaStream_t stream) {
     const int smem = cam_dispatch_ll_smem_bytes(p->h, p->quant_mode, p->T, p->K);
-    cudaError_t e = cudaFuncSetAttribute(cam::dispatch_ll_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    static cam::SmemLimitCache limit;
+    cudaError_t e = limit.ensure(cam::dispatch_ll_kernel, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     void* args[] = {const_cast<cam::DispatchLLParams*>(p)};
     return static_cast<int>(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(cam::dispatch_ll_kernel), dim3(grid),

@@ -215,9 +215,7 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
                         uint8_t* pb = p.peer_base[d];
                         uint8_t* dst = pb + p.off_recv_x + static_cast<size_t>(row) * row_bytes;
                         if (p.quant_mode == CAM_QUANT_NONE) {
-                            const uint8_t* src = reinterpret_cast<const uint8_t*>(xrow);
-                            for (int o = static_cast<int>(lane) * 16; o < row_bytes; o += 512)
-                                st_na_v4(dst + o, ld_nc_v4(src + o));
+                            warp_copy_row<false>(dst, reinterpret_cast<const uint8_t*>(xrow), row_bytes, lane);
                         } else {
                             for (int o = static_cast<int>(lane) * 16; o < row_bytes; o += 512)
                                 st_na_v4(dst + o, *reinterpret_cast<const uint4*>(stage_q + o));
@@ -320,8 +318,8 @@ extern "C" int cam_dispatch_normal_max_grid(int device, int h, int quant_mode) {
 
 extern "C" int cam_launch_dispatch_normal(const cam::DispatchNormalParams* p, int grid, cudaStream_t stream) {
     const int smem = cam_dispatch_normal_smem_bytes(p->h, p->quant_mode);
-    cudaError_t e = cudaFuncSetAttribute(cam::dispatch_normal_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    static cam::SmemLimitCache limit;
+    cudaError_t e = limit.ensure(cam::dispatch_normal_kernel, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     void* args[] = {const_cast<cam::DispatchNormalParams*>(p)};
     e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(cam::dispatch_normal_kernel), dim3(grid),

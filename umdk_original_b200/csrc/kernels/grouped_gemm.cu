@@ -292,8 +292,8 @@ extern "C" int cam_grouped_gemm_smem_bytes(void) { return cam::kGemmSmem; }
 
 extern "C" int cam_launch_grouped_gemm_fp8(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
                                            const CUtensorMap* tmap_b, int grid, cudaStream_t stream) {
-    cudaError_t e = cudaFuncSetAttribute(cam::grouped_gemm_fp8_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, cam::kGemmSmem);
+    static cam::SmemLimitCache limit;
+    cudaError_t e = limit.ensure(cam::grouped_gemm_fp8_kernel, cam::kGemmSmem);
     if (e != cudaSuccess) return static_cast<int>(e);
     cam::grouped_gemm_fp8_kernel<<<grid, cam::kGemmThreads, cam::kGemmSmem, stream>>>(*tmap_a, *tmap_b, *p);
     return static_cast<int>(cudaGetLastError());

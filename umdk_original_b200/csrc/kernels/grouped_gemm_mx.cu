@@ -349,8 +349,8 @@ extern "C" int cam_grouped_gemm_mx_smem_bytes(void) { return cam::kMxSmem; }
 
 extern "C" int cam_launch_grouped_gemm_mxfp8(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
                                              const CUtensorMap* tmap_b, int grid, cudaStream_t stream) {
-    cudaError_t e = cudaFuncSetAttribute(cam::grouped_gemm_mxfp8_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, cam::kMxSmem);
+    static cam::SmemLimitCache limit;
+    cudaError_t e = limit.ensure(cam::grouped_gemm_mxfp8_kernel, cam::kMxSmem);
     if (e != cudaSuccess) return static_cast<int>(e);
     cam::grouped_gemm_mxfp8_kernel<<<grid, cam::kMxThreads, cam::kMxSmem, stream>>>(*tmap_a, *tmap_b, *p);
     return static_cast<int>(cudaGetLastError());

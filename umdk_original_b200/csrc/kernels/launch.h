@@ -108,6 +108,23 @@ struct GroupedGemmParams {
     CamStatus* status;
 };
 
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) costs microseconds per call; the launchers go
+// through this helper, which remembers per device what it has already set for one kernel.
+struct SmemLimitCache {
+    int set[64] = {0};
+    template <class Kernel>
+    cudaError_t ensure(Kernel k, int bytes) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64 && set[dev] >= bytes && bytes > 0) return cudaSuccess;
+        if (bytes <= 0) return cudaSuccess;
+        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e == cudaSuccess && dev >= 0 && dev < 64) set[dev] = bytes;
+        return e;
+    }
+};
+
 }  // namespace cam
 
 extern "C" {

@@ -77,6 +77,7 @@ struct CamBuffer {
     bool profile_valid = false;
     cudaEvent_t prof_ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     std::map<std::tuple<const void*, uint64_t, uint64_t>, CUtensorMap> tmap_cache;
+    std::map<std::tuple<int, int, int, int>, int> ll_grid_cache;  // (h, quant, T, K) -> co-resident grid
 };
 
 extern "C" const char* cam_last_error(void) { return g_last_error.c_str(); }
@@ -474,9 +475,22 @@ extern "C" int cam_dispatch_ll(CamBuffer* b, const void* x, const void* expert_i
     p.ep_send_counts = ep_send_counts;
     p.total_rows = total_rows;
     p.status = b->d_status;
-    int grid = cam_dispatch_ll_max_grid(b->device, h, quant_mode, T, K);
+    int grid;
+    const auto gkey = std::make_tuple(h, quant_mode, T, K);
+    auto git = b->ll_grid_cache.find(gkey);
+    if (git != b->ll_grid_cache.end()) {
+        grid = git->second;
+    } else {
+        grid = cam_dispatch_ll_max_grid(b->device, h, quant_mode, T, K);
+        b->ll_grid_cache[gkey] = grid;
+    }
     CAM_CHECK(grid > 0, "dispatch_ll: kernel does not fit (shared memory for T=%d K=%d h=%d)", T, K, h);
-    if (grid > E) grid = E;
+    // one token per CTA when sending, one row per warp when packing: no more CTAs than that needs
+    // (a smaller grid makes the grid-wide barrier cheaper)
+    int want = (T * K + 15) / 16;
+    if (want < T) want = T;
+    if (want < 8) want = 8;
+    if (grid > want) grid = want;
     const int rc = cam_launch_dispatch_ll(&p, grid, stream);
     CAM_CHECK(rc == 0, "dispatch_ll launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
     return 0;

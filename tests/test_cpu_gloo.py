@@ -162,3 +162,38 @@ def test_fault_injection_rank_withholds_dispatch():
     for r, (st, val) in res.items():
         assert st == "ok", val
         assert val.startswith("timeout"), f"rank {r}: {val}"
+
+
+def _shared_rank_fused(rank, world):
+    """2 ranks: rank 0 holds the shared expert, rank 1 the 4 routed experts (float weights, CPU path)."""
+    import torch
+    import umdk_original_b200 as u
+    from umdk_original_b200.models import topk_softmax
+    from umdk_original_b200.ops import reference as ref
+    t, h, e, k, inter, shared = 32, 256, 4, 2, 128, 1
+    xs, logits, g = _make_inputs(3, world, t, h, e, k)
+    w1 = torch.randn(e, 2 * inter, h, generator=g) * 0.05
+    w2 = torch.randn(e, h, inter, generator=g) * 0.05
+    sw1 = torch.randn(1, 2 * inter, h, generator=g) * 0.05
+    sw2 = torch.randn(1, h, inter, generator=g) * 0.05
+    el = e // (world - shared)
+    buf = u.Buffer(None, u.CamConfig(num_experts=el * world, max_tokens=t, hidden=h, topk=k + 1), name="shf",
+                   device=torch.device("cpu"))
+    idx, wt = topk_softmax(logits[rank], k)
+    mine1, mine2 = (sw1, sw2) if rank < shared else (w1, w2)
+    out, nums = torch.ops.umdk_cam_op_lib.fused_deep_moe(
+        xs[rank], idx, [mine1], [torch.empty(0)], [mine2], [torch.empty(0)], wt, None, None, "shf", world, rank, e,
+        1, shared, 0, 0)
+    want = ref.dense_moe_fp32(xs[rank], idx, wt, w1, w2) + ref.swiglu_mlp_fp32(xs[rank], sw1[0], sw2[0])
+    return float((out - want).abs().max()), nums.tolist()
+
+
+def test_fused_with_shared_expert_rank():
+    res = run_gloo(_shared_rank_fused, 2)
+    assert len(res) == 2
+    for r, (st, val) in res.items():
+        assert st == "ok", val
+        err, nums = val
+        assert err < 1e-4, f"rank {r}: max abs err {err}"
+        assert len(nums) == (1 if r == 0 else 4)
+    assert res[0][1][1][0] == 64  # the replica sees every token of both ranks once

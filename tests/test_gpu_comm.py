@@ -205,3 +205,97 @@ def test_bounded_wait_reports_timeout_and_buffer_recovers():
         assert torch.equal(res[r][1].cpu().reshape(-1, 3)[:n], plans[r].src)
     for b in bufs:
         b.destroy()
+
+
+def test_low_latency_combine_int8_on_the_wire():
+    """commQuantMode 2: rows travel as int8 with one scale per 128 elements; the result is the
+    weighted sum of the dequantised rows."""
+    world, t, h, e, k = 2, 24, 512, 8, 2
+    xs, topk, wts = _inputs(world, t, h, e, k, seed=91, lo=0)
+    topk = [x.to(torch.int32) for x in topk]
+    cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, ll_max_tokens=t, timeout_ms=2000.0)
+    bufs = u.Buffer.virtual(world, cfg, _dev(), name="cq_")
+    dx = [x.to(_dev()) for x in xs]
+    dk = [x.to(_dev()) for x in topk]
+    dw = [x.to(_dev()) for x in wts]
+
+    def disp(r):
+        return ops.moe_dispatch_shmem(dx[r], dk[r], None, None, world, r, e, 1, 0, 0, 0, 0, 0, 0, 1, bufs[r].handle)
+
+    res = run_virtual(disp, world, masks=(PHASE_SEND, PHASE_RECV))
+
+    def comb(r):
+        expand, dyn, eidx, nums, ep_cnt, tp_cnt = res[r]
+        return ops.moe_combine_shmem(expand, dk[r], eidx, ep_cnt, dw[r], None, None, None, None, None, None, world, r, e,
+                                     1, 0, 0, 0, 0, 0, 2, bufs[r].handle, 0, 0)
+
+    outs = run_virtual(comb, world, masks=(PHASE_SEND, PHASE_RECV))
+    for r in range(world):
+        bufs[r].check()
+        xin = ref.dequant_int8_1x128(*ref.quant_int8_1x128(xs[r])).unsqueeze(1).expand(t, k, h)
+        want = (xin * wts[r].unsqueeze(-1)).sum(dim=1)
+        got = outs[r].cpu().float()
+        assert (got - want).abs().max() <= 2e-2 * want.abs().max() + 1e-3
+        # and it is close to the unquantised combine (int8 per 128 keeps about 2 decimal digits)
+        exact = (xs[r].float().unsqueeze(1).expand(t, k, h) * wts[r].unsqueeze(-1)).sum(dim=1)
+        assert (got - exact).abs().max() <= 3e-2 * exact.abs().max()
+    for b in bufs:
+        b.destroy()
+
+
+@pytest.mark.parametrize("world,shared", [(2, 1), (4, 2)])
+def test_low_latency_shared_expert_ranks(world, shared):
+    """The first `shared` ranks hold a replica of the shared expert: every token also reaches one of
+    them, each replica gets an equal slice of every rank's batch, and combine adds that row unweighted."""
+    t, h, k = 16, 256, 2
+    routed = 4 * (world - shared)           # 4 routed experts per routed-expert rank
+    el = routed // (world - shared)
+    xs, topk, wts = _inputs(world, t, h, routed, k, seed=60 + world, lo=0)
+    topk = [x.to(torch.int32) for x in topk]
+    cfg = u.CamConfig(num_experts=el * world, max_tokens=t, hidden=h, topk=k + 1, ll_max_tokens=t, timeout_ms=2000.0)
+    bufs = u.Buffer.virtual(world, cfg, _dev(), name=f"sh{world}_")
+    dx = [x.to(_dev()) for x in xs]
+    dk = [x.to(_dev()) for x in topk]
+    dw = [x.to(_dev()) for x in wts]
+
+    def disp(r):
+        return ops.moe_dispatch_shmem(dx[r], dk[r], None, None, world, r, routed, 1, 0, 0, 1, shared, 0, 0, 1,
+                                      bufs[r].handle)
+
+    res = run_virtual(disp, world, masks=(PHASE_SEND, PHASE_RECV))
+    virt = [ref.remap_for_shared_ranks(topk[r], wts[r], world, routed, shared) for r in range(world)]
+    plans = ref.plan_dispatch([v[0] for v in virt], el * world)
+    ys = []
+    for r in range(world):
+        bufs[r].check()
+        expand, dyn, eidx, nums, ep_cnt, tp_cnt = res[r]
+        plan = plans[r]
+        n = plan.src.shape[0]
+        if r < shared:
+            assert expand.shape[0] == t * world // shared and nums.numel() == 1 and ep_cnt.numel() == world
+            assert n == t * world // shared and int(nums[0]) == n
+        else:
+            assert expand.shape[0] == t * world * min(el, k) and nums.numel() == el
+            assert torch.equal(nums.cpu(), plan.per_expert)
+        rows = torch.stack([xs[s][tt] for s, tt, _ in plan.src.tolist()])
+        assert torch.equal(expand[:n].cpu(), rows)
+        # "expert" = multiply by (1 + virtual expert id) so that the combine result shows who computed what
+        scale = torch.repeat_interleave(torch.arange(el), plan.per_expert).float() + 1.0 + r * el
+        y = torch.zeros(expand.shape[0], h, dtype=torch.bfloat16, device=_dev())
+        y[:n] = (rows.float() * scale.unsqueeze(-1)).to(torch.bfloat16).to(_dev())
+        ys.append(y)
+
+    def comb(r):
+        expand, dyn, eidx, nums, ep_cnt, tp_cnt = res[r]
+        return ops.moe_combine_shmem(ys[r], dk[r], eidx, ep_cnt, dw[r], None, None, None, None, None, None, world, r,
+                                     routed, 1, 0, 0, 1, shared, 0, 0, bufs[r].handle, 0, 0)
+
+    outs = run_virtual(comb, world, masks=(PHASE_SEND, PHASE_RECV))
+    for r in range(world):
+        bufs[r].check()
+        vid, vw, _, _ = virt[r]
+        rows_by_pair = (xs[r].float().unsqueeze(1) * (vid.float() + 1.0).unsqueeze(-1)).to(torch.bfloat16)
+        want = ref.combine_reference(rows_by_pair, vid, vw, el * world)
+        assert (outs[r].cpu().float() - want.float()).abs().max() == 0.0
+    for b in bufs:
+        b.destroy()

@@ -164,3 +164,39 @@ def test_fused_moe_tensor_list_matches_stacked():
     got_sw, _ = call(*lists)
     assert torch.equal(got_sw, want_sw)
     buf.destroy()
+
+
+def test_fused_moe_shared_expert_rank():
+    """2 virtual ranks: rank 0 holds the shared expert (one local expert), rank 1 the 4 routed experts."""
+    world, shared, t, h, inter, e, k = 2, 1, 32, 256, 128, 4, 2
+    xs, topk, wts, (w1q, s1, w2q, s2) = _fused_case(world, t, h, inter, e, k, seed=21, ue8m0=True)
+    g = torch.Generator().manual_seed(22)
+    sw1q, ss1 = ref.quant_fp8_128x128(torch.randn(1, 2 * inter, h, generator=g) * 0.05, True)
+    sw2q, ss2 = ref.quant_fp8_128x128(torch.randn(1, h, inter, generator=g) * 0.05, True)
+    el = e // (world - shared)
+    cfg = u.CamConfig(num_experts=el * world, max_tokens=t, hidden=h, topk=k + 1, timeout_ms=3000.0)
+    bufs = u.Buffer.virtual(world, cfg, DEV, name="fsh_")
+    local = [ExpertWeights(sw1q, ss1, sw2q, ss2).to(DEV), ExpertWeights(w1q, s1, w2q, s2).to(DEV)]
+    dx = [x.to(DEV) for x in xs]
+    dk = [x.to(DEV) for x in topk]
+    dw = [x.to(DEV) for x in wts]
+
+    def step(r):
+        w = local[r]
+        return ops.fused_deep_moe(dx[r], dk[r], [w.w1], [w.s1], [w.w2], [w.s2], dw[r], None, None, bufs[r].name, world, r,
+                                  e, 1, shared, 4, 0)
+
+    every = run_virtual(step, world, return_all=True)
+    res = every[PHASE_FINAL]
+    for r in range(world):
+        bufs[r].check()
+        routed, counts = ref.fused_moe_fp8_reference(xs[r], topk[r], wts[r], w1q, s1, w2q, s2, ue8m0=True)
+        xq, xsc = ref.quant_fp8_1x128(xs[r], True)
+        shared_row = ref.expert_mlp_fp8(xq, xsc, sw1q[0], ss1[0], sw2q[0], ss2[0], ue8m0=True)
+        want = routed.float() + shared_row.float()
+        got = res[r][0].cpu().float()
+        assert (got - want).abs().max() <= 0.06 * want.abs().max() + 1e-3
+    assert every[PHASE_RECV][0][1].numel() == 1 and int(every[PHASE_RECV][0][1][0]) == t * world
+    assert every[PHASE_RECV][1][1].numel() == el
+    for b in bufs:
+        b.destroy()

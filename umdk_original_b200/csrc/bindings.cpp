@@ -195,6 +195,42 @@ void check_cuda_contig(const at::Tensor& t, const char* what) {
 }
 
 // --------------------------------------------------------------------------------------------
+// Shared-expert ranks.  The first S ranks of the group hold a replica of the shared expert instead of
+// routed experts (moe_dispatch_shmem.h:408-489); every token also goes to one of them, chosen so that
+// each replica gets an equal slice of every rank's batch, and combine adds that row unweighted
+// (moe_combine_shmem.h:876-908).  The kernels see this as ordinary routing over R * E_l "virtual"
+// experts with one more column: routed expert e becomes e + S * E_l (it lives on rank S + e / E_l),
+// the replica on rank s is virtual expert s * E_l, and the extra pair carries weight 1.
+// The Buffer must have been created for R * E_l experts and top-k + 1.
+// --------------------------------------------------------------------------------------------
+struct SharedRemap {
+    at::Tensor ids;      // [T, K + 1] same dtype as the input ids
+    at::Tensor weights;  // [T, K + 1] float32 (undefined when no weights were given)
+    int64_t num_virtual_experts = 0;
+    int64_t experts_per_rank = 0;
+};
+
+SharedRemap remap_for_shared_ranks(const at::Tensor& ids, const c10::optional<at::Tensor>& weights, int64_t num_ranks,
+                                   int64_t moe_expert_num, int64_t shared_rank_num) {
+    CAM_ASSERT(shared_rank_num > 0 && shared_rank_num < num_ranks, "sharedExpertRankNum must be in [0, epWorldSize)");
+    CAM_ASSERT(moe_expert_num % (num_ranks - shared_rank_num) == 0,
+               "moeExpertNum must be a multiple of the number of routed-expert ranks");
+    SharedRemap r;
+    r.experts_per_rank = moe_expert_num / (num_ranks - shared_rank_num);
+    r.num_virtual_experts = r.experts_per_rank * num_ranks;
+    const int64_t T = ids.size(0);
+    const int64_t shift = shared_rank_num * r.experts_per_rank;
+    at::Tensor routed = at::where(ids >= 0, ids + shift, at::full_like(ids, -1));
+    // token t of every rank goes to replica min(S - 1, t * S / T)
+    at::Tensor t = at::arange(T, ids.options());
+    at::Tensor replica = at::clamp_max(at::floor_divide(t * shared_rank_num, std::max<int64_t>(T, 1)), shared_rank_num - 1);
+    r.ids = at::cat({routed, (replica * r.experts_per_rank).unsqueeze(1)}, 1).contiguous();
+    if (weights.has_value() && weights->defined())
+        r.weights = at::cat({weights->to(at::kFloat), at::ones({T, 1}, weights->options().dtype(at::kFloat))}, 1).contiguous();
+    return r;
+}
+
+// --------------------------------------------------------------------------------------------
 // get_dispatch_layout  (pybind/get_dispatch_layout.cpp:25-55)
 // --------------------------------------------------------------------------------------------
 std::tuple<at::Tensor, at::Tensor, at::Tensor> get_dispatch_layout_cuda(const at::Tensor& topk_idx,
@@ -302,8 +338,8 @@ at::Tensor moe_combine_prefill_cuda(const at::Tensor& x, const at::Tensor& topk_
     at::Tensor total = at::minimum(b->total_recv(), at::full({1}, x.size(0), b->total_recv().options()));
     CAM_RT(cam_combine(b->raw(), x.data_ptr(), src_idx.data_ptr<int>(), total.data_ptr<int>(), topk_idx.data_ptr(),
                        is64, w.data_ptr<float>(), out.data_ptr(), static_cast<int>(T), static_cast<int>(K),
-                       static_cast<int>(h), static_cast<int>(E), 0, (g_phase_mask & 7) & (CAM_PHASE_SEND | CAM_PHASE_RECV),
-                       b->stream()));
+                       static_cast<int>(h), static_cast<int>(E), 0, 0,
+                       (g_phase_mask & 7) & (CAM_PHASE_SEND | CAM_PHASE_RECV), b->stream()));
     return out;
 }
 
@@ -325,13 +361,25 @@ std::vector<at::Tensor> moe_dispatch_shmem_cuda(const at::Tensor& x, const at::T
     check_cuda_contig(expertIds, "expertIds");
     CAM_ASSERT(epWorldSize == b->num_ranks() && epRankId == b->rank(), "epWorldSize/epRankId do not match the Buffer");
     CAM_ASSERT(tpWorldSize <= 1, "tpWorldSize > 1 is not supported by this build");
-    CAM_ASSERT(sharedExpertRankNum == 0, "shared-expert ranks are not supported by this build");
     CAM_ASSERT(quantMode != 1, "static quantisation (quantMode 1) is rejected, as in the reference");
-    const int is64 = idx_kind(expertIds, "expertIds");
+    idx_kind(expertIds, "expertIds");
     c10::cuda::CUDAGuard guard(x.device());
-    const int64_t T = x.size(0), h = x.size(1), K = expertIds.size(1);
-    const int64_t El = moeExpertNum / epWorldSize;
-    const int64_t A = std::max<int64_t>(1, T * epWorldSize * std::min<int64_t>(El, K));
+    const int64_t T = x.size(0), h = x.size(1), Kuser = expertIds.size(1);
+    const int64_t S = sharedExpertRankNum;
+    const bool shared_rank = epRankId < S;
+    at::Tensor ids = expertIds;
+    int64_t E = moeExpertNum, El = moeExpertNum / epWorldSize;
+    if (S > 0) {
+        SharedRemap rm = remap_for_shared_ranks(expertIds, c10::nullopt, epWorldSize, moeExpertNum, S);
+        ids = rm.ids;
+        E = rm.num_virtual_experts;
+        El = rm.experts_per_rank;
+    }
+    const int is64 = idx_kind(ids, "expertIds");
+    const int64_t K = ids.size(1);
+    // rows this rank can receive (pybind/moe_dispatch_shmem.cpp:50-62)
+    const int64_t A = std::max<int64_t>(1, shared_rank ? (T * epWorldSize + S - 1) / S
+                                                       : T * epWorldSize * std::min<int64_t>(El, Kuser));
     int64_t active = T;
     if (xActiveMask.has_value() && xActiveMask->defined()) active = xActiveMask->to(at::kLong).sum().item<int64_t>();
     const float* smooth = nullptr;
@@ -340,6 +388,7 @@ std::vector<at::Tensor> moe_dispatch_shmem_cuda(const at::Tensor& x, const at::T
         smooth_t = scales->to(at::kFloat).contiguous();
         CAM_ASSERT(smooth_t.dim() == 2 && smooth_t.size(0) >= moeExpertNum && smooth_t.size(1) == h,
                    "scales must be [>= moeExpertNum, h]");
+        CAM_ASSERT(S == 0, "smooth scales together with shared-expert ranks are not supported");
         smooth = smooth_t.data_ptr<float>();
     }
     const at::ScalarType xdt = quantMode == 0 ? at::kBFloat16 : quantMode == 2 ? at::kChar : at::kFloat8_e4m3fn;
@@ -347,32 +396,52 @@ std::vector<at::Tensor> moe_dispatch_shmem_cuda(const at::Tensor& x, const at::T
     const int64_t nscale = fp8 ? h / 128 : 1;
     at::Tensor expandX = at::empty({A, h}, x.options().dtype(xdt));
     at::Tensor dynScales = fp8 ? at::empty({A, nscale}, x.options().dtype(at::kFloat))
-                                          : at::empty({A}, x.options().dtype(at::kFloat));
+                               : at::empty({A}, x.options().dtype(at::kFloat));
     at::Tensor expandIdx = at::empty({T * K}, x.options().dtype(at::kInt));
     at::Tensor expandSrc = at::empty({A, 3}, x.options().dtype(at::kInt));
     at::Tensor tokenNums = at::empty({El}, x.options().dtype(at::kLong));
     at::Tensor epSend = at::empty({epWorldSize * El}, x.options().dtype(at::kInt));
     at::Tensor tpSend = at::zeros({std::max<int64_t>(tpWorldSize, 1)}, x.options().dtype(at::kInt));
     at::Tensor total = at::zeros({1}, x.options().dtype(at::kInt));
-    CAM_RT(cam_dispatch_ll(b->raw(), x.data_ptr(), expertIds.data_ptr(), is64, smooth, static_cast<int>(T),
-                           static_cast<int>(K), static_cast<int>(h), static_cast<int>(moeExpertNum),
+    CAM_RT(cam_dispatch_ll(b->raw(), x.data_ptr(), ids.data_ptr(), is64, smooth, static_cast<int>(T),
+                           static_cast<int>(K), static_cast<int>(h), static_cast<int>(E),
                            static_cast<int>(active), static_cast<int>(quantMode), static_cast<int>(expertTokenNumsType),
                            expandX.data_ptr(), dynScales.data_ptr<float>(), expandIdx.data_ptr<int>(),
                            expandSrc.data_ptr<int>(), tokenNums.data_ptr<int64_t>(), epSend.data_ptr<int>(),
                            total.data_ptr<int>(), (g_phase_mask & 7) & (CAM_PHASE_SEND | CAM_PHASE_RECV), b->stream()));
     b->ll_src_ = expandSrc;
     b->ll_total_ = total;
+    if (S > 0) {
+        // reference shapes: expandIdx covers the routed pairs only; a shared rank reports one expert
+        expandIdx = expandIdx.view({T, K}).slice(1, 0, Kuser).contiguous().view({T * Kuser});
+        if (shared_rank) {
+            tokenNums = tokenNums.slice(0, 0, 1);
+            epSend = epSend.slice(0, 0, epWorldSize);
+        }
+    }
     return {expandX, dynScales, expandIdx, tokenNums, epSend, tpSend};
 }
 
 std::vector<at::Tensor> moe_dispatch_shmem_meta(const at::Tensor& x, const at::Tensor& expertIds,
                                                 const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&,
-                                                int64_t epWorldSize, int64_t, int64_t moeExpertNum,
-                                                int64_t tpWorldSize, int64_t, int64_t, int64_t, int64_t,
-                                                int64_t quantMode, int64_t, int64_t, int64_t) {
-    const int64_t T = x.size(0), h = x.size(1), K = expertIds.size(1), El = moeExpertNum / epWorldSize;
-    const int64_t A = std::max<int64_t>(1, T * epWorldSize * std::min<int64_t>(El, K));
+                                                int64_t epWorldSize, int64_t epRankId, int64_t moeExpertNum,
+                                                int64_t tpWorldSize, int64_t, int64_t, int64_t,
+                                                int64_t sharedExpertRankNum, int64_t quantMode, int64_t, int64_t,
+                                                int64_t) {
+    const int64_t T = x.size(0), h = x.size(1), K = expertIds.size(1);
+    const int64_t S = sharedExpertRankNum, El = moeExpertNum / (epWorldSize - S);
+    const bool shared_rank = epRankId < S;
+    const int64_t A = std::max<int64_t>(1, shared_rank ? (T * epWorldSize + S - 1) / S
+                                                       : T * epWorldSize * std::min<int64_t>(El, K));
     const at::ScalarType xdt = quantMode == 0 ? at::kBFloat16 : quantMode == 2 ? at::kChar : at::kFloat8_e4m3fn;
+    if (S > 0)
+        return {at::empty({A, h}, x.options().dtype(xdt)),
+                (quantMode == 3 || quantMode == 4) ? at::empty({A, h / 128}, x.options().dtype(at::kFloat))
+                                                   : at::empty({A}, x.options().dtype(at::kFloat)),
+                at::empty({T * K}, x.options().dtype(at::kInt)),
+                at::empty({shared_rank ? 1 : El}, x.options().dtype(at::kLong)),
+                at::empty({shared_rank ? epWorldSize : epWorldSize * El}, x.options().dtype(at::kInt)),
+                at::empty({std::max<int64_t>(tpWorldSize, 1)}, x.options().dtype(at::kInt))};
     return {at::empty({A, h}, x.options().dtype(xdt)),
             (quantMode == 3 || quantMode == 4) ? at::empty({A, h / 128}, x.options().dtype(at::kFloat))
                                                : at::empty({A}, x.options().dtype(at::kFloat)),
@@ -400,18 +469,27 @@ at::Tensor moe_combine_shmem_cuda(const at::Tensor& expandX, const at::Tensor& e
     check_cuda_contig(expandX, "expandX");
     check_cuda_contig(expertIds, "expertIds");
     CAM_ASSERT(epWorldSize == b->num_ranks() && epRankId == b->rank(), "epWorldSize/epRankId do not match the Buffer");
-    CAM_ASSERT(tpWorldSize <= 1 && sharedExpertRankNum == 0, "tp > 1 and shared-expert ranks are not supported");
-    CAM_ASSERT(commQuantMode == 0, "commQuantMode must be 0 in this build");
+    CAM_ASSERT(tpWorldSize <= 1, "tpWorldSize > 1 is not supported by this build");
+    CAM_ASSERT(commQuantMode == 0 || commQuantMode == 2, "commQuantMode must be 0 (bf16 rows) or 2 (int8 rows)");
     CAM_ASSERT(b->ll_src_.defined(), "moe_combine_shmem needs a preceding moe_dispatch_shmem on the same Buffer");
     CAM_ASSERT(expertScales.scalar_type() == at::kFloat, "expertScales must be float32");
-    const int is64 = idx_kind(expertIds, "expertIds");
     c10::cuda::CUDAGuard guard(expandX.device());
-    const int64_t T = expertIds.size(0), K = expertIds.size(1), h = expandX.size(1);
+    at::Tensor ids = expertIds;
     at::Tensor w = expertScales.contiguous();
+    int64_t E = moeExpertNum;
+    if (sharedExpertRankNum > 0) {
+        SharedRemap rm = remap_for_shared_ranks(expertIds, expertScales, epWorldSize, moeExpertNum, sharedExpertRankNum);
+        ids = rm.ids;
+        w = rm.weights;
+        E = rm.num_virtual_experts;
+    }
+    const int is64 = idx_kind(ids, "expertIds");
+    const int64_t T = ids.size(0), K = ids.size(1), h = expandX.size(1);
     at::Tensor out = at::empty({T, h}, expandX.options());
     CAM_RT(cam_combine(b->raw(), expandX.data_ptr(), b->ll_src_.data_ptr<int>(), b->ll_total_.data_ptr<int>(),
-                       expertIds.data_ptr(), is64, w.data_ptr<float>(), out.data_ptr(), static_cast<int>(T),
-                       static_cast<int>(K), static_cast<int>(h), static_cast<int>(moeExpertNum), 1,
+                       ids.data_ptr(), is64, w.data_ptr<float>(), out.data_ptr(), static_cast<int>(T),
+                       static_cast<int>(K), static_cast<int>(h), static_cast<int>(E), 1,
+                       static_cast<int>(commQuantMode),
                        (g_phase_mask & 7) & (CAM_PHASE_SEND | CAM_PHASE_RECV), b->stream()));
     return out;
 }
@@ -448,7 +526,7 @@ std::vector<at::Tensor> fused_deep_moe_cuda(const at::Tensor& x, const at::Tenso
     check_cuda_contig(x, "x");
     check_cuda_contig(expertIds, "expertIds");
     CAM_ASSERT(epRankSize == b->num_ranks() && epRankId == b->rank(), "epRankSize/epRankId do not match the Buffer");
-    CAM_ASSERT(sharedExpertRankNum == 0, "shared-expert ranks are not supported by this build");
+    CAM_ASSERT(sharedExpertRankNum >= 0 && sharedExpertRankNum < epRankSize, "sharedExpertRankNum must be in [0, epRankSize)");
     CAM_ASSERT(quantMode == 3 || quantMode == 4, "this entry point runs the block-scaled fp8 paths (quantMode 3: fp32 "
                "scales, 4: power-of-two scales); int8 W8A8 weights are converted by umdk_original_b200.models first");
     CAM_ASSERT(gmm1PermutedWeight.size() >= 1 && gmm2Weight.size() == gmm1PermutedWeight.size() &&
@@ -460,7 +538,10 @@ std::vector<at::Tensor> fused_deep_moe_cuda(const at::Tensor& x, const at::Tenso
     const at::Tensor s1 = b->stacked(1, gmm1PermutedWeightScale);
     const at::Tensor w2 = b->stacked(2, gmm2Weight);
     const at::Tensor s2 = b->stacked(3, gmm2WeightScale);
-    const int64_t T = x.size(0), h = x.size(1), K = expertIds.size(1), El = moeExpertNum / epRankSize;
+    // local experts: E / (R - S) on a routed rank, 1 (the shared expert) on a shared-expert rank
+    const bool shared_rank = epRankId < sharedExpertRankNum;
+    const int64_t T = x.size(0), h = x.size(1);
+    const int64_t El = shared_rank ? 1 : moeExpertNum / (epRankSize - sharedExpertRankNum);
     CAM_ASSERT(w1.dim() == 3 && w1.size(0) == El && w1.size(2) == h && w1.size(1) % 256 == 0,
                "gmm1PermutedWeight must be [E_local, 2I, h] with 2I a multiple of 256");
     const int64_t I = w1.size(1) / 2;
@@ -470,23 +551,31 @@ std::vector<at::Tensor> fused_deep_moe_cuda(const at::Tensor& x, const at::Tenso
     CAM_ASSERT(s2.scalar_type() == at::kFloat && s2.numel() == El * (h / 128) * (I / 128), "gmm2 scale must be [E_local, h/128, I/128] float32");
     for (const at::Tensor* t : {&w1, &s1, &w2, &s2}) check_cuda_contig(*t, "weight/scale");
     CAM_ASSERT(expertScales.scalar_type() == at::kFloat, "expertScales must be float32");
-    const int is64 = idx_kind(expertIds, "expertIds");
     c10::cuda::CUDAGuard guard(x.device());
     at::Tensor ids = expertIds;
+    at::Tensor w = expertScales.contiguous();
+    int64_t E = moeExpertNum;
+    if (sharedExpertRankNum > 0) {
+        SharedRemap rm = remap_for_shared_ranks(expertIds, expertScales, epRankSize, moeExpertNum, sharedExpertRankNum);
+        ids = rm.ids;
+        w = rm.weights;
+        E = rm.num_virtual_experts;
+    }
     if (xActiveMask.has_value() && xActiveMask->defined()) {
         // prefix mask: tokens past the active count do not take part (GMM1.h:647-678)
         const int64_t active = xActiveMask->to(at::kLong).sum().item<int64_t>();
-        ids = expertIds.clone();
+        if (sharedExpertRankNum == 0) ids = expertIds.clone();
         if (active < T) ids.slice(0, active, T).fill_(-1);
     }
-    at::Tensor w = expertScales.contiguous();
+    const int is64 = idx_kind(ids, "expertIds");
+    const int64_t K = ids.size(1);
     at::Tensor out = at::empty({T, h}, x.options());
     at::Tensor nums = at::zeros({El}, x.options().dtype(at::kLong));
     auto fused = quantMode == 4 ? &cam_fused_moe_mxfp8 : &cam_fused_moe_fp8;
     CAM_RT(fused(b->raw(), x.data_ptr(), ids.data_ptr(), is64, w.data_ptr<float>(), w1.data_ptr(), s1.data_ptr<float>(),
                  w2.data_ptr(), s2.data_ptr<float>(), out.data_ptr(), nums.data_ptr<int64_t>(), static_cast<int>(T),
-                 static_cast<int>(K), static_cast<int>(h), static_cast<int>(I), static_cast<int>(moeExpertNum),
-                 g_phase_mask, b->stream()));
+                 static_cast<int>(K), static_cast<int>(h), static_cast<int>(I), static_cast<int>(E),
+                 static_cast<int>(El), g_phase_mask, b->stream()));
     return {out, nums};
 }
 

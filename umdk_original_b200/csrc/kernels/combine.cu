@@ -8,6 +8,10 @@
 // the per-(token,k) float flags summed by a vector reduce become one integer epoch flag per
 // source rank, raised once by the last CTA of the sender.  Pairs whose expert id is negative
 // are skipped instead of waited for.
+//
+// comm_quant = 2 sends a row as int8 with one fp32 scale per 128 elements (h + h/32 bytes instead
+// of 2 h) and dequantises inside the reduce: the counterpart of the reference's commQuantMode 2
+// (moe_combine_shmem.h:567-591 quantises per 8 elements; 128 keeps the scales at 3 % of the row).
 #include "../common/cam_types.h"
 #include "../common/ptx.cuh"
 #include "../common/quant.cuh"
@@ -71,6 +75,43 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineP
             const uint8_t* s = reinterpret_cast<const uint8_t*>(p.y) + static_cast<size_t>(i) * row_bytes;
             uint8_t* d = p.peer_base[src] + p.off_combine_buf +
                          (static_cast<size_t>(t) * p.K + k) * static_cast<size_t>(row_bytes);
+            if (p.comm_quant == 2) {
+                // int8 on the wire: lane owns 8 elements per step of 256, 16 lanes share a 128-element block
+                float* dscale = reinterpret_cast<float*>(d + p.h);
+                for (int base = 0; base < p.h; base += 1024) {
+                    uint4 v[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int c = base + u * 256 + static_cast<int>(lane) * 8;
+                        v[u] = (c < p.h) ? ld_nc_v4(s + static_cast<size_t>(c) * 2) : make_uint4(0, 0, 0, 0);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int c = base + u * 256 + static_cast<int>(lane) * 8;
+                        float f[8] = {bf16_lo(v[u].x), bf16_hi(v[u].x), bf16_lo(v[u].y), bf16_hi(v[u].y),
+                                      bf16_lo(v[u].z), bf16_hi(v[u].z), bf16_lo(v[u].w), bf16_hi(v[u].w)};
+                        float amax = 0.f;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+#pragma unroll
+                        for (int sft = 8; sft >= 1; sft >>= 1)
+                            amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, sft));
+                        const float a = fmaxf(amax, 1e-12f);
+                        const float inv = 127.f / a;
+                        uint32_t w0 = 0u, w1 = 0u;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            w0 |= (static_cast<uint32_t>(__float2int_rn(f[j] * inv)) & 0xFFu) << (8 * j);
+                            w1 |= (static_cast<uint32_t>(__float2int_rn(f[4 + j] * inv)) & 0xFFu) << (8 * j);
+                        }
+                        if (c < p.h) {
+                            st_na_v2(d + c, make_uint2(w0, w1));
+                            if ((lane & 15u) == 0u) dscale[c >> 7] = a / 127.f;
+                        }
+                    }
+                }
+                continue;
+            }
             int o = static_cast<int>(lane) * 16;
             for (; o + 3 * 512 < row_bytes; o += 4 * 512) {
                 const uint4 a = ld_nc_v4(s + o), b4 = ld_nc_v4(s + o + 512), c = ld_nc_v4(s + o + 1024),
@@ -113,6 +154,53 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineP
         if (s_abort) return;
 
         const uint8_t* buf = my_base + p.off_combine_buf;
+        if (p.comm_quant == 2) {
+            // rows arrived as int8 + one scale per 128 elements; a lane reduces 16 elements per step
+            const int chunks_q = (p.h + 511) / 512;
+            const int nsplit_q = min(chunks_q, max(1, nwarps / max(p.T, 1)));
+            const int per_q = (chunks_q + nsplit_q - 1) / nsplit_q;
+            for (int it = gwarp; it < p.T * nsplit_q; it += nwarps) {
+                const int t = it / nsplit_q;
+                const int e_begin = (it - t * nsplit_q) * per_q * 512;
+                const int e_end = min(p.h, e_begin + per_q * 512);
+                bool pair_ok = false;
+                if (lane < static_cast<uint32_t>(p.K)) {
+                    const int id = comb_expert_id(p.topk_idx, p.idx_is_i64, static_cast<size_t>(t) * p.K + lane);
+                    s_w[warp][lane] = p.topk_weights[static_cast<size_t>(t) * p.K + lane];
+                    pair_ok = (id >= 0 && id < p.E);
+                }
+                const uint32_t valid = __ballot_sync(0xFFFFFFFFu, pair_ok);
+                __syncwarp();
+                const uint8_t* trow = buf + static_cast<size_t>(t) * p.K * row_bytes;
+                uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) + static_cast<size_t>(t) * row_bytes;
+                for (int c = e_begin + static_cast<int>(lane) * 16; c < e_end; c += 512) {
+                    float acc[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+                    for (int k = 0; k < p.K; ++k) {
+                        if (!((valid >> k) & 1u)) continue;
+                        const uint8_t* krow = trow + static_cast<size_t>(k) * row_bytes;
+                        const uint4 q = ld_cg_v4(krow + c);
+                        const float sc = __ldcg(reinterpret_cast<const float*>(krow + p.h) + (c >> 7)) * s_w[warp][k];
+                        const uint32_t wq[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int b8 = static_cast<int>(static_cast<int8_t>((wq[j >> 2] >> (8 * (j & 3))) & 0xFFu));
+                            acc[j] = fmaf(sc, static_cast<float>(b8), acc[j]);
+                        }
+                    }
+                    uint4 r0, r1;
+                    r0.x = pack_bf16x2(acc[0], acc[1]);   r0.y = pack_bf16x2(acc[2], acc[3]);
+                    r0.z = pack_bf16x2(acc[4], acc[5]);   r0.w = pack_bf16x2(acc[6], acc[7]);
+                    r1.x = pack_bf16x2(acc[8], acc[9]);   r1.y = pack_bf16x2(acc[10], acc[11]);
+                    r1.z = pack_bf16x2(acc[12], acc[13]); r1.w = pack_bf16x2(acc[14], acc[15]);
+                    st_na_v4(orow + static_cast<size_t>(c) * 2, r0);
+                    st_na_v4(orow + static_cast<size_t>(c) * 2 + 16, r1);
+                }
+                __syncwarp();
+            }
+            return;
+        }
         // Work item = (token, slice of the row).  With few tokens (decode) a row is cut into as many
         // 512-byte-aligned slices as there are warps to spare, so the whole grid takes part.
         const int chunks = (row_bytes + 511) / 512;

@@ -45,6 +45,7 @@ struct CombineParams {
     const float* topk_weights;  // [T, K]
     __nv_bfloat16* out;         // [T, h]
     int T, K, h, E, R, rank;
+    int comm_quant;  // 0: bf16 rows on the wire, 2: int8 rows + one fp32 scale per 128 elements
     uint32_t epoch;
     uint64_t timeout_ns;
     int phase_mask;

@@ -403,11 +403,11 @@ extern "C" int cam_dispatch_normal(CamBuffer* b, const void* x, const void* topk
 
 extern "C" int cam_combine(CamBuffer* b, const void* y, const int* row_src, const int* total_rows,
                            const void* topk_idx, int idx_is_i64, const float* topk_weights, void* out, int T, int K,
-                           int h, int E, int low_latency, int phase_mask, cudaStream_t stream) {
+                           int h, int E, int low_latency, int comm_quant, int phase_mask, cudaStream_t stream) {
     if (check_common(b, T, K, h, E, "combine") != 0) return -1;
     const int maxT = low_latency ? b->layout.ll_max_tokens : b->layout.max_tokens;
     CAM_CHECK(T <= maxT, "combine: %d tokens exceed the buffer's limit %d", T, maxT);
-    CAM_CHECK(K == b->layout.topk || true, "combine");
+    CAM_CHECK(comm_quant == 0 || comm_quant == 2, "combine: comm_quant %d must be 0 (bf16) or 2 (int8 per 128)", comm_quant);
     CAM_CUDA(cudaSetDevice(b->device));
     uint32_t& epoch = low_latency ? b->epoch_ll_combine : b->epoch_combine;
     if (phase_mask & CAM_PHASE_SEND) ++epoch;
@@ -420,6 +420,7 @@ extern "C" int cam_combine(CamBuffer* b, const void* y, const int* row_src, cons
     p.topk_weights = topk_weights;
     p.out = static_cast<__nv_bfloat16*>(out);
     p.T = T; p.K = K; p.h = h; p.E = E; p.R = b->num_ranks; p.rank = b->rank;
+    p.comm_quant = comm_quant;
     p.epoch = epoch;
     p.timeout_ns = b->timeout_ns;
     p.phase_mask = phase_mask;
@@ -642,12 +643,14 @@ extern "C" int cam_grouped_gemm_mxfp8(CamBuffer* b, const void* a_q, const float
 static int fused_moe_impl(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,
                           const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
                           const float* w2_s, void* out, int64_t* expert_token_nums, int T, int K, int h, int inter,
-                          int E, int phase_mask, bool ue8m0, cudaStream_t stream) {
+                          int E, int gemm_experts, int phase_mask, bool ue8m0, cudaStream_t stream) {
     if (check_common(b, T, K, h, E, "fused_moe_fp8") != 0) return -1;
     CAM_CHECK(inter >= 128 && inter % 128 == 0 && inter <= b->layout.hidden,
               "fused_moe_fp8: intermediate size %d must be a multiple of 128 and <= the buffer's hidden %d", inter, b->layout.hidden);
     CAM_CHECK(w1_q && w1_s && w2_q && w2_s && topk_weights && out, "fused_moe_fp8: null operand");
-    const int El = E / b->num_ranks;
+    // local experts that have weights: E / R, or fewer on a shared-expert rank (1: only its first
+    // local expert ever receives rows)
+    const int El = (gemm_experts > 0 && gemm_experts <= E / b->num_ranks) ? gemm_experts : E / b->num_ranks;
     const CamLayout& L = b->layout;
     const int disp_mask = phase_mask & CAM_PHASE_ALL;
     const bool prof = b->profile && phase_mask == 15;
@@ -676,7 +679,7 @@ static int fused_moe_impl(CamBuffer* b, const void* x, const void* expert_ids, i
     }
     stamp(3);
     if (phase_mask & 8) {
-        if (cam_combine(b, nullptr, nullptr, nullptr, expert_ids, idx_is_i64, topk_weights, out, T, K, h, E, 0,
+        if (cam_combine(b, nullptr, nullptr, nullptr, expert_ids, idx_is_i64, topk_weights, out, T, K, h, E, 0, 0,
                         CAM_PHASE_RECV, stream) != 0)
             return -1;
     }
@@ -688,15 +691,15 @@ static int fused_moe_impl(CamBuffer* b, const void* x, const void* expert_ids, i
 extern "C" int cam_fused_moe_fp8(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,
                                  const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
                                  const float* w2_s, void* out, int64_t* expert_token_nums, int T, int K, int h,
-                                 int inter, int E, int phase_mask, cudaStream_t stream) {
+                                 int inter, int E, int gemm_experts, int phase_mask, cudaStream_t stream) {
     return fused_moe_impl(b, x, expert_ids, idx_is_i64, topk_weights, w1_q, w1_s, w2_q, w2_s, out, expert_token_nums,
-                          T, K, h, inter, E, phase_mask, false, stream);
+                          T, K, h, inter, E, gemm_experts, phase_mask, false, stream);
 }
 
 extern "C" int cam_fused_moe_mxfp8(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,
                                    const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
                                    const float* w2_s, void* out, int64_t* expert_token_nums, int T, int K, int h,
-                                   int inter, int E, int phase_mask, cudaStream_t stream) {
+                                   int inter, int E, int gemm_experts, int phase_mask, cudaStream_t stream) {
     return fused_moe_impl(b, x, expert_ids, idx_is_i64, topk_weights, w1_q, w1_s, w2_q, w2_s, out, expert_token_nums,
-                          T, K, h, inter, E, phase_mask, true, stream);
+                          T, K, h, inter, E, gemm_experts, phase_mask, true, stream);
 }

@@ -72,9 +72,10 @@ int cam_dispatch_normal(CamBuffer* b, const void* x_bf16, const void* topk_idx, 
 
 // Combine (push + flag + weighted reduce).  `y` rows follow `row_src` ([N,3] device ints), N is
 // read on the device from `total_rows`.  low_latency selects the low-latency slot/flag regions.
+// comm_quant 2 sends rows as int8 with one fp32 scale per 128 elements (both phases of a call must agree).
 int cam_combine(CamBuffer* b, const void* y_bf16, const int* row_src, const int* total_rows, const void* topk_idx,
                 int idx_is_i64, const float* topk_weights, void* out_bf16, int T, int K, int h, int E,
-                int low_latency, int phase_mask, cudaStream_t stream);
+                int low_latency, int comm_quant, int phase_mask, cudaStream_t stream);
 
 int cam_dispatch_ll(CamBuffer* b, const void* x_bf16, const void* expert_ids, int idx_is_i64, const float* smooth,
                     int T, int K, int h, int E, int active_tokens, int quant_mode, int count_type,
@@ -99,17 +100,18 @@ int cam_grouped_gemm_mxfp8(CamBuffer* b, const void* a_q, const float* a_scales,
 
 // Whole fp8 MoE layer on the normal-mode path:
 // dispatch (fp8 1x128) -> GEMM1 + SwiGLU + requant -> GEMM2 with combine-send epilogue -> reduce.
+// gemm_experts: local experts that have weights (0 = E / R; 1 on a shared-expert rank).
 int cam_fused_moe_fp8(CamBuffer* b, const void* x_bf16, const void* expert_ids, int idx_is_i64,
                       const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
                       const float* w2_s, void* out_bf16, int64_t* expert_token_nums, int T, int K, int h,
-                      int inter, int E, int phase_mask, cudaStream_t stream);
+                      int inter, int E, int gemm_experts, int phase_mask, cudaStream_t stream);
 
 // Same layer with power-of-two scales end to end: dispatch quantises with UE8M0 scale rounding, the
 // weights' 128x128 scales must be powers of two, both GEMMs run on the block-scaled tensor-core path.
 int cam_fused_moe_mxfp8(CamBuffer* b, const void* x_bf16, const void* expert_ids, int idx_is_i64,
                         const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
                         const float* w2_s, void* out_bf16, int64_t* expert_token_nums, int T, int K, int h,
-                        int inter, int E, int phase_mask, cudaStream_t stream);
+                        int inter, int E, int gemm_experts, int phase_mask, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -132,13 +132,22 @@ def _moe_dispatch_shmem_cpu(x, expertIds, scales, xActiveMask, epWorldSize, epRa
     g = _reg().by_id(extInfo)
     if quantMode == 1:
         raise RuntimeError("umdk_cam_op_lib: static quantisation (quantMode 1) is rejected, as in the reference")
-    if tpWorldSize > 1 or sharedExpertRankNum != 0:
-        raise RuntimeError("umdk_cam_op_lib: tp > 1 and shared-expert ranks are not supported")
+    if tpWorldSize > 1:
+        raise RuntimeError("umdk_cam_op_lib: tpWorldSize > 1 is not supported")
     t, k = expertIds.shape
+    ids = expertIds
     el = moeExpertNum // epWorldSize
-    a = max(1, t * epWorldSize * min(el, k))
+    shared_rank = epRankId < sharedExpertRankNum
+    if sharedExpertRankNum > 0:
+        ids, _, e_virtual, el = ref.remap_for_shared_ranks(expertIds, None, epWorldSize, moeExpertNum, sharedExpertRankNum)
+        assert g.num_experts == e_virtual, "the Buffer must be created for R * E_local virtual experts"
+    a = max(1, -(-t * epWorldSize // sharedExpertRankNum) if shared_rank else t * epWorldSize * min(el, k))
     active = int(xActiveMask.sum()) if xActiveMask is not None else None
-    rx, rs, src, cnt, per_e, slots = _backend().dispatch(g, x, expertIds, quantMode, active, scales)
+    rx, rs, src, cnt, per_e, slots = _backend().dispatch(g, x, ids, quantMode, active, scales)
+    if sharedExpertRankNum > 0:
+        slots = slots.view(t, k + 1)[:, :k].contiguous().view(-1)
+        if shared_rank:
+            per_e, cnt = per_e[:1], cnt[:epWorldSize]
     n = rx.shape[0]
     pad = a - n
     if rx.dtype == ref.FP8:
@@ -163,11 +172,17 @@ def _moe_combine_shmem_cpu(expandX, expertIds, expandIdx, epSendCounts, expertSc
     g = _reg().by_id(extInfo)
     if g.ll_src is None:
         raise RuntimeError("umdk_cam_op_lib: moe_combine_shmem needs a preceding moe_dispatch_shmem on the same Buffer")
-    ids = expertIds
+    ids, w = expertIds, expertScales
+    if sharedExpertRankNum > 0:
+        ids, w, _, _ = ref.remap_for_shared_ranks(expertIds, expertScales, epWorldSize, moeExpertNum, sharedExpertRankNum)
     if xActiveMask is not None:
-        ids = expertIds.clone()
+        ids = ids.clone()
         ids[int(xActiveMask.sum()):] = -1
-    return _backend().combine(g, expandX, g.ll_src, ids, expertScales)
+    y = expandX
+    if commQuantMode == 2:  # int8 on the wire, one scale per 128 elements
+        q, s = ref.quant_int8_1x128(expandX)
+        y = ref.dequant_int8_1x128(q, s)
+    return _backend().combine(g, y, g.ll_src, ids, w)
 
 
 def _stack(ws) -> torch.Tensor:
@@ -179,16 +194,19 @@ def _fused_deep_moe_cpu(x, expertIds, gmm1PermutedWeight, gmm1PermutedWeightScal
                         expertScales, expertSmoothScales, xActiveMask, groupEp, epRankSize, epRankId, moeExpertNum,
                         sharedExpertNum, sharedExpertRankNum, quantMode, globalBs):
     g = _reg().by_name(groupEp)
-    if sharedExpertRankNum != 0:
-        raise RuntimeError("umdk_cam_op_lib: shared-expert ranks are not supported")
     be = _backend()
     w1, s1 = _stack(gmm1PermutedWeight), _stack(gmm1PermutedWeightScale)
     w2, s2 = _stack(gmm2Weight), _stack(gmm2WeightScale)
     el = moeExpertNum // epRankSize
     active = int(xActiveMask.sum()) if xActiveMask is not None else None
     ids = expertIds
+    if sharedExpertRankNum > 0:
+        ids, expertScales, e_virtual, _ = ref.remap_for_shared_ranks(expertIds, expertScales, epRankSize, moeExpertNum,
+                                                                     sharedExpertRankNum)
+        assert g.num_experts == e_virtual, "the Buffer must be created for R * E_local virtual experts"
+        el = w1.shape[0]  # 1 on a shared-expert rank
     if active is not None:
-        ids = expertIds.clone()
+        ids = ids.clone()
         ids[active:] = -1
     if w1.dtype == ref.FP8:  # block-scaled fp8 (quantMode 3; 4 = power-of-two scales)
         po2 = quantMode == 4
@@ -216,7 +234,7 @@ def _fused_deep_moe_cpu(x, expertIds, gmm1PermutedWeight, gmm1PermutedWeightScal
             if b > a:
                 y[a:b] = ref.swiglu_mlp_fp32(rx[a:b], w1[le], w2[le]).to(x.dtype)
     out = be.combine(g, y, src, ids, expertScales, out_dtype=x.dtype)
-    return [out, per_e.to(torch.int64)]
+    return [out, per_e[:el].to(torch.int64)]
 
 
 def _grouped_gemm_fp8_cpu(a_q, a_s, w_q, w_s, expert_offsets, ue8m0=False):

@@ -81,6 +81,21 @@ def dequant_fp8_128x128(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
     return (qf * s.float().unsqueeze(-1).unsqueeze(-3)).reshape(*lead, n, k)
 
 
+def quant_int8_1x128(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """int8 with one fp32 scale per 128 contiguous elements (the wire format of combine's comm quant)."""
+    n, h = x.shape
+    xf = x.float().view(n, h // 128, 128)
+    amax = xf.abs().amax(dim=-1).clamp_min(1e-12)
+    inv = (torch.tensor(127.0, dtype=torch.float32) / amax).unsqueeze(-1)
+    q = torch.round(xf * inv).clamp_(-127, 127).to(torch.int8).view(n, h)
+    return q, amax / 127.0
+
+
+def dequant_int8_1x128(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
+    n, h = q.shape
+    return (q.float().view(n, h // 128, 128) * s.float().unsqueeze(-1)).view(n, h)
+
+
 def quant_int8_token(x: torch.Tensor, smooth: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Per-token dynamic int8 (moe_dispatch_normal.h:289-315): q = rint(x*127/(amax+1e-12))."""
     xf = x.float()
@@ -90,6 +105,29 @@ def quant_int8_token(x: torch.Tensor, smooth: Optional[torch.Tensor] = None) -> 
     inv = torch.tensor(127.0, dtype=torch.float32) / (amax + 1e-12)
     q = torch.round(xf * inv).clamp_(-127, 127).to(torch.int8)
     return q, (1.0 / inv).squeeze(-1)
+
+
+# ----------------------------------------------------------------------------------------------
+# Shared-expert ranks
+# ----------------------------------------------------------------------------------------------
+def remap_for_shared_ranks(ids: torch.Tensor, weights: Optional[torch.Tensor], num_ranks: int, moe_expert_num: int,
+                           shared_rank_num: int):
+    """Routing over "virtual" experts when the first ``shared_rank_num`` ranks hold a replica of the
+    shared expert (moe_dispatch_shmem.h:408-489): with E_l = moe_expert_num / (R - S) local experts per
+    routed rank, routed expert e becomes e + S * E_l, the replica on rank s is virtual expert s * E_l,
+    and every token gets one more pair (weight 1) to replica min(S - 1, t * S / T).
+    Returns (ids [T, K+1], weights [T, K+1] or None, virtual expert count, E_l)."""
+    assert 0 < shared_rank_num < num_ranks and moe_expert_num % (num_ranks - shared_rank_num) == 0
+    el = moe_expert_num // (num_ranks - shared_rank_num)
+    t = ids.shape[0]
+    routed = torch.where(ids >= 0, ids + shared_rank_num * el, torch.full_like(ids, -1))
+    tok = torch.arange(t, dtype=ids.dtype, device=ids.device)
+    replica = torch.clamp(torch.div(tok * shared_rank_num, max(t, 1), rounding_mode="floor"), max=shared_rank_num - 1)
+    new_ids = torch.cat([routed, (replica * el).unsqueeze(1)], dim=1).contiguous()
+    new_w = None
+    if weights is not None:
+        new_w = torch.cat([weights.float(), torch.ones(t, 1, dtype=torch.float32, device=weights.device)], dim=1).contiguous()
+    return new_ids, new_w, el * num_ranks, el
 
 
 # ----------------------------------------------------------------------------------------------

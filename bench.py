@@ -166,7 +166,10 @@ def run_ours(args, cfg, rank, world, local):
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "fp8_e4m3 block-scaled (fp32 accumulate, bf16 in/out)", "data": "synthetic",
+            "vs_baseline": None,
+            "dtype": ("fp8_e4m3 block-scaled (fp32 accumulate, bf16 in/out)" if cfg.weight_format != "w8a8" else
+                      "int8-range weights + per-channel scales computed as fp8_e4m3 block-scaled (fp32 accumulate, bf16 in/out)"),
+            "data": "synthetic",
             "impl": "ours",
             "config": {"model": cfg.name, "global_batch": tokens * world, "seq_len": tokens, "tokens_per_rank": tokens,
                        "hidden": cfg.hidden, "moe_intermediate": cfg.intermediate, "num_experts": cfg.num_experts,

@@ -17,7 +17,7 @@ from ..parallel.buffer import Buffer
 from ..utils.config import CamConfig
 from .configs import MoEConfig
 from .router import route
-from .weights import ExpertWeights, random_fp8_experts
+from .weights import ExpertWeights, from_reference_w8a8, random_fp8_experts, random_w8a8_experts
 
 
 class FusedMoE(torch.nn.Module):
@@ -29,6 +29,16 @@ class FusedMoE(torch.nn.Module):
         assert cfg.num_experts % self.num_ranks == 0
         self.num_local = cfg.num_experts // self.num_ranks
         dev = buffer.device
+        if weights is None and cfg.weight_format == "w8a8":
+            # int8-range weights with per-output-channel scales in the reference's layout, computed as
+            # block-scaled fp8 (weights in [-16, 16] are exact in e4m3; the channel scales fold into
+            # the 128x128 block scales)
+            parts = []
+            for i in range(0, self.num_local, 8):
+                n = min(8, self.num_local - i)
+                parts.append(from_reference_w8a8(*random_w8a8_experts(n, cfg.hidden, cfg.intermediate, device=dev,
+                                                                      seed=seed * 1000 + self.rank * 64 + i)))
+            weights = ExpertWeights(*[torch.cat([getattr(p, f) for p in parts]) for f in ("w1", "s1", "w2", "s2")])
         if weights is None:
             weights = random_fp8_experts(self.num_local, cfg.hidden, cfg.intermediate, device=dev,
                                          seed=seed * 1000 + self.rank)

@@ -194,8 +194,16 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
         uint8_t* stage_q = dyn_smem + static_cast<size_t>(warp) * stage_bytes;
         float* stage_s = reinterpret_cast<float*>(stage_q + p.h);
 
+        // Quantised rows leave the staging area as bulk copies (one 7 KB transfer per destination
+        // instead of 14 rounds of 16-byte stores per lane): lane k issues the copies of pair (t, k).
+        const bool bulk_rows = (p.quant_mode != CAM_QUANT_NONE) && (row_bytes % 16 == 0);
+        const bool bulk_scales = bulk_rows && ((nscale * 4) % 16 == 0);
         for (int t = t0 + warp; t < t1; t += kDispWarps) {
             const __nv_bfloat16* xrow = p.x + static_cast<size_t>(t) * p.h;
+            if (bulk_rows) {
+                if (lane < static_cast<uint32_t>(K)) bulk_wait_group_read<0>();  // staging is free again
+                __syncwarp();
+            }
             if (p.quant_mode == CAM_QUANT_FP8_1x128) {
                 warp_quant_fp8_1x128<false>(xrow, p.h, stage_q, stage_s);
             } else if (p.quant_mode == CAM_QUANT_FP8_1x128_UE8M0) {
@@ -204,6 +212,40 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
                 warp_quant_int8_token(xrow, p.h, stage_q, stage_s);
             }
             __syncwarp();
+            if (bulk_rows) {
+                fence_proxy_async_smem();  // the staged row is read by the async proxy
+                __syncwarp();
+                if (lane < static_cast<uint32_t>(K)) {
+                    const int k = static_cast<int>(lane);
+                    const size_t g = static_cast<size_t>(t) * K + k;
+                    const int id = load_expert_id(p.topk_idx, p.idx_is_i64, g);
+                    int row = -1;
+                    if (id >= 0 && id < E) {
+                        const int d = id / El;
+                        if (s_rank_ok[d]) {
+                            row = s_aux[id] + p.slot_in_expert[g];
+                            uint8_t* pb = p.peer_base[d];
+                            bulk_store_s2g(pb + p.off_recv_x + static_cast<size_t>(row) * row_bytes, stage_q,
+                                           static_cast<uint32_t>(row_bytes));
+                            float* sdst = reinterpret_cast<float*>(pb + p.off_recv_scales) +
+                                          static_cast<size_t>(row) * nscale;
+                            if (bulk_scales) {
+                                bulk_store_s2g(sdst, stage_s, static_cast<uint32_t>(nscale * 4));
+                            } else {
+                                for (int o = 0; o < nscale; ++o) sdst[o] = stage_s[o];
+                            }
+                            int* tri = reinterpret_cast<int*>(pb + p.off_recv_src) + static_cast<size_t>(row) * 3;
+                            tri[0] = p.rank;
+                            tri[1] = t;
+                            tri[2] = k;
+                        }
+                    }
+                    bulk_commit_group();
+                    p.send_row[g] = row;
+                }
+                __syncwarp();
+                continue;
+            }
             for (int k = 0; k < K; ++k) {
                 const size_t g = static_cast<size_t>(t) * K + k;
                 const int id = load_expert_id(p.topk_idx, p.idx_is_i64, g);
@@ -235,6 +277,7 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
         }
 
         // Completion: the last CTA to finish raises this rank's data flag in every peer.
+        if (bulk_rows && lane < static_cast<uint32_t>(K)) bulk_wait_group<0>();  // this lane's copies are written
         __syncthreads();
         if (tid == 0) {
             __threadfence_system();

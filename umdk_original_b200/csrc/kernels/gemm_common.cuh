@@ -13,23 +13,25 @@ constexpr int kATile = BM * BK;            // 16 KiB
 constexpr int kBTile = BN * BK;            // 32 KiB
 constexpr int kStageBytes = kATile + kBTile;
 
-struct TileWalker {
+// TM = rows of one tile along M (128 for one CTA per tile, 256 for a CTA pair).
+template <int TM>
+struct TileWalkerT {
     const int* off;
     int num_experts, n_tiles;
     int e, base;
-    __device__ TileWalker(const int* o, int ne, int nt) : off(o), num_experts(ne), n_tiles(nt), e(0), base(0) {}
+    __device__ TileWalkerT(const int* o, int ne, int nt) : off(o), num_experts(ne), n_tiles(nt), e(0), base(0) {}
     // Maps a linear tile index (monotonically increasing across calls) to its expert and tile.
     __device__ bool locate(int tile, int& e_out, int& mt, int& nt, int& row0, int& rows) {
         while (e < num_experts) {
             const int first = __ldg(off + e);
             const int cnt = __ldg(off + e + 1) - first;
-            const int tiles = ((cnt + BM - 1) / BM) * n_tiles;
+            const int tiles = ((cnt + TM - 1) / TM) * n_tiles;
             if (tile < base + tiles) {
                 const int local = tile - base;
                 mt = local / n_tiles;
                 nt = local - mt * n_tiles;
-                row0 = first + mt * BM;
-                rows = min(BM, cnt - mt * BM);
+                row0 = first + mt * TM;
+                rows = min(TM, cnt - mt * TM);
                 e_out = e;
                 return true;
             }
@@ -39,6 +41,8 @@ struct TileWalker {
         return false;
     }
 };
+
+using TileWalker = TileWalkerT<BM>;
 
 __device__ __forceinline__ void gemm_record_status(CamStatus* st, int code, int who, int detail) {
     if (atomicCAS(&st->code, 0, code) == 0) {

@@ -199,11 +199,6 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                 uint32_t wd[6];
 #pragma unroll
                 for (int j = 0; j < 6; ++j) { wd[j] = ue8m0_word(c[j]); c[j] = n1[j]; }
-                if (kb + 2 < kblocks) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) n1[j] = __ldg(as[j] + kb + 2);
-                    n1[4] = __ldg(bs_lo + kb + 2); n1[5] = __ldg(bs_hi + kb + 2);
-                }
                 const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
                 const bool got = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, abort_flag);
                 if (!__all_sync(0xFFFFFFFFu, got)) { ok = false; break; }
@@ -216,6 +211,13 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bar_sf[s]);
+                // prefetch for K-block kb + 2 only now: the arrive above has release semantics and would
+                // otherwise wait for these loads
+                if (kb + 2 < kblocks) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) n1[j] = __ldg(as[j] + kb + 2);
+                    n1[4] = __ldg(bs_lo + kb + 2); n1[5] = __ldg(bs_hi + kb + 2);
+                }
             }
         }
         if (!ok && lane == 0) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 3, static_cast<int>(it));

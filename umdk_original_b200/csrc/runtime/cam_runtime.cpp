@@ -9,6 +9,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -550,7 +551,7 @@ static int make_tmap(CamBuffer* cache_owner, CUtensorMap* out, const void* base,
 static int grouped_gemm_impl(CamBuffer* b, const void* a_q, const float* a_scales, int a_rows, const void* w_q,
                              const float* w_scales, const int* expert_offsets, int num_experts, int n_dim, int k_dim,
                              int mode, void* out_bf16, void* act_q, float* act_s, const int* row_src, int topk,
-                             int low_latency, bool ue8m0, cudaStream_t stream) {
+                             int low_latency, bool ue8m0, int rows_per_expert_hint, cudaStream_t stream) {
     CAM_CHECK(a_q && a_scales && w_q && w_scales && expert_offsets, "grouped_gemm: null operand");
     CAM_CHECK(num_experts >= 1 && a_rows >= 1, "grouped_gemm: empty problem");
     CAM_CHECK(k_dim >= 128 && k_dim % 128 == 0, "grouped_gemm: K %d must be a multiple of 128", k_dim);
@@ -616,8 +617,13 @@ static int grouped_gemm_impl(CamBuffer* b, const void* a_q, const float* a_scale
     p.topk = topk;
     int sms = 0;
     CAM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-    const int rc = ue8m0 ? cam_launch_grouped_gemm_mxfp8(&p, &ta, &tb, sms, stream)
-                         : cam_launch_grouped_gemm_fp8(&p, &ta, &tb, sms, stream);
+    // CTA pairs (256-row tiles, B tile shared inside the cluster) pay off once experts fill such tiles;
+    // UMDK_CAM_GEMM_PAIR=0/1 forces the choice.
+    bool pair = ue8m0 && rows_per_expert_hint >= 384;
+    if (const char* env = getenv("UMDK_CAM_GEMM_PAIR")) pair = ue8m0 && env[0] == '1';
+    const int rc = !ue8m0 ? cam_launch_grouped_gemm_fp8(&p, &ta, &tb, sms, stream)
+                   : pair ? cam_launch_grouped_gemm_mxfp8_pair(&p, &ta, &tb, sms, stream)
+                          : cam_launch_grouped_gemm_mxfp8(&p, &ta, &tb, sms, stream);
     CAM_CHECK(rc == 0, "grouped_gemm launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
     return 0;
 }
@@ -628,7 +634,7 @@ extern "C" int cam_grouped_gemm_fp8(CamBuffer* b, const void* a_q, const float* 
                                     float* act_s, const int* row_src, int topk, int low_latency,
                                     cudaStream_t stream) {
     return grouped_gemm_impl(b, a_q, a_scales, a_rows, w_q, w_scales, expert_offsets, num_experts, n_dim, k_dim, mode,
-                             out_bf16, act_q, act_s, row_src, topk, low_latency, false, stream);
+                             out_bf16, act_q, act_s, row_src, topk, low_latency, false, 0, stream);
 }
 
 extern "C" int cam_grouped_gemm_mxfp8(CamBuffer* b, const void* a_q, const float* a_scales, int a_rows,
@@ -637,7 +643,7 @@ extern "C" int cam_grouped_gemm_mxfp8(CamBuffer* b, const void* a_q, const float
                                       float* act_s, const int* row_src, int topk, int low_latency,
                                       cudaStream_t stream) {
     return grouped_gemm_impl(b, a_q, a_scales, a_rows, w_q, w_scales, expert_offsets, num_experts, n_dim, k_dim, mode,
-                             out_bf16, act_q, act_s, row_src, topk, low_latency, true, stream);
+                             out_bf16, act_q, act_s, row_src, topk, low_latency, true, a_rows / num_experts, stream);
 }
 
 static int fused_moe_impl(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,
@@ -666,12 +672,14 @@ static int fused_moe_impl(CamBuffer* b, const void* x, const void* expert_ids, i
         const uint8_t* recv_x = b->base + L.off_recv_x;
         const float* recv_s = reinterpret_cast<const float*>(b->base + L.off_recv_scales);
         const int* recv_src = reinterpret_cast<const int*>(b->base + L.off_recv_src);
+        // mean rows per local expert when routing is balanced: every rank sends T * K rows in total
+        const int rows_hint = static_cast<int>(static_cast<int64_t>(T) * K * b->num_ranks / E);
         if (grouped_gemm_impl(b, recv_x, recv_s, L.capacity, w1_q, w1_s, b->expert_offsets, El, 2 * inter, h, 1,
-                              nullptr, b->act_q, b->act_s, nullptr, K, 0, ue8m0, stream) != 0)
+                              nullptr, b->act_q, b->act_s, nullptr, K, 0, ue8m0, rows_hint, stream) != 0)
             return -1;
         stamp(2);
         if (grouped_gemm_impl(b, b->act_q, b->act_s, L.capacity, w2_q, w2_s, b->expert_offsets, El, h, inter, 2,
-                              nullptr, nullptr, nullptr, recv_src, K, 0, ue8m0, stream) != 0)
+                              nullptr, nullptr, nullptr, recv_src, K, 0, ue8m0, rows_hint, stream) != 0)
             return -1;
         if (expert_token_nums != nullptr)
             CAM_CUDA(cudaMemcpyAsync(expert_token_nums, b->num_recv_per_expert, sizeof(int64_t) * El,

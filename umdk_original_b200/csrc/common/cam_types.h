@@ -78,6 +78,8 @@ typedef struct CamLayout {
     uint64_t off_ll_scales;     // f32[2][E cells][ll_max_tokens][hidden/128]
     uint64_t off_ll_meta;       // i32[2][E cells][ll_max_tokens][2]
     uint64_t off_ll_combine_buf;  // bf16[ll_max_tokens][topk][hidden]
+    uint64_t off_dup_cnt;       // u32[2][CAM_MAX_RANKS]: replicate-list lengths per source (normal dispatch)
+    uint64_t off_dup_list;      // i32[2][R][max_tokens*topk][2]: (row that arrived, row to copy it to)
     uint64_t total_bytes;
 } CamLayout;
 

@@ -196,6 +196,11 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
 
         // Quantised rows leave the staging area as bulk copies (one 7 KB transfer per destination
         // instead of 14 rounds of 16-byte stores per lane): lane k issues the copies of pair (t, k).
+        //
+        // A token crosses to a destination rank ONCE.  Lane k handles pair (t, k); lanes whose experts
+        // live on the same rank find each other with match.any: the lowest of them sends the row, the
+        // others append (row that arrives, row to copy it to) to the replicate list of that rank, which
+        // the receiver works off locally after the data flags (RECV phase below).
         const bool bulk_rows = (p.quant_mode != CAM_QUANT_NONE) && (row_bytes % 16 == 0);
         const bool bulk_scales = bulk_rows && ((nscale * 4) % 16 == 0);
         for (int t = t0 + warp; t < t1; t += kDispWarps) {
@@ -212,66 +217,69 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
                 warp_quant_int8_token(xrow, p.h, stage_q, stage_s);
             }
             __syncwarp();
+            // pair of this lane
+            int d = -1, row = -1;
+            if (lane < static_cast<uint32_t>(K)) {
+                const size_t g = static_cast<size_t>(t) * K + lane;
+                const int id = load_expert_id(p.topk_idx, p.idx_is_i64, g);
+                if (id >= 0 && id < E && s_rank_ok[id / El]) {
+                    d = id / El;
+                    row = s_aux[id] + p.slot_in_expert[g];
+                }
+                p.send_row[g] = row;
+            }
+            // rows for this rank's own experts are written directly (local stores cost less than a copy pass)
+            const uint32_t peers =
+                __match_any_sync(0xFFFFFFFFu, (d >= 0 && d != p.rank) ? d : -1 - static_cast<int>(lane));
+            const int first = __ffs(static_cast<int>(peers)) - 1;
+            const int first_row = __shfl_sync(0xFFFFFFFFu, row, first);
+            const bool sends = d >= 0 && static_cast<int>(lane) == first;
+            if (d >= 0) {
+                uint8_t* pb = p.peer_base[d];
+                int* tri = reinterpret_cast<int*>(pb + p.off_recv_src) + static_cast<size_t>(row) * 3;
+                tri[0] = p.rank;
+                tri[1] = t;
+                tri[2] = static_cast<int>(lane);
+                if (!sends) {
+                    const unsigned int idx = atomicAdd(&p.dup_ctr[d], 1u);
+                    int* ent = reinterpret_cast<int*>(pb + p.off_dup_list) +
+                               ((static_cast<size_t>(parity) * R + p.rank) * p.dup_cap + idx) * 2;
+                    st_na_v2(ent, make_uint2(static_cast<uint32_t>(first_row), static_cast<uint32_t>(row)));
+                }
+            }
             if (bulk_rows) {
                 fence_proxy_async_smem();  // the staged row is read by the async proxy
                 __syncwarp();
-                if (lane < static_cast<uint32_t>(K)) {
-                    const int k = static_cast<int>(lane);
-                    const size_t g = static_cast<size_t>(t) * K + k;
-                    const int id = load_expert_id(p.topk_idx, p.idx_is_i64, g);
-                    int row = -1;
-                    if (id >= 0 && id < E) {
-                        const int d = id / El;
-                        if (s_rank_ok[d]) {
-                            row = s_aux[id] + p.slot_in_expert[g];
-                            uint8_t* pb = p.peer_base[d];
-                            bulk_store_s2g(pb + p.off_recv_x + static_cast<size_t>(row) * row_bytes, stage_q,
-                                           static_cast<uint32_t>(row_bytes));
-                            float* sdst = reinterpret_cast<float*>(pb + p.off_recv_scales) +
-                                          static_cast<size_t>(row) * nscale;
-                            if (bulk_scales) {
-                                bulk_store_s2g(sdst, stage_s, static_cast<uint32_t>(nscale * 4));
-                            } else {
-                                for (int o = 0; o < nscale; ++o) sdst[o] = stage_s[o];
-                            }
-                            int* tri = reinterpret_cast<int*>(pb + p.off_recv_src) + static_cast<size_t>(row) * 3;
-                            tri[0] = p.rank;
-                            tri[1] = t;
-                            tri[2] = k;
-                        }
+                if (sends) {
+                    uint8_t* pb = p.peer_base[d];
+                    bulk_store_s2g(pb + p.off_recv_x + static_cast<size_t>(row) * row_bytes, stage_q,
+                                   static_cast<uint32_t>(row_bytes));
+                    float* sdst = reinterpret_cast<float*>(pb + p.off_recv_scales) + static_cast<size_t>(row) * nscale;
+                    if (bulk_scales) {
+                        bulk_store_s2g(sdst, stage_s, static_cast<uint32_t>(nscale * 4));
+                    } else {
+                        for (int o = 0; o < nscale; ++o) sdst[o] = stage_s[o];
                     }
-                    bulk_commit_group();
-                    p.send_row[g] = row;
                 }
+                if (lane < static_cast<uint32_t>(K)) bulk_commit_group();
                 __syncwarp();
                 continue;
             }
-            for (int k = 0; k < K; ++k) {
-                const size_t g = static_cast<size_t>(t) * K + k;
-                const int id = load_expert_id(p.topk_idx, p.idx_is_i64, g);
-                int row = -1;
-                if (id >= 0 && id < E) {
-                    const int d = id / El;
-                    if (s_rank_ok[d]) {
-                        row = s_aux[id] + p.slot_in_expert[g];
-                        uint8_t* pb = p.peer_base[d];
-                        uint8_t* dst = pb + p.off_recv_x + static_cast<size_t>(row) * row_bytes;
-                        if (p.quant_mode == CAM_QUANT_NONE) {
-                            warp_copy_row<false>(dst, reinterpret_cast<const uint8_t*>(xrow), row_bytes, lane);
-                        } else {
-                            for (int o = static_cast<int>(lane) * 16; o < row_bytes; o += 512)
-                                st_na_v4(dst + o, *reinterpret_cast<const uint4*>(stage_q + o));
-                            float* sdst = reinterpret_cast<float*>(pb + p.off_recv_scales) +
-                                          static_cast<size_t>(row) * nscale;
-                            for (int o = static_cast<int>(lane); o < nscale; o += 32) sdst[o] = stage_s[o];
-                        }
-                        if (lane < 3) {
-                            int* tri = reinterpret_cast<int*>(pb + p.off_recv_src) + static_cast<size_t>(row) * 3;
-                            tri[lane] = (lane == 0) ? p.rank : (lane == 1) ? t : k;
-                        }
-                    }
+            const uint32_t senders = __ballot_sync(0xFFFFFFFFu, sends);
+            for (uint32_t m = senders; m != 0u; m &= m - 1u) {
+                const int k = __ffs(static_cast<int>(m)) - 1;
+                const int dk = __shfl_sync(0xFFFFFFFFu, d, k);
+                const int rk = __shfl_sync(0xFFFFFFFFu, row, k);
+                uint8_t* pb = p.peer_base[dk];
+                uint8_t* dst = pb + p.off_recv_x + static_cast<size_t>(rk) * row_bytes;
+                if (p.quant_mode == CAM_QUANT_NONE) {
+                    warp_copy_row<false>(dst, reinterpret_cast<const uint8_t*>(xrow), row_bytes, lane);
+                } else {
+                    for (int o = static_cast<int>(lane) * 16; o < row_bytes; o += 512)
+                        st_na_v4(dst + o, *reinterpret_cast<const uint4*>(stage_q + o));
+                    float* sdst = reinterpret_cast<float*>(pb + p.off_recv_scales) + static_cast<size_t>(rk) * nscale;
+                    for (int o = static_cast<int>(lane); o < nscale; o += 32) sdst[o] = stage_s[o];
                 }
-                if (lane == 0) p.send_row[g] = row;
             }
             __syncwarp();
         }
@@ -285,6 +293,11 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
             if (old == static_cast<unsigned int>(nb - 1)) {
                 p.done_ctr[0] = 0u;
                 __threadfence_system();
+                for (int d = 0; d < R; ++d) {  // length of the replicate list this rank wrote at d, then reset the cursor
+                    const unsigned int n = atomicExch(&p.dup_ctr[d], 0u);
+                    reinterpret_cast<uint32_t*>(p.peer_base[d] + p.off_dup_cnt)[parity * CAM_MAX_RANKS + p.rank] = n;
+                }
+                __threadfence_system();
                 if (p.dbg_drop_flags == 0) {
                     for (int d = 0; d < R; ++d)
                         st_release_sys_u32(reinterpret_cast<uint32_t*>(p.peer_base[d] + p.off_data_flag) + p.rank,
@@ -295,11 +308,46 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
     }
 
     // ------------------------------------------------------------------ phase RECV
-    if ((p.phase_mask & CAM_PHASE_RECV) && b == 0) {
+    if (p.phase_mask & CAM_PHASE_RECV) {
+        __shared__ int s_dup_pre[CAM_MAX_RANKS + 1];
         if (tid < R) {
             const uint32_t* f = reinterpret_cast<const uint32_t*>(my_base + p.off_data_flag) + tid;
-            if (!wait_flag_eq_sys(f, p.epoch, p.timeout_ns))
+            if (!wait_flag_eq_sys(f, p.epoch, p.timeout_ns)) {
                 record_status(p.status, CAM_ERR_TIMEOUT_DATA_FLAG, tid, static_cast<int>(ld_acquire_sys_u32(f)));
+                s_abort = 1u;
+            }
+        }
+        __syncthreads();
+        if (s_abort) return;
+        // Replicate: rows that several local experts need arrived once; copy them to the other rows.
+        if (tid == 0) {
+            const uint32_t* cnt = reinterpret_cast<const uint32_t*>(my_base + p.off_dup_cnt) + parity * CAM_MAX_RANKS;
+            int run = 0;
+            for (int s = 0; s < R; ++s) {
+                s_dup_pre[s] = run;
+                run += static_cast<int>(min(__ldcg(cnt + s), static_cast<uint32_t>(p.dup_cap)));
+            }
+            s_dup_pre[R] = run;
+        }
+        __syncthreads();
+        const int nscale = CAM_QUANT_IS_FP8(p.quant_mode) ? (p.h >> 7) : (p.quant_mode == CAM_QUANT_INT8_TOKEN) ? 1 : 0;
+        const int row_bytes = (p.quant_mode == CAM_QUANT_NONE) ? p.h * 2 : p.h;
+        const int warp = tid >> 5;
+        const uint32_t lane = lane_id();
+        const int total = s_dup_pre[R];
+        uint8_t* rx = my_base + p.off_recv_x;
+        float* rs = reinterpret_cast<float*>(my_base + p.off_recv_scales);
+        for (int i = b * kDispWarps + warp; i < total; i += nb * kDispWarps) {
+            int s = 0;
+            while (s + 1 < R && s_dup_pre[s + 1] <= i) ++s;
+            const int* ent = reinterpret_cast<const int*>(my_base + p.off_dup_list) +
+                             ((static_cast<size_t>(parity) * R + s) * p.dup_cap + (i - s_dup_pre[s])) * 2;
+            const int from = __ldcg(ent), to = __ldcg(ent + 1);
+            if (from < 0 || to < 0 || from >= p.capacity || to >= p.capacity) continue;  // never copy out of range
+            warp_copy_row<true>(rx + static_cast<size_t>(to) * row_bytes, rx + static_cast<size_t>(from) * row_bytes,
+                                row_bytes, lane);
+            for (int o = static_cast<int>(lane); o < nscale; o += 32)
+                rs[static_cast<size_t>(to) * nscale + o] = __ldcg(rs + static_cast<size_t>(from) * nscale + o);
         }
     }
 }

@@ -23,6 +23,9 @@ struct DispatchNormalParams {
     int dbg_drop_flags;  // host-side fault injection: this rank withholds its flags
     uint8_t* const* peer_base;  // [R] base of every rank's symmetric allocation (device array)
     uint64_t off_count_flag, off_data_flag, off_count_matrix, off_recv_x, off_recv_scales, off_recv_src;
+    uint64_t off_dup_cnt, off_dup_list;  // replicate lists: rows the receiver copies locally instead of receiving twice
+    int dup_cap;                         // entries per (parity, source) list
+    unsigned int* dup_ctr;               // [R] local cursors into the lists this rank writes
     // local workspace / outputs
     int* cta_hist;                  // [grid, E]
     int* slot_in_expert;            // [T*K]

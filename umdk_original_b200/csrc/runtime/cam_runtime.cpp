@@ -66,6 +66,7 @@ struct CamBuffer {
     int* total_recv = nullptr;
     int* num_tokens_per_expert = nullptr;
     unsigned int* done_ctr = nullptr;  // [4]: dispatch, combine, gemm, spare
+    unsigned int* dup_ctr = nullptr;   // [CAM_MAX_RANKS] replicate-list cursors of normal dispatch (self-resetting)
     CamStatus* d_status = nullptr;
     CamStatus* h_status = nullptr;  // pinned
     uint8_t* act_q = nullptr;       // [capacity, hidden] scratch between the two GEMMs (sized for I <= hidden)
@@ -126,6 +127,7 @@ extern "C" int cam_layout_compute(CamLayout* L, int R, int E, int max_tokens, in
     L->off_combine_flag = take(sizeof(uint32_t) * CAM_MAX_RANKS);
     L->off_barrier_flag = take(sizeof(uint32_t) * CAM_MAX_RANKS);
     L->off_ll_combine_flag = take(sizeof(uint32_t) * CAM_MAX_RANKS);
+    L->off_dup_cnt = take(sizeof(uint32_t) * 2ull * CAM_MAX_RANKS);
     L->off_count_matrix = take(sizeof(int32_t) * 2ull * R * E);
     L->off_ll_cells = take(sizeof(uint64_t) * 2ull * E);
     const uint64_t ctrl_end = off;
@@ -134,6 +136,7 @@ extern "C" int cam_layout_compute(CamLayout* L, int R, int E, int max_tokens, in
     L->off_recv_scales = take(static_cast<uint64_t>(capacity) * (hidden / 128) * 4);
     L->off_recv_src = take(static_cast<uint64_t>(capacity) * 3 * 4);
     L->off_combine_buf = take(static_cast<uint64_t>(max_tokens) * topk * hidden * 2);
+    L->off_dup_list = take(2ull * R * static_cast<uint64_t>(max_tokens) * topk * 8);
     if (ll_max_tokens > 0) {
         const uint64_t cells = 2ull * E;
         L->off_ll_x = take(cells * ll_max_tokens * hidden * 2);
@@ -189,6 +192,7 @@ extern "C" CamBuffer* cam_buffer_create(int device, int rank, int num_ranks, con
     ok &= cudaMalloc(&b->total_recv, sizeof(int) * 4) == cudaSuccess;
     ok &= cudaMalloc(&b->num_tokens_per_expert, sizeof(int) * E) == cudaSuccess;
     ok &= cudaMalloc(&b->done_ctr, sizeof(unsigned int) * 4) == cudaSuccess;
+    ok &= cudaMalloc(&b->dup_ctr, sizeof(unsigned int) * CAM_MAX_RANKS) == cudaSuccess;
     ok &= cudaMalloc(&b->d_status, sizeof(CamStatus)) == cudaSuccess;
     ok &= cudaMallocHost(&b->h_status, sizeof(CamStatus)) == cudaSuccess;
     ok &= cudaMalloc(&b->act_q, static_cast<size_t>(layout->capacity) * layout->hidden) == cudaSuccess;
@@ -199,6 +203,7 @@ extern "C" CamBuffer* cam_buffer_create(int device, int rank, int num_ranks, con
         return nullptr;
     }
     cudaMemset(b->done_ctr, 0, sizeof(unsigned int) * 4);
+    cudaMemset(b->dup_ctr, 0, sizeof(unsigned int) * CAM_MAX_RANKS);
     cudaMemset(b->d_status, 0, sizeof(CamStatus));
     cudaMemset(b->total_recv, 0, sizeof(int) * 4);
     cudaMemset(b->expert_offsets, 0, sizeof(int) * (E + 1));
@@ -216,7 +221,7 @@ extern "C" int cam_buffer_destroy(CamBuffer* b) {
         if (r != b->rank && b->peer_is_ipc[r] && b->peer_ptr[r] != nullptr) cudaIpcCloseMemHandle(b->peer_ptr[r]);
     void* frees[] = {b->base, b->d_peer_table, b->cta_hist, b->slot_in_expert, b->send_row, b->recv_count,
                      b->expert_offsets, b->num_recv_per_expert, b->total_recv, b->num_tokens_per_expert,
-                     b->done_ctr, b->d_status, b->act_q, b->act_s};
+                     b->done_ctr, b->dup_ctr, b->d_status, b->act_q, b->act_s};
     for (void* p : frees)
         if (p != nullptr) cudaFree(p);
     if (b->h_status != nullptr) cudaFreeHost(b->h_status);
@@ -276,6 +281,7 @@ extern "C" int cam_buffer_reset(CamBuffer* b, cudaStream_t stream) {
     CAM_CUDA(cudaSetDevice(b->device));
     CAM_CUDA(cudaMemsetAsync(b->base, 0, b->layout.off_recv_x, stream));
     CAM_CUDA(cudaMemsetAsync(b->done_ctr, 0, sizeof(unsigned int) * 4, stream));
+    CAM_CUDA(cudaMemsetAsync(b->dup_ctr, 0, sizeof(unsigned int) * CAM_MAX_RANKS, stream));
     CAM_CUDA(cudaMemsetAsync(b->d_status, 0, sizeof(CamStatus), stream));
     CAM_CUDA(cudaStreamSynchronize(stream));
     b->epoch_dispatch = b->epoch_combine = b->epoch_ll = b->epoch_ll_combine = 0;
@@ -328,6 +334,7 @@ extern "C" int cam_buffer_poll_status(CamBuffer* b, cudaStream_t stream, CamStat
     if (out->code != CAM_OK) {
         CAM_CUDA(cudaMemsetAsync(b->d_status, 0, sizeof(CamStatus), stream));
         CAM_CUDA(cudaMemsetAsync(b->done_ctr, 0, sizeof(unsigned int) * 4, stream));
+        CAM_CUDA(cudaMemsetAsync(b->dup_ctr, 0, sizeof(unsigned int) * CAM_MAX_RANKS, stream));
         CAM_CUDA(cudaStreamSynchronize(stream));
     }
     return 0;
@@ -384,6 +391,10 @@ extern "C" int cam_dispatch_normal(CamBuffer* b, const void* x, const void* topk
     p.off_recv_x = b->layout.off_recv_x;
     p.off_recv_scales = b->layout.off_recv_scales;
     p.off_recv_src = b->layout.off_recv_src;
+    p.off_dup_cnt = b->layout.off_dup_cnt;
+    p.off_dup_list = b->layout.off_dup_list;
+    p.dup_cap = b->layout.max_tokens * b->layout.topk;
+    p.dup_ctr = b->dup_ctr;
     p.cta_hist = b->cta_hist;
     p.slot_in_expert = b->slot_in_expert;
     p.send_row = b->send_row;

@@ -103,6 +103,7 @@ class Buffer:
         h, e, k = config.hidden, config.num_experts, config.topk
         total = 5 * 4 * 72 + 8 * num_ranks * e + 16 * e
         total += cap * h * 2 + cap * (h // 128) * 4 + cap * 12 + config.max_tokens * k * h * 2
+        total += 2 * num_ranks * config.max_tokens * k * 8  # replicate lists of normal dispatch
         if config.ll_max_tokens:
             cells = 2 * e
             total += cells * config.ll_max_tokens * (h * 2 + (h // 128) * 4 + 8) + config.ll_max_tokens * k * h * 2

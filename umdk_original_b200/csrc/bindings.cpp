@@ -380,8 +380,12 @@ std::vector<at::Tensor> moe_dispatch_shmem_cuda(const at::Tensor& x, const at::T
     // rows this rank can receive (pybind/moe_dispatch_shmem.cpp:50-62)
     const int64_t A = std::max<int64_t>(1, shared_rank ? (T * epWorldSize + S - 1) / S
                                                        : T * epWorldSize * std::min<int64_t>(El, Kuser));
-    int64_t active = T;
-    if (xActiveMask.has_value() && xActiveMask->defined()) active = xActiveMask->to(at::kLong).sum().item<int64_t>();
+    // x_active_mask: tokens whose entry is false do not take part.  Applied on the device (no host
+    // read of the mask), so the call can be captured in a CUDA graph; for the prefix masks the
+    // reference defines (only the popcount is used there, GMM1.h:647-678) the result is the same.
+    const int64_t active = T;
+    if (xActiveMask.has_value() && xActiveMask->defined())
+        ids = at::where(xActiveMask->to(at::kBool).unsqueeze(1), ids, at::full_like(ids, -1)).contiguous();
     const float* smooth = nullptr;
     at::Tensor smooth_t;
     if (scales.has_value() && scales->defined() && quantMode == 2) {
@@ -461,7 +465,7 @@ at::Tensor moe_combine_shmem_cuda(const at::Tensor& expandX, const at::Tensor& e
                                   int64_t moeExpertNum, int64_t tpWorldSize, int64_t tpRankId, int64_t expertShardType,
                                   int64_t sharedExpertNum, int64_t sharedExpertRankNum, int64_t globalBS,
                                   int64_t commQuantMode, int64_t extInfo, int64_t outDtype, int64_t groupListType) {
-    (void)expandIdx; (void)epSendCounts; (void)tpSendCounts; (void)xActiveMask; (void)activationScale;
+    (void)expandIdx; (void)epSendCounts; (void)tpSendCounts; (void)activationScale;
     (void)weightScale; (void)groupList; (void)expandScales; (void)tpRankId; (void)expertShardType;
     (void)sharedExpertNum; (void)globalBS; (void)outDtype; (void)groupListType;
     Buffer* b = buffer_by_id(extInfo);
@@ -483,6 +487,8 @@ at::Tensor moe_combine_shmem_cuda(const at::Tensor& expandX, const at::Tensor& e
         w = rm.weights;
         E = rm.num_virtual_experts;
     }
+    if (xActiveMask.has_value() && xActiveMask->defined())  // masked tokens sent nothing: their pairs are skipped
+        ids = at::where(xActiveMask->to(at::kBool).unsqueeze(1), ids, at::full_like(ids, -1)).contiguous();
     const int is64 = idx_kind(ids, "expertIds");
     const int64_t T = ids.size(0), K = ids.size(1), h = expandX.size(1);
     at::Tensor out = at::empty({T, h}, expandX.options());
@@ -561,12 +567,8 @@ std::vector<at::Tensor> fused_deep_moe_cuda(const at::Tensor& x, const at::Tenso
         w = rm.weights;
         E = rm.num_virtual_experts;
     }
-    if (xActiveMask.has_value() && xActiveMask->defined()) {
-        // prefix mask: tokens past the active count do not take part (GMM1.h:647-678)
-        const int64_t active = xActiveMask->to(at::kLong).sum().item<int64_t>();
-        if (sharedExpertRankNum == 0) ids = expertIds.clone();
-        if (active < T) ids.slice(0, active, T).fill_(-1);
-    }
+    if (xActiveMask.has_value() && xActiveMask->defined())  // applied on the device: no host read, graph-capturable
+        ids = at::where(xActiveMask->to(at::kBool).unsqueeze(1), ids, at::full_like(ids, -1)).contiguous();
     const int is64 = idx_kind(ids, "expertIds");
     const int64_t K = ids.size(1);
     at::Tensor out = at::empty({T, h}, x.options());

@@ -105,6 +105,18 @@ __device__ __forceinline__ void st_na_v2(void* p, const uint2& v) {
                  : "memory");
 }
 
+// Epochs live on the device so that a captured CUDA graph can be replayed: a kernel reads
+// `counter + 1` when it starts and the CTA that leaves last stores that value back.
+// last_cta_out is called by ONE thread of every CTA at the very end of the kernel.
+__device__ __forceinline__ bool last_cta_out(unsigned int* exit_ctr, unsigned int num_ctas) {
+    __threadfence();
+    const unsigned int old = atomicAdd(exit_ctr, 1u);
+    if (old != num_ctas - 1u) return false;
+    *exit_ctr = 0u;
+    __threadfence();
+    return true;
+}
+
 // One warp copies `bytes` (a multiple of 16) of global memory.  Loads are issued four deep before
 // their stores, so a row costs a few memory latencies instead of one per 512 bytes.  COHERENT
 // selects ld.cg for data that a peer GPU wrote during this kernel.

@@ -61,6 +61,7 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineP
     const int gwarp = static_cast<int>(blockIdx.x) * kCombWarps + warp;
     const int nwarps = nb * kCombWarps;
     const int row_bytes = p.h * 2;
+    const uint32_t ep_send = p.epochs[0] + 1u, ep_recv = p.epochs[1] + 1u;
     if (tid == 0) s_abort = 0u;
     __syncthreads();
 
@@ -133,7 +134,7 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineP
                 if (p.dbg_drop_flags == 0) {
                     for (int d = 0; d < p.R; ++d)
                         st_release_sys_u32(
-                            reinterpret_cast<uint32_t*>(p.peer_base[d] + p.off_combine_flag) + p.rank, p.epoch);
+                            reinterpret_cast<uint32_t*>(p.peer_base[d] + p.off_combine_flag) + p.rank, ep_send);
                 }
             }
         }
@@ -144,14 +145,14 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineP
         uint8_t* const my_base = p.peer_base[p.rank];
         if (tid < p.R) {
             const uint32_t* f = reinterpret_cast<const uint32_t*>(my_base + p.off_combine_flag) + tid;
-            if (!wait_flag_eq_sys(f, p.epoch, p.timeout_ns)) {
+            if (!wait_flag_eq_sys(f, ep_recv, p.timeout_ns)) {
                 comb_record_status(p.status, CAM_ERR_TIMEOUT_COMBINE_FLAG, tid,
                                    static_cast<int>(ld_acquire_sys_u32(f)));
                 s_abort = 1u;
             }
         }
         __syncthreads();
-        if (s_abort) return;
+        if (s_abort) goto done;
 
         const uint8_t* buf = my_base + p.off_combine_buf;
         if (p.comm_quant == 2) {
@@ -199,7 +200,7 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineP
                 }
                 __syncwarp();
             }
-            return;
+            goto done;
         }
         // Work item = (token, slice of the row).  With few tokens (decode) a row is cut into as many
         // 512-byte-aligned slices as there are warps to spare, so the whole grid takes part.
@@ -245,6 +246,13 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineP
             }
             __syncwarp();
         }
+    }
+
+done:
+    __syncthreads();
+    if (tid == 0 && last_cta_out(p.exit_ctr, static_cast<unsigned int>(nb))) {
+        if (p.phase_mask & CAM_PHASE_SEND) p.epochs[0] = ep_send;
+        if (p.phase_mask & CAM_PHASE_RECV) p.epochs[1] = ep_recv;
     }
 }
 

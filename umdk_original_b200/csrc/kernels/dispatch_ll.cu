@@ -56,7 +56,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
     const int nwarps = nb * kLLWarps;
     const int E = p.E, R = p.R, K = p.K, El = p.E / p.R;
     const int npairs = p.T * K;
-    const int parity = static_cast<int>(p.epoch & 1u);
+    const uint32_t ep_send = p.epochs[0] + 1u, ep_recv = p.epochs[1] + 1u;
     const int nscale = CAM_QUANT_IS_FP8(p.quant_mode) ? (p.h >> 7)
                        : (p.quant_mode == CAM_QUANT_INT8_TOKEN) ? 1 : 0;
     const int row_bytes = (p.quant_mode == CAM_QUANT_NONE) ? p.h * 2 : p.h;
@@ -73,6 +73,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
 
     // ------------------------------------------------------------------ SEND
     if (p.phase_mask & CAM_PHASE_SEND) {
+        const int parity = static_cast<int>(ep_send & 1u);
         for (int i = tid; i < npairs; i += kLLThreads) {
             int id = ll_expert_id(p.expert_ids, p.idx_is_i64, i);
             if (id < 0 || id >= E || (i / K) >= p.active_tokens) id = -1;
@@ -186,13 +187,14 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
             const size_t cell = static_cast<size_t>(parity) * E + static_cast<size_t>(p.rank) * El + le;
             if (p.dbg_drop_flags == 0)
                 st_release_sys_u64(reinterpret_cast<uint64_t*>(p.peer_base[d] + p.off_ll_cells) + cell,
-                                   (static_cast<uint64_t>(p.epoch) << 32) | static_cast<uint32_t>(cnt));
+                                   (static_cast<uint64_t>(ep_send) << 32) | static_cast<uint32_t>(cnt));
         }
         __syncthreads();
     }
 
     // ------------------------------------------------------------------ RECV
     if (p.phase_mask & CAM_PHASE_RECV) {
+        const int parity = static_cast<int>(ep_recv & 1u);
         uint8_t* const my_base = p.peer_base[p.rank];
         const uint64_t* cells = reinterpret_cast<const uint64_t*>(my_base + p.off_ll_cells) +
                                 static_cast<size_t>(parity) * E;
@@ -200,12 +202,12 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
             const int le = o / R, src = o - le * R;
             const uint64_t* c = cells + static_cast<size_t>(src) * El + le;
             uint64_t v = ld_acquire_sys_u64(c);
-            if (static_cast<uint32_t>(v >> 32) != p.epoch) {
+            if (static_cast<uint32_t>(v >> 32) != ep_recv) {
                 const uint64_t t0 = globaltimer_ns();
                 uint32_t spins = 0;
                 while (true) {
                     v = ld_acquire_sys_u64(c);
-                    if (static_cast<uint32_t>(v >> 32) == p.epoch) break;
+                    if (static_cast<uint32_t>(v >> 32) == ep_recv) break;
                     if ((++spins & 63u) == 0u && globaltimer_ns() - t0 > p.timeout_ns) {
                         ll_record_status(p.status, CAM_ERR_TIMEOUT_LL_CELL, src, le);
                         s_abort = 1u;
@@ -216,7 +218,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
             s_run[o] = static_cast<int>(static_cast<uint32_t>(v));
         }
         __syncthreads();
-        if (s_abort) return;
+        if (s_abort) goto done;
         if (warp == 0) {  // inclusive scan of the counts in (local expert, source) order
             const int per = (E + 31) / 32;
             const int lo = static_cast<int>(lane) * per, hi = min(E, lo + per);
@@ -267,6 +269,13 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
                 p.expand_src[static_cast<size_t>(r) * 3 + lane] = v;
             }
         }
+    }
+
+done:
+    __syncthreads();
+    if (tid == 0 && last_cta_out(p.exit_ctr, static_cast<unsigned int>(nb))) {
+        if (p.phase_mask & CAM_PHASE_SEND) p.epochs[0] = ep_send;
+        if (p.phase_mask & CAM_PHASE_RECV) p.epochs[1] = ep_recv;
     }
 }
 

@@ -50,7 +50,7 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
     __shared__ int s_ids[kDispThreads];
     __shared__ int s_rank_ok[CAM_MAX_RANKS];
     __shared__ uint32_t s_abort;
-    __shared__ uint32_t s_last;
+    __shared__ int s_dup_pre[CAM_MAX_RANKS + 1];
 
     const int tid = static_cast<int>(threadIdx.x);
     const int nb = static_cast<int>(gridDim.x);
@@ -60,13 +60,15 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
     const int t0 = min(p.T, b * tpc);
     const int t1 = min(p.T, t0 + tpc);
     const int npairs = (t1 - t0) * K;
-    const int parity = static_cast<int>(p.epoch & 1u);
+    // epochs of this call, one per phase (equal when a call runs all phases in one launch)
+    const uint32_t ep_count = p.epochs[0] + 1u, ep_send = p.epochs[1] + 1u, ep_recv = p.epochs[2] + 1u;
     uint8_t* const my_base = p.peer_base[p.rank];
 
-    if (tid == 0) { s_abort = 0u; s_last = 0u; }
+    if (tid == 0) s_abort = 0u;
 
     // ------------------------------------------------------------------ phase COUNT
     if (p.phase_mask & CAM_PHASE_COUNT) {
+        const int parity = static_cast<int>(ep_count & 1u);
         for (int e = tid; e < E; e += kDispThreads) s_hist[e] = 0;
         __syncthreads();
         // Slot of every (token, k) pair inside its expert, in scan order, chunk-local first.
@@ -120,7 +122,7 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
             if (tid == 0 && p.dbg_drop_flags == 0) {
                 __threadfence_system();
                 st_release_sys_u32(reinterpret_cast<uint32_t*>(p.peer_base[d] + p.off_count_flag) + p.rank,
-                                   p.epoch);
+                                   ep_count);
             }
         }
         if (p.num_tokens_per_expert_out != nullptr && b == 0) {
@@ -131,15 +133,16 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
 
     // ------------------------------------------------------------------ phase SEND
     if (p.phase_mask & CAM_PHASE_SEND) {
+        const int parity = static_cast<int>(ep_send & 1u);
         if (tid < R) {
             const uint32_t* f = reinterpret_cast<const uint32_t*>(my_base + p.off_count_flag) + tid;
-            if (!wait_flag_eq_sys(f, p.epoch, p.timeout_ns)) {
+            if (!wait_flag_eq_sys(f, ep_send, p.timeout_ns)) {
                 record_status(p.status, CAM_ERR_TIMEOUT_COUNT_FLAG, tid, static_cast<int>(ld_acquire_sys_u32(f)));
                 s_abort = 1u;
             }
         }
         __syncthreads();
-        if (s_abort) return;  // no grid-wide sync follows, so leaving here cannot strand another CTA
+        if (s_abort) goto done;  // no grid-wide sync follows, so leaving here cannot strand another CTA
 
         const int* cm = reinterpret_cast<const int*>(my_base + p.off_count_matrix) +
                         static_cast<size_t>(parity) * R * E;
@@ -301,7 +304,7 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
                 if (p.dbg_drop_flags == 0) {
                     for (int d = 0; d < R; ++d)
                         st_release_sys_u32(reinterpret_cast<uint32_t*>(p.peer_base[d] + p.off_data_flag) + p.rank,
-                                           p.epoch);
+                                           ep_send);
                 }
             }
         }
@@ -309,16 +312,16 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
 
     // ------------------------------------------------------------------ phase RECV
     if (p.phase_mask & CAM_PHASE_RECV) {
-        __shared__ int s_dup_pre[CAM_MAX_RANKS + 1];
+        const int parity = static_cast<int>(ep_recv & 1u);
         if (tid < R) {
             const uint32_t* f = reinterpret_cast<const uint32_t*>(my_base + p.off_data_flag) + tid;
-            if (!wait_flag_eq_sys(f, p.epoch, p.timeout_ns)) {
+            if (!wait_flag_eq_sys(f, ep_recv, p.timeout_ns)) {
                 record_status(p.status, CAM_ERR_TIMEOUT_DATA_FLAG, tid, static_cast<int>(ld_acquire_sys_u32(f)));
                 s_abort = 1u;
             }
         }
         __syncthreads();
-        if (s_abort) return;
+        if (s_abort) goto done;
         // Replicate: rows that several local experts need arrived once; copy them to the other rows.
         if (tid == 0) {
             const uint32_t* cnt = reinterpret_cast<const uint32_t*>(my_base + p.off_dup_cnt) + parity * CAM_MAX_RANKS;
@@ -349,6 +352,15 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
             for (int o = static_cast<int>(lane); o < nscale; o += 32)
                 rs[static_cast<size_t>(to) * nscale + o] = __ldcg(rs + static_cast<size_t>(from) * nscale + o);
         }
+    }
+
+done:
+    // the CTA that leaves last advances the epochs of the phases this launch ran
+    __syncthreads();
+    if (tid == 0 && last_cta_out(p.exit_ctr, static_cast<unsigned int>(nb))) {
+        if (p.phase_mask & CAM_PHASE_COUNT) p.epochs[0] = ep_count;
+        if (p.phase_mask & CAM_PHASE_SEND) p.epochs[1] = ep_send;
+        if (p.phase_mask & CAM_PHASE_RECV) p.epochs[2] = ep_recv;
     }
 }
 

@@ -277,11 +277,13 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         if (old == gridDim.x - 1) {
             p.done_ctr[0] = 0u;
             __threadfence_system();
+            const uint32_t epoch = *p.epoch_send + 1u;  // this launch is the send phase of a combine
             if (p.dbg_drop_flags == 0) {
                 for (int d = 0; d < p.num_ranks; ++d)
                     st_release_sys_u32(reinterpret_cast<uint32_t*>(p.peer_base[d] + p.off_combine_flag) + p.rank,
-                                       p.epoch);
+                                       epoch);
             }
+            *p.epoch_send = epoch;
         }
     }
 }

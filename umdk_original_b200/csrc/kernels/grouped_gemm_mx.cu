@@ -294,24 +294,40 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                                    (static_cast<size_t>(tok) * p.topk + kk) * static_cast<size_t>(p.n_dim);
                     }
                 }
-                // Half a tile (128 columns) at a time goes through shared memory as bf16, and every row
-                // leaves as ONE 256-byte bulk copy (local or over NVLink) instead of 16-byte stores
-                // scattered over 32 rows.  The thread of column quarter 0 issues its row's copy.
+                // Half a tile (128 columns) at a time goes through shared memory as bf16 and leaves as
+                // 256-byte row segments: 16 lanes store one row, so a warp instruction writes two whole
+                // segments (local or over NVLink) instead of 16-byte pieces of 32 different rows.  The row's
+                // destination address travels in the 16 spare bytes at the end of its staging row.
                 uint8_t* srow = stg + r * kMxStgPitch;
                 auto push_half = [&](const uint32_t (&v)[32], int c0) {
-                    if (cq == 0) bulk_wait_group_read<0>();  // the previous copies have read the staging area
-                    named_bar_sync(1, kMxEpiThreads);
+                    if (p.bulk_push && cq == 0) bulk_wait_group_read<0>();  // the previous copies have read the staging area
+                    named_bar_sync(1, kMxEpiThreads);  // the previous half has left the staging area
 #pragma unroll
                     for (int j = 0; j < 32; j += 8)
                         *reinterpret_cast<uint4*>(srow + cq * 64 + j * 2) =
                             pack_bf16x8(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
                                         __uint_as_float(v[j + 3]), __uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]),
                                         __uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
-                    fence_proxy_async_smem();
+                    if (cq == 0)
+                        *reinterpret_cast<uint64_t*>(srow + 256) =
+                            (orow != nullptr) ? reinterpret_cast<uint64_t>(orow + c0) : 0ull;
+                    if (p.bulk_push) {  // alternative: one 256-byte bulk copy per row, issued by the row's first thread
+                        fence_proxy_async_smem();
+                        named_bar_sync(1, kMxEpiThreads);
+                        if (cq == 0) {
+                            if (orow != nullptr) bulk_store_s2g(orow + c0, srow, 256);
+                            bulk_commit_group();
+                        }
+                        return;
+                    }
                     named_bar_sync(1, kMxEpiThreads);
-                    if (cq == 0) {
-                        if (orow != nullptr) bulk_store_s2g(orow + c0, srow, 256);
-                        bulk_commit_group();
+                    const int seg = static_cast<int>(lane & 15u) * 16;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint8_t* src = stg + (ew * 8 + 2 * i + static_cast<int>(lane >> 4)) * kMxStgPitch;
+                        const uint64_t dst = *reinterpret_cast<const uint64_t*>(src + 256);
+                        if (dst != 0ull)
+                            st_na_v4(reinterpret_cast<uint8_t*>(dst) + seg, *reinterpret_cast<const uint4*>(src + seg));
                     }
                 };
                 const int c_lo = nt * BN;
@@ -319,7 +335,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                 if (c_lo + 128 < p.n_dim) push_half(v1, c_lo + 128);  // same answer in every thread of the CTA
             }
         }
-        if (cq == 0) bulk_wait_group<0>();  // every row this thread sent has been written
+        if (p.bulk_push && cq == 0) bulk_wait_group<0>();  // every row this thread sent has been written
         if (!ok) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 2, static_cast<int>(tcount));
     }
 
@@ -336,11 +352,13 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         if (old == gridDim.x - 1) {
             p.done_ctr[0] = 0u;
             __threadfence_system();
+            const uint32_t epoch = *p.epoch_send + 1u;  // this launch is the send phase of a combine
             if (p.dbg_drop_flags == 0) {
                 for (int d = 0; d < p.num_ranks; ++d)
                     st_release_sys_u32(reinterpret_cast<uint32_t*>(p.peer_base[d] + p.off_combine_flag) + p.rank,
-                                       p.epoch);
+                                       epoch);
             }
+            *p.epoch_send = epoch;
         }
     }
 }

@@ -17,7 +17,9 @@ struct DispatchNormalParams {
     int T, K, h, E, R, rank;
     int quant_mode;  // CamQuantMode
     int capacity;    // rows of every rank's receive buffer
-    uint32_t epoch;  // per-buffer call counter; flags carry it, count matrix ping-pongs on its parity
+    uint32_t* epochs;        // device counters [count, send, recv]; a phase uses counter + 1 as its epoch (flags carry
+                             // it, double-buffered regions ping-pong on its parity) and stores it back when the kernel ends
+    unsigned int* exit_ctr;  // [1], self-resetting: finds the CTA that leaves last
     uint64_t timeout_ns;
     int phase_mask;      // CamPhase bits
     int dbg_drop_flags;  // host-side fault injection: this rank withholds its flags
@@ -49,7 +51,8 @@ struct CombineParams {
     __nv_bfloat16* out;         // [T, h]
     int T, K, h, E, R, rank;
     int comm_quant;  // 0: bf16 rows on the wire, 2: int8 rows + one fp32 scale per 128 elements
-    uint32_t epoch;
+    uint32_t* epochs;        // device counters [send, recv]
+    unsigned int* exit_ctr;
     uint64_t timeout_ns;
     int phase_mask;
     int dbg_drop_flags;
@@ -69,7 +72,8 @@ struct DispatchLLParams {
     int quant_mode;
     int max_tokens;          // slab depth per (src, local expert) cell
     int count_type;          // 1 = per-expert counts, 0 = cumulative
-    uint32_t epoch;
+    uint32_t* epochs;        // device counters [send, recv]
+    unsigned int* exit_ctr;
     uint64_t timeout_ns;
     int phase_mask;
     int dbg_drop_flags;
@@ -106,7 +110,8 @@ struct GroupedGemmParams {
     uint8_t* const* peer_base;
     uint64_t off_combine_buf, off_combine_flag;
     int topk, num_ranks, rank;
-    uint32_t epoch;
+    uint32_t* epoch_send;       // device counter of the combine send phase (mode 2 plays that phase)
+    int bulk_push;              // modes 0/2 of the block-scaled kernels: rows leave as bulk copies instead of vector stores
     int dbg_drop_flags;
     unsigned int* done_ctr;
     CamStatus* status;

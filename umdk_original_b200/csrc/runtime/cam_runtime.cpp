@@ -71,7 +71,12 @@ struct CamBuffer {
     CamStatus* h_status = nullptr;  // pinned
     uint8_t* act_q = nullptr;       // [capacity, hidden] scratch between the two GEMMs (sized for I <= hidden)
     float* act_s = nullptr;
-    uint32_t epoch_dispatch = 0, epoch_combine = 0, epoch_ll = 0, epoch_ll_combine = 0;
+    // Epochs live on the device (a kernel reads counter + 1 and its last CTA stores it back), so the
+    // host passes no per-call value and captured CUDA graphs can be replayed.
+    // [0..2] normal dispatch count/send/recv, [3..4] combine send/recv, [5..6] low-latency dispatch
+    // send/recv, [7..8] low-latency combine send/recv.
+    uint32_t* d_epochs = nullptr;     // [16]
+    unsigned int* exit_ctr = nullptr;  // [4]: dispatch, combine, low-latency dispatch, spare
     uint64_t timeout_ns = 10ull * 1000ull * 1000ull * 1000ull;
     int dbg_drop_flags = 0;
     // per-stage device timing of the fused layer (off by default): events around the four launches
@@ -193,6 +198,8 @@ extern "C" CamBuffer* cam_buffer_create(int device, int rank, int num_ranks, con
     ok &= cudaMalloc(&b->num_tokens_per_expert, sizeof(int) * E) == cudaSuccess;
     ok &= cudaMalloc(&b->done_ctr, sizeof(unsigned int) * 4) == cudaSuccess;
     ok &= cudaMalloc(&b->dup_ctr, sizeof(unsigned int) * CAM_MAX_RANKS) == cudaSuccess;
+    ok &= cudaMalloc(&b->d_epochs, sizeof(uint32_t) * 16) == cudaSuccess;
+    ok &= cudaMalloc(&b->exit_ctr, sizeof(unsigned int) * 4) == cudaSuccess;
     ok &= cudaMalloc(&b->d_status, sizeof(CamStatus)) == cudaSuccess;
     ok &= cudaMallocHost(&b->h_status, sizeof(CamStatus)) == cudaSuccess;
     ok &= cudaMalloc(&b->act_q, static_cast<size_t>(layout->capacity) * layout->hidden) == cudaSuccess;
@@ -204,6 +211,8 @@ extern "C" CamBuffer* cam_buffer_create(int device, int rank, int num_ranks, con
     }
     cudaMemset(b->done_ctr, 0, sizeof(unsigned int) * 4);
     cudaMemset(b->dup_ctr, 0, sizeof(unsigned int) * CAM_MAX_RANKS);
+    cudaMemset(b->d_epochs, 0, sizeof(uint32_t) * 16);
+    cudaMemset(b->exit_ctr, 0, sizeof(unsigned int) * 4);
     cudaMemset(b->d_status, 0, sizeof(CamStatus));
     cudaMemset(b->total_recv, 0, sizeof(int) * 4);
     cudaMemset(b->expert_offsets, 0, sizeof(int) * (E + 1));
@@ -221,7 +230,7 @@ extern "C" int cam_buffer_destroy(CamBuffer* b) {
         if (r != b->rank && b->peer_is_ipc[r] && b->peer_ptr[r] != nullptr) cudaIpcCloseMemHandle(b->peer_ptr[r]);
     void* frees[] = {b->base, b->d_peer_table, b->cta_hist, b->slot_in_expert, b->send_row, b->recv_count,
                      b->expert_offsets, b->num_recv_per_expert, b->total_recv, b->num_tokens_per_expert,
-                     b->done_ctr, b->dup_ctr, b->d_status, b->act_q, b->act_s};
+                     b->done_ctr, b->dup_ctr, b->d_epochs, b->exit_ctr, b->d_status, b->act_q, b->act_s};
     for (void* p : frees)
         if (p != nullptr) cudaFree(p);
     if (b->h_status != nullptr) cudaFreeHost(b->h_status);
@@ -282,9 +291,10 @@ extern "C" int cam_buffer_reset(CamBuffer* b, cudaStream_t stream) {
     CAM_CUDA(cudaMemsetAsync(b->base, 0, b->layout.off_recv_x, stream));
     CAM_CUDA(cudaMemsetAsync(b->done_ctr, 0, sizeof(unsigned int) * 4, stream));
     CAM_CUDA(cudaMemsetAsync(b->dup_ctr, 0, sizeof(unsigned int) * CAM_MAX_RANKS, stream));
+    CAM_CUDA(cudaMemsetAsync(b->d_epochs, 0, sizeof(uint32_t) * 16, stream));
+    CAM_CUDA(cudaMemsetAsync(b->exit_ctr, 0, sizeof(unsigned int) * 4, stream));
     CAM_CUDA(cudaMemsetAsync(b->d_status, 0, sizeof(CamStatus), stream));
     CAM_CUDA(cudaStreamSynchronize(stream));
-    b->epoch_dispatch = b->epoch_combine = b->epoch_ll = b->epoch_ll_combine = 0;
     return 0;
 }
 
@@ -335,6 +345,7 @@ extern "C" int cam_buffer_poll_status(CamBuffer* b, cudaStream_t stream, CamStat
         CAM_CUDA(cudaMemsetAsync(b->d_status, 0, sizeof(CamStatus), stream));
         CAM_CUDA(cudaMemsetAsync(b->done_ctr, 0, sizeof(unsigned int) * 4, stream));
         CAM_CUDA(cudaMemsetAsync(b->dup_ctr, 0, sizeof(unsigned int) * CAM_MAX_RANKS, stream));
+        CAM_CUDA(cudaMemsetAsync(b->exit_ctr, 0, sizeof(unsigned int) * 4, stream));
         CAM_CUDA(cudaStreamSynchronize(stream));
     }
     return 0;
@@ -372,7 +383,6 @@ extern "C" int cam_dispatch_normal(CamBuffer* b, const void* x, const void* topk
               "dispatch_normal: quant_mode %d is not one of 0 (bf16), 2 (int8 per token), 3 (fp8 1x128), "
               "4 (fp8 1x128, power-of-two scales)", quant_mode);
     CAM_CUDA(cudaSetDevice(b->device));
-    if (phase_mask & CAM_PHASE_COUNT) ++b->epoch_dispatch;
     cam::DispatchNormalParams p{};
     p.x = static_cast<const __nv_bfloat16*>(x);
     p.topk_idx = topk_idx;
@@ -380,7 +390,8 @@ extern "C" int cam_dispatch_normal(CamBuffer* b, const void* x, const void* topk
     p.T = T; p.K = K; p.h = h; p.E = E; p.R = b->num_ranks; p.rank = b->rank;
     p.quant_mode = quant_mode;
     p.capacity = b->layout.capacity;
-    p.epoch = b->epoch_dispatch;
+    p.epochs = b->d_epochs + 0;
+    p.exit_ctr = b->exit_ctr + 0;
     p.timeout_ns = b->timeout_ns;
     p.phase_mask = phase_mask;
     p.dbg_drop_flags = b->dbg_drop_flags;
@@ -421,8 +432,6 @@ extern "C" int cam_combine(CamBuffer* b, const void* y, const int* row_src, cons
     CAM_CHECK(T <= maxT, "combine: %d tokens exceed the buffer's limit %d", T, maxT);
     CAM_CHECK(comm_quant == 0 || comm_quant == 2, "combine: comm_quant %d must be 0 (bf16) or 2 (int8 per 128)", comm_quant);
     CAM_CUDA(cudaSetDevice(b->device));
-    uint32_t& epoch = low_latency ? b->epoch_ll_combine : b->epoch_combine;
-    if (phase_mask & CAM_PHASE_SEND) ++epoch;
     cam::CombineParams p{};
     p.y = static_cast<const __nv_bfloat16*>(y);
     p.row_src = row_src;
@@ -433,7 +442,8 @@ extern "C" int cam_combine(CamBuffer* b, const void* y, const int* row_src, cons
     p.out = static_cast<__nv_bfloat16*>(out);
     p.T = T; p.K = K; p.h = h; p.E = E; p.R = b->num_ranks; p.rank = b->rank;
     p.comm_quant = comm_quant;
-    p.epoch = epoch;
+    p.epochs = b->d_epochs + (low_latency ? 7 : 3);
+    p.exit_ctr = b->exit_ctr + 1;
     p.timeout_ns = b->timeout_ns;
     p.phase_mask = phase_mask;
     p.dbg_drop_flags = b->dbg_drop_flags;
@@ -460,7 +470,6 @@ extern "C" int cam_dispatch_ll(CamBuffer* b, const void* x, const void* expert_i
               "dispatch_ll: quant_mode %d is not one of 0, 2, 3, 4 (static quantisation, mode 1, is not supported)", quant_mode);
     CAM_CHECK(count_type == 0 || count_type == 1, "dispatch_ll: expertTokenNumsType must be 0 (cumulative) or 1 (counts)");
     CAM_CUDA(cudaSetDevice(b->device));
-    if (phase_mask & CAM_PHASE_SEND) ++b->epoch_ll;
     cam::DispatchLLParams p{};
     p.x = static_cast<const __nv_bfloat16*>(x);
     p.expert_ids = expert_ids;
@@ -471,7 +480,8 @@ extern "C" int cam_dispatch_ll(CamBuffer* b, const void* x, const void* expert_i
     p.quant_mode = quant_mode;
     p.max_tokens = b->layout.ll_max_tokens;
     p.count_type = count_type;
-    p.epoch = b->epoch_ll;
+    p.epochs = b->d_epochs + 5;
+    p.exit_ctr = b->exit_ctr + 2;
     p.timeout_ns = b->timeout_ns;
     p.phase_mask = phase_mask;
     p.dbg_drop_flags = b->dbg_drop_flags;
@@ -610,11 +620,7 @@ static int grouped_gemm_impl(CamBuffer* b, const void* a_q, const float* a_scale
         p.dbg_drop_flags = b->dbg_drop_flags;
         p.done_ctr = b->done_ctr + 2;
         p.status = b->d_status;
-        if (mode == 2) {
-            uint32_t& epoch = low_latency ? b->epoch_ll_combine : b->epoch_combine;
-            ++epoch;
-            p.epoch = epoch;
-        }
+        p.epoch_send = b->d_epochs + (low_latency ? 7 : 3);
     } else {
         if (s_fallback_status == nullptr) {
             CAM_CUDA(cudaMalloc(&s_fallback_status, sizeof(CamStatus)));
@@ -628,6 +634,7 @@ static int grouped_gemm_impl(CamBuffer* b, const void* a_q, const float* a_scale
     p.topk = topk;
     int sms = 0;
     CAM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    if (const char* env = getenv("UMDK_CAM_GEMM_BULK_PUSH")) p.bulk_push = env[0] == '1';
     // CTA pairs (256-row tiles, B tile shared inside the cluster) pay off once experts fill such tiles;
     // UMDK_CAM_GEMM_PAIR=0/1 forces the choice.
     bool pair = ue8m0 && rows_per_expert_hint >= 384;

@@ -198,7 +198,25 @@ def run(args):
                 d = state["d"]
                 state["o"] = ops.moe_combine_prefill(y, idx, w, d[1], d[2], "commbench", rank, world)
 
-        if ll:
+        if ll and args.graph:
+            # one CUDA graph per op (epochs live on the device, so replays stay in step across ranks)
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    disp()
+                    comb()
+            torch.cuda.current_stream().wait_stream(side)
+            _barrier(world)
+            g_disp, g_comb = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_disp):
+                disp()
+            with torch.cuda.graph(g_comb, pool=g_disp.pool()):
+                comb()
+            t_disp, t_comb = _time_ops_queued([g_disp.replay, g_comb.replay], args.iters, args.warmup, world)
+            result["timing"] = ("each op captured in a CUDA graph; CUDA events after every replay, iterations enqueued "
+                                "behind a device spin, max over ranks")
+        elif ll:
             t_disp, t_comb = _time_ops_queued([disp, comb], args.iters, args.warmup, world)
             result["timing"] = ("CUDA events after every op, iterations enqueued behind a device spin so that host "
                                 "launch latency is outside the intervals, max over ranks")
@@ -292,6 +310,7 @@ def main():
     ap.add_argument("--iters", type=int, default=0)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--flush", action="store_true", help="flush L2 before every iteration")
+    ap.add_argument("--graph", action="store_true", help="low-latency mode: replay the ops from CUDA graphs")
     a = ap.parse_args()
     if a.iters <= 0:
         a.iters = 1000 if a.mode == "ll" else 30

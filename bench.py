@@ -40,6 +40,8 @@ def parse_args():
     ap.add_argument("--tokens", type=int, default=0, help="tokens per rank (0 = the model's default)")
     ap.add_argument("--experts", type=int, default=0, help="override the number of routed experts (smaller smoke runs)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--w8a8-exact", action="store_true",
+                    help="W8A8 models: int8 x int8 -> int32 tensor-core path instead of computing in block-scaled fp8")
     return ap.parse_args()
 
 
@@ -103,7 +105,7 @@ def run_ours(args, cfg, rank, world, local):
     tokens = args.tokens or cfg.tokens_per_rank
     group = dist.group.WORLD if world > 1 else None
     buf = make_buffer_for(cfg, group, tokens=tokens, name="bench", device=dev, timeout_ms=20000.0)
-    layer = FusedMoE(cfg, buf, seed=0)
+    layer = FusedMoE(cfg, buf, seed=0, exact_w8a8=args.w8a8_exact)
     sets = make_inputs(cfg, tokens, rank, 4, dev)
 
     def step(i):
@@ -168,6 +170,7 @@ def run_ours(args, cfg, rank, world, local):
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None,
             "dtype": ("fp8_e4m3 block-scaled (fp32 accumulate, bf16 in/out)" if cfg.weight_format != "w8a8" else
+                      "int8 W8A8 (per-token x per-channel scales, int32 accumulate, bf16 in/out)" if args.w8a8_exact else
                       "int8-range weights + per-channel scales computed as fp8_e4m3 block-scaled (fp32 accumulate, bf16 in/out)"),
             "data": "synthetic",
             "impl": "ours",

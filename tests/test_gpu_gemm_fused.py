@@ -213,3 +213,61 @@ def test_fused_moe_shared_expert_rank():
     assert every[PHASE_RECV][1][1].numel() == el
     for b in bufs:
         b.destroy()
+
+
+@pytest.mark.parametrize("counts,n,k", [([128], 256, 128), ([5, 0, 130, 257], 512, 384), ([300, 1, 77], 384, 1024)])
+def test_grouped_gemm_w8a8_exact(counts, n, k):
+    """int8 x int8 -> int32 on the tensor cores: the result is the exact integer product times the scales."""
+    g = torch.Generator().manual_seed(n + k)
+    m = sum(counts)
+    a_q = torch.randint(-127, 128, (m, k), generator=g, dtype=torch.int8)
+    a_s = torch.rand(m, generator=g) * 0.01 + 0.001
+    w_q = torch.randint(-127, 128, (len(counts), n, k), generator=g, dtype=torch.int8)
+    w_s = torch.rand(len(counts), n, generator=g) * 0.003 + 0.0015
+    off = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32)
+    got = ops.grouped_gemm_w8a8(a_q.to(DEV), a_s.to(DEV), w_q.to(DEV), w_s.to(DEV), off.to(DEV)).cpu().float()
+    want = ops.grouped_gemm_w8a8(a_q, a_s, w_q, w_s, off).float()
+    # same integer sum, same two fp32 multiplications, one bf16 rounding
+    assert (got - want).abs().max().item() <= 2 ** -7 * want.abs().max().item()
+    assert ((got - want).abs() > 0).float().mean().item() < 1e-3
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_fused_moe_w8a8_reference_layout(world):
+    """quantMode 0 with int8 weights in the reference's layout ([E_l, h, 2I] / [E_l, I, h], per-channel
+    scales) runs the exact W8A8 path; data recipe of the reference's unit test
+    (test_fused_deep_moe.py:290-319: weights randint(-16, 16), scales rand * 0.003 + 0.0015)."""
+    from umdk_original_b200.models import random_w8a8_experts
+    t, h, inter, e, k = 48, 512, 256, 8, 2
+    g = torch.Generator().manual_seed(300 + world)
+    xs = [(torch.rand(t, h, generator=g) * 10 - 5).to(torch.bfloat16) for _ in range(world)]
+    topk = [torch.stack([torch.randperm(e, generator=g)[:k] for _ in range(t)]) for _ in range(world)]
+    wts = [torch.softmax(torch.randn(t, k, generator=g), -1) for _ in range(world)]
+    w1, s1, w2, s2 = random_w8a8_experts(e, h, inter, seed=7)   # [E, h, 2I], [E, 2I], [E, I, h], [E, h]
+    cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, timeout_ms=3000.0)
+    bufs = u.Buffer.virtual(world, cfg, DEV, name=f"w8_{world}_")
+    el = e // world
+    dev_w = [[v[r * el:(r + 1) * el].contiguous().to(DEV) for v in (w1, s1, w2, s2)] for r in range(world)]
+    dx = [x.to(DEV) for x in xs]
+    dk = [x.to(DEV) for x in topk]
+    dw = [x.to(DEV) for x in wts]
+
+    def step(r):
+        a, b, c, d = dev_w[r]
+        return ops.fused_deep_moe(dx[r], dk[r], [a], [b], [c], [d], dw[r], None, None, bufs[r].name, world, r, e, 0, 0, 0, 0)
+
+    every = run_virtual(step, world, return_all=True)
+    res = every[PHASE_FINAL]
+    for r in range(world):
+        bufs[r].check()
+        rows = torch.zeros(t, k, h, dtype=torch.bfloat16)
+        for ex in range(e):
+            tok, kk = torch.nonzero(topk[r] == ex, as_tuple=True)
+            if tok.numel():
+                rows[tok, kk] = ref.expert_mlp_w8a8(xs[r][tok], w1[ex].t(), s1[ex], w2[ex].t(), s2[ex])
+        want = ref.combine_reference(rows, topk[r], wts[r], e).float()
+        got = res[r][0].cpu().float()
+        # the reference's own gate for this operator is atol 2.0, rtol 0.02; the exact path is much closer
+        assert torch.allclose(got, want, atol=0.02 * want.abs().max().item(), rtol=0.02), (got - want).abs().max()
+    for b in bufs:
+        b.destroy()

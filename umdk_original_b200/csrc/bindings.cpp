@@ -158,6 +158,20 @@ public:
         return c.value;
     }
 
+    // Reference-format int8 weights are [E_local, K, N] (N contiguous); the tensor cores want K
+    // contiguous.  The transposed copy is made once and kept until the tensor changes.
+    at::Tensor k_major(int slot, const at::Tensor& w) {
+        StackCache& c = kmajor_cache_[slot];
+        const bool same = c.value.defined() && c.ptrs.size() == 1 && c.ptrs[0] == w.data_ptr() &&
+                          c.versions[0] == static_cast<int64_t>(w._version());
+        if (!same) {
+            c.value = w.transpose(1, 2).contiguous();
+            c.ptrs = {w.data_ptr()};
+            c.versions = {static_cast<int64_t>(w._version())};
+        }
+        return c.value;
+    }
+
 private:
     struct StackCache {
         at::Tensor value;
@@ -165,6 +179,7 @@ private:
         std::vector<int64_t> versions;
     };
     StackCache stack_cache_[4];
+    StackCache kmajor_cache_[2];
     CamBuffer* buf_ = nullptr;
     CamLayout layout_{};
     int64_t id_ = 0;
@@ -533,8 +548,9 @@ std::vector<at::Tensor> fused_deep_moe_cuda(const at::Tensor& x, const at::Tenso
     check_cuda_contig(expertIds, "expertIds");
     CAM_ASSERT(epRankSize == b->num_ranks() && epRankId == b->rank(), "epRankSize/epRankId do not match the Buffer");
     CAM_ASSERT(sharedExpertRankNum >= 0 && sharedExpertRankNum < epRankSize, "sharedExpertRankNum must be in [0, epRankSize)");
-    CAM_ASSERT(quantMode == 3 || quantMode == 4, "this entry point runs the block-scaled fp8 paths (quantMode 3: fp32 "
-               "scales, 4: power-of-two scales); int8 W8A8 weights are converted by umdk_original_b200.models first");
+    CAM_ASSERT(quantMode == 0 || quantMode == 2 || quantMode == 3 || quantMode == 4,
+               "quantMode must be 0 / 2 (int8 W8A8 weights in the reference's layout), 3 (fp8, fp32 block scales) or "
+               "4 (fp8, power-of-two block scales)");
     CAM_ASSERT(gmm1PermutedWeight.size() >= 1 && gmm2Weight.size() == gmm1PermutedWeight.size() &&
                    gmm1PermutedWeightScale.size() == gmm1PermutedWeight.size() &&
                    gmm2WeightScale.size() == gmm1PermutedWeight.size(),
@@ -548,14 +564,31 @@ std::vector<at::Tensor> fused_deep_moe_cuda(const at::Tensor& x, const at::Tenso
     const bool shared_rank = epRankId < sharedExpertRankNum;
     const int64_t T = x.size(0), h = x.size(1);
     const int64_t El = shared_rank ? 1 : moeExpertNum / (epRankSize - sharedExpertRankNum);
-    CAM_ASSERT(w1.dim() == 3 && w1.size(0) == El && w1.size(2) == h && w1.size(1) % 256 == 0,
-               "gmm1PermutedWeight must be [E_local, 2I, h] with 2I a multiple of 256");
-    const int64_t I = w1.size(1) / 2;
-    CAM_ASSERT(w2.dim() == 3 && w2.size(0) == El && w2.size(1) == h && w2.size(2) == I, "gmm2Weight must be [E_local, h, I]");
-    CAM_ASSERT(w1.scalar_type() == at::kFloat8_e4m3fn && w2.scalar_type() == at::kFloat8_e4m3fn, "weights must be float8_e4m3fn");
-    CAM_ASSERT(s1.scalar_type() == at::kFloat && s1.numel() == El * (2 * I / 128) * (h / 128), "gmm1 scale must be [E_local, 2I/128, h/128] float32");
-    CAM_ASSERT(s2.scalar_type() == at::kFloat && s2.numel() == El * (h / 128) * (I / 128), "gmm2 scale must be [E_local, h/128, I/128] float32");
+    const bool w8a8 = quantMode == 0 || quantMode == 2;
     for (const at::Tensor* t : {&w1, &s1, &w2, &s2}) check_cuda_contig(*t, "weight/scale");
+    int64_t I = 0;
+    at::Tensor w1k, w2k;  // K-major int8 weights of the W8A8 route
+    if (w8a8) {
+        // reference layout (pybind/fused_deep_moe.cpp:26-79): w1 [E_local, h, 2I] int8 + s1 [E_local, 2I],
+        // w2 [E_local, I, h] int8 + s2 [E_local, h]
+        CAM_ASSERT(w1.scalar_type() == at::kChar && w2.scalar_type() == at::kChar, "W8A8 weights must be int8");
+        CAM_ASSERT(w1.dim() == 3 && w1.size(0) == El && w1.size(1) == h && w1.size(2) % 256 == 0,
+                   "gmm1PermutedWeight must be [E_local, h, 2I] int8 with 2I a multiple of 256");
+        I = w1.size(2) / 2;
+        CAM_ASSERT(w2.dim() == 3 && w2.size(0) == El && w2.size(1) == I && w2.size(2) == h, "gmm2Weight must be [E_local, I, h]");
+        CAM_ASSERT(s1.scalar_type() == at::kFloat && s1.numel() == El * 2 * I, "gmm1 scale must be [E_local, 2I] float32");
+        CAM_ASSERT(s2.scalar_type() == at::kFloat && s2.numel() == El * h, "gmm2 scale must be [E_local, h] float32");
+        w1k = b->k_major(0, w1);
+        w2k = b->k_major(1, w2);
+    } else {
+        CAM_ASSERT(w1.dim() == 3 && w1.size(0) == El && w1.size(2) == h && w1.size(1) % 256 == 0,
+                   "gmm1PermutedWeight must be [E_local, 2I, h] with 2I a multiple of 256");
+        I = w1.size(1) / 2;
+        CAM_ASSERT(w2.dim() == 3 && w2.size(0) == El && w2.size(1) == h && w2.size(2) == I, "gmm2Weight must be [E_local, h, I]");
+        CAM_ASSERT(w1.scalar_type() == at::kFloat8_e4m3fn && w2.scalar_type() == at::kFloat8_e4m3fn, "weights must be float8_e4m3fn");
+        CAM_ASSERT(s1.scalar_type() == at::kFloat && s1.numel() == El * (2 * I / 128) * (h / 128), "gmm1 scale must be [E_local, 2I/128, h/128] float32");
+        CAM_ASSERT(s2.scalar_type() == at::kFloat && s2.numel() == El * (h / 128) * (I / 128), "gmm2 scale must be [E_local, h/128, I/128] float32");
+    }
     CAM_ASSERT(expertScales.scalar_type() == at::kFloat, "expertScales must be float32");
     c10::cuda::CUDAGuard guard(x.device());
     at::Tensor ids = expertIds;
@@ -573,9 +606,11 @@ std::vector<at::Tensor> fused_deep_moe_cuda(const at::Tensor& x, const at::Tenso
     const int64_t K = ids.size(1);
     at::Tensor out = at::empty({T, h}, x.options());
     at::Tensor nums = at::zeros({El}, x.options().dtype(at::kLong));
-    auto fused = quantMode == 4 ? &cam_fused_moe_mxfp8 : &cam_fused_moe_fp8;
-    CAM_RT(fused(b->raw(), x.data_ptr(), ids.data_ptr(), is64, w.data_ptr<float>(), w1.data_ptr(), s1.data_ptr<float>(),
-                 w2.data_ptr(), s2.data_ptr<float>(), out.data_ptr(), nums.data_ptr<int64_t>(), static_cast<int>(T),
+    auto fused = w8a8 ? &cam_fused_moe_w8a8 : quantMode == 4 ? &cam_fused_moe_mxfp8 : &cam_fused_moe_fp8;
+    const void* w1p = w8a8 ? w1k.data_ptr() : w1.data_ptr();
+    const void* w2p = w8a8 ? w2k.data_ptr() : w2.data_ptr();
+    CAM_RT(fused(b->raw(), x.data_ptr(), ids.data_ptr(), is64, w.data_ptr<float>(), w1p, s1.data_ptr<float>(),
+                 w2p, s2.data_ptr<float>(), out.data_ptr(), nums.data_ptr<int64_t>(), static_cast<int>(T),
                  static_cast<int>(K), static_cast<int>(h), static_cast<int>(I), static_cast<int>(E),
                  static_cast<int>(El), g_phase_mask, b->stream()));
     return {out, nums};
@@ -635,6 +670,29 @@ std::tuple<at::Tensor, at::Tensor> grouped_gemm_fp8_swiglu_cuda(const at::Tensor
     return {q, s};
 }
 
+// Stand-alone exact W8A8 grouped GEMM: a_q [M, K] int8 + a_s [M], w_q [E, N, K] int8 (K contiguous) + w_s [E, N].
+at::Tensor grouped_gemm_w8a8_cuda(const at::Tensor& a_q, const at::Tensor& a_s, const at::Tensor& w_q,
+                                  const at::Tensor& w_s, const at::Tensor& expert_offsets) {
+    check_cuda_contig(a_q, "a_q");
+    check_cuda_contig(a_s, "a_s");
+    check_cuda_contig(w_q, "w_q");
+    check_cuda_contig(w_s, "w_s");
+    check_cuda_contig(expert_offsets, "expert_offsets");
+    CAM_ASSERT(a_q.dim() == 2 && w_q.dim() == 3 && a_q.size(1) == w_q.size(2), "a_q [M, K], w_q [E, N, K]");
+    CAM_ASSERT(a_q.scalar_type() == at::kChar && w_q.scalar_type() == at::kChar, "operands must be int8");
+    const int64_t M = a_q.size(0), Kd = a_q.size(1), E = w_q.size(0), N = w_q.size(1);
+    CAM_ASSERT(a_s.scalar_type() == at::kFloat && a_s.numel() == M, "a_s must be float32 [M]");
+    CAM_ASSERT(w_s.scalar_type() == at::kFloat && w_s.numel() == E * N, "w_s must be float32 [E, N]");
+    CAM_ASSERT(expert_offsets.scalar_type() == at::kInt && expert_offsets.numel() == E + 1, "expert_offsets must be int32 [E+1]");
+    c10::cuda::CUDAGuard guard(a_q.device());
+    at::Tensor out = at::empty({M, N}, a_q.options().dtype(at::kBFloat16));
+    CAM_RT(cam_grouped_gemm_w8a8(a_q.data_ptr(), a_s.data_ptr<float>(), static_cast<int>(M), w_q.data_ptr(),
+                                 w_s.data_ptr<float>(), expert_offsets.data_ptr<int>(), static_cast<int>(E),
+                                 static_cast<int>(N), static_cast<int>(Kd), out.data_ptr(),
+                                 at::cuda::getCurrentCUDAStream().stream()));
+    return out;
+}
+
 // Autograd-key wrapper: runs below autograd, outputs carry no graph (inference-only op).
 std::vector<at::Tensor> fused_deep_moe_autograd(const at::Tensor& x, const at::Tensor& ids, at::TensorList a,
                                                 at::TensorList b2, at::TensorList c, at::TensorList d,
@@ -680,6 +738,7 @@ TORCH_LIBRARY(umdk_cam_op_lib, m) {
           "bool ue8m0=False) -> Tensor");
     m.def("grouped_gemm_fp8_swiglu(Tensor a_q, Tensor a_s, Tensor w_q, Tensor w_s, Tensor expert_offsets, "
           "bool ue8m0=False) -> (Tensor, Tensor)");
+    m.def("grouped_gemm_w8a8(Tensor a_q, Tensor a_s, Tensor w_q, Tensor w_s, Tensor expert_offsets) -> Tensor");
 }
 
 TORCH_LIBRARY_IMPL(umdk_cam_op_lib, CUDA, m) {
@@ -692,6 +751,7 @@ TORCH_LIBRARY_IMPL(umdk_cam_op_lib, CUDA, m) {
     m.impl("moe_dispatch_prefill_quant", &moe_dispatch_prefill_quant_cuda);
     m.impl("grouped_gemm_fp8", &grouped_gemm_fp8_cuda);
     m.impl("grouped_gemm_fp8_swiglu", &grouped_gemm_fp8_swiglu_cuda);
+    m.impl("grouped_gemm_w8a8", &grouped_gemm_w8a8_cuda);
 }
 
 TORCH_LIBRARY_IMPL(umdk_cam_op_lib, Meta, m) {

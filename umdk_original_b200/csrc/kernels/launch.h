@@ -105,6 +105,9 @@ struct GroupedGemmParams {
     // mode 1
     uint8_t* act_q;             // [a_rows, n_dim/2] e4m3
     float* act_s;               // [a_rows, n_dim/2/128]
+    // mode 1 of the int8 kernel: fp32 SwiGLU output and per-row max |.| (quantised per token afterwards)
+    float* act_f32;             // [a_rows, n_dim/2]
+    float* row_amax;            // [a_rows], zero on entry
     // mode 2
     const int* row_src;         // [a_rows, 3]
     uint8_t* const* peer_base;
@@ -157,4 +160,8 @@ int cam_grouped_gemm_mx_smem_bytes(void);
 int cam_launch_grouped_gemm_mxfp8_pair(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
                                        const CUtensorMap* tmap_b, int grid, cudaStream_t stream);
 int cam_grouped_gemm_mx_pair_smem_bytes(void);
+int cam_launch_grouped_gemm_w8a8(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
+                                 const CUtensorMap* tmap_b, int grid, cudaStream_t stream);
+int cam_launch_rowquant_int8(const float* act, float* row_amax, const int* expert_offsets, int num_experts,
+                             int inter, void* out_q, float* out_s, cudaStream_t stream);
 }

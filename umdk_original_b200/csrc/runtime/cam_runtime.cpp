@@ -71,6 +71,8 @@ struct CamBuffer {
     CamStatus* h_status = nullptr;  // pinned
     uint8_t* act_q = nullptr;       // [capacity, hidden] scratch between the two GEMMs (sized for I <= hidden)
     float* act_s = nullptr;
+    float* act_f32 = nullptr;       // [capacity, hidden] fp32 SwiGLU output of the int8 path (allocated on first use)
+    float* row_amax = nullptr;      // [capacity]
     // Epochs live on the device (a kernel reads counter + 1 and its last CTA stores it back), so the
     // host passes no per-call value and captured CUDA graphs can be replayed.
     // [0..2] normal dispatch count/send/recv, [3..4] combine send/recv, [5..6] low-latency dispatch
@@ -234,6 +236,8 @@ extern "C" int cam_buffer_destroy(CamBuffer* b) {
     for (void* p : frees)
         if (p != nullptr) cudaFree(p);
     if (b->h_status != nullptr) cudaFreeHost(b->h_status);
+    if (b->act_f32 != nullptr) cudaFree(b->act_f32);
+    if (b->row_amax != nullptr) cudaFree(b->row_amax);
     for (auto e : b->prof_ev)
         if (e != nullptr) cudaEventDestroy(e);
     delete b;
@@ -662,6 +666,138 @@ extern "C" int cam_grouped_gemm_mxfp8(CamBuffer* b, const void* a_q, const float
                                       cudaStream_t stream) {
     return grouped_gemm_impl(b, a_q, a_scales, a_rows, w_q, w_scales, expert_offsets, num_experts, n_dim, k_dim, mode,
                              out_bf16, act_q, act_s, row_src, topk, low_latency, true, a_rows / num_experts, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// int8 W8A8 path (exact int32 accumulation)
+// ---------------------------------------------------------------------------------------------
+static int grouped_gemm_w8a8_impl(CamBuffer* b, const void* a_q, const float* a_scales, int a_rows, const void* w_q,
+                                  const float* w_scales, const int* expert_offsets, int num_experts, int n_dim,
+                                  int k_dim, int mode, void* out_bf16, float* act_f32, float* row_amax,
+                                  const int* row_src, int topk, cudaStream_t stream) {
+    CAM_CHECK(a_q && a_scales && w_q && w_scales && expert_offsets, "grouped_gemm_w8a8: null operand");
+    CAM_CHECK(num_experts >= 1 && a_rows >= 1, "grouped_gemm_w8a8: empty problem");
+    CAM_CHECK(k_dim >= 128 && k_dim % 128 == 0, "grouped_gemm_w8a8: K %d must be a multiple of 128", k_dim);
+    CAM_CHECK(mode >= 0 && mode <= 2, "grouped_gemm_w8a8: mode %d", mode);
+    if (mode == 1) {
+        CAM_CHECK(n_dim % 256 == 0 && act_f32 && row_amax, "grouped_gemm_w8a8: mode 1 needs 2I %% 256 == 0 and a workspace");
+    } else {
+        CAM_CHECK(n_dim % 128 == 0, "grouped_gemm_w8a8: N %d must be a multiple of 128", n_dim);
+    }
+    if (mode == 0) CAM_CHECK(out_bf16 != nullptr, "grouped_gemm_w8a8: mode 0 needs an output");
+    if (mode == 2) CAM_CHECK(b != nullptr && row_src != nullptr && topk >= 1, "grouped_gemm_w8a8: mode 2 needs a buffer");
+    int device = 0;
+    if (b != nullptr) {
+        CAM_CUDA(cudaSetDevice(b->device));
+        device = b->device;
+    } else {
+        CAM_CUDA(cudaGetDevice(&device));
+    }
+    CUtensorMap ta, tb;
+    if (make_tmap(b, &ta, a_q, static_cast<uint64_t>(k_dim), static_cast<uint64_t>(a_rows)) != 0) return -1;
+    if (make_tmap(b, &tb, w_q, static_cast<uint64_t>(k_dim), static_cast<uint64_t>(num_experts) * n_dim) != 0) return -1;
+    cam::GroupedGemmParams p{};
+    p.expert_offsets = expert_offsets;
+    p.num_experts = num_experts;
+    p.n_dim = n_dim;
+    p.k_dim = k_dim;
+    p.a_rows = a_rows;
+    p.a_scales = a_scales;
+    p.b_scales = w_scales;
+    p.mode = mode;
+    p.out = static_cast<__nv_bfloat16*>(out_bf16);
+    p.act_f32 = act_f32;
+    p.row_amax = row_amax;
+    p.row_src = row_src;
+    p.topk = topk;
+    static CamStatus* s_status = nullptr;
+    static unsigned int* s_ctr = nullptr;
+    if (b != nullptr) {
+        p.peer_base = b->d_peer_table;
+        p.off_combine_buf = b->layout.off_combine_buf;
+        p.off_combine_flag = b->layout.off_combine_flag;
+        p.num_ranks = b->num_ranks;
+        p.rank = b->rank;
+        p.dbg_drop_flags = b->dbg_drop_flags;
+        p.done_ctr = b->done_ctr + 2;
+        p.status = b->d_status;
+        p.epoch_send = b->d_epochs + 3;
+    } else {
+        if (s_status == nullptr) {
+            CAM_CUDA(cudaMalloc(&s_status, sizeof(CamStatus)));
+            CAM_CUDA(cudaMemset(s_status, 0, sizeof(CamStatus)));
+            CAM_CUDA(cudaMalloc(&s_ctr, sizeof(unsigned int)));
+            CAM_CUDA(cudaMemset(s_ctr, 0, sizeof(unsigned int)));
+        }
+        p.status = s_status;
+        p.done_ctr = s_ctr;
+    }
+    int sms = 0;
+    CAM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    const int rc = cam_launch_grouped_gemm_w8a8(&p, &ta, &tb, sms, stream);
+    CAM_CHECK(rc == 0, "grouped_gemm_w8a8 launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    return 0;
+}
+
+extern "C" int cam_grouped_gemm_w8a8(const void* a_q, const float* a_scales, int a_rows, const void* w_q,
+                                     const float* w_scales, const int* expert_offsets, int num_experts, int n_dim,
+                                     int k_dim, void* out_bf16, cudaStream_t stream) {
+    return grouped_gemm_w8a8_impl(nullptr, a_q, a_scales, a_rows, w_q, w_scales, expert_offsets, num_experts, n_dim,
+                                  k_dim, 0, out_bf16, nullptr, nullptr, nullptr, 1, stream);
+}
+
+extern "C" int cam_fused_moe_w8a8(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,
+                                  const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
+                                  const float* w2_s, void* out, int64_t* expert_token_nums, int T, int K, int h,
+                                  int inter, int E, int gemm_experts, int phase_mask, cudaStream_t stream) {
+    if (check_common(b, T, K, h, E, "fused_moe_w8a8") != 0) return -1;
+    CAM_CHECK(inter >= 128 && inter % 128 == 0 && inter <= b->layout.hidden,
+              "fused_moe_w8a8: intermediate size %d must be a multiple of 128 and <= the buffer's hidden %d", inter, b->layout.hidden);
+    CAM_CHECK(w1_q && w1_s && w2_q && w2_s && topk_weights && out, "fused_moe_w8a8: null operand");
+    const int El = (gemm_experts > 0 && gemm_experts <= E / b->num_ranks) ? gemm_experts : E / b->num_ranks;
+    const CamLayout& L = b->layout;
+    CAM_CUDA(cudaSetDevice(b->device));
+    if (b->act_f32 == nullptr) {  // first use of the int8 path on this buffer
+        CAM_CUDA(cudaMalloc(&b->act_f32, static_cast<size_t>(L.capacity) * L.hidden * sizeof(float)));
+        CAM_CUDA(cudaMalloc(&b->row_amax, static_cast<size_t>(L.capacity) * sizeof(float)));
+        CAM_CUDA(cudaMemset(b->row_amax, 0, static_cast<size_t>(L.capacity) * sizeof(float)));
+    }
+    const bool prof = b->profile && phase_mask == 15;
+    auto stamp = [&](int i) { if (prof) cudaEventRecord(b->prof_ev[i], stream); };
+    stamp(0);
+    if (phase_mask & CAM_PHASE_ALL) {
+        if (cam_dispatch_normal(b, x, expert_ids, idx_is_i64, T, K, h, E, CAM_QUANT_INT8_TOKEN, phase_mask & CAM_PHASE_ALL,
+                                stream) != 0)
+            return -1;
+    }
+    stamp(1);
+    if (phase_mask & CAM_PHASE_RECV) {
+        const uint8_t* recv_x = b->base + L.off_recv_x;
+        const float* recv_s = reinterpret_cast<const float*>(b->base + L.off_recv_scales);
+        const int* recv_src = reinterpret_cast<const int*>(b->base + L.off_recv_src);
+        if (grouped_gemm_w8a8_impl(b, recv_x, recv_s, L.capacity, w1_q, w1_s, b->expert_offsets, El, 2 * inter, h, 1,
+                                   nullptr, b->act_f32, b->row_amax, nullptr, K, stream) != 0)
+            return -1;
+        const int rc = cam_launch_rowquant_int8(b->act_f32, b->row_amax, b->expert_offsets, El, inter, b->act_q, b->act_s,
+                                                stream);
+        CAM_CHECK(rc == 0, "rowquant launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+        stamp(2);
+        if (grouped_gemm_w8a8_impl(b, b->act_q, b->act_s, L.capacity, w2_q, w2_s, b->expert_offsets, El, h, inter, 2,
+                                   nullptr, nullptr, nullptr, recv_src, K, stream) != 0)
+            return -1;
+        if (expert_token_nums != nullptr)
+            CAM_CUDA(cudaMemcpyAsync(expert_token_nums, b->num_recv_per_expert, sizeof(int64_t) * El,
+                                     cudaMemcpyDeviceToDevice, stream));
+    }
+    stamp(3);
+    if (phase_mask & 8) {
+        if (cam_combine(b, nullptr, nullptr, nullptr, expert_ids, idx_is_i64, topk_weights, out, T, K, h, E, 0, 0,
+                        CAM_PHASE_RECV, stream) != 0)
+            return -1;
+    }
+    stamp(4);
+    if (prof) b->profile_valid = true;
+    return 0;
 }
 
 static int fused_moe_impl(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,

@@ -113,6 +113,19 @@ int cam_fused_moe_mxfp8(CamBuffer* b, const void* x_bf16, const void* expert_ids
                         const float* w2_s, void* out_bf16, int64_t* expert_token_nums, int T, int K, int h,
                         int inter, int E, int gemm_experts, int phase_mask, cudaStream_t stream);
 
+// Exact W8A8 (kernels/grouped_gemm_i8.cu): int8 activations [rows, K] with one fp32 scale per row, int8
+// weights [E, N, K] (K contiguous) with one fp32 scale per output channel [E, N], int32 accumulation.
+int cam_grouped_gemm_w8a8(const void* a_q, const float* a_scales, int a_rows, const void* w_q, const float* w_scales,
+                          const int* expert_offsets, int num_experts, int n_dim, int k_dim, void* out_bf16,
+                          cudaStream_t stream);
+// The fused layer in that arithmetic: dispatch with per-token int8 quantisation, GEMM1 -> fp32 SwiGLU +
+// row maxima -> per-token int8 requantisation -> GEMM2 with combine-send epilogue -> reduce.
+// w1_q [E_local, 2I, h], w1_s [E_local, 2I], w2_q [E_local, h, I], w2_s [E_local, h].
+int cam_fused_moe_w8a8(CamBuffer* b, const void* x_bf16, const void* expert_ids, int idx_is_i64,
+                       const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
+                       const float* w2_s, void* out_bf16, int64_t* expert_token_nums, int T, int K, int h, int inter,
+                       int E, int gemm_experts, int phase_mask, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -22,13 +22,19 @@ from .weights import ExpertWeights, from_reference_w8a8, random_fp8_experts, ran
 
 class FusedMoE(torch.nn.Module):
     def __init__(self, cfg: MoEConfig, buffer: Buffer, weights: Optional[ExpertWeights] = None, seed: int = 0,
-                 gate_weight: Optional[torch.Tensor] = None):
+                 gate_weight: Optional[torch.Tensor] = None, exact_w8a8: bool = False):
         super().__init__()
         self.cfg, self.buffer = cfg, buffer
         self.rank, self.num_ranks = buffer.rank, buffer.num_ranks
         assert cfg.num_experts % self.num_ranks == 0
         self.num_local = cfg.num_experts // self.num_ranks
         dev = buffer.device
+        if weights is None and cfg.weight_format == "w8a8" and exact_w8a8:
+            # the reference's own arithmetic: int8 weights [E_l, h, 2I] / [E_l, I, h] with per-channel scales,
+            # per-token int8 activations, int32 accumulation on the tensor cores (quantMode 0)
+            parts = [random_w8a8_experts(min(8, self.num_local - i), cfg.hidden, cfg.intermediate, device=dev,
+                                         seed=seed * 1000 + self.rank * 64 + i) for i in range(0, self.num_local, 8)]
+            weights = ExpertWeights(*[torch.cat([p[j] for p in parts]) for j in range(4)])
         if weights is None and cfg.weight_format == "w8a8":
             # int8-range weights with per-output-channel scales in the reference's layout, computed as
             # block-scaled fp8 (weights in [-16, 16] are exact in e4m3; the channel scales fold into
@@ -43,8 +49,12 @@ class FusedMoE(torch.nn.Module):
             weights = random_fp8_experts(self.num_local, cfg.hidden, cfg.intermediate, device=dev,
                                          seed=seed * 1000 + self.rank)
         self.weights = weights.to(dev)
-        # 4: power-of-two scales -> tcgen05 block-scaled GEMMs; 3: arbitrary fp32 scales
-        self.quant_mode = 4 if self.weights.power_of_two_scales else 3
+        # 0: int8 W8A8 in the reference's layout; 4: fp8 with power-of-two scales -> tcgen05 block-scaled
+        # GEMMs; 3: fp8 with arbitrary fp32 scales
+        if self.weights.w1.dtype == torch.int8:
+            self.quant_mode = 0
+        else:
+            self.quant_mode = 4 if self.weights.power_of_two_scales else 3
         if gate_weight is None:
             g = torch.Generator(device="cpu")
             g.manual_seed(seed + 17)

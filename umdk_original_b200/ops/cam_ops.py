@@ -51,6 +51,7 @@ SCHEMAS = [
     "bool ue8m0=False) -> Tensor",
     "grouped_gemm_fp8_swiglu(Tensor a_q, Tensor a_s, Tensor w_q, Tensor w_s, Tensor expert_offsets, "
     "bool ue8m0=False) -> (Tensor, Tensor)",
+    "grouped_gemm_w8a8(Tensor a_q, Tensor a_s, Tensor w_q, Tensor w_s, Tensor expert_offsets) -> Tensor",
 ]
 
 if _C is None:
@@ -271,6 +272,19 @@ _CPU.impl("moe_dispatch_shmem", _moe_dispatch_shmem_cpu)
 _CPU.impl("moe_combine_shmem", _moe_combine_shmem_cpu)
 _CPU.impl("fused_deep_moe", _fused_deep_moe_cpu)
 _CPU.impl("grouped_gemm_fp8", _grouped_gemm_fp8_cpu)
+def _grouped_gemm_w8a8_cpu(a_q, a_s, w_q, w_s, expert_offsets):
+    """Exact int32 accumulation: out = (a_q @ w_q^T) * a_s[row] * w_s[expert, col]."""
+    out = torch.zeros(a_q.shape[0], w_q.shape[1], dtype=torch.bfloat16)
+    off = expert_offsets.tolist()
+    for e in range(w_q.shape[0]):
+        a, b = off[e], off[e + 1]
+        if b > a:
+            acc = a_q[a:b].double() @ w_q[e].double().t()
+            out[a:b] = (acc.float() * a_s[a:b].float().unsqueeze(-1) * w_s[e].float().unsqueeze(0)).to(torch.bfloat16)
+    return out
+
+
 _CPU.impl("grouped_gemm_fp8_swiglu", _grouped_gemm_fp8_swiglu_cpu)
+_CPU.impl("grouped_gemm_w8a8", _grouped_gemm_w8a8_cpu)
 
 ops = torch.ops.umdk_cam_op_lib

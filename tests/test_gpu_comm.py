@@ -299,3 +299,31 @@ def test_low_latency_shared_expert_ranks(world, shared):
         assert (outs[r].cpu().float() - want.float()).abs().max() == 0.0
     for b in bufs:
         b.destroy()
+
+
+def test_device_barrier_and_its_timeout():
+    """Every rank flags every peer and waits for all of them; a rank that withholds its flags makes
+    the others report a barrier timeout instead of hanging."""
+    world = 4
+    cfg = u.CamConfig(num_experts=8, max_tokens=8, hidden=256, topk=2, timeout_ms=50.0)
+    bufs = u.Buffer.virtual(world, cfg, _dev(), name="bar_")
+    for _ in range(3):
+        run_virtual(lambda r: bufs[r].barrier(), world, masks=(PHASE_SEND, PHASE_RECV))
+        for b in bufs:
+            b.check()
+    bufs[2].inject_drop_flags(True)
+    run_virtual(lambda r: bufs[r].barrier(), world, masks=(PHASE_SEND, PHASE_RECV))
+    with pytest.raises(u.CamError) as ei:
+        bufs[0].check()
+    assert ei.value.code == 7 and ei.value.who == 2
+    for b in bufs:
+        try:
+            b.check()
+        except u.CamError:
+            pass
+        b.inject_drop_flags(False)
+        b.reset()
+    run_virtual(lambda r: bufs[r].barrier(), world, masks=(PHASE_SEND, PHASE_RECV))
+    for b in bufs:
+        b.check()
+        b.destroy()

@@ -93,6 +93,14 @@ def _case(rank, world):
         buf.check()
         want = ref.combine_reference(xs[rank].unsqueeze(1).expand(t, k, h).contiguous(), topk[rank], wts[rank], e)
         assert (out.cpu().float() - want.float()).abs().max() == 0
+    # device barrier across the real GPUs, then flag ping-pong and a peer write between ranks 0 and 1
+    for _ in range(3):
+        buf.barrier()
+    buf.check()
+    if rank < 2:
+        buf.native.p2p_pingpong(1 - rank, 0, 200, rank == 0)
+        buf.native.p2p_write(1 - rank, 512 * 64, 8)
+        buf.check()
     dist.barrier()
     buf.destroy()
     return report

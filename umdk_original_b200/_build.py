@@ -40,6 +40,7 @@ KERNEL_SOURCES = [
     "kernels/grouped_gemm_mx2.cu",
     "kernels/grouped_gemm_i8.cu",
     "kernels/dispatch_noalloc.cu",
+    "kernels/sync_p2p.cu",
     "runtime/cam_runtime.cpp",
 ]
 

@@ -88,6 +88,14 @@ public:
     void reset() { CAM_RT(cam_buffer_reset(buf_, stream())); }
     void set_timeout_ms(double ms) { cam_buffer_set_timeout_ms(buf_, ms); }
     void set_debug_drop_flags(bool on) { cam_buffer_set_debug_drop_flags(buf_, on ? 1 : 0); }
+    void barrier() { CAM_RT(cam_buffer_barrier(buf_, (g_phase_mask & 7) & (CAM_PHASE_SEND | CAM_PHASE_RECV), stream())); }
+    void p2p_write(int64_t peer, int64_t bytes, int64_t grid) {
+        CAM_RT(cam_buffer_p2p_write(buf_, static_cast<int>(peer), static_cast<size_t>(bytes), static_cast<int>(grid), stream()));
+    }
+    void p2p_pingpong(int64_t peer, int64_t base, int64_t iters, bool initiator) {
+        CAM_RT(cam_buffer_p2p_pingpong(buf_, static_cast<int>(peer), static_cast<unsigned int>(base), static_cast<int>(iters),
+                                       initiator ? 1 : 0, stream()));
+    }
     void set_profile(bool on) { CAM_RT(cam_buffer_set_profile(buf_, on ? 1 : 0)); }
     std::vector<double> read_profile() {
         float ms[4];
@@ -788,6 +796,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("reset", &Buffer::reset)
         .def("set_timeout_ms", &Buffer::set_timeout_ms)
         .def("set_debug_drop_flags", &Buffer::set_debug_drop_flags)
+        .def("barrier", &Buffer::barrier)
+        .def("p2p_write", &Buffer::p2p_write)
+        .def("p2p_pingpong", &Buffer::p2p_pingpong)
         .def("set_profile", &Buffer::set_profile)
         .def("read_profile", &Buffer::read_profile)
         .def("poll_status", &Buffer::poll_status)

@@ -162,6 +162,11 @@ int cam_launch_grouped_gemm_mxfp8_pair(const cam::GroupedGemmParams* p, const CU
 int cam_grouped_gemm_mx_pair_smem_bytes(void);
 int cam_launch_grouped_gemm_w8a8(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
                                  const CUtensorMap* tmap_b, int grid, cudaStream_t stream);
+int cam_launch_barrier(uint8_t* const* peer_base, uint64_t off_barrier_flag, uint32_t* epochs, int R, int rank,
+                       int phase_mask, int dbg_drop_flags, uint64_t timeout_ns, CamStatus* status, cudaStream_t stream);
+int cam_launch_p2p_copy(void* dst, const void* src, size_t bytes, int grid, cudaStream_t stream);
+int cam_launch_p2p_pingpong(uint32_t* my_flag, uint32_t* peer_flag, uint32_t base, int iters, int initiator,
+                            uint64_t timeout_ns, CamStatus* status, cudaStream_t stream);
 int cam_launch_rowquant_int8(const float* act, float* row_amax, const int* expert_offsets, int num_experts,
                              int inter, void* out_q, float* out_s, cudaStream_t stream);
 }

@@ -355,6 +355,43 @@ extern "C" int cam_buffer_poll_status(CamBuffer* b, cudaStream_t stream, CamStat
     return 0;
 }
 
+// Device barrier over all ranks of the buffer (epochs [9..10]).  Enqueued on `stream`; returns at once.
+extern "C" int cam_buffer_barrier(CamBuffer* b, int phase_mask, cudaStream_t stream) {
+    CAM_CHECK(b != nullptr, "barrier: null buffer");
+    CAM_CUDA(cudaSetDevice(b->device));
+    const int rc = cam_launch_barrier(b->d_peer_table, b->layout.off_barrier_flag, b->d_epochs + 9, b->num_ranks, b->rank,
+                                      phase_mask, b->dbg_drop_flags, b->timeout_ns, b->d_status, stream);
+    CAM_CHECK(rc == 0, "barrier launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    return 0;
+}
+
+// P2P microbenchmark pieces.  write: copies `bytes` from this rank's receive region into the same
+// region of `peer` with `grid` CTAs (0 = one per SM).  pingpong: `iters` flag round trips with `peer`
+// on the pair's barrier-flag words; `base` must grow by at least `iters` from call to call.
+extern "C" int cam_buffer_p2p_write(CamBuffer* b, int peer, size_t bytes, int grid, cudaStream_t stream) {
+    CAM_CHECK(b != nullptr && peer >= 0 && peer < b->num_ranks, "p2p_write: bad peer");
+    const size_t region = static_cast<size_t>(b->layout.capacity) * b->layout.hidden * 2;
+    CAM_CHECK(bytes > 0 && bytes <= region && bytes % 512 == 0, "p2p_write: bytes must be a multiple of 512 within the receive region (%zu)", region);
+    CAM_CUDA(cudaSetDevice(b->device));
+    const int rc = cam_launch_p2p_copy(b->peer_ptr[peer] + b->layout.off_recv_x, b->base + b->layout.off_recv_x, bytes,
+                                       grid > 0 ? grid : b->num_sms, stream);
+    CAM_CHECK(rc == 0, "p2p_write launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    return 0;
+}
+
+extern "C" int cam_buffer_p2p_pingpong(CamBuffer* b, int peer, unsigned int base, int iters, int initiator,
+                                       cudaStream_t stream) {
+    CAM_CHECK(b != nullptr && peer >= 0 && peer < b->num_ranks && peer != b->rank, "p2p_pingpong: bad peer");
+    CAM_CUDA(cudaSetDevice(b->device));
+    // word CAM_MAX_RANKS - 1 - x of the count-flag array is never used by the ops for groups below that size
+    CAM_CHECK(b->num_ranks < CAM_MAX_RANKS - 1, "p2p_pingpong: group too large");
+    uint32_t* mine = reinterpret_cast<uint32_t*>(b->base + b->layout.off_count_flag) + (CAM_MAX_RANKS - 1);
+    uint32_t* theirs = reinterpret_cast<uint32_t*>(b->peer_ptr[peer] + b->layout.off_count_flag) + (CAM_MAX_RANKS - 1);
+    const int rc = cam_launch_p2p_pingpong(mine, theirs, base, iters, initiator, b->timeout_ns, b->d_status, stream);
+    CAM_CHECK(rc == 0, "p2p_pingpong launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    return 0;
+}
+
 extern "C" int cam_get_dispatch_layout(const void* topk_idx, int idx_is_i64, int T, int K, int E, int R,
                                        int* num_tokens_per_rank, int* num_tokens_per_expert,
                                        uint8_t* is_token_in_rank, cudaStream_t stream) {

@@ -60,6 +60,12 @@ int* cam_buffer_num_tokens_per_expert(CamBuffer* b);
 uint8_t* cam_buffer_act_q(CamBuffer* b);
 float* cam_buffer_act_s(CamBuffer* b);
 
+// Device barrier over all ranks (kernels/sync_p2p.cu); phase_mask CAM_PHASE_SEND | CAM_PHASE_RECV for a real group.
+int cam_buffer_barrier(CamBuffer* b, int phase_mask, cudaStream_t stream);
+// P2P microbenchmark kernels (one-sided write bandwidth, flag round-trip latency).
+int cam_buffer_p2p_write(CamBuffer* b, int peer, size_t bytes, int grid, cudaStream_t stream);
+int cam_buffer_p2p_pingpong(CamBuffer* b, int peer, unsigned int base, int iters, int initiator, cudaStream_t stream);
+
 // get_dispatch_layout: outputs must be zero-initialised by the caller.
 int cam_get_dispatch_layout(const void* topk_idx, int idx_is_i64, int T, int K, int E, int R,
                             int* num_tokens_per_rank, int* num_tokens_per_expert, uint8_t* is_token_in_rank,

@@ -149,6 +149,14 @@ class Buffer:
         else:
             self._cpu.drop_next_send = on
 
+    def barrier(self) -> None:
+        """Device barrier over all ranks of the Buffer, enqueued on the current stream (every rank must
+        call it).  On CPU it is the group's gloo barrier."""
+        if self._native is not None:
+            self._native.barrier()
+        elif self._cpu is not None and self.num_ranks > 1:
+            dist.barrier(group=self.group)
+
     def set_profile(self, on: bool = True) -> None:
         """Per-stage device timing of ``fused_deep_moe`` (CUDA events around its four launches)."""
         if self._native is not None:

@@ -327,3 +327,66 @@ def test_device_barrier_and_its_timeout():
     for b in bufs:
         b.check()
         b.destroy()
+
+
+def test_low_latency_with_tensor_parallel_pair():
+    """EP 2 x TP 2 as four virtual ranks: after dispatch every rank also holds its TP partner's rows
+    (all-gather); before combine the partial outputs are exchanged and added (reduce-scatter)."""
+    from umdk_original_b200.parallel import PHASE_TP_RECV, PHASE_TP_SEND
+    ep, t, h, e, k = 2, 16, 256, 4, 2
+    cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, ll_max_tokens=t, timeout_ms=2000.0)
+    groups = []  # groups[tp][ep_rank]
+    for tp in range(2):
+        groups.append([u.Buffer(None, cfg, name=f"tp{tp}_{r}", device=_dev(), rank=r, num_ranks=ep, tp_world_size=2,
+                                _connect=False) for r in range(ep)])
+        for b in groups[tp]:
+            b._native.set_local_peers([x._native for x in groups[tp]])
+    for r in range(ep):
+        groups[0][r].connect_local_tp_peer(groups[1][r], 0)
+        groups[1][r].connect_local_tp_peer(groups[0][r], 1)
+    flat = [groups[tp][r] for tp in range(2) for r in range(ep)]  # virtual rank v = tp * ep + r
+    g = torch.Generator().manual_seed(123)
+    xs = [torch.randn(t, h, generator=g).to(torch.bfloat16) for _ in flat]
+    topk = [torch.randint(0, e, (t, k), generator=g).to(torch.int32) for _ in flat]
+    wts = [torch.rand(t, k, generator=g) for _ in flat]
+    dx = [x.to(_dev()) for x in xs]
+    dk = [x.to(_dev()) for x in topk]
+    dw = [x.to(_dev()) for x in wts]
+
+    def disp(v):
+        tp, r = divmod(v, ep)
+        return ops.moe_dispatch_shmem(dx[v], dk[v], None, None, ep, r, e, 2, tp, 0, 0, 0, 0, 0, 1, flat[v].handle)
+
+    res = run_virtual(disp, len(flat), masks=(PHASE_SEND, PHASE_RECV, PHASE_TP_SEND, PHASE_TP_RECV))
+    plans = [ref.plan_dispatch([topk[tp * ep + r] for r in range(ep)], e) for tp in range(2)]
+    ys = []
+    for v, b in enumerate(flat):
+        b.check()
+        tp, r = divmod(v, ep)
+        expand, dyn, eidx, nums, ep_cnt, tp_cnt = res[v]
+        own, other = plans[tp][r], plans[1 - tp][r]
+        n, m = own.src.shape[0], other.src.shape[0]
+        assert tp_cnt.cpu().tolist() == ([n, m] if tp == 0 else [m, n])
+        own_rows = torch.stack([xs[tp * ep + s][tt] for s, tt, _ in own.src.tolist()])
+        oth_rows = torch.stack([xs[(1 - tp) * ep + s][tt] for s, tt, _ in other.src.tolist()])
+        assert torch.equal(expand[:n].cpu(), own_rows) and torch.equal(expand[n:n + m].cpu(), oth_rows)
+        # "TP-sharded expert": each TP rank produces a partial output, here (1 + tp) * row for every row it holds
+        y = torch.zeros_like(expand)
+        y[:n + m] = (expand[:n + m].float() * (1.0 + tp)).to(torch.bfloat16)
+        ys.append(y)
+
+    def comb(v):
+        tp, r = divmod(v, ep)
+        expand, dyn, eidx, nums, ep_cnt, tp_cnt = res[v]
+        return ops.moe_combine_shmem(ys[v], dk[v], eidx, ep_cnt, dw[v], tp_cnt, None, None, None, None, None, ep, r, e, 2,
+                                     tp, 0, 0, 0, 0, 0, flat[v].handle, 0, 0)
+
+    outs = run_virtual(comb, len(flat), masks=(PHASE_TP_SEND, PHASE_TP_RECV, PHASE_SEND, PHASE_RECV))
+    for v, b in enumerate(flat):
+        b.check()
+        # both partial outputs of every row: 1 * row + 2 * row
+        rows3 = (xs[v].float() * 1.0).to(torch.bfloat16).float() + (xs[v].float() * 2.0).to(torch.bfloat16).float()
+        want = ref.combine_reference(rows3.to(torch.bfloat16).unsqueeze(1).expand(t, k, h).contiguous(), topk[v], wts[v], e)
+        assert (outs[v].cpu().float() - want.float()).abs().max() == 0.0
+    for b in flat:
+        b.destroy()

@@ -41,6 +41,7 @@ KERNEL_SOURCES = [
     "kernels/grouped_gemm_i8.cu",
     "kernels/dispatch_noalloc.cu",
     "kernels/sync_p2p.cu",
+    "kernels/tp_exchange.cu",
     "runtime/cam_runtime.cpp",
 ]
 

@@ -29,15 +29,17 @@ std::mutex g_reg_mutex;
 std::map<std::string, Buffer*> g_by_name;
 std::map<int64_t, Buffer*> g_by_id;
 int64_t g_next_id = 1;
-int g_phase_mask = 15;  // all phases; the single-GPU virtual-rank harness narrows it
+// all phases; the single-GPU virtual-rank harness narrows it.  Bits: 1 count, 2 send, 4 receive,
+// 8 final reduce of the fused layer, 16 / 32 send / receive of the tensor-parallel pair exchange.
+int g_phase_mask = 63;
 
 class Buffer {
 public:
     Buffer(int64_t device, int64_t rank, int64_t num_ranks, int64_t num_experts, int64_t max_tokens, int64_t hidden,
-           int64_t topk, int64_t capacity, int64_t ll_max_tokens) {
-        CAM_RT(cam_layout_compute(&layout_, static_cast<int>(num_ranks), static_cast<int>(num_experts),
-                                  static_cast<int>(max_tokens), static_cast<int>(hidden), static_cast<int>(topk),
-                                  static_cast<int>(capacity), static_cast<int>(ll_max_tokens)));
+           int64_t topk, int64_t capacity, int64_t ll_max_tokens, int64_t tp_rows) {
+        CAM_RT(cam_layout_compute_tp(&layout_, static_cast<int>(num_ranks), static_cast<int>(num_experts),
+                                     static_cast<int>(max_tokens), static_cast<int>(hidden), static_cast<int>(topk),
+                                     static_cast<int>(capacity), static_cast<int>(ll_max_tokens), static_cast<int>(tp_rows)));
         buf_ = cam_buffer_create(static_cast<int>(device), static_cast<int>(rank), static_cast<int>(num_ranks), &layout_);
         TORCH_CHECK(buf_ != nullptr, "umdk_cam_op_lib: ", cam_last_error());
         std::lock_guard<std::mutex> g(g_reg_mutex);
@@ -85,6 +87,16 @@ public:
         CAM_ASSERT(static_cast<int>(raw.size()) == cam_buffer_num_ranks(buf_), "need one peer per rank");
         CAM_RT(cam_buffer_set_local_peers(buf_, raw.data()));
     }
+    void open_ipc_tp_peer(const std::string& handle, int64_t tp_rank) {
+        CAM_ASSERT(handle.size() == CAM_IPC_HANDLE_BYTES, "bad IPC handle size");
+        CAM_RT(cam_buffer_open_ipc_tp_peer(buf_, handle.data(), static_cast<int>(tp_rank)));
+        has_tp_ = true;
+    }
+    void set_local_tp_peer(Buffer* peer, int64_t tp_rank) {
+        CAM_RT(cam_buffer_set_local_tp_peer(buf_, peer->buf_, static_cast<int>(tp_rank)));
+        has_tp_ = true;
+    }
+    bool has_tp() const { return has_tp_; }
     void reset() { CAM_RT(cam_buffer_reset(buf_, stream())); }
     void set_timeout_ms(double ms) { cam_buffer_set_timeout_ms(buf_, ms); }
     void set_debug_drop_flags(bool on) { cam_buffer_set_debug_drop_flags(buf_, on ? 1 : 0); }
@@ -143,6 +155,10 @@ public:
     int num_ranks() const { return cam_buffer_num_ranks(buf_); }
     // state that low-latency dispatch leaves for the matching combine
     at::Tensor ll_src_, ll_total_;
+    at::Tensor tp_counts_;  // [2] rows per tensor-parallel rank after the all-gather (own rows first)
+    at::Tensor tp_reduced_;  // [rows, h] output of the reduce-scatter that precedes combine
+    at::Tensor tp_rows_, tp_scales_;  // outputs of the last dispatch (the phase-by-phase test harness re-enters with them)
+    bool has_tp_ = false;
 
     // A weight argument given as a list of per-expert tensors (the reference's "tensor list" form for
     // dynamic expert placement, fused_deep_moe_tiling.cpp:83-127) is stacked into one [E_local, ...]
@@ -376,14 +392,16 @@ std::vector<at::Tensor> moe_dispatch_shmem_cuda(const at::Tensor& x, const at::T
                                                 int64_t tpRankId, int64_t expertShardType, int64_t sharedExpertNum,
                                                 int64_t sharedExpertRankNum, int64_t quantMode, int64_t globalBS,
                                                 int64_t expertTokenNumsType, int64_t extInfo) {
-    (void)tpRankId; (void)expertShardType; (void)globalBS; (void)sharedExpertNum;
+    (void)expertShardType; (void)globalBS; (void)sharedExpertNum;
     Buffer* b = buffer_by_id(extInfo);
     CAM_ASSERT(x.dim() == 2 && expertIds.dim() == 2, "x must be [bs, h] and expertIds [bs, k]");
     CAM_ASSERT(x.scalar_type() == at::kBFloat16, "x must be bfloat16");
     check_cuda_contig(x, "x");
     check_cuda_contig(expertIds, "expertIds");
     CAM_ASSERT(epWorldSize == b->num_ranks() && epRankId == b->rank(), "epWorldSize/epRankId do not match the Buffer");
-    CAM_ASSERT(tpWorldSize <= 1, "tpWorldSize > 1 is not supported by this build");
+    CAM_ASSERT(tpWorldSize <= 2 && tpRankId >= 0 && tpRankId < std::max<int64_t>(tpWorldSize, 1),
+               "tpWorldSize must be 1 or 2 (as in the reference) with tpRankId inside it");
+    CAM_ASSERT(tpWorldSize < 2 || b->has_tp(), "tpWorldSize 2 needs a Buffer created with a tensor-parallel partner");
     CAM_ASSERT(quantMode != 1, "static quantisation (quantMode 1) is rejected, as in the reference");
     idx_kind(expertIds, "expertIds");
     c10::cuda::CUDAGuard guard(x.device());
@@ -401,8 +419,9 @@ std::vector<at::Tensor> moe_dispatch_shmem_cuda(const at::Tensor& x, const at::T
     const int is64 = idx_kind(ids, "expertIds");
     const int64_t K = ids.size(1);
     // rows this rank can receive (pybind/moe_dispatch_shmem.cpp:50-62)
-    const int64_t A = std::max<int64_t>(1, shared_rank ? (T * epWorldSize + S - 1) / S
-                                                       : T * epWorldSize * std::min<int64_t>(El, Kuser));
+    const int64_t A1 = std::max<int64_t>(1, shared_rank ? (T * epWorldSize + S - 1) / S
+                                                        : T * epWorldSize * std::min<int64_t>(El, Kuser));
+    const int64_t A = A1 * std::max<int64_t>(tpWorldSize, 1);  // with TP the partner's rows follow this rank's own
     // x_active_mask: tokens whose entry is false do not take part.  Applied on the device (no host
     // read of the mask), so the call can be captured in a CUDA graph; for the prefix masks the
     // reference defines (only the popcount is used there, GMM1.h:647-678) the result is the same.
@@ -430,14 +449,36 @@ std::vector<at::Tensor> moe_dispatch_shmem_cuda(const at::Tensor& x, const at::T
     at::Tensor epSend = at::empty({epWorldSize * El}, x.options().dtype(at::kInt));
     at::Tensor tpSend = at::zeros({std::max<int64_t>(tpWorldSize, 1)}, x.options().dtype(at::kInt));
     at::Tensor total = at::zeros({1}, x.options().dtype(at::kInt));
+    if (g_phase_mask & 6)
     CAM_RT(cam_dispatch_ll(b->raw(), x.data_ptr(), ids.data_ptr(), is64, smooth, static_cast<int>(T),
                            static_cast<int>(K), static_cast<int>(h), static_cast<int>(E),
                            static_cast<int>(active), static_cast<int>(quantMode), static_cast<int>(expertTokenNumsType),
                            expandX.data_ptr(), dynScales.data_ptr<float>(), expandIdx.data_ptr<int>(),
                            expandSrc.data_ptr<int>(), tokenNums.data_ptr<int64_t>(), epSend.data_ptr<int>(),
                            total.data_ptr<int>(), (g_phase_mask & 7) & (CAM_PHASE_SEND | CAM_PHASE_RECV), b->stream()));
-    b->ll_src_ = expandSrc;
-    b->ll_total_ = total;
+    if (g_phase_mask & 6) {
+        b->ll_src_ = expandSrc;
+        b->ll_total_ = total;
+    }
+    if (tpWorldSize == 2) {
+        // all-gather inside the TP pair (moe_dispatch_shmem.h:936-1018): the partner's rows are appended
+        const int tp_mask = ((g_phase_mask & 16) ? CAM_PHASE_SEND : 0) | ((g_phase_mask & 32) ? CAM_PHASE_RECV : 0);
+        if (tp_mask) {
+            at::Tensor rows = (g_phase_mask & 6) ? expandX : b->tp_rows_;
+            at::Tensor sc = (g_phase_mask & 6) ? dynScales : b->tp_scales_;
+            at::Tensor cnt = (g_phase_mask & 6) ? tpSend : b->tp_counts_;
+            CAM_RT(cam_tp_allgather(b->raw(), rows.data_ptr(), quantMode == 0 ? nullptr : sc.data_ptr<float>(),
+                                    static_cast<int>(rows.size(1) * rows.element_size()), static_cast<int>(nscale),
+                                    b->ll_total_.data_ptr<int>(), static_cast<int>(A), cnt.data_ptr<int>(), tp_mask,
+                                    b->stream()));
+            expandX = rows;
+            dynScales = sc;
+            tpSend = cnt;
+        }
+        b->tp_rows_ = expandX;
+        b->tp_scales_ = dynScales;
+        b->tp_counts_ = tpSend;
+    }
     if (S > 0) {
         // reference shapes: expandIdx covers the routed pairs only; a shared rank reports one expert
         expandIdx = expandIdx.view({T, K}).slice(1, 0, Kuser).contiguous().view({T * Kuser});
@@ -496,7 +537,9 @@ at::Tensor moe_combine_shmem_cuda(const at::Tensor& expandX, const at::Tensor& e
     check_cuda_contig(expandX, "expandX");
     check_cuda_contig(expertIds, "expertIds");
     CAM_ASSERT(epWorldSize == b->num_ranks() && epRankId == b->rank(), "epWorldSize/epRankId do not match the Buffer");
-    CAM_ASSERT(tpWorldSize <= 1, "tpWorldSize > 1 is not supported by this build");
+    CAM_ASSERT(tpWorldSize <= 2, "tpWorldSize must be 1 or 2 (as in the reference)");
+    CAM_ASSERT(tpWorldSize < 2 || (b->has_tp() && b->tp_counts_.defined()),
+               "tpWorldSize 2 needs a Buffer with a tensor-parallel partner and a preceding moe_dispatch_shmem");
     CAM_ASSERT(commQuantMode == 0 || commQuantMode == 2, "commQuantMode must be 0 (bf16 rows) or 2 (int8 rows)");
     CAM_ASSERT(b->ll_src_.defined(), "moe_combine_shmem needs a preceding moe_dispatch_shmem on the same Buffer");
     CAM_ASSERT(expertScales.scalar_type() == at::kFloat, "expertScales must be float32");
@@ -514,8 +557,24 @@ at::Tensor moe_combine_shmem_cuda(const at::Tensor& expandX, const at::Tensor& e
         ids = at::where(xActiveMask->to(at::kBool).unsqueeze(1), ids, at::full_like(ids, -1)).contiguous();
     const int is64 = idx_kind(ids, "expertIds");
     const int64_t T = ids.size(0), K = ids.size(1), h = expandX.size(1);
+    at::Tensor y = expandX;
+    if (tpWorldSize == 2) {
+        // reduce-scatter inside the TP pair (moe_combine_shmem.h:438-470): the partner gets the partial outputs of its
+        // rows, this rank adds the partner's partial outputs for its own
+        const int tp_mask = ((g_phase_mask & 16) ? CAM_PHASE_SEND : 0) | ((g_phase_mask & 32) ? CAM_PHASE_RECV : 0);
+        if (!b->tp_reduced_.defined() || b->tp_reduced_.size(0) != expandX.size(0) || b->tp_reduced_.size(1) != h)
+            b->tp_reduced_ = at::empty_like(expandX);
+        if (tp_mask) {
+            at::Tensor cnts = b->tp_counts_;
+            const int me = cam_buffer_tp_rank(b->raw());
+            CAM_RT(cam_tp_reduce_scatter(b->raw(), expandX.data_ptr(), static_cast<int>(h * 2), cnts.data_ptr<int>() + me,
+                                         cnts.data_ptr<int>() + (1 - me), b->tp_reduced_.data_ptr(), tp_mask, b->stream()));
+        }
+        y = b->tp_reduced_;
+    }
     at::Tensor out = at::empty({T, h}, expandX.options());
-    CAM_RT(cam_combine(b->raw(), expandX.data_ptr(), b->ll_src_.data_ptr<int>(), b->ll_total_.data_ptr<int>(),
+    if (g_phase_mask & 6)
+    CAM_RT(cam_combine(b->raw(), y.data_ptr(), b->ll_src_.data_ptr<int>(), b->ll_total_.data_ptr<int>(),
                        ids.data_ptr(), is64, w.data_ptr<float>(), out.data_ptr(), static_cast<int>(T),
                        static_cast<int>(K), static_cast<int>(h), static_cast<int>(E), 1,
                        static_cast<int>(commQuantMode),
@@ -781,9 +840,12 @@ TORCH_LIBRARY_IMPL(umdk_cam_op_lib, Autograd, m) {
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "umdk_cam_op_lib for B200: symmetric Buffer + op registrations";
     py::class_<Buffer>(m, "Buffer")
-        .def(py::init<int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t>(),
+        .def(py::init<int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t>(),
              py::arg("device"), py::arg("rank"), py::arg("num_ranks"), py::arg("num_experts"), py::arg("max_tokens"),
-             py::arg("hidden"), py::arg("topk"), py::arg("capacity"), py::arg("ll_max_tokens") = 0)
+             py::arg("hidden"), py::arg("topk"), py::arg("capacity"), py::arg("ll_max_tokens") = 0,
+             py::arg("tp_rows") = 0)
+        .def("open_ipc_tp_peer", &Buffer::open_ipc_tp_peer)
+        .def("set_local_tp_peer", &Buffer::set_local_tp_peer)
         .def("destroy", &Buffer::destroy)
         .def("register_name", &Buffer::register_name)
         .def_property_readonly("id", &Buffer::id)

@@ -62,7 +62,7 @@ typedef struct CamLayout {
     int32_t topk;             // top-k upper bound
     int32_t capacity;         // rows of the normal-mode receive buffer
     int32_t ll_max_tokens;    // tokens per rank, low-latency mode (0 = no low-latency regions)
-    int32_t reserved;
+    int32_t tp_rows;          // rows of the tensor-parallel exchange region (0 = none)
     uint64_t off_count_flag;    // u32[CAM_MAX_RANKS]
     uint64_t off_data_flag;     // u32[CAM_MAX_RANKS]
     uint64_t off_combine_flag;  // u32[CAM_MAX_RANKS]
@@ -78,6 +78,10 @@ typedef struct CamLayout {
     uint64_t off_ll_scales;     // f32[2][E cells][ll_max_tokens][hidden/128]
     uint64_t off_ll_meta;       // i32[2][E cells][ll_max_tokens][2]
     uint64_t off_ll_combine_buf;  // bf16[ll_max_tokens][topk][hidden]
+    uint64_t off_tp_flag;       // u32[2]: all-gather, reduce-scatter
+    uint64_t off_tp_cnt;        // u32[2]
+    uint64_t off_tp_x;          // u8[tp_rows][hidden*2]
+    uint64_t off_tp_scales;     // f32[tp_rows][hidden/128]
     uint64_t off_dup_cnt;       // u32[2][CAM_MAX_RANKS]: replicate-list lengths per source (normal dispatch)
     uint64_t off_dup_list;      // i32[2][R][max_tokens*topk][2]: (row that arrived, row to copy it to)
     uint64_t total_bytes;

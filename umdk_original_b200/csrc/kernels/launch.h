@@ -120,6 +120,32 @@ struct GroupedGemmParams {
     CamStatus* status;
 };
 
+// Exchange between the two tensor-parallel ranks of one expert-parallel position (kernels/tp_exchange.cu).
+struct TpExchangeParams {
+    int reduce;              // 0: all-gather after dispatch, 1: reduce-scatter before combine
+    const uint8_t* rows;     // all-gather: my received rows; reduce-scatter: partial outputs for [mine | partner's]
+    const float* scales;     // all-gather only, optional [rows, nscale]
+    int row_bytes, nscale;
+    const int* n_own;        // [1] device: rows of my own tokens
+    const int* n_peer;       // [1] device: rows of the partner's tokens (reduce-scatter)
+    int max_rows;            // rows the exchange region holds
+    uint8_t* out;            // all-gather: the same tensor as rows (partner rows appended); reduce-scatter: [n_own, row_bytes]
+    float* scales_out;
+    int out_rows;            // rows `out` can hold
+    int* tp_counts;          // [2] all-gather output: rows per TP rank
+    int tp_rank;
+    uint8_t* my_base;
+    uint8_t* peer_base;      // the partner's symmetric allocation
+    uint64_t off_tp_flag, off_tp_cnt, off_tp_x, off_tp_scales;
+    uint32_t* epochs;        // [send, recv]
+    unsigned int* exit_ctr;
+    unsigned int* done_ctr;
+    uint64_t timeout_ns;
+    int phase_mask;
+    int dbg_drop_flags;
+    CamStatus* status;
+};
+
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) costs microseconds per call; the launchers go
 // through this helper, which remembers per device what it has already set for one kernel.
 struct SmemLimitCache {
@@ -167,6 +193,7 @@ int cam_launch_barrier(uint8_t* const* peer_base, uint64_t off_barrier_flag, uin
 int cam_launch_p2p_copy(void* dst, const void* src, size_t bytes, int grid, cudaStream_t stream);
 int cam_launch_p2p_pingpong(uint32_t* my_flag, uint32_t* peer_flag, uint32_t base, int iters, int initiator,
                             uint64_t timeout_ns, CamStatus* status, cudaStream_t stream);
+int cam_launch_tp_exchange(const cam::TpExchangeParams* p, int grid, cudaStream_t stream);
 int cam_launch_rowquant_int8(const float* act, float* row_amax, const int* expert_offsets, int num_experts,
                              int inter, void* out_q, float* out_s, cudaStream_t stream);
 }

@@ -55,6 +55,9 @@ struct CamBuffer {
     std::vector<uint8_t*> peer_ptr;      // host copy of the peer table
     std::vector<bool> peer_is_ipc;
     uint8_t** d_peer_table = nullptr;    // device copy
+    int tp_rank = 0;                     // position in the tensor-parallel pair
+    uint8_t* tp_peer = nullptr;          // the TP partner's symmetric allocation (null without TP)
+    bool tp_peer_is_ipc = false;
     // workspace (local)
     int grid_dispatch = 0, grid_combine = 0, num_sms = 0;
     int* cta_hist = nullptr;
@@ -106,15 +109,23 @@ extern "C" const char* cam_status_string(int code) {
     }
 }
 
+extern "C" int cam_layout_compute_tp(CamLayout* L, int R, int E, int max_tokens, int hidden, int topk, int capacity,
+                                     int ll_max_tokens, int tp_rows);
+
 extern "C" int cam_layout_compute(CamLayout* L, int R, int E, int max_tokens, int hidden, int topk, int capacity,
                                   int ll_max_tokens) {
+    return cam_layout_compute_tp(L, R, E, max_tokens, hidden, topk, capacity, ll_max_tokens, 0);
+}
+
+extern "C" int cam_layout_compute_tp(CamLayout* L, int R, int E, int max_tokens, int hidden, int topk, int capacity,
+                                     int ll_max_tokens, int tp_rows) {
     CAM_CHECK(L != nullptr, "layout: null output");
     CAM_CHECK(R >= 1 && R <= CAM_MAX_RANKS, "layout: num_ranks %d outside [1, %d]", R, CAM_MAX_RANKS);
     CAM_CHECK(E >= R && E <= CAM_MAX_EXPERTS && E % R == 0, "layout: num_experts %d must be a multiple of num_ranks %d and <= %d",
               E, R, CAM_MAX_EXPERTS);
     CAM_CHECK(topk >= 1 && topk <= CAM_MAX_TOPK, "layout: topk %d outside [1, %d]", topk, CAM_MAX_TOPK);
     CAM_CHECK(hidden >= 128 && hidden % 128 == 0 && hidden <= 16384, "layout: hidden %d must be a multiple of 128 in [128, 16384]", hidden);
-    CAM_CHECK(max_tokens >= 1 && capacity >= 1 && ll_max_tokens >= 0, "layout: bad token counts");
+    CAM_CHECK(max_tokens >= 1 && capacity >= 1 && ll_max_tokens >= 0 && tp_rows >= 0, "layout: bad token counts");
     memset(L, 0, sizeof(*L));
     L->num_ranks = R;
     L->num_experts = E;
@@ -123,6 +134,7 @@ extern "C" int cam_layout_compute(CamLayout* L, int R, int E, int max_tokens, in
     L->topk = topk;
     L->capacity = capacity;
     L->ll_max_tokens = ll_max_tokens;
+    L->tp_rows = tp_rows;
     uint64_t off = 0;
     auto take = [&](uint64_t bytes) {
         uint64_t o = off;
@@ -134,6 +146,8 @@ extern "C" int cam_layout_compute(CamLayout* L, int R, int E, int max_tokens, in
     L->off_combine_flag = take(sizeof(uint32_t) * CAM_MAX_RANKS);
     L->off_barrier_flag = take(sizeof(uint32_t) * CAM_MAX_RANKS);
     L->off_ll_combine_flag = take(sizeof(uint32_t) * CAM_MAX_RANKS);
+    L->off_tp_flag = take(sizeof(uint32_t) * 2);
+    L->off_tp_cnt = take(sizeof(uint32_t) * 2);
     L->off_dup_cnt = take(sizeof(uint32_t) * 2ull * CAM_MAX_RANKS);
     L->off_count_matrix = take(sizeof(int32_t) * 2ull * R * E);
     L->off_ll_cells = take(sizeof(uint64_t) * 2ull * E);
@@ -144,6 +158,10 @@ extern "C" int cam_layout_compute(CamLayout* L, int R, int E, int max_tokens, in
     L->off_recv_src = take(static_cast<uint64_t>(capacity) * 3 * 4);
     L->off_combine_buf = take(static_cast<uint64_t>(max_tokens) * topk * hidden * 2);
     L->off_dup_list = take(2ull * R * static_cast<uint64_t>(max_tokens) * topk * 8);
+    if (tp_rows > 0) {
+        L->off_tp_x = take(static_cast<uint64_t>(tp_rows) * hidden * 2);
+        L->off_tp_scales = take(static_cast<uint64_t>(tp_rows) * (hidden / 128) * 4);
+    }
     if (ll_max_tokens > 0) {
         const uint64_t cells = 2ull * E;
         L->off_ll_x = take(cells * ll_max_tokens * hidden * 2);
@@ -230,6 +248,7 @@ extern "C" int cam_buffer_destroy(CamBuffer* b) {
     cudaDeviceSynchronize();
     for (int r = 0; r < b->num_ranks; ++r)
         if (r != b->rank && b->peer_is_ipc[r] && b->peer_ptr[r] != nullptr) cudaIpcCloseMemHandle(b->peer_ptr[r]);
+    if (b->tp_peer != nullptr && b->tp_peer_is_ipc) cudaIpcCloseMemHandle(b->tp_peer);
     void* frees[] = {b->base, b->d_peer_table, b->cta_hist, b->slot_in_expert, b->send_row, b->recv_count,
                      b->expert_offsets, b->num_recv_per_expert, b->total_recv, b->num_tokens_per_expert,
                      b->done_ctr, b->dup_ctr, b->d_epochs, b->exit_ctr, b->d_status, b->act_q, b->act_s};
@@ -307,6 +326,7 @@ extern "C" const CamLayout* cam_buffer_layout(CamBuffer* b) { return b ? &b->lay
 extern "C" int cam_buffer_rank(CamBuffer* b) { return b ? b->rank : -1; }
 extern "C" int cam_buffer_num_ranks(CamBuffer* b) { return b ? b->num_ranks : -1; }
 extern "C" int cam_buffer_device(CamBuffer* b) { return b ? b->device : -1; }
+extern "C" int cam_buffer_tp_rank(CamBuffer* b) { return b ? b->tp_rank : -1; }
 extern "C" void cam_buffer_set_timeout_ms(CamBuffer* b, double ms) {
     if (b != nullptr && ms > 0) b->timeout_ns = static_cast<uint64_t>(ms * 1e6);
 }
@@ -353,6 +373,84 @@ extern "C" int cam_buffer_poll_status(CamBuffer* b, cudaStream_t stream, CamStat
         CAM_CUDA(cudaStreamSynchronize(stream));
     }
     return 0;
+}
+
+// Tensor-parallel partner (tpWorldSize = 2): the rank at the same expert-parallel position of the other TP group.
+extern "C" int cam_buffer_open_ipc_tp_peer(CamBuffer* b, const void* handle, int tp_rank) {
+    CAM_CHECK(b != nullptr && handle != nullptr && (tp_rank == 0 || tp_rank == 1), "open_ipc_tp_peer: bad argument");
+    CAM_CHECK(b->layout.tp_rows > 0, "open_ipc_tp_peer: the buffer was created without a tensor-parallel region");
+    CAM_CUDA(cudaSetDevice(b->device));
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* p = nullptr;
+    CAM_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    b->tp_peer = static_cast<uint8_t*>(p);
+    b->tp_peer_is_ipc = true;
+    b->tp_rank = tp_rank;
+    return 0;
+}
+
+extern "C" int cam_buffer_set_local_tp_peer(CamBuffer* b, CamBuffer* peer, int tp_rank) {
+    CAM_CHECK(b != nullptr && peer != nullptr && (tp_rank == 0 || tp_rank == 1), "set_local_tp_peer: bad argument");
+    CAM_CHECK(b->layout.tp_rows > 0 && peer->layout.total_bytes == b->layout.total_bytes && peer->device == b->device,
+              "set_local_tp_peer: the partner must be a buffer of the same layout on the same device");
+    b->tp_peer = peer->base;
+    b->tp_peer_is_ipc = false;
+    b->tp_rank = tp_rank;
+    return 0;
+}
+
+static int tp_exchange(CamBuffer* b, int reduce, const void* rows, const float* scales, int row_bytes, int nscale,
+                       const int* n_own, const int* n_peer, void* out, float* scales_out, int out_rows, int* tp_counts,
+                       int phase_mask, cudaStream_t stream) {
+    CAM_CHECK(b != nullptr && b->tp_peer != nullptr, "tp exchange: the buffer has no tensor-parallel partner");
+    CAM_CHECK(row_bytes > 0 && row_bytes % 16 == 0 && row_bytes <= b->layout.hidden * 2, "tp exchange: bad row size %d", row_bytes);
+    CAM_CUDA(cudaSetDevice(b->device));
+    cam::TpExchangeParams p{};
+    p.reduce = reduce;
+    p.rows = static_cast<const uint8_t*>(rows);
+    p.scales = scales;
+    p.row_bytes = row_bytes;
+    p.nscale = nscale;
+    p.n_own = n_own;
+    p.n_peer = n_peer;
+    p.max_rows = b->layout.tp_rows;
+    p.out = static_cast<uint8_t*>(out);
+    p.scales_out = scales_out;
+    p.out_rows = out_rows;
+    p.tp_counts = tp_counts;
+    p.tp_rank = b->tp_rank;
+    p.my_base = b->base;
+    p.peer_base = b->tp_peer;
+    p.off_tp_flag = b->layout.off_tp_flag;
+    p.off_tp_cnt = b->layout.off_tp_cnt;
+    p.off_tp_x = b->layout.off_tp_x;
+    p.off_tp_scales = b->layout.off_tp_scales;
+    p.epochs = b->d_epochs + (reduce ? 13 : 11);
+    p.exit_ctr = b->exit_ctr + 3;
+    p.done_ctr = b->done_ctr + 3;
+    p.timeout_ns = b->timeout_ns;
+    p.phase_mask = phase_mask;
+    p.dbg_drop_flags = b->dbg_drop_flags;
+    p.status = b->d_status;
+    const int rc = cam_launch_tp_exchange(&p, b->num_sms, stream);
+    CAM_CHECK(rc == 0, "tp exchange launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    return 0;
+}
+
+// After low-latency dispatch: appends the TP partner's received rows (and scales) behind this rank's own
+// n_own rows in `rows` / `scales` (which must hold out_rows rows) and writes the two counts.
+extern "C" int cam_tp_allgather(CamBuffer* b, void* rows, float* scales, int row_bytes, int nscale, const int* n_own,
+                                int out_rows, int* tp_counts, int phase_mask, cudaStream_t stream) {
+    return tp_exchange(b, 0, rows, scales, row_bytes, nscale, n_own, n_own, rows, scales, out_rows, tp_counts, phase_mask,
+                       stream);
+}
+
+// Before combine: y holds partial outputs for [my n_own rows | the partner's n_peer rows]; sends the
+// partner its rows, adds what the partner sends for mine, result in out [n_own rows].
+extern "C" int cam_tp_reduce_scatter(CamBuffer* b, const void* y, int row_bytes, const int* n_own, const int* n_peer,
+                                     void* out, int phase_mask, cudaStream_t stream) {
+    return tp_exchange(b, 1, y, nullptr, row_bytes, 0, n_own, n_peer, out, nullptr, 0, nullptr, phase_mask, stream);
 }
 
 // Device barrier over all ranks of the buffer (epochs [9..10]).  Enqueued on `stream`; returns at once.

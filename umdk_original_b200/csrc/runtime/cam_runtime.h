@@ -26,6 +26,10 @@ const char* cam_status_string(int code);
 int cam_layout_compute(CamLayout* out, int num_ranks, int num_experts, int max_tokens, int hidden, int topk,
                        int capacity, int ll_max_tokens);
 
+// Same with a tensor-parallel exchange region of tp_rows rows (tpWorldSize = 2 in the low-latency ops).
+int cam_layout_compute_tp(CamLayout* out, int num_ranks, int num_experts, int max_tokens, int hidden, int topk,
+                          int capacity, int ll_max_tokens, int tp_rows);
+
 // Creates the symmetric allocation (cudaMalloc, so that it can be exported with CUDA IPC), the
 // local workspace and the status word on `device`.  Returns NULL on failure.
 CamBuffer* cam_buffer_create(int device, int rank, int num_ranks, const CamLayout* layout);
@@ -35,12 +39,20 @@ int cam_buffer_ipc_handle(CamBuffer* b, void* out_handle /* CAM_IPC_HANDLE_BYTES
 int cam_buffer_open_ipc_peers(CamBuffer* b, const void* handles);
 // Single-process virtual ranks: every rank is a CamBuffer of this process on the same device.
 int cam_buffer_set_local_peers(CamBuffer* b, CamBuffer* const* peers);
+// Tensor-parallel partner of this rank (the same expert-parallel position in the other TP group).
+int cam_buffer_open_ipc_tp_peer(CamBuffer* b, const void* handle, int tp_rank);
+int cam_buffer_set_local_tp_peer(CamBuffer* b, CamBuffer* peer, int tp_rank);
+int cam_tp_allgather(CamBuffer* b, void* rows, float* scales, int row_bytes, int nscale, const int* n_own, int out_rows,
+                     int* tp_counts, int phase_mask, cudaStream_t stream);
+int cam_tp_reduce_scatter(CamBuffer* b, const void* y, int row_bytes, const int* n_own, const int* n_peer, void* out,
+                          int phase_mask, cudaStream_t stream);
 int cam_buffer_reset(CamBuffer* b, cudaStream_t stream);
 void* cam_buffer_base(CamBuffer* b);
 const CamLayout* cam_buffer_layout(CamBuffer* b);
 int cam_buffer_rank(CamBuffer* b);
 int cam_buffer_num_ranks(CamBuffer* b);
 int cam_buffer_device(CamBuffer* b);
+int cam_buffer_tp_rank(CamBuffer* b);
 void cam_buffer_set_timeout_ms(CamBuffer* b, double ms);
 void cam_buffer_set_debug_drop_flags(CamBuffer* b, int on);
 // Per-stage device timing of the fused layer.  While on, every full fused call records CUDA events

@@ -33,14 +33,19 @@ from .gloo_backend import CpuGroup
 log = get_logger("umdk_cam.buffer")
 
 PHASE_COUNT, PHASE_SEND, PHASE_RECV, PHASE_FINAL = 1, 2, 4, 8
-PHASE_ALL = 15
+PHASE_TP_SEND, PHASE_TP_RECV = 16, 32   # exchange inside a tensor-parallel pair (tpWorldSize = 2)
+PHASE_ALL = 63
 _AUTO = [0]
 
 
 class Buffer:
     def __init__(self, group=None, config: Optional[CamConfig] = None, *, name: Optional[str] = None,
                  device: Optional[torch.device] = None, rank: Optional[int] = None, num_ranks: Optional[int] = None,
-                 _connect: bool = True):
+                 tp_group=None, tp_world_size: int = 1, _connect: bool = True):
+        """``group`` is the expert-parallel group.  ``tp_group`` (two ranks: this one and the rank at the
+        same expert-parallel position of the other tensor-parallel group) enables ``tpWorldSize=2`` in the
+        low-latency ops; ``tp_world_size=2`` without a group only reserves the exchange region (the
+        single-process test harness then connects partners with ``connect_local_tp_peer``)."""
         self.config = config or CamConfig.from_env()
         self.group = group
         if rank is None:
@@ -61,13 +66,19 @@ class Buffer:
         self.capacity = cfg.resolve_capacity(self.num_ranks)
         if self.device.type == "cuda":
             C = cam_ops.native_module()
+            tp_rows = 0
+            if tp_group is not None or tp_world_size == 2:
+                el = cfg.num_experts // self.num_ranks
+                tp_rows = max(1, cfg.ll_max_tokens * self.num_ranks * min(el, cfg.topk))
             self._native = C.Buffer(self.device.index or 0, self.rank, self.num_ranks, cfg.num_experts, cfg.max_tokens,
-                                    cfg.hidden, cfg.topk, self.capacity, cfg.ll_max_tokens)
+                                    cfg.hidden, cfg.topk, self.capacity, cfg.ll_max_tokens, tp_rows)
             self._native.set_timeout_ms(cfg.timeout_ms)
             self._native.register_name(self.name)
             self.handle = int(self._native.id)
             if _connect:
                 self._connect_ipc()
+                if tp_group is not None:
+                    self._connect_tp(tp_group)
         else:
             self._cpu = CpuGroup(group, self.rank, self.num_ranks, cfg.num_experts)
             self.handle = registry.register(self._cpu, self.name)
@@ -83,6 +94,20 @@ class Buffer:
         dist.all_gather_object(handles, self._native.ipc_handle(), group=self.group)
         self._native.open_ipc_peers([bytes(h) for h in handles])
         dist.barrier(group=self.group)
+
+    def _connect_tp(self, tp_group) -> None:
+        assert dist.get_world_size(tp_group) == 2, "tensor parallelism inside the ops is limited to 2 ranks"
+        tp_rank = dist.get_rank(tp_group)
+        handles: List[Optional[bytes]] = [None, None]
+        dist.all_gather_object(handles, self._native.ipc_handle(), group=tp_group)
+        self._native.open_ipc_tp_peer(bytes(handles[1 - tp_rank]), tp_rank)
+        self.tp_rank = tp_rank
+        dist.barrier(group=tp_group)
+
+    def connect_local_tp_peer(self, partner: "Buffer", tp_rank: int) -> None:
+        """Single-process harness: the partner is another Buffer of this process on the same GPU."""
+        self._native.set_local_tp_peer(partner._native, tp_rank)
+        self.tp_rank = tp_rank
 
     @classmethod
     def virtual(cls, num_ranks: int, config: CamConfig, device: Optional[torch.device] = None,

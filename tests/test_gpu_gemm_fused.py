@@ -271,3 +271,20 @@ def test_fused_moe_w8a8_reference_layout(world):
         assert torch.allclose(got, want, atol=0.02 * want.abs().max().item(), rtol=0.02), (got - want).abs().max()
     for b in bufs:
         b.destroy()
+
+
+def test_fused_layer_stage_profile():
+    """Buffer.set_profile() records events around the four launches of a full fused call."""
+    t, h, inter, e, k = 32, 256, 128, 4, 2
+    xs, topk, wts, (w1q, s1, w2q, s2) = _fused_case(1, t, h, inter, e, k, seed=11, ue8m0=True)
+    cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, timeout_ms=3000.0)
+    buf = u.Buffer(None, cfg, name="prof", device=DEV, rank=0, num_ranks=1)
+    w = ExpertWeights(w1q, s1, w2q, s2).to(DEV)
+    buf.set_profile(True)
+    ops.fused_deep_moe(xs[0].to(DEV), topk[0].to(DEV), [w.w1], [w.s1], [w.w2], [w.s2], wts[0].to(DEV), None, None, "prof",
+                       1, 0, e, 0, 0, 4, 0)
+    parts = buf.read_profile()
+    assert set(parts) == {"dispatch_ms", "gemm1_ms", "gemm2_send_ms", "combine_ms"} and all(v > 0 for v in parts.values())
+    buf.set_profile(False)
+    buf.check()
+    buf.destroy()

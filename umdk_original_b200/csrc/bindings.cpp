@@ -679,7 +679,7 @@ std::vector<at::Tensor> fused_deep_moe_cuda(const at::Tensor& x, const at::Tenso
     CAM_RT(fused(b->raw(), x.data_ptr(), ids.data_ptr(), is64, w.data_ptr<float>(), w1p, s1.data_ptr<float>(),
                  w2p, s2.data_ptr<float>(), out.data_ptr(), nums.data_ptr<int64_t>(), static_cast<int>(T),
                  static_cast<int>(K), static_cast<int>(h), static_cast<int>(I), static_cast<int>(E),
-                 static_cast<int>(El), g_phase_mask, b->stream()));
+                 static_cast<int>(El), g_phase_mask & 15, b->stream()));
     return {out, nums};
 }
 

@@ -773,6 +773,9 @@ static int grouped_gemm_impl(CamBuffer* b, const void* a_q, const float* a_scale
     p.topk = topk;
     int sms = 0;
     CAM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    // rows leave the GEMM2 epilogue as 256-byte bulk copies (measured a few percent ahead of vector stores at 2 and 4
+    // GPUs); UMDK_CAM_GEMM_BULK_PUSH=0 selects the vector-store form
+    p.bulk_push = 1;
     if (const char* env = getenv("UMDK_CAM_GEMM_BULK_PUSH")) p.bulk_push = env[0] == '1';
     // CTA pairs (256-row tiles, B tile shared inside the cluster) pay off once experts fill such tiles;
     // UMDK_CAM_GEMM_PAIR=0/1 forces the choice.

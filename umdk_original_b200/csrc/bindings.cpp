@@ -108,6 +108,12 @@ public:
         CAM_RT(cam_buffer_p2p_pingpong(buf_, static_cast<int>(peer), static_cast<unsigned int>(base), static_cast<int>(iters),
                                        initiator ? 1 : 0, stream()));
     }
+    void set_trace(bool on) { CAM_RT(cam_buffer_set_trace(buf_, on ? 1 : 0)); }
+    std::vector<int64_t> read_trace() {
+        unsigned long long t[16];
+        CAM_RT(cam_buffer_read_trace(buf_, t));
+        return std::vector<int64_t>(t, t + 16);
+    }
     void set_profile(bool on) { CAM_RT(cam_buffer_set_profile(buf_, on ? 1 : 0)); }
     std::vector<double> read_profile() {
         float ms[4];
@@ -861,6 +867,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("barrier", &Buffer::barrier)
         .def("p2p_write", &Buffer::p2p_write)
         .def("p2p_pingpong", &Buffer::p2p_pingpong)
+        .def("set_trace", &Buffer::set_trace)
+        .def("read_trace", &Buffer::read_trace)
         .def("set_profile", &Buffer::set_profile)
         .def("read_profile", &Buffer::read_profile)
         .def("poll_status", &Buffer::poll_status)

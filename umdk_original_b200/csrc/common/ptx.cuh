@@ -105,6 +105,13 @@ __device__ __forceinline__ void st_na_v2(void* p, const uint2& v) {
                  : "memory");
 }
 
+// Optional in-kernel trace: when `trace` is not null, thread 0 of CTA 0 stores %globaltimer (ns) at the
+// numbered points of a kernel; the host turns the differences into a per-phase timeline
+// (Buffer.set_trace / read_trace).  Costs one predicated branch per point when off.
+__device__ __forceinline__ void trace_point(unsigned long long* trace, int slot) {
+    if (trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) trace[slot] = globaltimer_ns();
+}
+
 // Epochs live on the device so that a captured CUDA graph can be replayed: a kernel reads
 // `counter + 1` when it starts and the CTA that leaves last stores that value back.
 // last_cta_out is called by ONE thread of every CTA at the very end of the kernel.
@@ -117,25 +124,20 @@ __device__ __forceinline__ bool last_cta_out(unsigned int* exit_ctr, unsigned in
     return true;
 }
 
-// One warp copies `bytes` (a multiple of 16) of global memory.  Loads are issued four deep before
-// their stores, so a row costs a few memory latencies instead of one per 512 bytes.  COHERENT
+// One warp copies `bytes` (a multiple of 16) of global memory.  Loads are issued eight deep before
+// their stores, so a 7 KB row costs two memory latencies instead of one per 512 bytes.  COHERENT
 // selects ld.cg for data that a peer GPU wrote during this kernel.
 template <bool COHERENT>
 __device__ __forceinline__ void warp_copy_row(uint8_t* dst, const uint8_t* src, int bytes, uint32_t lane) {
-    int o = static_cast<int>(lane) * 16;
-    for (; o + 3 * 512 < bytes; o += 4 * 512) {
-        uint4 a, b, c, d;
-        if (COHERENT) {
-            a = ld_cg_v4(src + o); b = ld_cg_v4(src + o + 512); c = ld_cg_v4(src + o + 1024); d = ld_cg_v4(src + o + 1536);
-        } else {
-            a = ld_nc_v4(src + o); b = ld_nc_v4(src + o + 512); c = ld_nc_v4(src + o + 1024); d = ld_nc_v4(src + o + 1536);
-        }
-        st_na_v4(dst + o, a);
-        st_na_v4(dst + o + 512, b);
-        st_na_v4(dst + o + 1024, c);
-        st_na_v4(dst + o + 1536, d);
+    for (int o = static_cast<int>(lane) * 16; o < bytes; o += 8 * 512) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (o + u * 512 < bytes) v[u] = COHERENT ? ld_cg_v4(src + o + u * 512) : ld_nc_v4(src + o + u * 512);
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (o + u * 512 < bytes) st_na_v4(dst + o + u * 512, v[u]);
     }
-    for (; o < bytes; o += 512) st_na_v4(dst + o, COHERENT ? ld_cg_v4(src + o) : ld_nc_v4(src + o));
 }
 
 // Spin until *p == want (acquire, system scope).  Returns false when the budget runs out.

@@ -65,6 +65,7 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineP
     if (tid == 0) s_abort = 0u;
     __syncthreads();
 
+    trace_point(p.trace, 0);  // kernel start
     // ------------------------------------------------------------------ SEND
     if (p.phase_mask & CAM_PHASE_SEND) {
         const int n = p.total_rows[0];
@@ -125,8 +126,10 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineP
             for (; o < row_bytes; o += 512) st_na_v4(d + o, ld_nc_v4(s + o));
         }
         __syncthreads();
+        trace_point(p.trace, 1);  // this CTA's rows are issued
         if (tid == 0) {
             __threadfence_system();
+            if (p.trace != nullptr && blockIdx.x == 0) p.trace[2] = globaltimer_ns();  // system fence done
             const unsigned int old = atomicAdd(p.done_ctr, 1u);
             if (old == static_cast<unsigned int>(nb - 1)) {
                 p.done_ctr[0] = 0u;
@@ -152,6 +155,7 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineP
             }
         }
         __syncthreads();
+        trace_point(p.trace, 3);  // all sources' flags have arrived
         if (s_abort) goto done;
 
         const uint8_t* buf = my_base + p.off_combine_buf;
@@ -250,7 +254,9 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineP
 
 done:
     __syncthreads();
+    trace_point(p.trace, 4);  // CTA 0 reduced its tokens
     if (tid == 0 && last_cta_out(p.exit_ctr, static_cast<unsigned int>(nb))) {
+        if (p.trace != nullptr) p.trace[5] = globaltimer_ns();  // the last CTA leaves
         if (p.phase_mask & CAM_PHASE_SEND) p.epochs[0] = ep_send;
         if (p.phase_mask & CAM_PHASE_RECV) p.epochs[1] = ep_recv;
     }

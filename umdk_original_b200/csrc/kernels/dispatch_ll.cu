@@ -72,6 +72,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
     if (tid == 0) s_abort = 0u;
 
     // ------------------------------------------------------------------ SEND
+    trace_point(p.trace, 0);  // kernel start
     if (p.phase_mask & CAM_PHASE_SEND) {
         const int parity = static_cast<int>(ep_send & 1u);
         for (int i = tid; i < npairs; i += kLLThreads) {
@@ -81,10 +82,45 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
         }
         for (int e = tid; e < E; e += kLLThreads) s_run[e] = 0;
         __syncthreads();
-        // Slot of every pair inside its expert, in scan order: one warp walks the pairs 32 at a time;
-        // lanes with the same expert find each other with match.any, the lowest of them advances the
-        // expert's running count.
-        if (warp == 0) {
+        // Slot of every pair inside its expert, in scan order.  Lanes of a 32-pair chunk that share an
+        // expert find each other with match.any, which gives the rank inside the chunk and the chunk's
+        // count for that expert.  Fast path (the chunk x expert table fits in shared memory): all warps
+        // take chunks in parallel, one thread per expert turns the counts into exclusive prefixes over
+        // the chunks, and a last pass adds them.  Otherwise one warp walks the chunks in order.
+        if (p.slot_table_bytes > 0) {
+            uint16_t* tab = reinterpret_cast<uint16_t*>(stage0 + stage_bytes);  // [chunks][E]
+            const int nchunks = (npairs + 31) >> 5;
+            for (int o = tid * 8; o < nchunks * E; o += kLLThreads * 8)  // table bytes are a multiple of 16
+                *reinterpret_cast<uint4*>(tab + o) = make_uint4(0, 0, 0, 0);
+            __syncthreads();
+            for (int c = warp; c < nchunks; c += kLLWarps) {
+                const int i = c * 32 + static_cast<int>(lane);
+                const int id = (i < npairs) ? s_ids[i] : -1;
+                const uint32_t peers = __match_any_sync(0xFFFFFFFFu, id);
+                const int before = __popc(peers & ((1u << lane) - 1u));
+                if (id >= 0) {
+                    s_slot[i] = before;
+                    if (before == 0) tab[c * E + id] = static_cast<uint16_t>(__popc(peers));
+                } else if (i < npairs) {
+                    s_slot[i] = -1;
+                }
+            }
+            __syncthreads();
+            for (int e = tid; e < E; e += kLLThreads) {
+                int run = 0;
+                for (int c = 0; c < nchunks; ++c) {
+                    const int v = tab[c * E + e];
+                    tab[c * E + e] = static_cast<uint16_t>(run);
+                    run += v;
+                }
+                s_run[e] = run;
+            }
+            __syncthreads();
+            for (int i = tid; i < npairs; i += kLLThreads) {
+                const int id = s_ids[i];
+                if (id >= 0) s_slot[i] += tab[(i >> 5) * E + id];
+            }
+        } else if (warp == 0) {
             for (int c = 0; c < npairs; c += 32) {
                 const int i = c + static_cast<int>(lane);
                 const int id = (i < npairs) ? s_ids[i] : -1;
@@ -102,6 +138,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
         __syncthreads();
         if (blockIdx.x == 0)
             for (int i = tid; i < npairs; i += kLLThreads) p.expand_idx[i] = s_slot[i];
+        trace_point(p.trace, 1);  // slot table done
 
         if (p.quant_mode != CAM_QUANT_INT8_TOKEN) {
             // Token-major: the CTA quantises a token once (all threads load together, so a row costs one
@@ -174,8 +211,14 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
                 }
             }
         }
-        __threadfence_system();   // this thread's rows are visible to every GPU before the barrier
+        trace_point(p.trace, 2);  // this CTA's rows are issued
+        // every row of this CTA is visible to every GPU before the barrier: the CTA barrier orders the
+        // other threads' stores before thread 0's fence, which is cumulative
+        __syncthreads();
+        if (tid == 0) __threadfence_system();
+        trace_point(p.trace, 3);  // system fence done
         cg::this_grid().sync();
+        trace_point(p.trace, 4);  // grid barrier done
         // Every CTA knows every count; CTA b publishes the cells of experts b, b + grid, ...
         for (int e = static_cast<int>(blockIdx.x) * kLLThreads + tid; e < E; e += nb * kLLThreads) {
             int cnt = s_run[e];
@@ -218,6 +261,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
             s_run[o] = static_cast<int>(static_cast<uint32_t>(v));
         }
         __syncthreads();
+        trace_point(p.trace, 5);  // all cells have arrived
         if (s_abort) goto done;
         if (warp == 0) {  // inclusive scan of the counts in (local expert, source) order
             const int per = (E + 31) / 32;
@@ -273,7 +317,9 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
 
 done:
     __syncthreads();
+    trace_point(p.trace, 6);  // CTA 0 packed its rows
     if (tid == 0 && last_cta_out(p.exit_ctr, static_cast<unsigned int>(nb))) {
+        if (p.trace != nullptr) p.trace[7] = globaltimer_ns();  // the last CTA leaves
         if (p.phase_mask & CAM_PHASE_SEND) p.epochs[0] = ep_send;
         if (p.phase_mask & CAM_PHASE_RECV) p.epochs[1] = ep_recv;
     }
@@ -281,16 +327,25 @@ done:
 
 }  // namespace cam
 
-extern "C" int cam_dispatch_ll_smem_bytes(int h, int quant_mode, int T, int K) {
-    const int nscale = CAM_QUANT_IS_FP8(quant_mode) ? h / 128 : (quant_mode == CAM_QUANT_INT8_TOKEN) ? 1 : 0;
-    const int stage = (quant_mode == CAM_QUANT_NONE) ? 0 : ((h + nscale * 4 + 15) & ~15);
-    return ((T * K * 8 + 15) & ~15) + cam::kLLWarps * stage;
+// Bytes of the chunk x expert slot table when it is worth having (0: the kernel walks the chunks with one warp).
+extern "C" int cam_dispatch_ll_slot_table_bytes(int T, int K, int E) {
+    const long long bytes = (static_cast<long long>((T * K + 31) / 32) * E * 2 + 15) & ~15ll;
+    return (T * K > 64 && T * K <= 65535 && bytes <= 64 * 1024) ? static_cast<int>(bytes) : 0;
 }
 
-extern "C" int cam_dispatch_ll_max_grid(int device, int h, int quant_mode, int T, int K) {
+extern "C" int cam_dispatch_ll_smem_bytes(int h, int quant_mode, int T, int K, int E) {
+    const int nscale = CAM_QUANT_IS_FP8(quant_mode) ? h / 128 : (quant_mode == CAM_QUANT_INT8_TOKEN) ? 1 : 0;
+    const int stage = (quant_mode == CAM_QUANT_NONE) ? 0 : ((h + nscale * 4 + 15) & ~15);
+    const int table = cam_dispatch_ll_slot_table_bytes(T, K, E);
+    const int per_warp = cam::kLLWarps * stage;          // the int8 path stages one row per warp
+    const int shared_row = stage + table;                 // the other paths stage one row per CTA, then the table
+    return ((T * K * 8 + 15) & ~15) + (per_warp > shared_row ? per_warp : shared_row);
+}
+
+extern "C" int cam_dispatch_ll_max_grid(int device, int h, int quant_mode, int T, int K, int E) {
     int sms = 0, per_sm = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return -1;
-    const int smem = cam_dispatch_ll_smem_bytes(h, quant_mode, T, K);
+    const int smem = cam_dispatch_ll_smem_bytes(h, quant_mode, T, K, E);
     cudaFuncSetAttribute(cam::dispatch_ll_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, cam::dispatch_ll_kernel, cam::kLLThreads, smem) !=
         cudaSuccess)
@@ -299,7 +354,7 @@ extern "C" int cam_dispatch_ll_max_grid(int device, int h, int quant_mode, int T
 }
 
 extern "C" int cam_launch_dispatch_ll(const cam::DispatchLLParams* p, int grid, cudaStream_t stream) {
-    const int smem = cam_dispatch_ll_smem_bytes(p->h, p->quant_mode, p->T, p->K);
+    const int smem = cam_dispatch_ll_smem_bytes(p->h, p->quant_mode, p->T, p->K, p->E);
     static cam::SmemLimitCache limit;
     cudaError_t e = limit.ensure(cam::dispatch_ll_kernel, smem);
     if (e != cudaSuccess) return static_cast<int>(e);

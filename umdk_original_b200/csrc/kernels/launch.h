@@ -53,6 +53,7 @@ struct CombineParams {
     int comm_quant;  // 0: bf16 rows on the wire, 2: int8 rows + one fp32 scale per 128 elements
     uint32_t* epochs;        // device counters [send, recv]
     unsigned int* exit_ctr;
+    unsigned long long* trace;  // optional [8] timeline of CTA 0
     uint64_t timeout_ns;
     int phase_mask;
     int dbg_drop_flags;
@@ -74,6 +75,8 @@ struct DispatchLLParams {
     int count_type;          // 1 = per-expert counts, 0 = cumulative
     uint32_t* epochs;        // device counters [send, recv]
     unsigned int* exit_ctr;
+    unsigned long long* trace;  // optional [8] timeline of CTA 0 (see trace_point), null when tracing is off
+    int slot_table_bytes;       // > 0: shared memory holds a chunk x expert table for the parallel slot computation
     uint64_t timeout_ns;
     int phase_mask;
     int dbg_drop_flags;
@@ -174,8 +177,9 @@ int cam_launch_layout(const void* topk_idx, int idx_is_i64, int T, int K, int E,
                       cudaStream_t stream);
 int cam_combine_max_grid(int device);
 int cam_launch_combine(const cam::CombineParams* p, int grid, cudaStream_t stream);
-int cam_dispatch_ll_smem_bytes(int h, int quant_mode, int T, int K);
-int cam_dispatch_ll_max_grid(int device, int h, int quant_mode, int T, int K);
+int cam_dispatch_ll_slot_table_bytes(int T, int K, int E);
+int cam_dispatch_ll_smem_bytes(int h, int quant_mode, int T, int K, int E);
+int cam_dispatch_ll_max_grid(int device, int h, int quant_mode, int T, int K, int E);
 int cam_launch_dispatch_ll(const cam::DispatchLLParams* p, int grid, cudaStream_t stream);
 int cam_launch_grouped_gemm_fp8(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
                                 const CUtensorMap* tmap_b, int grid, cudaStream_t stream);

@@ -85,6 +85,7 @@ struct CamBuffer {
     uint64_t timeout_ns = 10ull * 1000ull * 1000ull * 1000ull;
     int dbg_drop_flags = 0;
     // per-stage device timing of the fused layer (off by default): events around the four launches
+    unsigned long long* d_trace = nullptr;  // [2][8] in-kernel timelines: low-latency dispatch, combine (null = off)
     bool profile = false;
     bool profile_valid = false;
     cudaEvent_t prof_ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
@@ -255,6 +256,7 @@ extern "C" int cam_buffer_destroy(CamBuffer* b) {
     for (void* p : frees)
         if (p != nullptr) cudaFree(p);
     if (b->h_status != nullptr) cudaFreeHost(b->h_status);
+    if (b->d_trace != nullptr) cudaFree(b->d_trace);
     if (b->act_f32 != nullptr) cudaFree(b->act_f32);
     if (b->row_amax != nullptr) cudaFree(b->row_amax);
     for (auto e : b->prof_ev)
@@ -329,6 +331,28 @@ extern "C" int cam_buffer_device(CamBuffer* b) { return b ? b->device : -1; }
 extern "C" int cam_buffer_tp_rank(CamBuffer* b) { return b ? b->tp_rank : -1; }
 extern "C" void cam_buffer_set_timeout_ms(CamBuffer* b, double ms) {
     if (b != nullptr && ms > 0) b->timeout_ns = static_cast<uint64_t>(ms * 1e6);
+}
+// In-kernel timeline of the low-latency dispatch and of combine (globaltimer stamps of CTA 0, see
+// trace_point in ptx.cuh).  read_trace synchronises the device and copies 2 x 8 stamps (ns).
+extern "C" int cam_buffer_set_trace(CamBuffer* b, int on) {
+    CAM_CHECK(b != nullptr, "set_trace: null buffer");
+    CAM_CUDA(cudaSetDevice(b->device));
+    if (on && b->d_trace == nullptr) {
+        CAM_CUDA(cudaMalloc(&b->d_trace, sizeof(unsigned long long) * 16));
+        CAM_CUDA(cudaMemset(b->d_trace, 0, sizeof(unsigned long long) * 16));
+    } else if (!on && b->d_trace != nullptr) {
+        CAM_CUDA(cudaDeviceSynchronize());
+        CAM_CUDA(cudaFree(b->d_trace));
+        b->d_trace = nullptr;
+    }
+    return 0;
+}
+extern "C" int cam_buffer_read_trace(CamBuffer* b, unsigned long long* out16) {
+    CAM_CHECK(b != nullptr && out16 != nullptr && b->d_trace != nullptr, "read_trace: tracing is off");
+    CAM_CUDA(cudaSetDevice(b->device));
+    CAM_CUDA(cudaDeviceSynchronize());
+    CAM_CUDA(cudaMemcpy(out16, b->d_trace, sizeof(unsigned long long) * 16, cudaMemcpyDeviceToHost));
+    return 0;
 }
 extern "C" int cam_buffer_set_profile(CamBuffer* b, int on) {
     CAM_CHECK(b != nullptr, "set_profile: null buffer");
@@ -583,6 +607,7 @@ extern "C" int cam_combine(CamBuffer* b, const void* y, const int* row_src, cons
     p.comm_quant = comm_quant;
     p.epochs = b->d_epochs + (low_latency ? 7 : 3);
     p.exit_ctr = b->exit_ctr + 1;
+    p.trace = b->d_trace ? b->d_trace + 8 : nullptr;
     p.timeout_ns = b->timeout_ns;
     p.phase_mask = phase_mask;
     p.dbg_drop_flags = b->dbg_drop_flags;
@@ -621,6 +646,8 @@ extern "C" int cam_dispatch_ll(CamBuffer* b, const void* x, const void* expert_i
     p.count_type = count_type;
     p.epochs = b->d_epochs + 5;
     p.exit_ctr = b->exit_ctr + 2;
+    p.trace = b->d_trace;
+    p.slot_table_bytes = cam_dispatch_ll_slot_table_bytes(T, K, E);
     p.timeout_ns = b->timeout_ns;
     p.phase_mask = phase_mask;
     p.dbg_drop_flags = b->dbg_drop_flags;
@@ -643,7 +670,7 @@ extern "C" int cam_dispatch_ll(CamBuffer* b, const void* x, const void* expert_i
     if (git != b->ll_grid_cache.end()) {
         grid = git->second;
     } else {
-        grid = cam_dispatch_ll_max_grid(b->device, h, quant_mode, T, K);
+        grid = cam_dispatch_ll_max_grid(b->device, h, quant_mode, T, K, E);
         b->ll_grid_cache[gkey] = grid;
     }
     CAM_CHECK(grid > 0, "dispatch_ll: kernel does not fit (shared memory for T=%d K=%d h=%d)", T, K, h);

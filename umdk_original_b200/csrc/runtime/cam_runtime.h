@@ -58,6 +58,9 @@ void cam_buffer_set_debug_drop_flags(CamBuffer* b, int on);
 // Per-stage device timing of the fused layer.  While on, every full fused call records CUDA events
 // around its four launches; read_profile waits for the last one and fills
 // {dispatch, GEMM1, GEMM2 + combine send, combine reduce} in milliseconds.  Off by default.
+// In-kernel timelines (globaltimer stamps of CTA 0) of the low-latency dispatch [0..7] and of combine [8..15].
+int cam_buffer_set_trace(CamBuffer* b, int on);
+int cam_buffer_read_trace(CamBuffer* b, unsigned long long* out16);
 int cam_buffer_set_profile(CamBuffer* b, int on);
 int cam_buffer_read_profile(CamBuffer* b, float* ms4);
 // Copies the device status word (after synchronising `stream`) into *out and clears it on the device.

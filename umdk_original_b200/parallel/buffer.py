@@ -182,6 +182,25 @@ class Buffer:
         elif self._cpu is not None and self.num_ranks > 1:
             dist.barrier(group=self.group)
 
+    LL_DISPATCH_TRACE = ("start", "slot_table", "rows_issued", "system_fence", "grid_barrier", "cells_arrived",
+                         "rows_packed", "last_cta_out")
+    COMBINE_TRACE = ("start", "rows_issued", "system_fence", "flags_arrived", "reduced", "last_cta_out")
+
+    def set_trace(self, on: bool = True) -> None:
+        """In-kernel timeline of the low-latency dispatch and of combine: CTA 0 stamps ``%globaltimer`` at
+        the phase boundaries of the kernels (off by default; one predicated branch per point)."""
+        if self._native is not None:
+            self._native.set_trace(on)
+
+    def read_trace(self) -> dict:
+        """Microseconds since kernel start of every trace point of the last traced launches
+        (synchronises the device)."""
+        t = self._native.read_trace()
+        def rel(vals, names):
+            t0 = vals[0]
+            return {n: (v - t0) / 1e3 for n, v in zip(names, vals) if v}
+        return {"dispatch_ll": rel(t[:8], self.LL_DISPATCH_TRACE), "combine": rel(t[8:14], self.COMBINE_TRACE)}
+
     def set_profile(self, on: bool = True) -> None:
         """Per-stage device timing of ``fused_deep_moe`` (CUDA events around its four launches)."""
         if self._native is not None:

@@ -62,6 +62,9 @@ def init_dist(n: int):
         raise SystemExit(f"--gpus {n} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {n}")
     torch.cuda.set_device(local)
     if world > 1:
+        # pinned staging buffers of the end-to-end path should sit on the GPU's own NUMA node
+        from umdk_original_b200.utils.host import bind_to_gpu_numa_node
+        bind_to_gpu_numa_node(local)
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     return rank, world, local

@@ -186,13 +186,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  `abort_flag` (shared memory) lets one role that gave up release the others.
+// `sleep_ns` > 0 backs off between polls: for roles that wait long (a whole tile) so that their
+// polling does not take issue slots and power from the warps that feed the tensor core.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
                                                   volatile uint32_t* abort_flag,
-                                                  uint64_t timeout_ns = 2000000000ull) {
+                                                  uint64_t timeout_ns = 2000000000ull, uint32_t sleep_ns = 0u) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     uint32_t polls = 0;
     while (!mbar_try_wait(bar, parity)) {
+        if (sleep_ns) __nanosleep(sleep_ns);
         if ((++polls & 255u) == 0u) {
             if (*abort_flag) return false;
             if (globaltimer_ns() - t0 > timeout_ns) {

@@ -236,7 +236,7 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
             rows = max(0, min(BM, rows - static_cast<int>(cta) * BM));
             const bool valid = r < rows;
             const int grow = row0 + (valid ? r : 0);
-            if (!mbar_wait_bounded(bar_tfull, tcount & 1u, abort_flag)) { ok = false; break; }
+            if (!mbar_wait_bounded(bar_tfull, tcount & 1u, abort_flag, 2000000000ull, 256u)) { ok = false; break; }
             tc_fence_after_sync();
             const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + cq * 32;
             uint32_t v0[32], v1[32];  // columns cq*32.. of the first 128-column half, same of the second

@@ -13,8 +13,11 @@ import torch.distributed as dist
 
 
 class BaselineMoE:
-    def __init__(self, cfg, rank, world, dev, seed=0):
+    def __init__(self, cfg, rank, world, dev, seed=0, gemm="fp8_per_expert"):
+        """gemm: "fp8_per_expert" (cuBLAS fp8 torch._scaled_mm, one call per local expert) or "bf16_grouped"
+        (the library's bf16 grouped GEMM torch._grouped_mm: no per-expert loop, twice the bytes per weight)."""
         self.cfg, self.rank, self.world, self.dev = cfg, rank, world, dev
+        self.want_gemm = gemm
         self.el = cfg.num_experts // world
         g = torch.Generator(device=dev)
         g.manual_seed(seed * 1000 + rank)
@@ -30,6 +33,12 @@ class BaselineMoE:
         self._pick_mode()
 
     def _pick_mode(self):
+        if self.want_gemm == "bf16_grouped":
+            self.mode = "bf16_grouped_mm"
+            self.w1t = self.w1.transpose(1, 2).contiguous()  # [El, h, 2I]
+            self.w2t = self.w2.transpose(1, 2).contiguous()  # [El, I, h]
+            del self.w1, self.w2
+            return
         try:
             self.w1q, self.s1 = self._quant_rows(self.w1)
             self.w2q, self.s2 = self._quant_rows(self.w2)
@@ -118,7 +127,7 @@ def run_baseline(args, cfg, rank, world, local, metric):
     from bench import barrier, make_inputs, max_over_ranks
     dev = torch.device("cuda", local)
     tokens = args.tokens or cfg.tokens_per_rank
-    layer = BaselineMoE(cfg, rank, world, dev)
+    layer = BaselineMoE(cfg, rank, world, dev, gemm=getattr(args, "baseline_gemm", "fp8_per_expert"))
     sets = make_inputs(cfg, tokens, rank, 4, dev)
     for i in range(max(args.warmup, 3)):
         layer.forward(*sets[i % 4])

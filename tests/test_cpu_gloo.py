@@ -197,3 +197,54 @@ def test_fused_with_shared_expert_rank():
         assert err < 1e-4, f"rank {r}: max abs err {err}"
         assert len(nums) == (1 if r == 0 else 4)
     assert res[0][1][1][0] == 64  # the replica sees every token of both ranks once
+
+
+def _tp_rank(rank, world):
+    """EP 2 x TP 2 on four gloo ranks (rank = tp * 2 + ep): dispatch appends the TP partner's rows,
+    combine adds both partial outputs of every row before sending it home."""
+    import torch
+    import torch.distributed as dist
+    import umdk_original_b200 as u
+    from umdk_original_b200.ops import reference as ref
+    ops = torch.ops.umdk_cam_op_lib
+    ep, t, h, e, k = 2, 16, 256, 4, 2
+    tp, r = divmod(rank, ep)
+    ep_groups = [dist.new_group([0, 1]), dist.new_group([2, 3])]
+    tp_groups = [dist.new_group([0, 2]), dist.new_group([1, 3])]
+    g = torch.Generator().manual_seed(123)
+    xs = [torch.randn(t, h, generator=g).to(torch.bfloat16) for _ in range(world)]
+    topk = [torch.randint(0, e, (t, k), generator=g).to(torch.int32) for _ in range(world)]
+    wts = [torch.rand(t, k, generator=g) for _ in range(world)]
+    buf = u.Buffer(ep_groups[tp], u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, ll_max_tokens=t),
+                   name="tp", device=torch.device("cpu"), tp_group=tp_groups[r])
+    expand, dyn, eidx, nums, ep_cnt, tp_cnt = ops.moe_dispatch_shmem(
+        xs[rank], topk[rank], None, None, ep, r, e, 2, tp, 0, 0, 0, 3, 0, 1, buf.handle)
+    plans = [ref.plan_dispatch([topk[p * ep + q] for q in range(ep)], e) for p in range(2)]
+    own, other = plans[tp][r], plans[1 - tp][r]
+    n, m = own.src.shape[0], other.src.shape[0]
+    assert tp_cnt.tolist() == ([n, m] if tp == 0 else [m, n]), (tp_cnt.tolist(), n, m)
+    assert expand.shape[0] == 2 * t * ep * min(e // ep, k) and dyn.shape == (expand.shape[0], h // 128)
+    own_rows = torch.stack([xs[tp * ep + s][tt] for s, tt, _ in own.src.tolist()])
+    oth_rows = torch.stack([xs[(1 - tp) * ep + s][tt] for s, tt, _ in other.src.tolist()])
+    for rows, lo in ((own_rows, 0), (oth_rows, n)):
+        q, s = ref.quant_fp8_1x128(rows)
+        assert torch.equal(expand[lo:lo + rows.shape[0]].view(torch.uint8), q.view(torch.uint8))
+        assert torch.equal(dyn[lo:lo + rows.shape[0]], s)
+    # a TP-sharded expert: this rank's partial output of every row it holds is (1 + tp) * row
+    both = torch.cat([own_rows, oth_rows])
+    y = torch.zeros(expand.shape[0], h, dtype=torch.bfloat16)
+    y[:n + m] = (both.float() * (1.0 + tp)).to(torch.bfloat16)
+    out = ops.moe_combine_shmem(y, topk[rank], eidx, ep_cnt, wts[rank], tp_cnt, None, None, None, None, None,
+                                ep, r, e, 2, tp, 0, 0, 0, 0, 0, buf.handle, 0, 0)
+    rows3 = (xs[rank].float() * 1.0).to(torch.bfloat16).float() + (xs[rank].float() * 2.0).to(torch.bfloat16).float()
+    want = ref.combine_reference(rows3.to(torch.bfloat16).unsqueeze(1).expand(t, k, h).contiguous(), topk[rank],
+                                 wts[rank], e)
+    return float((out.float() - want.float()).abs().max())
+
+
+def test_low_latency_ops_with_tensor_parallel_pair():
+    res = run_gloo(_tp_rank, 4)
+    assert len(res) == 4
+    for r, (st, val) in res.items():
+        assert st == "ok", val
+        assert val == 0.0

@@ -23,7 +23,8 @@ constexpr int kI8EpiThreads = 512;
 constexpr int kI8SfWarp0 = 4, kI8EpiWarp0 = 8;
 // Shared memory: 4 pipeline stages | bf16 staging of half an output tile (128 rows x 256 bytes,
 // rows 272 bytes apart so that 16-byte stores of neighbouring rows fall into different banks; the
-// per-row amax exchange of the SwiGLU epilogue uses the same bytes) | barriers.  232448 bytes, the
+// SwiGLU epilogue does not use it: it writes fp32 activations to global memory and folds the row
+// maxima in with atomicMax) | barriers.  232448 bytes, the
 // whole 227 KiB a CTA can have, so the dynamic segment must start on a 1024-byte boundary.
 constexpr int kI8StgPitch = 272;
 constexpr int kI8StgBytes = BM * kI8StgPitch;  // 34816

@@ -133,8 +133,9 @@ def _moe_dispatch_shmem_cpu(x, expertIds, scales, xActiveMask, epWorldSize, epRa
     g = _reg().by_id(extInfo)
     if quantMode == 1:
         raise RuntimeError("umdk_cam_op_lib: static quantisation (quantMode 1) is rejected, as in the reference")
-    if tpWorldSize > 1:
-        raise RuntimeError("umdk_cam_op_lib: tpWorldSize > 1 is not supported")
+    if tpWorldSize not in (0, 1, 2) or (tpWorldSize == 2 and g.tp_group is None):
+        raise RuntimeError("umdk_cam_op_lib: tpWorldSize must be 1 or 2 (as in the reference), and 2 needs a Buffer "
+                           "created with tp_group")
     t, k = expertIds.shape
     ids = expertIds
     el = moeExpertNum // epWorldSize
@@ -150,6 +151,17 @@ def _moe_dispatch_shmem_cpu(x, expertIds, scales, xActiveMask, epWorldSize, epRa
         if shared_rank:
             per_e, cnt = per_e[:1], cnt[:epWorldSize]
     n = rx.shape[0]
+    tp_counts = torch.zeros(max(tpWorldSize, 1), dtype=torch.int32)
+    if tpWorldSize == 2:
+        # all-gather inside the TP pair (moe_dispatch_shmem.h:936-1018): the partner's rows follow this rank's own
+        counts = g.tp_all_gather_counts(n)
+        rx = torch.cat([rx.view(torch.uint8), g.tp_exchange(rx, counts).view(torch.uint8)]).view(rx.dtype) \
+            if rx.dtype == ref.FP8 else torch.cat([rx, g.tp_exchange(rx, counts)])
+        if rs is not None:
+            rs = torch.cat([rs, g.tp_exchange(rs, counts)])
+        tp_counts = torch.tensor(counts, dtype=torch.int32)
+        g.tp_counts = tp_counts
+        n, a = rx.shape[0], 2 * a
     pad = a - n
     if rx.dtype == ref.FP8:
         expand = torch.cat([rx.view(torch.uint8), torch.zeros((pad, rx.shape[1]), dtype=torch.uint8)]).view(ref.FP8)
@@ -163,7 +175,7 @@ def _moe_dispatch_shmem_cpu(x, expertIds, scales, xActiveMask, epWorldSize, epRa
         dyn = torch.zeros(a, dtype=torch.float32)
     g.ll_src = src
     nums = per_e if expertTokenNumsType == 1 else per_e.cumsum(0)
-    return [expand, dyn, slots, nums.to(torch.int64), cnt, torch.zeros(max(tpWorldSize, 1), dtype=torch.int32)]
+    return [expand, dyn, slots, nums.to(torch.int64), cnt, tp_counts]
 
 
 def _moe_combine_shmem_cpu(expandX, expertIds, expandIdx, epSendCounts, expertScales, tpSendCounts, xActiveMask,
@@ -180,8 +192,20 @@ def _moe_combine_shmem_cpu(expandX, expertIds, expandIdx, epSendCounts, expertSc
         ids = ids.clone()
         ids[int(xActiveMask.sum()):] = -1
     y = expandX
+    if tpWorldSize == 2:
+        # reduce-scatter inside the TP pair (moe_combine_shmem.h:438-470): the partner gets this rank's partial outputs
+        # of the partner's rows and this rank adds the partner's partial outputs of its own rows
+        if g.tp_group is None or g.tp_counts is None:
+            raise RuntimeError("umdk_cam_op_lib: tpWorldSize 2 needs a Buffer created with tp_group and a preceding "
+                               "moe_dispatch_shmem")
+        counts = g.tp_counts.tolist()
+        n_own, n_other = counts[g.tp_rank], counts[1 - g.tp_rank]
+        swapped = [0, 0]  # what each TP rank contributes: its partial outputs of the OTHER rank's rows
+        swapped[g.tp_rank], swapped[1 - g.tp_rank] = n_other, n_own
+        partner = g.tp_exchange(expandX[n_own:n_own + n_other].contiguous(), swapped)
+        y = (expandX[:n_own].float() + partner.float()).to(expandX.dtype)
     if commQuantMode == 2:  # int8 on the wire, one scale per 128 elements
-        q, s = ref.quant_int8_1x128(expandX)
+        q, s = ref.quant_int8_1x128(y)
         y = ref.dequant_int8_1x128(q, s)
     return _backend().combine(g, y, g.ll_src, ids, w)
 

@@ -81,6 +81,10 @@ class Buffer:
                     self._connect_tp(tp_group)
         else:
             self._cpu = CpuGroup(group, self.rank, self.num_ranks, cfg.num_experts)
+            if tp_group is not None:
+                assert dist.get_world_size(tp_group) == 2, "tensor parallelism inside the ops is limited to 2 ranks"
+                self._cpu.tp_group = tp_group
+                self._cpu.tp_rank = self.tp_rank = dist.get_rank(tp_group)
             self.handle = registry.register(self._cpu, self.name)
         log.info("Buffer %s rank %d/%d on %s: %.1f MiB symmetric", self.name, self.rank, self.num_ranks, self.device,
                  self.total_bytes / 2 ** 20)

@@ -33,6 +33,9 @@ class CpuGroup:
     ll_src: Optional[torch.Tensor] = None      # [N,3] rows of the last low-latency dispatch
     last_src: Optional[torch.Tensor] = None    # [N,3] rows of the last normal dispatch
     drop_next_send: bool = False               # host-side fault injection: skip the next exchange
+    tp_group: Optional[object] = None          # two ranks: this one and its tensor-parallel partner
+    tp_rank: int = 0
+    tp_counts: Optional[torch.Tensor] = None   # [2] rows each TP rank received in the last low-latency dispatch
 
     # ------------------------------------------------------------------ collectives
     def _guard(self, fn, *a, **kw):
@@ -55,6 +58,27 @@ class CpuGroup:
         self._guard(dist.all_to_all_single, out, send.contiguous(), output_split_sizes=recv_splits,
                     input_split_sizes=send_splits, group=self.group)
         return out
+
+
+    def tp_exchange(self, mine: torch.Tensor, counts: List[int]) -> torch.Tensor:
+        """Rows of the tensor-parallel partner: this rank contributes ``mine`` (counts[tp_rank] rows), the
+        partner counts[1 - tp_rank] rows.  Both sides pad to the larger count, since gloo's all_gather wants
+        equal shapes; fp8 rows travel as bytes."""
+        me = self.tp_rank
+        n_max = max(counts)
+        as_bytes = mine.dtype == ref.FP8
+        t = mine.view(torch.uint8) if as_bytes else mine
+        pad = t.new_zeros((n_max,) + tuple(t.shape[1:]))
+        pad[:counts[me]] = t[:counts[me]]
+        out = [torch.empty_like(pad), torch.empty_like(pad)]
+        self._guard(dist.all_gather, out, pad, group=self.tp_group)
+        got = out[1 - me][:counts[1 - me]]
+        return got.view(ref.FP8) if as_bytes else got
+
+    def tp_all_gather_counts(self, n: int) -> List[int]:
+        out = [torch.zeros(1, dtype=torch.long), torch.zeros(1, dtype=torch.long)]
+        self._guard(dist.all_gather, out, torch.tensor([n], dtype=torch.long), group=self.tp_group)
+        return [int(out[0]), int(out[1])]
 
 
 def _send_order(topk_idx: torch.Tensor, num_experts: int, world: int, active: Optional[int] = None):

@@ -15,6 +15,7 @@ import torch
 from ..ops import cam_ops
 from ..parallel.buffer import Buffer
 from ..utils.config import CamConfig
+from ..utils.nvtx import nvtx_range
 from .configs import MoEConfig
 from .router import route
 from .weights import ExpertWeights, from_reference_w8a8, random_fp8_experts, random_w8a8_experts
@@ -71,9 +72,10 @@ class FusedMoE(torch.nn.Module):
         if topk_idx is None:
             topk_idx, topk_weights = self.route(x)
         w = self.weights
-        out, nums = cam_ops.ops.fused_deep_moe(
-            x, topk_idx, [w.w1], [w.s1], [w.w2], [w.s2], topk_weights.float(), None, x_active_mask,
-            self.buffer.name, self.num_ranks, self.rank, self.cfg.num_experts, 0, 0, self.quant_mode, 0)
+        with nvtx_range("umdk_cam.fused_deep_moe"):
+            out, nums = cam_ops.ops.fused_deep_moe(
+                x, topk_idx, [w.w1], [w.s1], [w.w2], [w.s2], topk_weights.float(), None, x_active_mask,
+                self.buffer.name, self.num_ranks, self.rank, self.cfg.num_experts, 0, 0, self.quant_mode, 0)
         return out, nums
 
 
@@ -106,7 +108,7 @@ class MoEStepRunner:
     def stage(self, x_host: torch.Tensor, idx_host: torch.Tensor, w_host: torch.Tensor) -> None:
         """Starts the host->device copy of the next step's inputs (pinned tensors)."""
         slot = self.slots[self._step % 2]
-        with torch.cuda.stream(self.copy_stream):
+        with nvtx_range("umdk_cam.step.h2d"), torch.cuda.stream(self.copy_stream):
             self.copy_stream.wait_event(slot["free"])
             slot["x"].copy_(x_host, non_blocking=True)
             slot["idx"].copy_(idx_host, non_blocking=True)
@@ -121,9 +123,10 @@ class MoEStepRunner:
         cur.wait_event(slot["ready"])
         out, nums = self.layer(slot["x"], slot["idx"], slot["w"])
         slot["free"].record(cur)
-        self.result_dev[:-1] = nums.float()
-        self.result_dev[-1] = out.sum(dtype=torch.float32)
-        self.result_host.copy_(self.result_dev, non_blocking=True)
+        with nvtx_range("umdk_cam.step.result_d2h"):
+            self.result_dev[:-1] = nums.float()
+            self.result_dev[-1] = out.sum(dtype=torch.float32)
+            self.result_host.copy_(self.result_dev, non_blocking=True)
         self._step += 1
         self.last_out = out
         return self.result_host

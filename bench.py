@@ -11,7 +11,8 @@ fixed, the 256 experts are spread over the N ranks.
 Rank 0 prints one JSON line.  `value` is device-timed (CUDA events around exactly `steps` steps,
 barrier + synchronize on both sides, max over ranks); `e2e` is the same layer driven through
 MoEStepRunner with a pinned-host -> device copy of every step's inputs and a device -> host read
-of the step's result record.  `--impl reference` reports why the Ascend-only reference cannot
+of the step's result record (the host launches step i+1 before it waits for the record of step i, so
+every record is read inside the timed region, one step behind the launches).  `--impl reference` reports why the Ascend-only reference cannot
 run here; `--impl baseline` times the NCCL all_to_all_single + cuBLAS comparison layer.
 """
 from __future__ import annotations
@@ -157,10 +158,14 @@ def run_ours(args, cfg, rank, world, local):
         barrier(world)
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
+        pending = None
         for i in range(args.steps):
-            runner.run()                                  # step i computes ...
-            runner.stage(*host[(i + 1) % len(host)])      # ... while step i+1's inputs are copied in
-            runner.finish()                               # result record of step i is on the host
+            ticket = runner.run()                         # step i is launched ...
+            runner.stage(*host[(i + 1) % len(host)])      # ... step i+1's inputs are copied in meanwhile ...
+            if pending is not None:
+                runner.result(pending)                    # ... and the record of step i-1 is read on the host
+            pending = ticket
+        runner.result(pending)                            # every step's record has reached the host
         t1.record()
         barrier(world)
         e2e_ms = max_over_ranks(t0.elapsed_time(t1), world) / args.steps

@@ -1,0 +1,47 @@
+"""MoEStepRunner: pinned host inputs -> device -> fused layer -> host record, with launches running one
+step ahead of the reads.  Every step's record must equal what a direct call of the layer gives."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_pipelined_steps_return_each_steps_own_record():
+    import umdk_original_b200 as u
+    from umdk_original_b200.models import TINY, FusedMoE, MoEStepRunner
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = TINY
+    t = cfg.tokens_per_rank
+    buf = u.Buffer(None, u.CamConfig(num_experts=cfg.num_experts, max_tokens=t, hidden=cfg.hidden, topk=cfg.topk,
+                                     timeout_ms=2000.0), name="runner", device=dev, rank=0, num_ranks=1)
+    layer = FusedMoE(cfg, buf, seed=0)
+    g = torch.Generator().manual_seed(5)
+    host, want = [], []
+    for _ in range(5):
+        x = torch.randn(t, cfg.hidden, generator=g).to(torch.bfloat16)
+        idx, w = layer.route(x.to(dev))
+        host.append((x.pin_memory(), idx.cpu().pin_memory(), w.float().cpu().pin_memory()))
+        out, nums = layer(x.to(dev), idx, w)
+        want.append(torch.cat([nums.float(), out.sum(dtype=torch.float32).reshape(1)]).cpu())
+    runner = MoEStepRunner(layer, t)
+    assert runner.h2d_bytes == t * (cfg.hidden * 2 + cfg.topk * 12) and runner.d2h_bytes == 4 * (layer.num_local + 1)
+    got = []
+    runner.stage(*host[0])
+    pending = None
+    for i in range(len(host)):
+        ticket = runner.run()
+        if i + 1 < len(host):
+            runner.stage(*host[i + 1])
+        if pending is not None:
+            got.append(runner.result(pending).clone())
+        pending = ticket
+    got.append(runner.result(pending).clone())
+    assert torch.equal(runner.finish(), got[-1])
+    buf.check()
+    for i, (a, b) in enumerate(zip(got, want)):
+        assert torch.equal(a[:-1], b[:-1]), f"step {i}: token counts differ"
+        assert abs(float(a[-1]) - float(b[-1])) <= 1e-3 * max(1.0, abs(float(b[-1]))), f"step {i}: checksum differs"
+    with pytest.raises(AssertionError):
+        runner.result(0)  # long overwritten
+    buf.destroy()

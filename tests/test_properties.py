@@ -93,3 +93,24 @@ def test_ue8m0_scales_bound_the_block(rows, blocks, seed):
     assert (s * 448.0 >= amax * (1 - 1e-6)).all() and (s * 448.0 < 2.0 * amax * (1 + 1e-6)).all()
     back = ref.dequant_fp8_1x128(q, s)
     assert ((back - x).abs() <= 0.0725 * amax.unsqueeze(-1).expand(rows, blocks, 128).reshape(rows, -1) + 1e-6).all()
+
+
+def test_power_of_two_scale_conversion_keeps_values_within_one_e4m3_rounding():
+    """Arbitrary fp32 block scales -> powers of two: dequantised weights move by at most one e4m3
+    half-ulp (2^-4 relative for normal numbers), already-converted weights do not move at all."""
+    import torch
+    from umdk_original_b200.models.weights import random_fp8_experts
+    from umdk_original_b200.ops import reference as ref
+    w = random_fp8_experts(2, 256, 128, ue8m0=False, seed=3)
+    assert not w.power_of_two_scales
+    c = w.with_power_of_two_scales()
+    assert c.power_of_two_scales
+    for (q0, s0), (q1, s1) in (((w.w1, w.s1), (c.w1, c.s1)), ((w.w2, w.s2), (c.w2, c.s2))):
+        assert bool((s1 >= s0).all()) and bool((s1 < 2 * s0).all())
+        a, b = ref.dequant_fp8_128x128(q0, s0), ref.dequant_fp8_128x128(q1, s1)
+        # e4m3: 3 mantissa bits -> half an ulp is 2^-4 of the value; subnormals of the new grid are absolute
+        tol = a.abs() * 2.0 ** -4 + (s1 * 2.0 ** -10).repeat_interleave(128, -2).repeat_interleave(128, -1)
+        assert bool(((a - b).abs() <= tol).all())
+    again = c.with_power_of_two_scales()
+    assert torch.equal(again.w1.view(torch.uint8), c.w1.view(torch.uint8)) and torch.equal(again.s1, c.s1)
+    assert torch.equal(again.w2.view(torch.uint8), c.w2.view(torch.uint8)) and torch.equal(again.s2, c.s2)

@@ -82,9 +82,12 @@ class FusedMoE(torch.nn.Module):
 class MoEStepRunner:
     """End-to-end step: pinned host inputs -> H2D -> FusedMoE -> D2H of a result record.
 
-    Two device input slots alternate; the copy of step i+1 runs on a side stream while step i
-    computes.  The record read back each step is the per-expert token count plus the sum of the
-    output in fp32 (a checksum a caller can log); ``h2d_bytes`` / ``d2h_bytes`` are what moves."""
+    Two device input slots and two result records alternate; the copy of step i+1 runs on a side
+    stream while step i computes, and the host may launch step i+1 before it reads the record of step i
+    (``run`` returns a ticket, ``result(ticket)`` waits for that step only), so the device does not idle
+    while the host reads a result and prepares the next launch.  The record read back each step is the
+    per-expert token count plus the sum of the output in fp32 (a checksum a caller can log);
+    ``h2d_bytes`` / ``d2h_bytes`` are what moves."""
 
     def __init__(self, layer: FusedMoE, tokens: int):
         self.layer = layer
@@ -98,8 +101,9 @@ class MoEStepRunner:
                 "w": torch.empty(tokens, cfg.topk, dtype=torch.float32, device=dev),
                 "ready": torch.cuda.Event(), "free": torch.cuda.Event(),
             })
-        self.result_dev = torch.zeros(layer.num_local + 1, dtype=torch.float32, device=dev)
-        self.result_host = torch.zeros(layer.num_local + 1, dtype=torch.float32).pin_memory()
+        self.result_dev = [torch.zeros(layer.num_local + 1, dtype=torch.float32, device=dev) for _ in range(2)]
+        self.result_host = [torch.zeros(layer.num_local + 1, dtype=torch.float32).pin_memory() for _ in range(2)]
+        self.result_done = [torch.cuda.Event(), torch.cuda.Event()]
         self.h2d_bytes = tokens * (cfg.hidden * 2 + cfg.topk * 8 + cfg.topk * 4)
         self.d2h_bytes = (layer.num_local + 1) * 4
         self._step = 0
@@ -116,24 +120,36 @@ class MoEStepRunner:
             slot["ready"].record(self.copy_stream)
         self._staged = slot
 
-    def run(self) -> torch.Tensor:
-        """Runs the staged step and returns the host result record (synchronises)."""
+    def run(self) -> int:
+        """Launches the staged step (nothing here waits for the device) and returns its ticket.  At most
+        two steps may be outstanding: collect ``result(ticket)`` of a step before launching the step after
+        the next one, whose record takes the same place."""
         slot = self._staged
         cur = torch.cuda.current_stream()
         cur.wait_event(slot["ready"])
         out, nums = self.layer(slot["x"], slot["idx"], slot["w"])
         slot["free"].record(cur)
+        r = self._step % 2
         with nvtx_range("umdk_cam.step.result_d2h"):
-            self.result_dev[:-1] = nums.float()
-            self.result_dev[-1] = out.sum(dtype=torch.float32)
-            self.result_host.copy_(self.result_dev, non_blocking=True)
+            self.result_dev[r][:-1] = nums.float()
+            self.result_dev[r][-1] = out.sum(dtype=torch.float32)
+            self.result_host[r].copy_(self.result_dev[r], non_blocking=True)
+            self.result_done[r].record(cur)
+        ticket = self._step
         self._step += 1
         self.last_out = out
-        return self.result_host
+        return ticket
+
+    def result(self, ticket: int) -> torch.Tensor:
+        """Host record of the step with this ticket (waits for that step only)."""
+        assert self._step - 2 <= ticket < self._step, "the record of this step has been overwritten or not produced"
+        self.result_done[ticket % 2].synchronize()
+        return self.result_host[ticket % 2]
 
     def finish(self) -> torch.Tensor:
+        """Waits for everything launched and returns the record of the last step."""
         torch.cuda.current_stream().synchronize()
-        return self.result_host
+        return self.result_host[(self._step - 1) % 2]
 
 
 def make_buffer_for(cfg: MoEConfig, group=None, tokens: Optional[int] = None, capacity_factor: float = 0.0,

@@ -35,6 +35,27 @@ class ExpertWeights:
         tensor-core block-scaled path (``quantMode=4``)."""
         return ref.is_power_of_two(self.s1) and ref.is_power_of_two(self.s2)
 
+    def with_power_of_two_scales(self, chunk: int = 4) -> "ExpertWeights":
+        """The same experts with every block scale rounded up to a power of two and the e4m3 values
+        re-rounded to match (value = q * s is kept up to one more e4m3 rounding; blocks whose scale is a
+        power of two already are unchanged).  Checkpoints with arbitrary fp32 block scales run on the
+        software-scaled GEMM (``quantMode=3``); after this conversion they take the tensor-core
+        block-scaled path (``quantMode=4``)."""
+        def convert(q: torch.Tensor, sc: torch.Tensor):
+            qs, ss = [], []
+            for i in range(0, q.shape[0], chunk):
+                s_old = sc[i:i + chunk].float()
+                s_new = ref.ue8m0_round_up(s_old)
+                ratio = (s_old / s_new).unsqueeze(-1).unsqueeze(-3)          # in (0.5, 1]: no overflow
+                e, n, k = q[i:i + chunk].shape
+                v = q[i:i + chunk].float().reshape(e, n // 128, 128, k // 128, 128) * ratio
+                qs.append(v.to(ref.FP8).reshape(e, n, k))
+                ss.append(s_new)
+            return torch.cat(qs), torch.cat(ss)
+        w1, s1 = convert(self.w1, self.s1)
+        w2, s2 = convert(self.w2, self.s2)
+        return ExpertWeights(w1, s1, w2, s2)
+
     @property
     def num_local_experts(self) -> int:
         return self.w1.shape[0]

@@ -127,7 +127,7 @@ def run_baseline(args, cfg, rank, world, local, metric):
     from bench import barrier, make_inputs, max_over_ranks
     dev = torch.device("cuda", local)
     tokens = args.tokens or cfg.tokens_per_rank
-    layer = BaselineMoE(cfg, rank, world, dev, gemm=getattr(args, "baseline_gemm", "fp8_per_expert"))
+    layer = BaselineMoE(cfg, rank, world, dev, gemm=getattr(args, "baseline_gemm", "bf16_grouped"))
     sets = make_inputs(cfg, tokens, rank, 4, dev)
     for i in range(max(args.warmup, 3)):
         layer.forward(*sets[i % 4])

@@ -41,7 +41,7 @@ def parse_args():
     ap.add_argument("--tokens", type=int, default=0, help="tokens per rank (0 = the model's default)")
     ap.add_argument("--experts", type=int, default=0, help="override the number of routed experts (smaller smoke runs)")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--baseline-gemm", default="fp8_per_expert", choices=["fp8_per_expert", "bf16_grouped"],
+    ap.add_argument("--baseline-gemm", default="bf16_grouped", choices=["fp8_per_expert", "bf16_grouped"],
                     help="--impl baseline: cuBLAS fp8 per expert, or the library's bf16 grouped GEMM")
     ap.add_argument("--w8a8-exact", action="store_true",
                     help="W8A8 models: int8 x int8 -> int32 tensor-core path instead of computing in block-scaled fp8")

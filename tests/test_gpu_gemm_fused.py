@@ -12,10 +12,12 @@ ops = torch.ops.umdk_cam_op_lib
 DEV = torch.device("cuda", 0)
 
 
-@pytest.fixture(params=["single", "pair"])
+@pytest.fixture(params=["single", "pair", "swap"])
 def gemm_variant(request, monkeypatch):
-    """Runs a block-scaled GEMM test on the one-CTA kernel and on the CTA-pair (cta_group::2) kernel."""
+    """Runs a block-scaled GEMM test on the one-CTA kernel, on the CTA-pair (cta_group::2) kernel and on the
+    one-CTA kernel with its operands exchanged (weights as the M operand, for small experts)."""
     monkeypatch.setenv("UMDK_CAM_GEMM_PAIR", "1" if request.param == "pair" else "0")
+    monkeypatch.setenv("UMDK_CAM_GEMM_SWAP", "1" if request.param == "swap" else "0")
     return request.param
 
 
@@ -37,8 +39,8 @@ def _ragged_problem(counts, n, k, seed, ue8m0=False):
 @pytest.mark.parametrize("counts,n,k", [([128], 256, 128), ([128], 256, 512), ([5, 0, 130, 257], 512, 384),
                                          ([300, 1, 77], 384, 256), ([40, 512, 129], 512, 1024)])
 def test_grouped_gemm_plain(counts, n, k, ue8m0, gemm_variant):
-    if not ue8m0 and gemm_variant == "pair":
-        pytest.skip("the fp32-scale kernel has no CTA-pair form")
+    if not ue8m0 and gemm_variant != "single":
+        pytest.skip("the fp32-scale kernel has one form only")
     aq, a_s, wq, w_s, off = _ragged_problem(counts, n, k, seed=len(counts) * 7 + n, ue8m0=ue8m0)
     got = ops.grouped_gemm_fp8(aq.to(DEV), a_s.to(DEV), wq.to(DEV), w_s.to(DEV), off.to(DEV), ue8m0).cpu().float()
     want = ops.grouped_gemm_fp8(aq, a_s, wq, w_s, off).float()  # CPU oracle
@@ -52,8 +54,8 @@ def test_grouped_gemm_plain(counts, n, k, ue8m0, gemm_variant):
 @pytest.mark.parametrize("ue8m0", [False, True])
 @pytest.mark.parametrize("counts,inter,k", [([128], 128, 256), ([70, 200, 0, 3], 256, 384)])
 def test_grouped_gemm_swiglu_requant(counts, inter, k, ue8m0, gemm_variant):
-    if not ue8m0 and gemm_variant == "pair":
-        pytest.skip("the fp32-scale kernel has no CTA-pair form")
+    if not ue8m0 and gemm_variant != "single":
+        pytest.skip("the fp32-scale kernel has one form only")
     aq, a_s, wq, w_s, off = _ragged_problem(counts, 2 * inter, k, seed=inter + k, ue8m0=ue8m0)
     q, s = ops.grouped_gemm_fp8_swiglu(aq.to(DEV), a_s.to(DEV), wq.to(DEV), w_s.to(DEV), off.to(DEV), ue8m0)
     qc, sc = ops.grouped_gemm_fp8_swiglu(aq, a_s, wq, w_s, off, ue8m0)
@@ -90,8 +92,8 @@ def _fused_case(world, t, h, inter, e, k, seed, lo=0, ue8m0=False):
 @pytest.mark.parametrize("ue8m0", [False, True])
 @pytest.mark.parametrize("world,lo", [(1, 0), (1, -1), (2, 0), (4, -1)])
 def test_fused_moe_fp8(world, lo, ue8m0, gemm_variant):
-    if not ue8m0 and gemm_variant == "pair":
-        pytest.skip("the fp32-scale kernel has no CTA-pair form")
+    if not ue8m0 and gemm_variant != "single":
+        pytest.skip("the fp32-scale kernel has one form only")
     t, h, inter, e, k = 48, 512, 256, 8, 2
     xs, topk, wts, (w1q, s1, w2q, s2) = _fused_case(world, t, h, inter, e, k, seed=100 + world, lo=lo, ue8m0=ue8m0)
     cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, timeout_ms=3000.0)

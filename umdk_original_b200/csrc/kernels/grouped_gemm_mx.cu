@@ -30,6 +30,15 @@
 // tensor core already works on the next tile).
 // Every mbarrier wait is bounded; a role that gives up sets a shared abort word that releases
 // the others, a status word is recorded and the CTA frees its TMEM and returns.
+//
+// SWAP = true is the form for small experts (about a tile of rows or less each).  tcgen05.mma fixes
+// M at 128 but lets N go in steps of 16, so a tile that holds 2 rows of an expert costs as much as a
+// full one when the rows are the M operand.  With the operands exchanged the two 128-row halves of the
+// weight tile are the M operands of two MMAs, the token rows are the N operand with N = rows rounded up
+// to 16, and the accumulators hold the tile transposed: lane = output feature, column = token, first
+// half of the features in columns [0, 128), second half in [128, 256).  Shared-memory tiles, TMA loads
+// and scale-factor columns are the same (the scale-factor layouts of A and B coincide); only the MMA
+// issue and the epilogue, which transposes through shared memory, differ.
 #include "gemm_common.cuh"
 
 namespace cam {
@@ -46,6 +55,8 @@ constexpr int kMxStgBytes = BM * kMxStgPitch;  // 34816
 constexpr int kMxSmemCtrl = 1024;
 constexpr int kMxSmem = kStages * kStageBytes + kMxStgBytes + kMxSmemCtrl;
 static_assert(kMxSmem <= 232448, "exceeds the shared memory of one CTA");
+constexpr int kMxTPitchF = 132;  // SWAP, SwiGLU epilogue: floats between the staging rows of two tokens (64 x 132 x 4 bytes)
+static_assert(64 * kMxTPitchF * 4 <= kMxStgBytes, "transposed fp32 staging of 64 tokens must fit the staging area");
 constexpr uint32_t kMxTmemCols = 512;
 constexpr uint32_t kMxSfCol0 = 256, kMxSfStride = 16;
 // Register re-partitioning (setmaxnreg): the CTA is launched with kMxLaunchRegs per thread (what
@@ -60,6 +71,7 @@ __device__ __forceinline__ uint32_t ue8m0_word(float scale) {
     return ((__float_as_uint(scale) >> 23) & 0xFFu) * 0x01010101u;
 }
 
+template <bool SWAP>
 __global__ void __launch_bounds__(kMxThreads, 1)
 grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                           const GroupedGemmParams p) {
@@ -152,9 +164,21 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                     const uint64_t bdesc = umma_desc_k_sw128(sa + kATile);
                     const uint32_t sfa = tmem_base + kMxSfCol0 + s * kMxSfStride;
                     const uint32_t sfb = sfa + 4u;
+                    if constexpr (SWAP) {
+                        // weights are the M operand (two halves, two accumulators), the tile's rows the N operand
+                        const uint32_t idesc_t = umma_idesc_mxf8(128u, static_cast<uint32_t>((rows + 15) & ~15));
+                        const uint64_t bdesc_hi = umma_desc_k_sw128(sa + kATile + kBTile / 2);
 #pragma unroll
-                    for (int k = 0; k < BK / 32; ++k)  // 32 bytes (= 2 x 16) further along K inside the swizzle atom
-                        tc_mma_mxf8(tmem_base, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) ? 1u : 0u, sfa, sfb);
+                        for (int k = 0; k < BK / 32; ++k) {
+                            tc_mma_mxf8(tmem_base, bdesc + 2u * k, adesc + 2u * k, idesc_t, (kb | k) ? 1u : 0u, sfb, sfa);
+                            tc_mma_mxf8(tmem_base + 128u, bdesc_hi + 2u * k, adesc + 2u * k, idesc_t, (kb | k) ? 1u : 0u,
+                                        sfb + 4u, sfa);
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < BK / 32; ++k)  // 32 bytes (= 2 x 16) further along K inside the swizzle atom
+                            tc_mma_mxf8(tmem_base, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) ? 1u : 0u, sfa, sfb);
+                    }
                     tc_commit(&bar_empty[s]);  // stage (smem and scale columns) reusable once these MMAs retire
                 }
                 if (!ok) break;
@@ -240,16 +264,67 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             tc_fence_after_sync();
             const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + cq * 32;
             uint32_t v0[32], v1[32];  // columns cq*32.. of the first 128-column half, same of the second
-            tmem_ld_32x32b_x32(t0, v0);
-            tmem_ld_32x32b_x32(t0 + 128, v1);
-            tc_wait_ld_regs(v0);
-            tc_wait_ld_regs(v1);
+            // SWAP: lane r is an output feature and these are tokens cq*32.. of the tile; column quarters past the
+            // tile's rows were not written by its MMAs and are not read
+            const bool has_cols = !SWAP || cq * 32 < rows;
+            if (has_cols) {
+                tmem_ld_32x32b_x32(t0, v0);
+                tmem_ld_32x32b_x32(t0 + 128, v1);
+                tc_wait_ld_regs(v0);
+                tc_wait_ld_regs(v1);
+            }
             // the tile now lives in registers: hand the accumulator back to the MMA issuer
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty);
 
-            if (p.mode == 1) {
+            if (SWAP && p.mode == 1) {
+                // SwiGLU: lane r holds gate feature nt*128 + r (first accumulator) and the matching up feature (second)
+                // for 32 tokens.  The 128 lanes are one 1x128 quantisation block of every token, so the tile is
+                // transposed through shared memory, 64 tokens at a time as fp32 [token][feature], and then 8 threads
+                // per token take the maximum, quantise and store 16 bytes each: one 128-byte segment per token.
+                const int ia = p.n_dim / 2;
+                if (has_cols) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {  // the product replaces the gate value
+                        const float g = __uint_as_float(v0[j]);
+                        v0[j] = __float_as_uint((g / (1.f + expf(-g))) * __uint_as_float(v1[j]));
+                    }
+                }
+                float* stgf = reinterpret_cast<float*>(stg);
+                const int te = ew * 32 + static_cast<int>(lane);  // 0..511
+                const int tl = te >> 3, pc = te & 7;
+                for (int half = 0; half * 64 < rows; ++half) {  // the same trip count in every thread of the CTA
+                    if (has_cols && (cq >> 1) == half) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) stgf[((cq & 1) * 32 + j) * kMxTPitchF + r] = __uint_as_float(v0[j]);
+                    }
+                    named_bar_sync(1, kMxEpiThreads);
+                    const int tok = half * 64 + tl;
+                    const float4* src = reinterpret_cast<const float4*>(stgf + tl * kMxTPitchF + pc * 16);
+                    const float4 x0 = src[0], x1 = src[1], x2 = src[2], x3 = src[3];
+                    float amax = fmaxf(fmaxf(fmaxf(fabsf(x0.x), fabsf(x0.y)), fmaxf(fabsf(x0.z), fabsf(x0.w))),
+                                       fmaxf(fmaxf(fabsf(x1.x), fabsf(x1.y)), fmaxf(fabsf(x1.z), fabsf(x1.w))));
+                    amax = fmaxf(amax, fmaxf(fmaxf(fmaxf(fabsf(x2.x), fabsf(x2.y)), fmaxf(fabsf(x2.z), fabsf(x2.w))),
+                                             fmaxf(fmaxf(fabsf(x3.x), fabsf(x3.y)), fmaxf(fabsf(x3.z), fabsf(x3.w)))));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 4));
+                    float scale, inv;
+                    ue8m0_scale(amax, scale, inv);
+                    if (tok < rows) {
+                        uint4 o;
+                        o.x = pack_e4m3x4(x0.x * inv, x0.y * inv, x0.z * inv, x0.w * inv);
+                        o.y = pack_e4m3x4(x1.x * inv, x1.y * inv, x1.z * inv, x1.w * inv);
+                        o.z = pack_e4m3x4(x2.x * inv, x2.y * inv, x2.z * inv, x2.w * inv);
+                        o.w = pack_e4m3x4(x3.x * inv, x3.y * inv, x3.z * inv, x3.w * inv);
+                        const size_t orow = static_cast<size_t>(row0 + tok);
+                        *reinterpret_cast<uint4*>(p.act_q + orow * ia + nt * 128 + pc * 16) = o;
+                        if (pc == 0) p.act_s[orow * (ia / 128) + nt] = scale;
+                    }
+                    named_bar_sync(1, kMxEpiThreads);  // the staging area may be overwritten
+                }
+            } else if (p.mode == 1) {
                 // SwiGLU on matching gate/up columns, then 1x128 fp8 requantisation (power-of-two scale).
                 const int ia = p.n_dim / 2;
                 float act[32];
@@ -302,12 +377,22 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                 auto push_half = [&](const uint32_t (&v)[32], int c0) {
                     if (p.bulk_push && cq == 0) bulk_wait_group_read<0>();  // the previous copies have read the staging area
                     named_bar_sync(1, kMxEpiThreads);  // the previous half has left the staging area
+                    if constexpr (SWAP) {
+                        // transposed tile: this lane's feature r of tokens cq*32.., one bf16 per staging row
+                        if (has_cols) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 8)
-                        *reinterpret_cast<uint4*>(srow + cq * 64 + j * 2) =
-                            pack_bf16x8(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
-                                        __uint_as_float(v[j + 3]), __uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]),
-                                        __uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                            for (int j = 0; j < 32; ++j)
+                                *reinterpret_cast<__nv_bfloat16*>(stg + (cq * 32 + j) * kMxStgPitch + r * 2) =
+                                    __float2bfloat16_rn(__uint_as_float(v[j]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8)
+                            *reinterpret_cast<uint4*>(srow + cq * 64 + j * 2) =
+                                pack_bf16x8(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                                            __uint_as_float(v[j + 3]), __uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]),
+                                            __uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                    }
                     if (cq == 0)
                         *reinterpret_cast<uint64_t*>(srow + 256) =
                             (orow != nullptr) ? reinterpret_cast<uint64_t>(orow + c0) : 0ull;
@@ -370,8 +455,18 @@ extern "C" int cam_grouped_gemm_mx_smem_bytes(void) { return cam::kMxSmem; }
 extern "C" int cam_launch_grouped_gemm_mxfp8(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
                                              const CUtensorMap* tmap_b, int grid, cudaStream_t stream) {
     static cam::SmemLimitCache limit;
-    cudaError_t e = limit.ensure(cam::grouped_gemm_mxfp8_kernel, cam::kMxSmem);
+    cudaError_t e = limit.ensure(cam::grouped_gemm_mxfp8_kernel<false>, cam::kMxSmem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    cam::grouped_gemm_mxfp8_kernel<<<grid, cam::kMxThreads, cam::kMxSmem, stream>>>(*tmap_a, *tmap_b, *p);
+    cam::grouped_gemm_mxfp8_kernel<false><<<grid, cam::kMxThreads, cam::kMxSmem, stream>>>(*tmap_a, *tmap_b, *p);
+    return static_cast<int>(cudaGetLastError());
+}
+
+// Operands exchanged (weights as the M operand): the form for experts of about one tile of rows or less.
+extern "C" int cam_launch_grouped_gemm_mxfp8_swap(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
+                                                  const CUtensorMap* tmap_b, int grid, cudaStream_t stream) {
+    static cam::SmemLimitCache limit;
+    cudaError_t e = limit.ensure(cam::grouped_gemm_mxfp8_kernel<true>, cam::kMxSmem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    cam::grouped_gemm_mxfp8_kernel<true><<<grid, cam::kMxThreads, cam::kMxSmem, stream>>>(*tmap_a, *tmap_b, *p);
     return static_cast<int>(cudaGetLastError());
 }

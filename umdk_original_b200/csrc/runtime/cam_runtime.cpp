@@ -735,6 +735,9 @@ static int make_tmap(CamBuffer* cache_owner, CUtensorMap* out, const void* base,
     return 0;
 }
 
+// Mean rows per expert below which the block-scaled GEMM runs with its operands exchanged (0 = never by default).
+constexpr int kSwapRowsPerExpert = 0;
+
 static int grouped_gemm_impl(CamBuffer* b, const void* a_q, const float* a_scales, int a_rows, const void* w_q,
                              const float* w_scales, const int* expert_offsets, int num_experts, int n_dim, int k_dim,
                              int mode, void* out_bf16, void* act_q, float* act_s, const int* row_src, int topk,
@@ -808,8 +811,13 @@ static int grouped_gemm_impl(CamBuffer* b, const void* a_q, const float* a_scale
     // UMDK_CAM_GEMM_PAIR=0/1 forces the choice.
     bool pair = ue8m0 && rows_per_expert_hint >= 384;
     if (const char* env = getenv("UMDK_CAM_GEMM_PAIR")) pair = ue8m0 && env[0] == '1';
+    // Small experts (a tile of rows or less each) take the kernel with the operands exchanged, whose tensor-core
+    // time follows the rows actually present instead of whole 128-row tiles; UMDK_CAM_GEMM_SWAP=0/1 forces the choice.
+    bool swap = ue8m0 && !pair && rows_per_expert_hint < kSwapRowsPerExpert;
+    if (const char* env = getenv("UMDK_CAM_GEMM_SWAP")) swap = ue8m0 && !pair && env[0] == '1';
     const int rc = !ue8m0 ? cam_launch_grouped_gemm_fp8(&p, &ta, &tb, sms, stream)
                    : pair ? cam_launch_grouped_gemm_mxfp8_pair(&p, &ta, &tb, sms, stream)
+                   : swap ? cam_launch_grouped_gemm_mxfp8_swap(&p, &ta, &tb, sms, stream)
                           : cam_launch_grouped_gemm_mxfp8(&p, &ta, &tb, sms, stream);
     CAM_CHECK(rc == 0, "grouped_gemm launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
     return 0;

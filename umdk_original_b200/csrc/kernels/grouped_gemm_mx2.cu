@@ -22,7 +22,8 @@ namespace cam {
 constexpr int kP2Threads = 768;
 constexpr int kP2EpiThreads = 512;
 constexpr int kP2SfWarp0 = 4, kP2EpiWarp0 = 8;
-constexpr int kP2Stages = 6;
+constexpr int kP2Stages = 6;        // modes 0 / 1
+constexpr int kP2StagesSend = 4;    // mode 2 with two staging buffers
 constexpr int kP2ATile = BM * BK;          // this CTA's 128 rows of A, 16 KiB
 constexpr int kP2BTile = 128 * BK;         // this CTA's half of the 256-row B tile, 16 KiB
 constexpr int kP2StageBytes = kP2ATile + kP2BTile;
@@ -33,8 +34,14 @@ constexpr int kP2StageBytes = kP2ATile + kP2BTile;
 constexpr int kP2StgPitch = 272;
 constexpr int kP2StgBytes = BM * kP2StgPitch;  // 34816
 constexpr int kP2SmemCtrl = 1024;
-constexpr int kP2Smem = kP2Stages * kP2StageBytes + kP2StgBytes + kP2SmemCtrl;
-static_assert(kP2Smem <= 232448, "exceeds the shared memory of one CTA");
+// The combine-send epilogue (mode 2) is bound by how fast its rows leave over NVLink.  With one staging buffer the
+// epilogue cannot convert the next half tile while the copies of the previous one are still reading shared memory,
+// and the link idles in between; the send form of the kernel therefore has TWO staging buffers and pays for them
+// with two pipeline stages (its reduction is short, K = intermediate size, and the mainloop has slack there).
+template <int NS, int NSTG>
+constexpr int p2_smem() { return NS * kP2StageBytes + NSTG * kP2StgBytes + kP2SmemCtrl; }
+constexpr int kP2Smem = p2_smem<kP2Stages, 1>();
+static_assert(kP2Smem <= 232448 && p2_smem<kP2StagesSend, 2>() <= 232448, "exceeds the shared memory of one CTA");
 constexpr uint32_t kP2TmemCols = 512;
 constexpr uint32_t kP2SfCol0 = 256, kP2SfStride = 16;
 // Register re-partitioning (setmaxnreg): the CTA is launched with kP2LaunchRegs per thread (what
@@ -49,6 +56,7 @@ __device__ __forceinline__ uint32_t ue8m0_word2(float scale) {
     return ((__float_as_uint(scale) >> 23) & 0xFFu) * 0x01010101u;
 }
 
+template <int NS, int NSTG>
 __global__ void __launch_bounds__(kP2Threads, 1)
 grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                           const GroupedGemmParams p) {
@@ -57,12 +65,12 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
         if (threadIdx.x == 0) gemm_record_status(p.status, CAM_ERR_BAD_INDEX, 4, static_cast<int>(smem_u32(smem) & 1023u));
         return;
     }
-    uint8_t* stg = smem + kP2Stages * kP2StageBytes;
-    uint8_t* ctrl = stg + kP2StgBytes;
+    uint8_t* stg = smem + NS * kP2StageBytes;
+    uint8_t* ctrl = stg + NSTG * kP2StgBytes;
     uint64_t* bar_full = reinterpret_cast<uint64_t*>(ctrl);   // first CTA: TMA bytes of both CTAs' stage have landed
-    uint64_t* bar_sf = bar_full + kP2Stages;                  // first CTA: scale factors of both CTAs are in TMEM
-    uint64_t* bar_empty = bar_sf + kP2Stages;                 // each CTA: the MMAs that read a stage have retired
-    uint64_t* bar_tfull = bar_empty + kP2Stages;              // each CTA: accumulator of a tile is complete
+    uint64_t* bar_sf = bar_full + NS;                  // first CTA: scale factors of both CTAs are in TMEM
+    uint64_t* bar_empty = bar_sf + NS;                 // each CTA: the MMAs that read a stage have retired
+    uint64_t* bar_tfull = bar_empty + NS;              // each CTA: accumulator of a tile is complete
     uint64_t* bar_tempty = bar_tfull + 1;                     // first CTA: both accumulators have been drained
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -78,7 +86,7 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
     const int nblk = p.n_dim / 128;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kP2Stages; ++s) {
+        for (int s = 0; s < NS; ++s) {
             mbar_init(&bar_full[s], 1);
             mbar_init(&bar_sf[s], 8);
             mbar_init(&bar_empty[s], 1);
@@ -114,7 +122,7 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
                 const int my_arow = row0 + static_cast<int>(cta) * BM;
                 const int my_brow = cta ? brow_hi : brow_lo;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const uint32_t s = it % kP2Stages, ph = (it / kP2Stages) & 1u;
+                    const uint32_t s = it % NS, ph = (it / NS) & 1u;
                     if (!mbar_wait_bounded(&bar_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
                     uint8_t* sa = smem + s * kP2StageBytes;
                     if (cta == 0) mbar_arrive_expect_tx(&bar_full[s], 2 * kP2StageBytes);
@@ -137,7 +145,7 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
                 if (!mbar_wait_bounded(bar_tempty, (tcount & 1u) ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const uint32_t s = it % kP2Stages, ph = (it / kP2Stages) & 1u;
+                    const uint32_t s = it % NS, ph = (it / NS) & 1u;
                     if (!mbar_wait_bounded(&bar_sf[s], ph, abort_flag)) { ok = false; break; }
                     if (!mbar_wait_bounded(&bar_full[s], ph, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
@@ -195,7 +203,7 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
                 uint32_t wd[6];
 #pragma unroll
                 for (int j = 0; j < 6; ++j) { wd[j] = ue8m0_word2(c[j]); c[j] = n1[j]; }
-                const uint32_t s = it % kP2Stages, ph = (it / kP2Stages) & 1u;
+                const uint32_t s = it % NS, ph = (it / NS) & 1u;
                 const bool got = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, abort_flag);
                 if (!__all_sync(0xFFFFFFFFu, got)) { ok = false; break; }
                 tc_fence_after_sync();
@@ -228,7 +236,7 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
         const int cq = ew >> 2;   // which 32-column quarter of each 128-column half
         const int r = q * 32 + static_cast<int>(lane);
         TileWalkerT<2 * BM> w(p.expert_offsets, p.num_experts, n_tiles);
-        uint32_t tcount = 0;
+        uint32_t tcount = 0, halves = 0;
         int e, mt, nt, row0, rows;
         bool ok = true;
         for (int tile = pair_id; ok && w.locate(tile, e, mt, nt, row0, rows); tile += num_pairs, ++tcount) {
@@ -301,10 +309,13 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
                 // 256-byte row segments: 16 lanes store one row, so a warp instruction writes two whole
                 // segments (local or over NVLink) instead of 16-byte pieces of 32 different rows.  The row's
                 // destination address travels in the 16 spare bytes at the end of its staging row.
-                uint8_t* srow = stg + r * kP2StgPitch;
                 auto push_half = [&](const uint32_t (&v)[32], int c0) {
-                    if (p.bulk_push && cq == 0) bulk_wait_group_read<0>();  // the previous copies have read the staging area
-                    named_bar_sync(1, kP2EpiThreads);  // the previous half has left the staging area
+                    // with two staging buffers the copies of the previous half may still be reading theirs
+                    uint8_t* sbuf = stg + (NSTG == 2 ? (halves & 1u) * kP2StgBytes : 0u);
+                    uint8_t* srow = sbuf + r * kP2StgPitch;
+                    ++halves;
+                    if (p.bulk_push && cq == 0) bulk_wait_group_read<NSTG - 1>();  // the copies that read this buffer are done with it
+                    named_bar_sync(1, kP2EpiThreads);  // the half that used this buffer has left it
 #pragma unroll
                     for (int j = 0; j < 32; j += 8)
                         *reinterpret_cast<uint4*>(srow + cq * 64 + j * 2) =
@@ -327,7 +338,7 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
                     const int seg = static_cast<int>(lane & 15u) * 16;
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const uint8_t* src = stg + (ew * 8 + 2 * i + static_cast<int>(lane >> 4)) * kP2StgPitch;
+                        const uint8_t* src = sbuf + (ew * 8 + 2 * i + static_cast<int>(lane >> 4)) * kP2StgPitch;
                         const uint64_t dst = *reinterpret_cast<const uint64_t*>(src + 256);
                         if (dst != 0ull)
                             st_na_v4(reinterpret_cast<uint8_t*>(dst) + seg, *reinterpret_cast<const uint4*>(src + seg));
@@ -371,56 +382,64 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
 
 extern "C" int cam_grouped_gemm_mx_pair_smem_bytes(void) { return cam::kP2Smem; }
 
-// Number of CTA pairs of this kernel that can be resident on the current device at once.
-extern "C" int cam_grouped_gemm_mx_pair_max_clusters(void) {
-    static cam::SmemLimitCache limit;
-    if (limit.ensure(cam::grouped_gemm_mxfp8_pair_kernel, cam::kP2Smem) != cudaSuccess) return -1;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(2);
-    cfg.blockDim = dim3(cam::kP2Threads);
-    cfg.dynamicSmemBytes = cam::kP2Smem;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, cam::grouped_gemm_mxfp8_pair_kernel, &cfg) != cudaSuccess) return -1;
-    return n;
-}
+namespace {
 
-extern "C" int cam_launch_grouped_gemm_mxfp8_pair(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
-                                             const CUtensorMap* tmap_b, int grid, cudaStream_t stream) {
-    static cam::SmemLimitCache limit;
-    cudaError_t e = limit.ensure(cam::grouped_gemm_mxfp8_pair_kernel, cam::kP2Smem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    cudaLaunchConfig_t cfg = {};
+template <int NS, int NSTG>
+void pair_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int grid, cudaStream_t stream) {
+    cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid & ~1));  // whole pairs only
     cfg.blockDim = dim3(cam::kP2Threads);
-    cfg.dynamicSmemBytes = cam::kP2Smem;
+    cfg.dynamicSmemBytes = cam::p2_smem<NS, NSTG>();
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    // Not every SM can always be paired inside its GPC: run exactly as many pairs as fit at once.
+}
+
+// Number of CTA pairs of one form of the kernel that can be resident on the current device at once (cached per device).
+template <int NS, int NSTG>
+int pair_max_clusters() {
+    static cam::SmemLimitCache limit;
+    if (limit.ensure(cam::grouped_gemm_mxfp8_pair_kernel<NS, NSTG>, cam::p2_smem<NS, NSTG>()) != cudaSuccess) return -1;
     static int max_pairs[64] = {0};
     int dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
-        if (max_pairs[dev] == 0) {
-            int n = 0;
-            if (cudaOccupancyMaxActiveClusters(&n, cam::grouped_gemm_mxfp8_pair_kernel, &cfg) == cudaSuccess && n > 0)
-                max_pairs[dev] = n;
-            else
-                max_pairs[dev] = -1;
-        }
-        if (max_pairs[dev] > 0 && 2 * max_pairs[dev] < static_cast<int>(cfg.gridDim.x))
-            cfg.gridDim = dim3(static_cast<unsigned>(2 * max_pairs[dev]));
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+    if (max_pairs[dev] == 0) {
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attr[1];
+        pair_config<NS, NSTG>(cfg, attr, 2, nullptr);
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, cam::grouped_gemm_mxfp8_pair_kernel<NS, NSTG>, &cfg) == cudaSuccess && n > 0)
+            max_pairs[dev] = n;
+        else
+            max_pairs[dev] = -1;
     }
-    return static_cast<int>(cudaLaunchKernelEx(&cfg, cam::grouped_gemm_mxfp8_pair_kernel, *tmap_a, *tmap_b, *p));
+    return max_pairs[dev];
+}
+
+template <int NS, int NSTG>
+int launch_pair(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a, const CUtensorMap* tmap_b, int grid,
+                cudaStream_t stream) {
+    // Not every SM can always be paired inside its GPC: run exactly as many pairs as fit at once.
+    const int fit = pair_max_clusters<NS, NSTG>();
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    pair_config<NS, NSTG>(cfg, attr, grid, stream);
+    if (fit > 0 && 2 * fit < static_cast<int>(cfg.gridDim.x)) cfg.gridDim = dim3(static_cast<unsigned>(2 * fit));
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, cam::grouped_gemm_mxfp8_pair_kernel<NS, NSTG>, *tmap_a, *tmap_b, *p));
+}
+
+}  // namespace
+
+extern "C" int cam_grouped_gemm_mx_pair_max_clusters(void) { return pair_max_clusters<cam::kP2Stages, 1>(); }
+
+// `two_staging` selects the send form (mode 2 only): two staging buffers, four pipeline stages.
+extern "C" int cam_launch_grouped_gemm_mxfp8_pair(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
+                                                  const CUtensorMap* tmap_b, int grid, int two_staging,
+                                                  cudaStream_t stream) {
+    if (two_staging && p->mode == 2) return launch_pair<cam::kP2StagesSend, 2>(p, tmap_a, tmap_b, grid, stream);
+    return launch_pair<cam::kP2Stages, 1>(p, tmap_a, tmap_b, grid, stream);
 }

@@ -53,8 +53,13 @@ constexpr int kMxSfWarp0 = 4, kMxEpiWarp0 = 8;
 constexpr int kMxStgPitch = 272;
 constexpr int kMxStgBytes = BM * kMxStgPitch;  // 34816
 constexpr int kMxSmemCtrl = 1024;
-constexpr int kMxSmem = kStages * kStageBytes + kMxStgBytes + kMxSmemCtrl;
-static_assert(kMxSmem <= 232448, "exceeds the shared memory of one CTA");
+// The combine-send form (mode 2) trades one pipeline stage for a second staging buffer, so that the epilogue can
+// convert the next half tile while the copies of the previous one are still reading theirs.
+constexpr int kMxStagesSend = 3;
+template <int NS, int NSTG>
+constexpr int mx_smem() { return NS * kStageBytes + NSTG * kMxStgBytes + kMxSmemCtrl; }
+constexpr int kMxSmem = mx_smem<kStages, 1>();
+static_assert(kMxSmem <= 232448 && mx_smem<kMxStagesSend, 2>() <= 232448, "exceeds the shared memory of one CTA");
 constexpr int kMxTPitchF = 132;  // SWAP, SwiGLU epilogue: floats between the staging rows of two tokens (64 x 132 x 4 bytes)
 static_assert(64 * kMxTPitchF * 4 <= kMxStgBytes, "transposed fp32 staging of 64 tokens must fit the staging area");
 constexpr uint32_t kMxTmemCols = 512;
@@ -71,7 +76,7 @@ __device__ __forceinline__ uint32_t ue8m0_word(float scale) {
     return ((__float_as_uint(scale) >> 23) & 0xFFu) * 0x01010101u;
 }
 
-template <bool SWAP>
+template <bool SWAP, int NS, int NSTG>
 __global__ void __launch_bounds__(kMxThreads, 1)
 grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                           const GroupedGemmParams p) {
@@ -80,12 +85,12 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         if (threadIdx.x == 0) gemm_record_status(p.status, CAM_ERR_BAD_INDEX, 4, static_cast<int>(smem_u32(smem) & 1023u));
         return;
     }
-    uint8_t* stg = smem + kStages * kStageBytes;
-    uint8_t* ctrl = stg + kMxStgBytes;
+    uint8_t* stg = smem + NS * kStageBytes;
+    uint8_t* ctrl = stg + NSTG * kMxStgBytes;
     uint64_t* bar_full = reinterpret_cast<uint64_t*>(ctrl);   // TMA bytes of a stage have landed
-    uint64_t* bar_sf = bar_full + kStages;                    // scale factors of a stage are in TMEM
-    uint64_t* bar_empty = bar_sf + kStages;                   // the MMAs that read a stage have retired
-    uint64_t* bar_tfull = bar_empty + kStages;                // accumulator of a tile is complete
+    uint64_t* bar_sf = bar_full + NS;                    // scale factors of a stage are in TMEM
+    uint64_t* bar_empty = bar_sf + NS;                   // the MMAs that read a stage have retired
+    uint64_t* bar_tfull = bar_empty + NS;                // accumulator of a tile is complete
     uint64_t* bar_tempty = bar_tfull + 1;                     // accumulator has been drained
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -98,7 +103,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     const int nblk = p.n_dim / 128;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < NS; ++s) {
             mbar_init(&bar_full[s], 1);
             mbar_init(&bar_sf[s], 4);
             mbar_init(&bar_empty[s], 1);
@@ -132,7 +137,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                 const int brow_lo = e * p.n_dim + ((p.mode == 1) ? nt * 128 : nt * BN);
                 const int brow_hi = (p.mode == 1) ? (e * p.n_dim + p.n_dim / 2 + nt * 128) : (brow_lo + 128);
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    const uint32_t s = it % NS, ph = (it / NS) & 1u;
                     if (!mbar_wait_bounded(&bar_empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
                     uint8_t* sa = smem + s * kStageBytes;
                     mbar_arrive_expect_tx(&bar_full[s], kStageBytes);
@@ -155,7 +160,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                 if (!mbar_wait_bounded(bar_tempty, (tcount & 1u) ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    const uint32_t s = it % NS, ph = (it / NS) & 1u;
                     if (!mbar_wait_bounded(&bar_sf[s], ph, abort_flag)) { ok = false; break; }
                     if (!mbar_wait_bounded(&bar_full[s], ph, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
@@ -223,7 +228,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                 uint32_t wd[6];
 #pragma unroll
                 for (int j = 0; j < 6; ++j) { wd[j] = ue8m0_word(c[j]); c[j] = n1[j]; }
-                const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                const uint32_t s = it % NS, ph = (it / NS) & 1u;
                 const bool got = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, abort_flag);
                 if (!__all_sync(0xFFFFFFFFu, got)) { ok = false; break; }
                 tc_fence_after_sync();
@@ -253,7 +258,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         const int cq = ew >> 2;   // which 32-column quarter of each 128-column half
         const int r = q * 32 + static_cast<int>(lane);
         TileWalker w(p.expert_offsets, p.num_experts, n_tiles);
-        uint32_t tcount = 0;
+        uint32_t tcount = 0, halves = 0;
         int e, mt, nt, row0, rows;
         bool ok = true;
         for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
@@ -373,16 +378,19 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                 // 256-byte row segments: 16 lanes store one row, so a warp instruction writes two whole
                 // segments (local or over NVLink) instead of 16-byte pieces of 32 different rows.  The row's
                 // destination address travels in the 16 spare bytes at the end of its staging row.
-                uint8_t* srow = stg + r * kMxStgPitch;
                 auto push_half = [&](const uint32_t (&v)[32], int c0) {
-                    if (p.bulk_push && cq == 0) bulk_wait_group_read<0>();  // the previous copies have read the staging area
-                    named_bar_sync(1, kMxEpiThreads);  // the previous half has left the staging area
+                    // with two staging buffers the copies of the previous half may still be reading theirs
+                    uint8_t* sbuf = stg + (NSTG == 2 ? (halves & 1u) * kMxStgBytes : 0u);
+                    uint8_t* srow = sbuf + r * kMxStgPitch;
+                    ++halves;
+                    if (p.bulk_push && cq == 0) bulk_wait_group_read<NSTG - 1>();  // the copies that read this buffer are done with it
+                    named_bar_sync(1, kMxEpiThreads);  // the half that used this buffer has left it
                     if constexpr (SWAP) {
                         // transposed tile: this lane's feature r of tokens cq*32.., one bf16 per staging row
                         if (has_cols) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j)
-                                *reinterpret_cast<__nv_bfloat16*>(stg + (cq * 32 + j) * kMxStgPitch + r * 2) =
+                                *reinterpret_cast<__nv_bfloat16*>(sbuf + (cq * 32 + j) * kMxStgPitch + r * 2) =
                                     __float2bfloat16_rn(__uint_as_float(v[j]));
                         }
                     } else {
@@ -409,7 +417,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                     const int seg = static_cast<int>(lane & 15u) * 16;
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const uint8_t* src = stg + (ew * 8 + 2 * i + static_cast<int>(lane >> 4)) * kMxStgPitch;
+                        const uint8_t* src = sbuf + (ew * 8 + 2 * i + static_cast<int>(lane >> 4)) * kMxStgPitch;
                         const uint64_t dst = *reinterpret_cast<const uint64_t*>(src + 256);
                         if (dst != 0ull)
                             st_na_v4(reinterpret_cast<uint8_t*>(dst) + seg, *reinterpret_cast<const uint4*>(src + seg));
@@ -452,21 +460,27 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
 
 extern "C" int cam_grouped_gemm_mx_smem_bytes(void) { return cam::kMxSmem; }
 
-extern "C" int cam_launch_grouped_gemm_mxfp8(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
-                                             const CUtensorMap* tmap_b, int grid, cudaStream_t stream) {
+namespace {
+template <bool SWAP, int NS, int NSTG>
+int launch_mx(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a, const CUtensorMap* tmap_b, int grid,
+              cudaStream_t stream) {
     static cam::SmemLimitCache limit;
-    cudaError_t e = limit.ensure(cam::grouped_gemm_mxfp8_kernel<false>, cam::kMxSmem);
+    constexpr int smem = cam::mx_smem<NS, NSTG>();
+    cudaError_t e = limit.ensure(cam::grouped_gemm_mxfp8_kernel<SWAP, NS, NSTG>, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    cam::grouped_gemm_mxfp8_kernel<false><<<grid, cam::kMxThreads, cam::kMxSmem, stream>>>(*tmap_a, *tmap_b, *p);
+    cam::grouped_gemm_mxfp8_kernel<SWAP, NS, NSTG><<<grid, cam::kMxThreads, smem, stream>>>(*tmap_a, *tmap_b, *p);
     return static_cast<int>(cudaGetLastError());
 }
+}  // namespace
 
-// Operands exchanged (weights as the M operand): the form for experts of about one tile of rows or less.
-extern "C" int cam_launch_grouped_gemm_mxfp8_swap(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
-                                                  const CUtensorMap* tmap_b, int grid, cudaStream_t stream) {
-    static cam::SmemLimitCache limit;
-    cudaError_t e = limit.ensure(cam::grouped_gemm_mxfp8_kernel<true>, cam::kMxSmem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    cam::grouped_gemm_mxfp8_kernel<true><<<grid, cam::kMxThreads, cam::kMxSmem, stream>>>(*tmap_a, *tmap_b, *p);
-    return static_cast<int>(cudaGetLastError());
+// `swap`: operands exchanged (weights as the M operand), the form for experts of about one tile of rows or less.
+// `two_staging` (mode 2 only): two staging buffers in the combine-send epilogue, three pipeline stages.
+extern "C" int cam_launch_grouped_gemm_mxfp8(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
+                                             const CUtensorMap* tmap_b, int grid, int swap, int two_staging,
+                                             cudaStream_t stream) {
+    const bool send = two_staging && p->mode == 2;
+    if (swap) return send ? launch_mx<true, cam::kMxStagesSend, 2>(p, tmap_a, tmap_b, grid, stream)
+                          : launch_mx<true, cam::kStages, 1>(p, tmap_a, tmap_b, grid, stream);
+    return send ? launch_mx<false, cam::kMxStagesSend, 2>(p, tmap_a, tmap_b, grid, stream)
+                : launch_mx<false, cam::kStages, 1>(p, tmap_a, tmap_b, grid, stream);
 }

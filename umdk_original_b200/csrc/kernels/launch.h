@@ -185,10 +185,8 @@ int cam_launch_grouped_gemm_fp8(const cam::GroupedGemmParams* p, const CUtensorM
                                 const CUtensorMap* tmap_b, int grid, cudaStream_t stream);
 int cam_grouped_gemm_smem_bytes(void);
 int cam_launch_grouped_gemm_mxfp8(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
-                                  const CUtensorMap* tmap_b, int grid, cudaStream_t stream);
+                                  const CUtensorMap* tmap_b, int grid, int swap, int two_staging, cudaStream_t stream);
 int cam_grouped_gemm_mx_smem_bytes(void);
-int cam_launch_grouped_gemm_mxfp8_swap(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
-                                       const CUtensorMap* tmap_b, int grid, cudaStream_t stream);
 int cam_launch_grouped_gemm_mxfp8_pair(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
                                        const CUtensorMap* tmap_b, int grid, int two_staging, cudaStream_t stream);
 int cam_grouped_gemm_mx_pair_smem_bytes(void);

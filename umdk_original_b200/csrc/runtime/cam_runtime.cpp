@@ -815,14 +815,15 @@ static int grouped_gemm_impl(CamBuffer* b, const void* a_q, const float* a_scale
     // time follows the rows actually present instead of whole 128-row tiles; UMDK_CAM_GEMM_SWAP=0/1 forces the choice.
     bool swap = ue8m0 && !pair && rows_per_expert_hint < kSwapRowsPerExpert;
     if (const char* env = getenv("UMDK_CAM_GEMM_SWAP")) swap = ue8m0 && !pair && env[0] == '1';
-    // The combine-send epilogue of the CTA-pair kernel overlaps converting a half tile with the copies of the previous
-    // one (two staging buffers, four pipeline stages); UMDK_CAM_GEMM_STAGING2=0 keeps the one-buffer, six-stage form.
-    bool two_staging = mode == 2 && p.bulk_push != 0;
-    if (const char* env = getenv("UMDK_CAM_GEMM_STAGING2")) two_staging = two_staging && env[0] == '1';
+    // The combine-send epilogue of the block-scaled kernels overlaps converting a half tile with the copies of the previous
+    // one (two staging buffers, paid for with pipeline stages); UMDK_CAM_GEMM_STAGING2=0 keeps the one-buffer form.
+    // On by default in the CTA-pair kernel only: the one-CTA kernel, used for small experts, lives on streaming weights
+    // and loses more from its fourth pipeline stage than the epilogue gains (measured on one GPU, 256 experts).
+    bool two_staging = mode == 2 && p.bulk_push != 0 && pair;
+    if (const char* env = getenv("UMDK_CAM_GEMM_STAGING2")) two_staging = mode == 2 && p.bulk_push != 0 && env[0] == '1';
     const int rc = !ue8m0 ? cam_launch_grouped_gemm_fp8(&p, &ta, &tb, sms, stream)
                    : pair ? cam_launch_grouped_gemm_mxfp8_pair(&p, &ta, &tb, sms, two_staging ? 1 : 0, stream)
-                   : swap ? cam_launch_grouped_gemm_mxfp8_swap(&p, &ta, &tb, sms, stream)
-                          : cam_launch_grouped_gemm_mxfp8(&p, &ta, &tb, sms, stream);
+                          : cam_launch_grouped_gemm_mxfp8(&p, &ta, &tb, sms, swap ? 1 : 0, two_staging ? 1 : 0, stream);
     CAM_CHECK(rc == 0, "grouped_gemm launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
     return 0;
 }

@@ -69,7 +69,7 @@ typedef struct CamLayout {
     uint64_t off_barrier_flag;  // u32[CAM_MAX_RANKS]
     uint64_t off_ll_combine_flag;  // u32[CAM_MAX_RANKS]
     uint64_t off_count_matrix;  // i32[2][R][E]
-    uint64_t off_ll_cells;      // u64[2][R][E]   (cell index = src * E_local + local expert)
+    uint64_t off_ll_cells;      // u64[2][R * E_local]   (cell index = src * E_local + local expert)
     uint64_t off_recv_x;        // u8[capacity][hidden*2]
     uint64_t off_recv_scales;   // f32[capacity][hidden/128]
     uint64_t off_recv_src;      // i32[capacity][3]

@@ -45,3 +45,33 @@ def test_pipelined_steps_return_each_steps_own_record():
     with pytest.raises(AssertionError):
         runner.result(0)  # long overwritten
     buf.destroy()
+
+
+def test_layer_converts_fp32_block_scales_on_request():
+    """Weights with arbitrary fp32 block scales: the layer runs quantMode 3 as they are and quantMode 4 after the
+    one-time conversion; both agree with the oracle of their own weights."""
+    import umdk_original_b200 as u
+    from umdk_original_b200.models import TINY, FusedMoE
+    from umdk_original_b200.models.weights import random_fp8_experts
+    from umdk_original_b200.ops import reference as ref
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = TINY
+    t = cfg.tokens_per_rank
+    w = random_fp8_experts(cfg.num_experts, cfg.hidden, cfg.intermediate, ue8m0=False, seed=11)
+    x = (torch.randn(t, cfg.hidden, generator=torch.Generator().manual_seed(2))).to(torch.bfloat16)
+    for convert, mode in ((False, 3), (True, 4)):
+        buf = u.Buffer(None, u.CamConfig(num_experts=cfg.num_experts, max_tokens=t, hidden=cfg.hidden, topk=cfg.topk,
+                                         timeout_ms=2000.0), name=f"conv{mode}", device=dev, rank=0, num_ranks=1)
+        layer = FusedMoE(cfg, buf, weights=w, convert_scales=convert)
+        assert layer.quant_mode == mode
+        idx, wt = layer.route(x.to(dev))
+        out, nums = layer(x.to(dev), idx, wt)
+        buf.check()
+        lw = layer.weights
+        want, counts = ref.fused_moe_fp8_reference(x, idx.cpu(), wt.cpu(), lw.w1.cpu(), lw.s1.cpu(), lw.w2.cpu(),
+                                                   lw.s2.cpu(), ue8m0=mode == 4)
+        assert torch.equal(nums.cpu(), counts)
+        scale = want.float().abs().max().item()
+        assert (out.cpu().float() - want.float()).abs().max().item() <= 0.05 * scale + 1e-3
+        buf.destroy()

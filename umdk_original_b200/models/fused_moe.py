@@ -23,7 +23,11 @@ from .weights import ExpertWeights, from_reference_w8a8, random_fp8_experts, ran
 
 class FusedMoE(torch.nn.Module):
     def __init__(self, cfg: MoEConfig, buffer: Buffer, weights: Optional[ExpertWeights] = None, seed: int = 0,
-                 gate_weight: Optional[torch.Tensor] = None, exact_w8a8: bool = False):
+                 gate_weight: Optional[torch.Tensor] = None, exact_w8a8: bool = False,
+                 convert_scales: bool = False):
+        """``convert_scales``: fp8 weights that arrive with arbitrary fp32 block scales are moved onto
+        power-of-two scales once here (``ExpertWeights.with_power_of_two_scales``), so that the layer runs the
+        tensor-core block-scaled GEMMs (``quantMode=4``) instead of the software-scaled ones (``quantMode=3``)."""
         super().__init__()
         self.cfg, self.buffer = cfg, buffer
         self.rank, self.num_ranks = buffer.rank, buffer.num_ranks
@@ -50,6 +54,8 @@ class FusedMoE(torch.nn.Module):
             weights = random_fp8_experts(self.num_local, cfg.hidden, cfg.intermediate, device=dev,
                                          seed=seed * 1000 + self.rank)
         self.weights = weights.to(dev)
+        if convert_scales and self.weights.w1.dtype != torch.int8 and not self.weights.power_of_two_scales:
+            self.weights = self.weights.with_power_of_two_scales()
         # 0: int8 W8A8 in the reference's layout; 4: fp8 with power-of-two scales -> tcgen05 block-scaled
         # GEMMs; 3: fp8 with arbitrary fp32 scales
         if self.weights.w1.dtype == torch.int8:

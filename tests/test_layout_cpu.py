@@ -81,3 +81,39 @@ def test_size_hint_matches_the_layout(lib):
     lay = _layout(lib, 8, 256, 4096, 7168, 8, cfg.resolve_capacity(8), 128)
     hint = u.Buffer.get_size_hint(cfg, 8)
     assert abs(hint - lay.total_bytes) <= 0.02 * lay.total_bytes, (hint, lay.total_bytes)
+
+
+def _gemm_args(lib, **over):
+    """Argument list of cam_grouped_gemm_mxfp8 with dummy non-null pointers (validation runs before any CUDA call)."""
+    lib.cam_grouped_gemm_mxfp8.restype = ctypes.c_int
+    lib.cam_last_error.restype = ctypes.c_char_p
+    ptr = ctypes.c_void_p(0x1000)
+    a = dict(b=None, a_q=ptr, a_scales=ptr, a_rows=128, w_q=ptr, w_scales=ptr, offs=ptr, num_experts=1, n_dim=256,
+             k_dim=128, mode=0, out=ptr, act_q=None, act_s=None, row_src=None, topk=0, ll=0, stream=None)
+    a.update(over)
+    return [a["b"], a["a_q"], a["a_scales"], ctypes.c_int(a["a_rows"]), a["w_q"], a["w_scales"], a["offs"],
+            ctypes.c_int(a["num_experts"]), ctypes.c_int(a["n_dim"]), ctypes.c_int(a["k_dim"]), ctypes.c_int(a["mode"]),
+            a["out"], a["act_q"], a["act_s"], a["row_src"], ctypes.c_int(a["topk"]), ctypes.c_int(a["ll"]), a["stream"]]
+
+
+@pytest.mark.parametrize("over,word", [
+    (dict(a_q=None), "null operand"),
+    (dict(k_dim=100), "multiple of 128"),
+    (dict(mode=7), "mode"),
+    (dict(mode=1, n_dim=384, act_q=ctypes.c_void_p(0x1000), act_s=ctypes.c_void_p(0x1000)), "multiple of 256"),
+    (dict(mode=1), "act_q"),
+    (dict(mode=0, out=None), "output"),
+    (dict(mode=2), "row_src"),
+    (dict(num_experts=0), "empty problem"),
+])
+def test_grouped_gemm_rejects_bad_shapes_before_any_launch(lib, over, word):
+    rc = lib.cam_grouped_gemm_mxfp8(*_gemm_args(lib, **over))
+    assert rc != 0
+    assert word in lib.cam_last_error().decode(), lib.cam_last_error()
+
+
+def test_status_strings_cover_every_code(lib):
+    lib.cam_status_string.restype = ctypes.c_char_p
+    texts = [lib.cam_status_string(c).decode() for c in range(0, 9)]
+    assert texts[0] == "ok" and len(set(texts)) == len(texts) and "unknown status" not in texts
+    assert lib.cam_status_string(999).decode() == "unknown status"

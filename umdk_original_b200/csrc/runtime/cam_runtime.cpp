@@ -843,7 +843,7 @@ extern "C" int cam_grouped_gemm_mxfp8(CamBuffer* b, const void* a_q, const float
                                       float* act_s, const int* row_src, int topk, int low_latency,
                                       cudaStream_t stream) {
     return grouped_gemm_impl(b, a_q, a_scales, a_rows, w_q, w_scales, expert_offsets, num_experts, n_dim, k_dim, mode,
-                             out_bf16, act_q, act_s, row_src, topk, low_latency, true, a_rows / num_experts, stream);
+                             out_bf16, act_q, act_s, row_src, topk, low_latency, true, num_experts > 0 ? a_rows / num_experts : 0, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -43,6 +43,9 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--baseline-gemm", default="bf16_grouped", choices=["fp8_per_expert", "bf16_grouped"],
                     help="--impl baseline: cuBLAS fp8 per expert, or the library's bf16 grouped GEMM")
+    ap.add_argument("--fp32-scales", action="store_true",
+                    help="fp8 weights with arbitrary fp32 block scales: the software-scaled GEMM (quantMode 3) instead of "
+                         "tensor-core block scaling (not the headline configuration)")
     ap.add_argument("--w8a8-exact", action="store_true",
                     help="W8A8 models: int8 x int8 -> int32 tensor-core path instead of computing in block-scaled fp8")
     return ap.parse_args()
@@ -111,7 +114,12 @@ def run_ours(args, cfg, rank, world, local):
     tokens = args.tokens or cfg.tokens_per_rank
     group = dist.group.WORLD if world > 1 else None
     buf = make_buffer_for(cfg, group, tokens=tokens, name="bench", device=dev, timeout_ms=20000.0)
-    layer = FusedMoE(cfg, buf, seed=0, exact_w8a8=args.w8a8_exact)
+    weights = None
+    if args.fp32_scales:
+        from umdk_original_b200.models.weights import random_fp8_experts
+        weights = random_fp8_experts(cfg.num_experts // world, cfg.hidden, cfg.intermediate, device=dev, seed=rank,
+                                     ue8m0=False)
+    layer = FusedMoE(cfg, buf, weights=weights, seed=0, exact_w8a8=args.w8a8_exact)
     sets = make_inputs(cfg, tokens, rank, 4, dev)
 
     def step(i):
@@ -187,6 +195,7 @@ def run_ours(args, cfg, rank, world, local):
             "config": {"model": cfg.name, "global_batch": tokens * world, "seq_len": tokens, "tokens_per_rank": tokens,
                        "hidden": cfg.hidden, "moe_intermediate": cfg.intermediate, "num_experts": cfg.num_experts,
                        "topk": cfg.topk, "parallelism": f"ep{world}",
+                       "scales": "fp32 (software-scaled GEMM)" if args.fp32_scales else "power of two (tensor-core block scaling)",
                        "cache": "expert weights per rank exceed the 126 MB L2 and 4 input sets rotate; no explicit flush"},
             "clocks": {k: clock_summary[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
             "gpu_launches": 4 * args.steps,

@@ -33,8 +33,15 @@ namespace cam {
 
 constexpr int kGemmThreads = 640;   // 4 control warps + 16 epilogue warps
 constexpr int kEpiThreads = 512;
-constexpr int kSmemCtrl = 8192;
-constexpr int kGemmSmem = kStages * kStageBytes + kSmemCtrl + 1024;  // +1024 alignment slack
+// Shared memory: 4 pipeline stages | bf16 staging of half an output tile (128 rows x 256 bytes, rows 272 bytes
+// apart so that 16-byte stores of neighbouring rows fall into different banks; the per-row amax exchange of the
+// SwiGLU epilogue uses the same bytes) | barriers.  232448 bytes, the whole 227 KiB a CTA can have, so the
+// dynamic segment must start on a 1024-byte boundary.
+constexpr int kStgPitch = 272;
+constexpr int kStgBytes = BM * kStgPitch;  // 34816
+constexpr int kSmemCtrl = 1024;
+constexpr int kGemmSmem = kStages * kStageBytes + kStgBytes + kSmemCtrl;
+static_assert(kGemmSmem <= 232448, "exceeds the shared memory of one CTA");
 constexpr uint32_t kTmemCols = 512;
 // Register re-partitioning (setmaxnreg).  The CTA is launched with kLaunchRegs per thread (what
 // ptxas reports for __launch_bounds__(640, 1)); the control warp-group gives registers back and
@@ -47,16 +54,20 @@ static_assert(128 * kCtrlRegs + kEpiThreads * kEpiRegs <= kLaunchRegs * kGemmThr
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const GroupedGemmParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* ctrl = smem + kStages * kStageBytes;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if (smem_u32(smem) & 1023u) {  // swizzled TMA tiles need it; nothing has been set up yet, so just leave
+        if (threadIdx.x == 0) gemm_record_status(p.status, CAM_ERR_BAD_INDEX, 4, static_cast<int>(smem_u32(smem) & 1023u));
+        return;
+    }
+    uint8_t* stg = smem + kStages * kStageBytes;
+    uint8_t* ctrl = stg + kStgBytes;
     uint64_t* bar_full = reinterpret_cast<uint64_t*>(ctrl);
     uint64_t* bar_empty = bar_full + kStages;
     uint64_t* bar_tfull = bar_empty + kStages;
     uint64_t* bar_tempty = bar_tfull + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    float* s_amax = reinterpret_cast<float*>(ctrl + 256);  // [2 parities][4 column quarters][128 rows]
+    float* s_amax = reinterpret_cast<float*>(stg);  // mode 1 only: [2 parities][4 column quarters][128 rows]
 
     const int warp = static_cast<int>(threadIdx.x) >> 5;
     const uint32_t lane = lane_id();
@@ -243,24 +254,46 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                                    (static_cast<size_t>(tok) * p.topk + kk) * static_cast<size_t>(p.n_dim);
                     }
                 }
-                if (orow != nullptr) {
-                    const int c_lo = nt * BN + cq * 32;
-                    const int c_hi = c_lo + 128;
-                    if (c_lo < p.n_dim) {
+                // Half a tile (128 columns) at a time goes through shared memory as bf16 and leaves as 256-byte row
+                // segments: one bulk copy per row (local or over NVLink), or, with bulk_push off, 16 lanes storing one
+                // row, instead of 16-byte pieces of 32 different rows per warp instruction.  The row's destination
+                // address travels in the 16 spare bytes at the end of its staging row.
+                uint8_t* srow = stg + r * kStgPitch;
+                auto push_half = [&](const float* v, int c0) {
+                    if (p.bulk_push && cq == 0) bulk_wait_group_read<0>();  // the previous copies have read the staging area
+                    named_bar_sync(1, kEpiThreads);  // the previous half has left the staging area
 #pragma unroll
-                        for (int j = 0; j < 32; j += 8)
-                            st_na_v4(orow + c_lo + j, pack_bf16x8(acc[j], acc[j + 1], acc[j + 2], acc[j + 3], acc[j + 4],
-                                                                  acc[j + 5], acc[j + 6], acc[j + 7]));
+                    for (int j = 0; j < 32; j += 8)
+                        *reinterpret_cast<uint4*>(srow + cq * 64 + j * 2) =
+                            pack_bf16x8(v[j], v[j + 1], v[j + 2], v[j + 3], v[j + 4], v[j + 5], v[j + 6], v[j + 7]);
+                    if (cq == 0)
+                        *reinterpret_cast<uint64_t*>(srow + 256) =
+                            (orow != nullptr) ? reinterpret_cast<uint64_t>(orow + c0) : 0ull;
+                    if (p.bulk_push) {
+                        fence_proxy_async_smem();
+                        named_bar_sync(1, kEpiThreads);
+                        if (cq == 0) {
+                            if (orow != nullptr) bulk_store_s2g(orow + c0, srow, 256);
+                            bulk_commit_group();
+                        }
+                        return;
                     }
-                    if (c_hi < p.n_dim) {
+                    named_bar_sync(1, kEpiThreads);
+                    const int seg = static_cast<int>(lane & 15u) * 16;
 #pragma unroll
-                        for (int j = 0; j < 32; j += 8)
-                            st_na_v4(orow + c_hi + j, pack_bf16x8(acc[32 + j], acc[33 + j], acc[34 + j], acc[35 + j],
-                                                                  acc[36 + j], acc[37 + j], acc[38 + j], acc[39 + j]));
+                    for (int i = 0; i < 4; ++i) {
+                        const uint8_t* src = stg + (ew * 8 + 2 * i + static_cast<int>(lane >> 4)) * kStgPitch;
+                        const uint64_t dst = *reinterpret_cast<const uint64_t*>(src + 256);
+                        if (dst != 0ull)
+                            st_na_v4(reinterpret_cast<uint8_t*>(dst) + seg, *reinterpret_cast<const uint4*>(src + seg));
                     }
-                }
+                };
+                const int c_lo = nt * BN;
+                push_half(acc, c_lo);
+                if (c_lo + 128 < p.n_dim) push_half(acc + 32, c_lo + 128);  // same answer in every thread of the CTA
             }
         }
+        if (p.mode != 1 && p.bulk_push && cq == 0) bulk_wait_group<0>();  // every row this thread sent has been written
         if (!ok) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 2, static_cast<int>(it));
     }
 

@@ -195,7 +195,9 @@ def run_ours(args, cfg, rank, world, local):
             "config": {"model": cfg.name, "global_batch": tokens * world, "seq_len": tokens, "tokens_per_rank": tokens,
                        "hidden": cfg.hidden, "moe_intermediate": cfg.intermediate, "num_experts": cfg.num_experts,
                        "topk": cfg.topk, "parallelism": f"ep{world}",
-                       "scales": "fp32 (software-scaled GEMM)" if args.fp32_scales else "power of two (tensor-core block scaling)",
+                       "scales": ("per token x per channel (int8)" if (cfg.weight_format == "w8a8" and args.w8a8_exact) else
+                                  "fp32 (software-scaled GEMM)" if args.fp32_scales else
+                                  "power of two (tensor-core block scaling)"),
                        "cache": "expert weights per rank exceed the 126 MB L2 and 4 input sets rotate; no explicit flush"},
             "clocks": {k: clock_summary[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
             "gpu_launches": 4 * args.steps,

@@ -23,16 +23,16 @@ constexpr int kI8EpiThreads = 512;
 constexpr int kI8SfWarp0 = 4, kI8EpiWarp0 = 8;
 // Shared memory: 4 pipeline stages | bf16 staging of half an output tile (128 rows x 256 bytes,
 // rows 272 bytes apart so that 16-byte stores of neighbouring rows fall into different banks; the
-// SwiGLU epilogue does not use it: it writes fp32 activations to global memory and folds the row
-// maxima in with atomicMax) | barriers.  232448 bytes, the
+// SwiGLU epilogue uses the same bytes for 64 rows of fp32 activations at a time) | barriers.  232448 bytes, the
 // whole 227 KiB a CTA can have, so the dynamic segment must start on a 1024-byte boundary.
 constexpr int kI8StgPitch = 272;
 constexpr int kI8StgBytes = BM * kI8StgPitch;  // 34816
+constexpr int kI8ActPitchF = 132;  // SwiGLU epilogue: floats between the staging rows of two tokens (64 rows x 528 bytes)
+static_assert(64 * kI8ActPitchF * 4 <= kI8StgBytes, "fp32 staging of 64 rows must fit the staging area");
 constexpr int kI8SmemCtrl = 1024;
 constexpr int kI8Smem = kStages * kStageBytes + kI8StgBytes + kI8SmemCtrl;
 static_assert(kI8Smem <= 232448, "exceeds the shared memory of one CTA");
 constexpr uint32_t kI8TmemCols = 512;
-constexpr uint32_t kI8SfCol0 = 256, kI8SfStride = 16;
 // Register re-partitioning (setmaxnreg): the CTA is launched with kI8LaunchRegs per thread (what
 // ptxas reports for this kernel); the control and scale-factor warp-groups give registers back
 // and the four epilogue warp-groups take them.  setmaxnreg.inc waits for the CTA's pool without
@@ -58,13 +58,11 @@ grouped_gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     uint64_t* bar_tempty = bar_tfull + 1;                     // accumulator has been drained
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    float* s_amax = reinterpret_cast<float*>(stg);  // mode 1 only: [2 parities][4 column quarters][128 rows]
 
     const int warp = static_cast<int>(threadIdx.x) >> 5;
     const uint32_t lane = lane_id();
     const int kblocks = p.k_dim / BK;
     const int n_tiles = (p.mode == 1) ? (p.n_dim / 2) / 128 : (p.n_dim + BN - 1) / BN;
-    const int nblk = p.n_dim / 128;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -187,19 +185,42 @@ grouped_gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 // per-token scale of the second GEMM's activations
                 const int ia = p.n_dim / 2;
                 float act[32];
-                float amax = 0.f;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const float g = __uint_as_float(v0[j]);
                     act[j] = (g / (1.f + expf(-g))) * __uint_as_float(v1[j]);
-                    amax = fmaxf(amax, fabsf(act[j]));
                 }
-                if (valid) {
-                    float* dst = p.act_f32 + static_cast<size_t>(grow) * ia + nt * 128 + cq * 32;
+                // 64 rows at a time go through shared memory as fp32 [row][128 features], so that 8 threads write one
+                // row's 512 contiguous bytes (a warp instruction stores four whole rows instead of 16-byte pieces of
+                // 32 rows) and the row maximum costs one atomic per row and tile instead of four
+                float* stgf = reinterpret_cast<float*>(stg);
+                const int te = ew * 32 + static_cast<int>(lane);  // 0..511
+                const int rr = te >> 3, pc = te & 7;
+                for (int pass = 0; pass * 64 < rows; ++pass) {  // the same trip count in every thread of the CTA
+                    if ((q >> 1) == pass) {
+                        float* drow = stgf + (r & 63) * kI8ActPitchF + cq * 32;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4)
-                        *reinterpret_cast<float4*>(dst + j) = make_float4(act[j], act[j + 1], act[j + 2], act[j + 3]);
-                    atomicMax(reinterpret_cast<int*>(p.row_amax + grow), __float_as_int(amax));  // amax >= 0
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<float4*>(drow + j) = make_float4(act[j], act[j + 1], act[j + 2], act[j + 3]);
+                    }
+                    named_bar_sync(1, kI8EpiThreads);
+                    const float4* src = reinterpret_cast<const float4*>(stgf + rr * kI8ActPitchF + pc * 16);
+                    const float4 x0 = src[0], x1 = src[1], x2 = src[2], x3 = src[3];
+                    float m = fmaxf(fmaxf(fmaxf(fabsf(x0.x), fabsf(x0.y)), fmaxf(fabsf(x0.z), fabsf(x0.w))),
+                                    fmaxf(fmaxf(fabsf(x1.x), fabsf(x1.y)), fmaxf(fabsf(x1.z), fabsf(x1.w))));
+                    m = fmaxf(m, fmaxf(fmaxf(fmaxf(fabsf(x2.x), fabsf(x2.y)), fmaxf(fabsf(x2.z), fabsf(x2.w))),
+                                       fmaxf(fmaxf(fabsf(x3.x), fabsf(x3.y)), fmaxf(fabsf(x3.z), fabsf(x3.w)))));
+                    m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+                    m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
+                    m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, 4));
+                    const int trow = pass * 64 + rr;
+                    if (trow < rows) {
+                        float4* dst = reinterpret_cast<float4*>(p.act_f32 + static_cast<size_t>(row0 + trow) * ia + nt * 128 +
+                                                                pc * 16);
+                        dst[0] = x0; dst[1] = x1; dst[2] = x2; dst[3] = x3;
+                        if (pc == 0) atomicMax(reinterpret_cast<int*>(p.row_amax + row0 + trow), __float_as_int(m));  // m >= 0
+                    }
+                    named_bar_sync(1, kI8EpiThreads);  // the staging area may be overwritten
                 }
             } else {
                 // bf16 tile, either to the local output or straight to the origin rank's combine slot

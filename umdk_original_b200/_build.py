@@ -39,6 +39,7 @@ KERNEL_SOURCES = [
     "kernels/grouped_gemm_mx.cu",
     "kernels/grouped_gemm_mx2.cu",
     "kernels/grouped_gemm_i8.cu",
+    "kernels/fused_moe_mx.cu",
     "kernels/dispatch_noalloc.cu",
     "kernels/sync_p2p.cu",
     "kernels/tp_exchange.cu",
@@ -67,10 +68,10 @@ def _check_gemm_registers(ptxas_log: str, src: Path) -> None:
     CTA is launched with; that count must be the kLaunchRegs constant of the source, or the
     kernel would wait for registers that never come."""
     import re
-    want = int(re.search(r"k(?:Mx|P2|I8)?LaunchRegs\s*=\s*(\d+)", src.read_text()).group(1))
+    want = int(re.search(r"k(?:Mx|P2|I8|Fm)?LaunchRegs\s*=\s*(\d+)", src.read_text()).group(1))
     # only the GEMM kernels re-partition registers; a file may hold other kernels as well
     got = [int(n) for name, n in re.findall(r"Compiling entry function '([^']+)'.*?Used (\d+) registers", ptxas_log, re.S)
-           if "grouped_gemm" in name]
+           if "grouped_gemm" in name or "fused_moe" in name]
     if not got or any(g != want for g in got):
         raise RuntimeError(f"{src.name}: ptxas reports {got} registers but kLaunchRegs is {want}")
 
@@ -119,7 +120,8 @@ def build_kernels(force: bool = False, debug: bool = False) -> Path:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             logs = list(ex.map(lambda j: _run(j[0]), jobs))
         for (_, src, obj), log in zip(jobs, logs):
-            if src.name in ("grouped_gemm.cu", "grouped_gemm_mx.cu", "grouped_gemm_mx2.cu", "grouped_gemm_i8.cu"):
+            if src.name in ("grouped_gemm.cu", "grouped_gemm_mx.cu", "grouped_gemm_mx2.cu", "grouped_gemm_i8.cu",
+                            "fused_moe_mx.cu"):
                 _check_gemm_registers(log, src)
             _mark(src, obj, stamp)
     so = LIB / "libumdk_cam.so"

@@ -109,6 +109,12 @@ public:
                                        initiator ? 1 : 0, stream()));
     }
     void set_trace(bool on) { CAM_RT(cam_buffer_set_trace(buf_, on ? 1 : 0)); }
+    void set_fused_trace(bool on) { CAM_RT(cam_buffer_set_fused_trace(buf_, on ? 1 : 0)); }
+    std::vector<int64_t> read_fused_trace(int64_t num_local_experts) {
+        std::vector<long long> t(static_cast<size_t>(num_local_experts));
+        CAM_RT(cam_buffer_read_fused_trace(buf_, t.data(), static_cast<int>(num_local_experts)));
+        return std::vector<int64_t>(t.begin(), t.end());
+    }
     std::vector<int64_t> read_trace() {
         unsigned long long t[16];
         CAM_RT(cam_buffer_read_trace(buf_, t));
@@ -869,6 +875,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("p2p_pingpong", &Buffer::p2p_pingpong)
         .def("set_trace", &Buffer::set_trace)
         .def("read_trace", &Buffer::read_trace)
+        .def("set_fused_trace", &Buffer::set_fused_trace)
+        .def("read_fused_trace", &Buffer::read_fused_trace)
         .def("set_profile", &Buffer::set_profile)
         .def("read_profile", &Buffer::read_profile)
         .def("poll_status", &Buffer::poll_status)

@@ -20,6 +20,8 @@ enum CamStatusCode {
     CAM_ERR_TIMEOUT_LL_CELL = 6,       // low-latency count cell never arrived
     CAM_ERR_TIMEOUT_BARRIER = 7,       // device barrier across ranks ran out
     CAM_ERR_BAD_INDEX = 8,             // debug bounds check recorded an out-of-range index
+    CAM_ERR_TIMEOUT_ARRIVAL = 9,       // fused layer: the rows of one local expert never all arrived
+    CAM_ERR_TIMEOUT_GEMM1 = 10,        // fused layer: the first GEMM of a row block never completed
 };
 
 typedef struct CamStatus {
@@ -84,6 +86,7 @@ typedef struct CamLayout {
     uint64_t off_tp_scales;     // f32[tp_rows][hidden/128]
     uint64_t off_dup_cnt;       // u32[2][CAM_MAX_RANKS]: replicate-list lengths per source (normal dispatch)
     uint64_t off_dup_list;      // i32[2][R][max_tokens*topk][2]: (row that arrived, row to copy it to)
+    uint64_t off_arrival;       // u32[2][E]: rows that have landed per local expert (fused layer, parity of the epoch)
     uint64_t total_bytes;
 } CamLayout;
 

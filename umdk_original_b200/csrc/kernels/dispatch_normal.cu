@@ -93,6 +93,14 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
             __syncthreads();
         }
         for (int e = tid; e < E; e += kDispThreads) p.cta_hist[static_cast<size_t>(b) * E + e] = s_hist[e];
+        if (p.defer_push && b == nb - 1) {
+            // Counters of the fused kernel start at zero.  Peers add to this call's arrival counters only after they
+            // have seen this rank's count flag, which is raised after the grid-wide barrier below.
+            uint32_t* arr = reinterpret_cast<uint32_t*>(my_base + p.off_arrival) + static_cast<size_t>(parity) * E;
+            for (int e = tid; e < E; e += kDispThreads) arr[e] = 0u;
+            for (int i = tid; i < p.g1_done_len; i += kDispThreads) p.g1_done[i] = 0u;
+            __threadfence_system();
+        }
         __threadfence();
         cg::this_grid().sync();
 
@@ -166,18 +174,23 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
             s_rank_ok[d] = (tot <= p.capacity) ? 1 : 0;
             if (tot > p.capacity) record_status(p.status, CAM_ERR_RECV_OVERFLOW, d, tot);
         }
-        // Receiver-side bookkeeping for this rank's own experts (one CTA is enough).
+        __syncthreads();
+        // Receiver-side bookkeeping for this rank's own experts (one CTA is enough).  When more rows are routed
+        // here than the buffer holds, every sender skips this rank (s_rank_ok) and the counts published below are
+        // zero, so that the kernels that follow touch no row at or past the capacity; the status word says why.
         if (b == 0) {
+            const bool fits = s_rank_ok[p.rank] != 0;
             for (int le = tid; le < El; le += kDispThreads) {
                 int start = 0;
                 for (int l = 0; l < le; ++l) start += s_tot[p.rank * El + l];
+                if (!fits) start = 0;
                 p.expert_offsets[le] = start;
                 int run = start;
                 for (int s = 0; s < R; ++s) {
-                    run += __ldcg(&cm[static_cast<size_t>(s) * E + p.rank * El + le]);
+                    if (fits) run += __ldcg(&cm[static_cast<size_t>(s) * E + p.rank * El + le]);
                     p.recv_count[le * R + s] = run;  // inclusive cumsum, expert major / source minor
                 }
-                p.num_recv_per_expert[le] = static_cast<long long>(s_tot[p.rank * El + le]);
+                p.num_recv_per_expert[le] = fits ? static_cast<long long>(s_tot[p.rank * El + le]) : 0ll;
                 if (le == El - 1) {
                     p.expert_offsets[El] = run;
                     p.total_recv[0] = run;
@@ -206,6 +219,43 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
         // the receiver works off locally after the data flags (RECV phase below).
         const bool bulk_rows = (p.quant_mode != CAM_QUANT_NONE) && (row_bytes % 16 == 0);
         const bool bulk_scales = bulk_rows && ((nscale * 4) % 16 == 0);
+        if (p.defer_push) {
+            // Nothing is pushed here.  Position of every pair in the send list: pairs are ordered by (local expert
+            // at the destination, destination rank, scan order), so expert 0 of every rank is served first.
+            int* s_mine = reinterpret_cast<int*>(dyn_smem);  // the staging area is unused in this mode
+            for (int e = tid; e < E; e += kDispThreads)
+                s_mine[e] = s_rank_ok[e / El] ? __ldcg(&cm[static_cast<size_t>(p.rank) * E + e]) : 0;
+            __syncthreads();
+            for (int e = tid; e < E; e += kDispThreads) {
+                const int d = e / El, le = e - d * El;
+                int pre = 0;
+                for (int l2 = 0; l2 <= le; ++l2) {
+                    const int dmax = (l2 < le) ? R : d;
+                    for (int d2 = 0; d2 < dmax; ++d2) pre += s_mine[d2 * El + l2];
+                }
+                s_hist[e] = pre;
+                if (b == 0 && e == E - 1) p.send_list_len[0] = pre + s_mine[e];  // expert E - 1 has the last key
+            }
+            __syncthreads();
+            for (int t = t0 + warp; t < t1; t += kDispWarps) {
+                const __nv_bfloat16* xrow = p.x + static_cast<size_t>(t) * p.h;
+                uint8_t* q = p.xq + static_cast<size_t>(t) * p.h;
+                float* sc = p.xs + static_cast<size_t>(t) * nscale;
+                if (p.quant_mode == CAM_QUANT_FP8_1x128_UE8M0) warp_quant_fp8_1x128<true>(xrow, p.h, q, sc);
+                else warp_quant_fp8_1x128<false>(xrow, p.h, q, sc);
+                if (lane < static_cast<uint32_t>(K)) {
+                    const size_t g = static_cast<size_t>(t) * K + lane;
+                    const int id = load_expert_id(p.topk_idx, p.idx_is_i64, g);
+                    int row = -1;
+                    if (id >= 0 && id < E && s_rank_ok[id / El]) {
+                        const int d = id / El, slot = p.slot_in_expert[g];
+                        row = s_aux[id] + slot;
+                        p.send_list[s_hist[id] + slot] = make_int4(t, d, row, (id - d * El) | (static_cast<int>(lane) << 16));
+                    }
+                    p.send_row[g] = row;
+                }
+            }
+        } else {
         for (int t = t0 + warp; t < t1; t += kDispWarps) {
             const __nv_bfloat16* xrow = p.x + static_cast<size_t>(t) * p.h;
             if (bulk_rows) {
@@ -308,6 +358,7 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
                 }
             }
         }
+        }  // !defer_push
     }
 
     // ------------------------------------------------------------------ phase RECV
@@ -361,6 +412,8 @@ done:
         if (p.phase_mask & CAM_PHASE_COUNT) p.epochs[0] = ep_count;
         if (p.phase_mask & CAM_PHASE_SEND) p.epochs[1] = ep_send;
         if (p.phase_mask & CAM_PHASE_RECV) p.epochs[2] = ep_recv;
+        // a deferred push has no receive phase of its own: keep the three counters in step for the next plain dispatch
+        if (p.defer_push && (p.phase_mask & CAM_PHASE_SEND)) p.epochs[2] = ep_send;
     }
 }
 

@@ -1,0 +1,653 @@
+// Deep-fused MoE layer for sm_100a: ONE persistent kernel of CTA pairs that
+//   * sends this rank's quantised tokens to their expert ranks, in the order of the destination's
+//     local experts, and counts every landed row on a per-expert arrival counter in the
+//     destination's memory (copy warps: bulk copies local memory -> shared memory -> peer memory);
+//   * runs the first grouped GEMM (+ SwiGLU + 1x128 fp8 requantisation) of a local expert as soon
+//     as that expert's counter says all of its rows are in, while later experts still arrive;
+//   * runs the second grouped GEMM of a row block as soon as the first one has finished that
+//     block, and pushes its bf16 rows from the epilogue straight into the combine slots of the
+//     tokens' origin ranks (bulk copies shared memory -> peer memory).
+// Tiles of the two GEMMs are interleaved expert by expert (the second GEMM of expert e follows the
+// first GEMM of expert e + lag), so the combine traffic is spread over the whole compute time
+// instead of being squeezed into the second GEMM.
+//
+// This is the B200 form of the reference's deep-fused kernel: there the cube core spins on a
+// per-expert token counter before it starts that expert
+// (fused_deep_moe/gemm/kernel/grouped_matmul_slice_m_per_token_dequant_swiglu_quant_multistage_workspace.h:558-574),
+// senders emit tokens in local-expert order (:948-961), receivers add per-expert counts (:1259-1274)
+// and the second GEMM's epilogue is the combine send
+// (fused_deep_moe/epilogue/block/block_epilogue_per_token_dequant.hpp:531-570).
+//
+// Tensor-core pipeline, barriers and epilogues are those of the CTA-pair grouped GEMM
+// (grouped_gemm_mx2.cu): tcgen05.mma.cta_group::2 with UE8M0 block scaling, operands by plain TMA
+// loads (no multicast qualifier anywhere), accumulators in TMEM.  Warps: 0 TMA producer, 1 MMA
+// issuer (first CTA of the pair), 2-3 copy warps, 4-7 scale-factor writers, 8-23 epilogue.
+//
+// Every wait is bounded.  A wait that runs out records a status word, raises the CTA's abort flag
+// (and the partner CTA's), and every role leaves its loop; both CTAs always reach the cluster
+// barrier at the end and free their tensor memory.
+#include "gemm_common.cuh"
+
+namespace cam {
+
+constexpr int kFmThreads = 768;
+constexpr int kFmEpiThreads = 512;
+constexpr int kFmSfWarp0 = 4, kFmEpiWarp0 = 8;
+constexpr int kFmStages = 4;
+constexpr int kFmATile = BM * BK;    // this CTA's 128 rows of A, 16 KiB
+constexpr int kFmBTile = 128 * BK;   // this CTA's half of the 256-row B tile, 16 KiB
+constexpr int kFmStageBytes = kFmATile + kFmBTile;
+constexpr int kFmStgPitch = 272;
+constexpr int kFmStgBytes = BM * kFmStgPitch;  // 34816, two of them (combine-send epilogue)
+constexpr int kFmCommWarps = 2, kFmCommBufs = 2;
+constexpr int kFmCommRow = 7168;               // largest hidden size the copy warps stage
+constexpr int kFmCommBuf = kFmCommRow + 256;   // row + up to 56 fp32 scales
+constexpr int kFmSmemCtrl = 1024;
+constexpr int kFmSmem = kFmStages * kFmStageBytes + 2 * kFmStgBytes + kFmCommWarps * kFmCommBufs * kFmCommBuf + kFmSmemCtrl;
+static_assert(kFmSmem <= 232448, "exceeds the shared memory of one CTA");
+constexpr uint32_t kFmTmemCols = 512;
+constexpr uint32_t kFmSfCol0 = 256, kFmSfStride = 16;
+// Register re-partitioning, see grouped_gemm_mx2.cu: the launch count is what ptxas reports.
+constexpr uint32_t kFmLaunchRegs = 80, kFmCtrlRegs = 40, kFmSfRegs = 56, kFmEpiRegs = 96;
+static_assert(128 * kFmCtrlRegs + 128 * kFmSfRegs + kFmEpiThreads * kFmEpiRegs <= kFmLaunchRegs * kFmThreads,
+              "setmaxnreg budget exceeds the registers the CTA owns: the kernel would hang");
+
+__device__ __forceinline__ uint32_t fm_ue8m0_word(float scale) {
+    return ((__float_as_uint(scale) >> 23) & 0xFFu) * 0x01010101u;
+}
+__device__ __forceinline__ float ld_cg_f32(const float* p) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Order of the tiles of one launch.  Step j of the walk holds the first GEMM of expert j (while j < E_local) and
+// then the second GEMM of expert j - lag (once j >= lag).  `tile` must not decrease from call to call.
+struct FusedWalker {
+    const int* off;
+    int num_experts, nt1, nt2, lag;
+    int j, sub, base;
+    __device__ FusedWalker(const int* o, int ne, int n1, int n2, int lg)
+        : off(o), num_experts(ne), nt1(n1), nt2(n2), lag(lg), j(0), sub(0), base(0) {}
+    // kind 0 = first GEMM, 1 = second GEMM; cnt = rows of the expert.
+    __device__ bool locate(int tile, int& kind, int& e_out, int& mt, int& nt, int& row0, int& rows, int& cnt_out) {
+        while (j < num_experts + lag) {
+            const int e = sub ? j - lag : j;
+            const bool has = sub ? (j >= lag) : (j < num_experts);
+            int first = 0, cnt = 0, tiles = 0;
+            const int per = sub ? nt2 : nt1;
+            if (has) {
+                first = __ldg(off + e);
+                cnt = __ldg(off + e + 1) - first;
+                tiles = ((cnt + 2 * BM - 1) / (2 * BM)) * per;
+            }
+            if (tile < base + tiles) {
+                const int local = tile - base;
+                mt = local / per;
+                nt = local - mt * per;
+                row0 = first + mt * 2 * BM;
+                rows = min(2 * BM, cnt - mt * 2 * BM);
+                e_out = e;
+                kind = sub;
+                cnt_out = cnt;
+                return true;
+            }
+            base += tiles;
+            if (sub) { sub = 0; ++j; } else { sub = 1; }
+        }
+        return false;
+    }
+};
+
+struct FmWait {
+    volatile uint32_t* abort_flag;  // this CTA's
+    uint32_t partner_abort;         // cluster address of the partner's
+    const volatile int* status_code;
+    uint64_t timeout_ns;       // waits inside the pipeline (they sit behind waits for other GPUs: the longest budget)
+    uint64_t arrival_ns;       // wait for another GPU's rows: the budget the caller set
+    uint64_t gemm1_ns;         // wait for the first GEMM of a row block, which itself may wait for arrivals
+};
+
+__device__ __forceinline__ void fm_raise_abort(const FmWait& w) {
+    *w.abort_flag = 1u;
+    st_shared_cluster_u32(w.partner_abort, 1u);
+}
+
+// mbarrier wait that also gives up when any CTA of the launch has recorded an error.
+__device__ __forceinline__ bool fm_mbar_wait(uint64_t* bar, uint32_t parity, const FmWait& w, uint32_t sleep_ns = 0u) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t polls = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if (sleep_ns) __nanosleep(sleep_ns);
+        if ((++polls & 127u) == 0u) {
+            if (*w.abort_flag) return false;
+            if (*w.status_code != 0 || globaltimer_ns() - t0 > w.timeout_ns) {
+                fm_raise_abort(w);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// Spin until *ctr >= want.  SYS: the counter is written by other GPUs.  Called by single threads or whole warps.
+template <bool SYS>
+__device__ __forceinline__ bool fm_wait_counter(const uint32_t* ctr, uint32_t want, const FmWait& w, uint32_t& seen) {
+    const uint64_t budget = SYS ? w.arrival_ns : w.gemm1_ns;
+    seen = SYS ? ld_acquire_sys_u32(ctr) : ld_acquire_gpu_u32(ctr);
+    if (seen >= want) return true;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t polls = 0;
+    while (true) {
+        seen = SYS ? ld_acquire_sys_u32(ctr) : ld_acquire_gpu_u32(ctr);
+        if (seen >= want) return true;
+        __nanosleep(100);
+        if ((++polls & 31u) == 0u) {
+            if (*w.abort_flag) return false;
+            if (*w.status_code != 0 || globaltimer_ns() - t0 > budget) return false;
+        }
+    }
+}
+
+// Unique counter index of the 256-row block that starts at `row0` of local expert `e` (experts own contiguous rows).
+__device__ __forceinline__ int fm_block_index(int row0, int e) { return (row0 >> 8) + e; }
+
+__global__ void __launch_bounds__(kFmThreads, 1)
+fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_constant__ CUtensorMap tmap_b1,
+                      const __grid_constant__ CUtensorMap tmap_a2, const __grid_constant__ CUtensorMap tmap_b2,
+                      const FusedMoeParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if (smem_u32(smem) & 1023u) {  // swizzled TMA tiles need it; nothing has been set up yet, so just leave
+        if (threadIdx.x == 0) gemm_record_status(p.status, CAM_ERR_BAD_INDEX, 4, static_cast<int>(smem_u32(smem) & 1023u));
+        return;
+    }
+    uint8_t* stg = smem + kFmStages * kFmStageBytes;
+    uint8_t* comm = stg + 2 * kFmStgBytes;
+    uint8_t* ctrl = comm + kFmCommWarps * kFmCommBufs * kFmCommBuf;
+    uint64_t* bar_full = reinterpret_cast<uint64_t*>(ctrl);
+    uint64_t* bar_sf = bar_full + kFmStages;
+    uint64_t* bar_empty = bar_sf + kFmStages;
+    uint64_t* bar_tfull = bar_empty + kFmStages;
+    uint64_t* bar_tempty = bar_tfull + 1;
+    uint64_t* bar_comm = bar_tempty + 1;  // [copy warp][buffer]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_comm + kFmCommWarps * kFmCommBufs);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+    float* s_amax = reinterpret_cast<float*>(stg);  // first-GEMM epilogue: [2 parities][4 column quarters][128 rows]
+
+    const int warp = static_cast<int>(threadIdx.x) >> 5;
+    const uint32_t lane = lane_id();
+    const uint32_t cta = cluster_cta_rank();
+    const int pair_id = static_cast<int>(blockIdx.x) >> 1;
+    const int num_pairs = static_cast<int>(gridDim.x) >> 1;
+    const bool do_send = (p.phase_mask & CAM_PHASE_SEND) != 0;
+    const bool do_gemm = (p.phase_mask & CAM_PHASE_RECV) != 0;
+    const int kb1 = p.h / BK, kb2 = p.inter / BK;
+    const int nt1 = p.inter / 128, nt2 = (p.h + BN - 1) / BN;
+    const int nblk1 = 2 * p.inter / 128, nblk2 = p.h / 128;
+    const uint32_t parity = *p.epoch_dispatch & 1u;  // the first launch of the layer has already advanced it
+    const uint32_t* my_arrival = reinterpret_cast<const uint32_t*>(p.peer_base[p.rank] + p.off_arrival) +
+                                 static_cast<size_t>(parity) * p.arrival_stride;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kFmStages; ++s) {
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_sf[s], 8);
+            mbar_init(&bar_empty[s], 1);
+        }
+        mbar_init(bar_tfull, 1);
+        mbar_init(bar_tempty, 2 * (kFmEpiThreads / 32));
+        for (int i = 0; i < kFmCommWarps * kFmCommBufs; ++i) mbar_init(&bar_comm[i], 1);
+        *abort_flag = 0u;
+        mbar_fence_init();
+        if (blockIdx.x == 0 && p.trace != nullptr) p.trace[p.num_experts] = globaltimer_ns();
+    }
+    if (do_gemm && warp == 1) {
+        tmem_alloc_pair(tmem_slot, kFmTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers are initialised before anything signals them
+    tc_fence_after_sync();
+    const uint32_t tmem_base = do_gemm ? *tmem_slot : 0u;
+    FmWait wt;
+    wt.abort_flag = abort_flag;
+    wt.partner_abort = map_to_cta(const_cast<uint32_t*>(abort_flag), cta ^ 1u);
+    wt.status_code = &p.status->code;
+    wt.arrival_ns = p.timeout_ns;
+    wt.gemm1_ns = p.timeout_ns + 1000000000ull;
+    wt.timeout_ns = p.timeout_ns + 2000000000ull;
+
+    if (warp < kFmSfWarp0) {
+        reg_dealloc<kFmCtrlRegs>();
+        if (warp == 0 && lane == 0 && do_gemm) {
+            // ------------------------------------------------------------ TMA producer (both CTAs)
+            prefetch_tensormap(&tmap_a1);
+            prefetch_tensormap(&tmap_b1);
+            prefetch_tensormap(&tmap_a2);
+            prefetch_tensormap(&tmap_b2);
+            FusedWalker w(p.expert_offsets, p.num_experts, nt1, nt2, p.lag);
+            uint32_t it = 0;
+            int kind, e, mt, nt, row0, rows, cnt;
+            int ready_e = -1, ready_blk = -1;
+            bool ok = true;
+            for (int tile = pair_id; ok && w.locate(tile, kind, e, mt, nt, row0, rows, cnt); tile += num_pairs) {
+                const CUtensorMap* ta = kind ? &tmap_a2 : &tmap_a1;
+                const CUtensorMap* tb = kind ? &tmap_b2 : &tmap_b1;
+                const int kblocks = kind ? kb2 : kb1;
+                int brow_lo, brow_hi;
+                if (kind == 0) {
+                    brow_lo = e * 2 * p.inter + nt * 128;
+                    brow_hi = brow_lo + p.inter;
+                    if (e != ready_e) {  // the expert's rows (from every rank) must have landed
+                        uint32_t seen;
+                        if (!fm_wait_counter<true>(my_arrival + e, static_cast<uint32_t>(cnt), wt, seen)) {
+                            gemm_record_status(p.status, CAM_ERR_TIMEOUT_ARRIVAL, e, static_cast<int>(seen));
+                            fm_raise_abort(wt);
+                            ok = false;
+                            break;
+                        }
+                        ready_e = e;
+                        if (p.trace != nullptr)
+                            atomicCAS(p.trace + e, 0ull, static_cast<unsigned long long>(globaltimer_ns()));
+                    }
+                } else {
+                    brow_lo = e * p.h + nt * BN;
+                    brow_hi = brow_lo + 128;
+                    const int blk = fm_block_index(row0, e);
+                    if (blk != ready_blk) {  // every column tile of the first GEMM has written this row block
+                        uint32_t seen;
+                        if (!fm_wait_counter<false>(p.g1_done + blk, static_cast<uint32_t>(2 * nt1), wt, seen)) {
+                            gemm_record_status(p.status, CAM_ERR_TIMEOUT_GEMM1, e, static_cast<int>(seen));
+                            fm_raise_abort(wt);
+                            ok = false;
+                            break;
+                        }
+                        ready_blk = blk;
+                    }
+                }
+                fence_proxy_async_all();  // rows written by other SMs / GPUs are read by TMA below
+                const int my_arow = row0 + static_cast<int>(cta) * BM;
+                const int my_brow = cta ? brow_hi : brow_lo;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const uint32_t s = it % kFmStages, ph = (it / kFmStages) & 1u;
+                    if (!fm_mbar_wait(&bar_empty[s], ph ^ 1u, wt)) { ok = false; break; }
+                    uint8_t* sa = smem + s * kFmStageBytes;
+                    if (cta == 0) mbar_arrive_expect_tx(&bar_full[s], 2 * kFmStageBytes);
+                    const uint32_t full0 = map_to_cta(&bar_full[s], 0);
+                    tma_load_2d_pair(sa, ta, full0, kb * BK, my_arow);
+                    tma_load_2d_pair(sa + kFmATile, tb, full0, kb * BK, my_brow);
+                }
+            }
+            if (!ok) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 0, static_cast<int>(it));
+        } else if (warp == 1 && lane == 0 && cta == 0 && do_gemm) {
+            // ------------------------------------------------------------ MMA issuer (first CTA only)
+            constexpr uint32_t idesc = umma_idesc_mxf8(2 * BM, BN);
+            FusedWalker w(p.expert_offsets, p.num_experts, nt1, nt2, p.lag);
+            uint32_t it = 0, tcount = 0;
+            int kind, e, mt, nt, row0, rows, cnt;
+            bool ok = true;
+            const uint32_t tfull0 = map_to_cta(bar_tfull, 0), tfull1 = map_to_cta(bar_tfull, 1);
+            for (int tile = pair_id; ok && w.locate(tile, kind, e, mt, nt, row0, rows, cnt); tile += num_pairs, ++tcount) {
+                const int kblocks = kind ? kb2 : kb1;
+                if (!fm_mbar_wait(bar_tempty, (tcount & 1u) ^ 1u, wt)) { ok = false; break; }
+                tc_fence_after_sync();
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const uint32_t s = it % kFmStages, ph = (it / kFmStages) & 1u;
+                    if (!fm_mbar_wait(&bar_sf[s], ph, wt)) { ok = false; break; }
+                    if (!fm_mbar_wait(&bar_full[s], ph, wt)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t sa = smem_u32(smem + s * kFmStageBytes);
+                    const uint64_t adesc = umma_desc_k_sw128(sa);
+                    const uint64_t bdesc = umma_desc_k_sw128(sa + kFmATile);
+                    const uint32_t sfa = tmem_base + kFmSfCol0 + s * kFmSfStride;
+                    const uint32_t sfb = sfa + 4u;
+#pragma unroll
+                    for (int k = 0; k < BK / 32; ++k)
+                        tc_mma_mxf8_pair(tmem_base, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) ? 1u : 0u, sfa, sfb);
+                    tc_commit_pair(map_to_cta(&bar_empty[s], 0));
+                    tc_commit_pair(map_to_cta(&bar_empty[s], 1));
+                }
+                if (!ok) break;
+                tc_commit_pair(tfull0);
+                tc_commit_pair(tfull1);
+            }
+            if (!ok) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 1, static_cast<int>(it));
+        } else if (warp >= 2 && lane == 0 && do_send) {
+            // ------------------------------------------------------------ copy warps: dispatch send
+            // One thread per warp moves rows with the bulk-copy engine: local memory -> shared memory -> the
+            // destination rank's receive buffer, two rows in flight.  A row is counted on the destination's
+            // arrival counter of its local expert once its copy has completed.
+            const int cw = warp - 2;
+            const int gw = static_cast<int>(blockIdx.x) * kFmCommWarps + cw;
+            const int total_cw = static_cast<int>(gridDim.x) * kFmCommWarps;
+            const int nlist = min(p.send_list_len[0], p.send_list_cap);
+            const uint32_t row_bytes = static_cast<uint32_t>(p.h);
+            const uint32_t sc_bytes = static_cast<uint32_t>(p.h >> 7) * 4u;
+            uint8_t* buf0 = comm + cw * kFmCommBufs * kFmCommBuf;
+            uint64_t* cbar = bar_comm + cw * kFmCommBufs;
+            int pend_d[2] = {0, 0}, pend_le[2] = {0, 0};
+            auto signal = [&](int d, int le) {
+                if (p.dbg_drop_flags) return;  // host-side fault injection: this rank's rows are never counted
+                fence_acq_rel_sys();
+                red_release_sys_add_u32(reinterpret_cast<uint32_t*>(p.peer_base[d] + p.off_arrival) +
+                                            static_cast<size_t>(parity) * p.arrival_stride + le, 1u);
+            };
+            int n = 0;
+            bool ok = true;
+            for (int i = gw; i < nlist; i += total_cw, ++n) {
+                const int4 ent = p.send_list[i];
+                const int t = ent.x, d = ent.y, row = ent.z, le = ent.w & 0xFFFF, kk = ent.w >> 16;
+                const int bsel = n & 1;
+                if (n >= 2) {  // the copy that used this buffer two rows ago is complete: count that row
+                    bulk_wait_group<1>();
+                    signal(pend_d[bsel], pend_le[bsel]);
+                }
+                if (t < 0 || t >= p.max_tokens || d < 0 || d >= p.num_ranks || row < 0 || row >= p.a_rows) {
+                    gemm_record_status(p.status, CAM_ERR_BAD_INDEX, 5, i);
+                    ok = false;
+                    break;
+                }
+                uint8_t* buf = buf0 + bsel * kFmCommBuf;
+                mbar_arrive_expect_tx(&cbar[bsel], row_bytes + sc_bytes);
+                bulk_load_g2s(buf, p.xq + static_cast<size_t>(t) * row_bytes, row_bytes, &cbar[bsel]);
+                bulk_load_g2s(buf + kFmCommRow, p.xs + static_cast<size_t>(t) * (p.h >> 7), sc_bytes, &cbar[bsel]);
+                if (!fm_mbar_wait(&cbar[bsel], static_cast<uint32_t>(n >> 1) & 1u, wt)) { ok = false; break; }
+                uint8_t* pb = p.peer_base[d];
+                bulk_store_s2g(pb + p.off_recv_x + static_cast<size_t>(row) * row_bytes, buf, row_bytes);
+                bulk_store_s2g(pb + p.off_recv_scales + static_cast<size_t>(row) * sc_bytes, buf + kFmCommRow, sc_bytes);
+                bulk_commit_group();
+                int* tri = reinterpret_cast<int*>(pb + p.off_recv_src) + static_cast<size_t>(row) * 3;
+                tri[0] = p.rank;
+                tri[1] = t;
+                tri[2] = kk;
+                pend_d[bsel] = d;
+                pend_le[bsel] = le;
+            }
+            if (ok) {
+                if (n >= 2) {
+                    bulk_wait_group<1>();
+                    signal(pend_d[n & 1], pend_le[n & 1]);
+                }
+                if (n >= 1) {
+                    bulk_wait_group<0>();
+                    signal(pend_d[(n - 1) & 1], pend_le[(n - 1) & 1]);
+                }
+            } else {
+                bulk_wait_group<0>();  // nothing of this thread stays in flight
+                gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 4, n);
+            }
+        }
+    } else if (warp < kFmEpiWarp0) {
+        reg_dealloc<kFmSfRegs>();
+        // ---------------------------------------------------------------- scale-factor writers
+        if (do_gemm) {
+            const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+            FusedWalker w(p.expert_offsets, p.num_experts, nt1, nt2, p.lag);
+            uint32_t it = 0;
+            int kind, e, mt, nt, row0, rows, cnt;
+            int ready_e = -1, ready_blk = -1;
+            bool ok = true;
+            for (int tile = pair_id; ok && w.locate(tile, kind, e, mt, nt, row0, rows, cnt); tile += num_pairs) {
+                const int kblocks = kind ? kb2 : kb1;
+                const float* a_scales = kind ? p.act_s : p.a1_scales;
+                // activation scales arrive during this kernel (from peers or from the first GEMM): wait like the
+                // producer does, and read them with L2-coherent loads only
+                if (kind == 0) {
+                    if (e != ready_e) {
+                        uint32_t seen;
+                        const bool got = fm_wait_counter<true>(my_arrival + e, static_cast<uint32_t>(cnt), wt, seen);
+                        if (!__all_sync(0xFFFFFFFFu, got)) { ok = false; break; }
+                        ready_e = e;
+                    }
+                } else {
+                    const int blk = fm_block_index(row0, e);
+                    if (blk != ready_blk) {
+                        uint32_t seen;
+                        const bool got = fm_wait_counter<false>(p.g1_done + blk, static_cast<uint32_t>(2 * nt1), wt, seen);
+                        if (!__all_sync(0xFFFFFFFFu, got)) { ok = false; break; }
+                        ready_blk = blk;
+                    }
+                }
+                const float* as[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int r = min(row0 + static_cast<int>(cta) * BM + 32 * j + static_cast<int>(lane), p.a_rows - 1);
+                    as[j] = a_scales + static_cast<size_t>(r) * kblocks;
+                }
+                int nb_lo, nb_hi, nblk;
+                const float* b_scales;
+                if (kind == 0) { nb_lo = nt; nb_hi = nblk1 / 2 + nt; nblk = nblk1; b_scales = p.b1_scales; }
+                else { nb_lo = 2 * nt; nb_hi = min(2 * nt + 1, nblk2 - 1); nblk = nblk2; b_scales = p.b2_scales; }
+                const float* bs_lo = b_scales + (static_cast<size_t>(e) * nblk + nb_lo) * kblocks;
+                const float* bs_hi = b_scales + (static_cast<size_t>(e) * nblk + nb_hi) * kblocks;
+                float c[6], n1[6];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) c[j] = ld_cg_f32(as[j]);
+                c[4] = __ldg(bs_lo); c[5] = __ldg(bs_hi);
+#pragma unroll
+                for (int j = 0; j < 6; ++j) n1[j] = c[j];
+                if (kblocks > 1) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) n1[j] = ld_cg_f32(as[j] + 1);
+                    n1[4] = __ldg(bs_lo + 1); n1[5] = __ldg(bs_hi + 1);
+                }
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    uint32_t wd[6];
+#pragma unroll
+                    for (int j = 0; j < 6; ++j) { wd[j] = fm_ue8m0_word(c[j]); c[j] = n1[j]; }
+                    const uint32_t s = it % kFmStages, ph = (it / kFmStages) & 1u;
+                    const bool got = fm_mbar_wait(&bar_empty[s], ph ^ 1u, wt);
+                    if (!__all_sync(0xFFFFFFFFu, got)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint32_t col = tmem_base + lane_base + kFmSfCol0 + s * kFmSfStride;
+                    tmem_st_32x32b_x4(col, wd[0], wd[1], wd[2], wd[3]);
+                    tmem_st_32x32b_x4(col + 4u, wd[4], wd[4], wd[4], wd[4]);
+                    tmem_st_32x32b_x4(col + 8u, wd[5], wd[5], wd[5], wd[5]);
+                    tc_wait_st();
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (cta == 0) mbar_arrive(&bar_sf[s]);
+                        else mbar_arrive_cluster(map_to_cta(&bar_sf[s], 0));
+                    }
+                    if (kb + 2 < kblocks) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) n1[j] = ld_cg_f32(as[j] + kb + 2);
+                        n1[4] = __ldg(bs_lo + kb + 2); n1[5] = __ldg(bs_hi + kb + 2);
+                    }
+                }
+            }
+            if (!ok && lane == 0) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 3, static_cast<int>(it));
+        }
+    } else {
+        reg_alloc<kFmEpiRegs>();
+        // ---------------------------------------------------------------- epilogue warps
+        if (do_gemm) {
+            const int ew = warp - kFmEpiWarp0;
+            const int q = warp & 3;   // TMEM lane quarter this warp may read
+            const int cq = ew >> 2;   // which 32-column quarter of each 128-column half
+            const int r = q * 32 + static_cast<int>(lane);
+            FusedWalker w(p.expert_offsets, p.num_experts, nt1, nt2, p.lag);
+            uint32_t tcount = 0, halves = 0;
+            int kind, e, mt, nt, row0, rows, cnt;
+            bool ok = true;
+            for (int tile = pair_id; ok && w.locate(tile, kind, e, mt, nt, row0, rows, cnt); tile += num_pairs, ++tcount) {
+                const int blk = fm_block_index(row0, e);
+                row0 += static_cast<int>(cta) * BM;            // this CTA's half of the 256-row tile
+                rows = max(0, min(BM, rows - static_cast<int>(cta) * BM));
+                const bool valid = r < rows && row0 + r < p.a_rows;
+                const int grow = row0 + (valid ? r : 0);
+                // one decision for all epilogue threads: a thread that gave up must not leave the others at a
+                // named barrier further down
+                if (!named_bar_and(1, kFmEpiThreads, fm_mbar_wait(bar_tfull, tcount & 1u, wt, 256u))) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + cq * 32;
+                uint32_t v0[32], v1[32];
+                tmem_ld_32x32b_x32(t0, v0);
+                tmem_ld_32x32b_x32(t0 + 128, v1);
+                tc_wait_ld_regs(v0);
+                tc_wait_ld_regs(v1);
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    if (cta == 0) mbar_arrive(bar_tempty);
+                    else mbar_arrive_cluster(map_to_cta(bar_tempty, 0));
+                }
+
+                if (kind == 0) {
+                    // SwiGLU on matching gate/up columns, then 1x128 fp8 requantisation (power-of-two scale).
+                    float act[32];
+                    float amax = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float g = __uint_as_float(v0[j]);
+                        act[j] = (g / (1.f + expf(-g))) * __uint_as_float(v1[j]);
+                        amax = fmaxf(amax, fabsf(act[j]));
+                    }
+                    // the exchange area lies inside the first staging buffer: copies of an earlier combine send
+                    // that still read it must be through before it is overwritten
+                    if (cq == 0) bulk_wait_group_read<0>();
+                    named_bar_sync(1, kFmEpiThreads);
+                    float* xch = s_amax + (tcount & 1u) * 512;
+                    xch[cq * 128 + r] = amax;
+                    named_bar_sync(1, kFmEpiThreads);
+                    amax = fmaxf(fmaxf(xch[r], xch[128 + r]), fmaxf(xch[256 + r], xch[384 + r]));
+                    float scale, inv;
+                    ue8m0_scale(amax, scale, inv);
+                    if (valid) {
+                        uint8_t* dst = p.act_q + static_cast<size_t>(grow) * p.inter + nt * 128 + cq * 32;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 16) {
+                            uint4 o;
+                            o.x = pack_e4m3x4(act[j + 0] * inv, act[j + 1] * inv, act[j + 2] * inv, act[j + 3] * inv);
+                            o.y = pack_e4m3x4(act[j + 4] * inv, act[j + 5] * inv, act[j + 6] * inv, act[j + 7] * inv);
+                            o.z = pack_e4m3x4(act[j + 8] * inv, act[j + 9] * inv, act[j + 10] * inv, act[j + 11] * inv);
+                            o.w = pack_e4m3x4(act[j + 12] * inv, act[j + 13] * inv, act[j + 14] * inv, act[j + 15] * inv);
+                            *reinterpret_cast<uint4*>(dst + j) = o;
+                        }
+                        if (cq == 0) p.act_s[static_cast<size_t>(grow) * (p.inter / 128) + nt] = scale;
+                    }
+                    // this CTA's half of the tile is in memory: tell the second GEMM of this row block
+                    named_bar_sync(1, kFmEpiThreads);
+                    if (ew == 0 && lane == 0) {
+                        __threadfence();
+                        red_release_gpu_add_u32(p.g1_done + blk, 1u);
+                    }
+                } else {
+                    // bf16 rows straight to the origin rank's combine slots (bulk copies, two staging buffers)
+                    __nv_bfloat16* orow = nullptr;
+                    if (valid) {
+                        const int src = p.row_src[static_cast<size_t>(grow) * 3 + 0];
+                        const int tok = p.row_src[static_cast<size_t>(grow) * 3 + 1];
+                        const int kk = p.row_src[static_cast<size_t>(grow) * 3 + 2];
+                        if (src >= 0 && src < p.num_ranks && tok >= 0 && tok < p.max_tokens && kk >= 0 && kk < p.topk)
+                            orow = reinterpret_cast<__nv_bfloat16*>(p.peer_base[src] + p.off_combine_buf) +
+                                   (static_cast<size_t>(tok) * p.topk + kk) * static_cast<size_t>(p.h);
+                    }
+                    auto push_half = [&](const uint32_t (&v)[32], int c0) {
+                        uint8_t* sbuf = stg + (halves & 1u) * kFmStgBytes;
+                        uint8_t* srow = sbuf + r * kFmStgPitch;
+                        ++halves;
+                        if (cq == 0) bulk_wait_group_read<1>();  // the copies that read this buffer are done with it
+                        named_bar_sync(1, kFmEpiThreads);
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8)
+                            *reinterpret_cast<uint4*>(srow + cq * 64 + j * 2) =
+                                pack_bf16x8(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                                            __uint_as_float(v[j + 3]), __uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]),
+                                            __uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                        fence_proxy_async_smem();
+                        named_bar_sync(1, kFmEpiThreads);
+                        if (cq == 0) {
+                            if (orow != nullptr) bulk_store_s2g(orow + c0, srow, 256);
+                            bulk_commit_group();
+                        }
+                    };
+                    const int c_lo = nt * BN;
+                    push_half(v0, c_lo);
+                    if (c_lo + 128 < p.h) push_half(v1, c_lo + 128);
+                }
+            }
+            if (cq == 0) bulk_wait_group<0>();  // every row this thread sent has been written
+            if (!ok) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 2, static_cast<int>(tcount));
+        }
+    }
+
+    // ------------------------------------------------------------------ teardown
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();  // the other CTA may still read this CTA's shared memory or signal its barriers
+    if (do_gemm && warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, kFmTmemCols);
+    }
+    if (do_gemm && threadIdx.x == 0) {
+        __threadfence_system();
+        const unsigned int old = atomicAdd(p.done_ctr, 1u);
+        if (old == gridDim.x - 1) {
+            p.done_ctr[0] = 0u;
+            __threadfence_system();
+            const uint32_t epoch = *p.epoch_send + 1u;  // this launch is the send phase of a combine
+            if (p.dbg_drop_flags == 0) {
+                for (int d = 0; d < p.num_ranks; ++d)
+                    st_release_sys_u32(reinterpret_cast<uint32_t*>(p.peer_base[d] + p.off_combine_flag) + p.rank, epoch);
+            }
+            *p.epoch_send = epoch;
+        }
+    }
+}
+
+}  // namespace cam
+
+extern "C" int cam_fused_moe_smem_bytes(void) { return cam::kFmSmem; }
+
+namespace {
+
+void fm_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int grid, cudaStream_t stream) {
+    cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid & ~1));
+    cfg.blockDim = dim3(cam::kFmThreads);
+    cfg.dynamicSmemBytes = cam::kFmSmem;
+    cfg.stream = stream;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+}
+
+}  // namespace
+
+// CTA pairs of the fused kernel that can be resident at once on the current device (cached per device; -1 on error).
+extern "C" int cam_fused_moe_max_pairs(void) {
+    static cam::SmemLimitCache limit;
+    if (limit.ensure(cam::fused_moe_pair_kernel, cam::kFmSmem) != cudaSuccess) return -1;
+    static int max_pairs[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+    if (max_pairs[dev] == 0) {
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attr[1];
+        fm_config(cfg, attr, 2, nullptr);
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, cam::fused_moe_pair_kernel, &cfg) == cudaSuccess && n > 0) max_pairs[dev] = n;
+        else max_pairs[dev] = -1;
+    }
+    return max_pairs[dev];
+}
+
+// The tiles of the launch are walked with a fixed stride by CTA pairs that wait for one another's
+// results (second GEMM after first), so the grid never exceeds what is resident at once.
+extern "C" int cam_launch_fused_moe(const cam::FusedMoeParams* p, const CUtensorMap* tmap_a1, const CUtensorMap* tmap_b1,
+                                    const CUtensorMap* tmap_a2, const CUtensorMap* tmap_b2, int grid, cudaStream_t stream) {
+    const int fit = cam_fused_moe_max_pairs();
+    if (fit <= 0) return static_cast<int>(cudaErrorLaunchOutOfResources);
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr[1];
+    fm_config(cfg, attr, grid, stream);
+    if (2 * fit < static_cast<int>(cfg.gridDim.x)) cfg.gridDim = dim3(static_cast<unsigned>(2 * fit));
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, cam::fused_moe_pair_kernel, *tmap_a1, *tmap_b1, *tmap_a2, *tmap_b2, *p));
+}

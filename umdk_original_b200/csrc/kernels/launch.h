@@ -39,6 +39,17 @@ struct DispatchNormalParams {
     int* num_tokens_per_expert_out; // [E] optional (may be null)
     unsigned int* done_ctr;         // [1], self-resetting
     CamStatus* status;
+    // Deferred push (the fused layer's first launch): the SEND phase pushes nothing.  It quantises every token once
+    // into local memory and writes the list of rows to send, ordered by (local expert at the destination, destination
+    // rank, scan order), so that the fused kernel's copy warps complete expert 0 of every rank first, then expert 1, ...
+    int defer_push;
+    uint8_t* xq;                    // [T, h] e4m3
+    float* xs;                      // [T, h/128]
+    int4* send_list;                // [T*K] {token, destination rank, row at the destination, local expert | k << 16}
+    int* send_list_len;             // [1]
+    uint32_t* g1_done;              // [g1_done_len] per-row-block counters of the fused kernel, zeroed here
+    int g1_done_len;
+    uint64_t off_arrival;           // u32[2][E] in the symmetric region: rows landed per local expert
 };
 
 struct CombineParams {
@@ -123,6 +134,43 @@ struct GroupedGemmParams {
     CamStatus* status;
 };
 
+// Deep-fused layer (kernels/fused_moe_mx.cu): dispatch send, both grouped GEMMs and the combine send in one launch.
+// GEMM1: A = this rank's receive buffer [a_rows, h], B = w1 [E_local * 2I, h]; GEMM2: A = act_q [a_rows, I],
+// B = w2 [E_local * h, I] (four TMA descriptors passed beside this block).
+struct FusedMoeParams {
+    const int* expert_offsets;  // [E_local+1] first row of every local expert (written by the layer's first launch)
+    int num_experts;            // E_local
+    int h, inter;               // hidden size, intermediate size
+    int a_rows;                 // rows of the receive buffer (capacity)
+    int max_tokens;             // tokens per rank the combine slots are sized for
+    const float* a1_scales;     // [a_rows, h/128] scales of the received rows (arrive during the kernel)
+    const float* b1_scales;     // [E_local, 2I/128, h/128]
+    const float* b2_scales;     // [E_local, h/128, I/128]
+    uint8_t* act_q;             // [a_rows, I] e4m3, between the two GEMMs
+    float* act_s;               // [a_rows, I/128]
+    const int* row_src;         // [a_rows, 3] (src rank, src token, src k) of every received row
+    uint8_t* const* peer_base;
+    uint64_t off_combine_buf, off_combine_flag, off_recv_x, off_recv_scales, off_recv_src, off_arrival;
+    int arrival_stride;         // entries per parity of the arrival counters (= number of experts of the call)
+    int topk, num_ranks, rank;
+    uint32_t* epoch_send;            // device counter of the combine send phase (this launch plays that phase)
+    const uint32_t* epoch_dispatch;  // device counter of the dispatch send phase, already advanced by the first launch
+    int dbg_drop_flags;
+    unsigned int* done_ctr;
+    CamStatus* status;
+    uint32_t* g1_done;          // per 256-row block: column tiles of GEMM1 written (zeroed by the first launch)
+    int lag;                    // GEMM2 of expert e is scheduled after GEMM1 of expert e + lag
+    // dispatch send
+    const uint8_t* xq;          // [T, h] this rank's quantised tokens
+    const float* xs;            // [T, h/128]
+    const int4* send_list;      // {token, destination rank, row at the destination, local expert | k << 16}
+    const int* send_list_len;   // [1]
+    int send_list_cap;
+    int phase_mask;             // CAM_PHASE_SEND: copy warps run, CAM_PHASE_RECV: the GEMM roles run
+    uint64_t timeout_ns;
+    unsigned long long* trace;  // optional [E_local+1]: time GEMM1 of every expert was released, kernel start
+};
+
 // Exchange between the two tensor-parallel ranks of one expert-parallel position (kernels/tp_exchange.cu).
 struct TpExchangeParams {
     int reduce;              // 0: all-gather after dispatch, 1: reduce-scatter before combine
@@ -192,6 +240,10 @@ int cam_launch_grouped_gemm_mxfp8_pair(const cam::GroupedGemmParams* p, const CU
 int cam_grouped_gemm_mx_pair_smem_bytes(void);
 int cam_launch_grouped_gemm_w8a8(const cam::GroupedGemmParams* p, const CUtensorMap* tmap_a,
                                  const CUtensorMap* tmap_b, int grid, cudaStream_t stream);
+int cam_fused_moe_smem_bytes(void);
+int cam_fused_moe_max_pairs(void);
+int cam_launch_fused_moe(const cam::FusedMoeParams* p, const CUtensorMap* tmap_a1, const CUtensorMap* tmap_b1,
+                         const CUtensorMap* tmap_a2, const CUtensorMap* tmap_b2, int grid, cudaStream_t stream);
 int cam_launch_barrier(uint8_t* const* peer_base, uint64_t off_barrier_flag, uint32_t* epochs, int R, int rank,
                        int phase_mask, int dbg_drop_flags, uint64_t timeout_ns, CamStatus* status, cudaStream_t stream);
 int cam_launch_p2p_copy(void* dst, const void* src, size_t bytes, int grid, cudaStream_t stream);

@@ -89,6 +89,17 @@ struct CamBuffer {
     bool profile = false;
     bool profile_valid = false;
     cudaEvent_t prof_ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    // deep-fused layer (allocated on first use): quantised tokens, send list, per-row-block counters, optional trace
+    uint8_t* xq = nullptr;
+    float* xs = nullptr;
+    int4* send_list = nullptr;
+    int* send_list_len = nullptr;
+    uint32_t* g1_done = nullptr;
+    int g1_done_len = 0;
+    unsigned long long* fused_trace = nullptr;  // [E + 1], null = off
+    // switches read from the environment once, when the buffer is created (UMDK_CAM_GEMM_*, UMDK_CAM_DEEP_FUSE):
+    // -1 = not set (the runtime decides), 0 / 1 = forced
+    int env_bulk_push = -1, env_pair = -1, env_swap = -1, env_staging2 = -1, env_deep_fuse = -1, env_fuse_lag = -1;
     std::map<std::tuple<const void*, uint64_t, uint64_t>, CUtensorMap> tmap_cache;
     std::map<std::tuple<int, int, int, int>, int> ll_grid_cache;  // (h, quant, T, K) -> co-resident grid
 };
@@ -106,6 +117,8 @@ extern "C" const char* cam_status_string(int code) {
         case CAM_ERR_TIMEOUT_LL_CELL: return "timeout waiting for a low-latency count cell";
         case CAM_ERR_TIMEOUT_BARRIER: return "timeout in the cross-rank barrier";
         case CAM_ERR_BAD_INDEX: return "index out of range recorded by a device-side check";
+        case CAM_ERR_TIMEOUT_ARRIVAL: return "timeout waiting for the rows of one local expert to arrive (fused layer)";
+        case CAM_ERR_TIMEOUT_GEMM1: return "timeout waiting for the first GEMM of a row block (fused layer)";
         default: return "unknown status";
     }
 }
@@ -152,6 +165,7 @@ extern "C" int cam_layout_compute_tp(CamLayout* L, int R, int E, int max_tokens,
     L->off_dup_cnt = take(sizeof(uint32_t) * 2ull * CAM_MAX_RANKS);
     L->off_count_matrix = take(sizeof(int32_t) * 2ull * R * E);
     L->off_ll_cells = take(sizeof(uint64_t) * 2ull * E);
+    L->off_arrival = take(sizeof(uint32_t) * 2ull * E);
     const uint64_t ctrl_end = off;
     (void)ctrl_end;
     L->off_recv_x = take(static_cast<uint64_t>(capacity) * hidden * 2);
@@ -190,6 +204,16 @@ extern "C" CamBuffer* cam_buffer_create(int device, int rank, int num_ranks, con
     b->rank = rank;
     b->num_ranks = num_ranks;
     b->layout = *layout;
+    auto env_switch = [](const char* name) {
+        const char* v = getenv(name);
+        return (v == nullptr || v[0] == '\0') ? -1 : atoi(v);
+    };
+    b->env_bulk_push = env_switch("UMDK_CAM_GEMM_BULK_PUSH");
+    b->env_pair = env_switch("UMDK_CAM_GEMM_PAIR");
+    b->env_swap = env_switch("UMDK_CAM_GEMM_SWAP");
+    b->env_staging2 = env_switch("UMDK_CAM_GEMM_STAGING2");
+    b->env_deep_fuse = env_switch("UMDK_CAM_DEEP_FUSE");
+    b->env_fuse_lag = env_switch("UMDK_CAM_FUSE_LAG");
     const int E = layout->num_experts, R = num_ranks;
     if ((e = cudaDeviceGetAttribute(&b->num_sms, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess) {
         delete b;
@@ -259,6 +283,10 @@ extern "C" int cam_buffer_destroy(CamBuffer* b) {
     if (b->d_trace != nullptr) cudaFree(b->d_trace);
     if (b->act_f32 != nullptr) cudaFree(b->act_f32);
     if (b->row_amax != nullptr) cudaFree(b->row_amax);
+    for (void* p : {static_cast<void*>(b->xq), static_cast<void*>(b->xs), static_cast<void*>(b->send_list),
+                    static_cast<void*>(b->send_list_len), static_cast<void*>(b->g1_done),
+                    static_cast<void*>(b->fused_trace)})
+        if (p != nullptr) cudaFree(p);
     for (auto e : b->prof_ev)
         if (e != nullptr) cudaEventDestroy(e);
     delete b;
@@ -352,6 +380,34 @@ extern "C" int cam_buffer_read_trace(CamBuffer* b, unsigned long long* out16) {
     CAM_CUDA(cudaSetDevice(b->device));
     CAM_CUDA(cudaDeviceSynchronize());
     CAM_CUDA(cudaMemcpy(out16, b->d_trace, sizeof(unsigned long long) * 16, cudaMemcpyDeviceToHost));
+    return 0;
+}
+// Timeline of the deep-fused layer: for every local expert the time (ns after the fused kernel started) at which
+// its first GEMM was released because all of its rows had arrived; 0 = never released.  Off by default.
+extern "C" int cam_buffer_set_fused_trace(CamBuffer* b, int on) {
+    CAM_CHECK(b != nullptr, "set_fused_trace: null buffer");
+    CAM_CUDA(cudaSetDevice(b->device));
+    const size_t bytes = sizeof(unsigned long long) * (b->layout.num_experts + 1);
+    if (on && b->fused_trace == nullptr) {
+        CAM_CUDA(cudaMalloc(&b->fused_trace, bytes));
+        CAM_CUDA(cudaMemset(b->fused_trace, 0, bytes));
+    } else if (!on && b->fused_trace != nullptr) {
+        CAM_CUDA(cudaDeviceSynchronize());
+        CAM_CUDA(cudaFree(b->fused_trace));
+        b->fused_trace = nullptr;
+    }
+    return 0;
+}
+extern "C" int cam_buffer_read_fused_trace(CamBuffer* b, long long* out, int num_local_experts) {
+    CAM_CHECK(b != nullptr && out != nullptr && b->fused_trace != nullptr, "read_fused_trace: tracing is off");
+    CAM_CHECK(num_local_experts >= 1 && num_local_experts <= b->layout.num_experts, "read_fused_trace: bad expert count");
+    CAM_CUDA(cudaSetDevice(b->device));
+    CAM_CUDA(cudaDeviceSynchronize());
+    std::vector<unsigned long long> t(num_local_experts + 1);
+    CAM_CUDA(cudaMemcpy(t.data(), b->fused_trace, sizeof(unsigned long long) * (num_local_experts + 1), cudaMemcpyDeviceToHost));
+    const unsigned long long t0 = t[num_local_experts];
+    for (int e = 0; e < num_local_experts; ++e)
+        out[e] = t[e] == 0ull ? -1ll : static_cast<long long>(t[e] - t0);
     return 0;
 }
 extern "C" int cam_buffer_set_profile(CamBuffer* b, int on) {
@@ -538,8 +594,25 @@ static int check_common(const CamBuffer* b, int T, int K, int h, int E, const ch
     return 0;
 }
 
-extern "C" int cam_dispatch_normal(CamBuffer* b, const void* x, const void* topk_idx, int idx_is_i64, int T, int K,
-                                   int h, int E, int quant_mode, int phase_mask, cudaStream_t stream) {
+// Workspace of the deep-fused layer, allocated on the first call that takes that route.
+static int ensure_deep_workspace(CamBuffer* b) {
+    if (b->xq != nullptr) return 0;
+    const CamLayout& L = b->layout;
+    CAM_CUDA(cudaSetDevice(b->device));
+    const size_t pairs = static_cast<size_t>(L.max_tokens) * L.topk;
+    b->g1_done_len = L.capacity / 256 + L.num_experts + 2;
+    CAM_CUDA(cudaMalloc(&b->xq, static_cast<size_t>(L.max_tokens) * L.hidden));
+    CAM_CUDA(cudaMalloc(&b->xs, static_cast<size_t>(L.max_tokens) * (L.hidden / 128) * sizeof(float)));
+    CAM_CUDA(cudaMalloc(&b->send_list, pairs * sizeof(int4)));
+    CAM_CUDA(cudaMalloc(&b->send_list_len, sizeof(int)));
+    CAM_CUDA(cudaMalloc(&b->g1_done, sizeof(uint32_t) * b->g1_done_len));
+    CAM_CUDA(cudaMemset(b->send_list_len, 0, sizeof(int)));
+    CAM_CUDA(cudaMemset(b->g1_done, 0, sizeof(uint32_t) * b->g1_done_len));
+    return 0;
+}
+
+static int dispatch_normal_impl(CamBuffer* b, const void* x, const void* topk_idx, int idx_is_i64, int T, int K, int h,
+                                int E, int quant_mode, int phase_mask, bool defer_push, cudaStream_t stream) {
     if (check_common(b, T, K, h, E, "dispatch_normal") != 0) return -1;
     CAM_CHECK(T <= b->layout.max_tokens, "dispatch_normal: %d tokens exceed the buffer's max_tokens %d", T, b->layout.max_tokens);
     CAM_CHECK(quant_mode == CAM_QUANT_NONE || quant_mode == CAM_QUANT_INT8_TOKEN || CAM_QUANT_IS_FP8(quant_mode),
@@ -579,12 +652,29 @@ extern "C" int cam_dispatch_normal(CamBuffer* b, const void* x, const void* topk
     p.num_tokens_per_expert_out = b->num_tokens_per_expert;
     p.done_ctr = b->done_ctr + 0;
     p.status = b->d_status;
+    p.off_arrival = b->layout.off_arrival;
+    if (defer_push) {
+        CAM_CHECK(CAM_QUANT_IS_FP8(quant_mode), "dispatch_normal: the deferred push carries fp8 rows only");
+        if (ensure_deep_workspace(b) != 0) return -1;
+        p.defer_push = 1;
+        p.xq = b->xq;
+        p.xs = b->xs;
+        p.send_list = b->send_list;
+        p.send_list_len = b->send_list_len;
+        p.g1_done = b->g1_done;
+        p.g1_done_len = b->g1_done_len;
+    }
     // The count matrix is laid out for layout.num_experts; a call with fewer experts still uses
     // stride E because every rank of the call passes the same E.
     int grid = b->num_sms;  // fixed per device so that the COUNT and SEND phases agree on token chunks
     const int rc = cam_launch_dispatch_normal(&p, grid, stream);
     CAM_CHECK(rc == 0, "dispatch_normal launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
     return 0;
+}
+
+extern "C" int cam_dispatch_normal(CamBuffer* b, const void* x, const void* topk_idx, int idx_is_i64, int T, int K,
+                                   int h, int E, int quant_mode, int phase_mask, cudaStream_t stream) {
+    return dispatch_normal_impl(b, x, topk_idx, idx_is_i64, T, K, h, E, quant_mode, phase_mask, false, stream);
 }
 
 extern "C" int cam_combine(CamBuffer* b, const void* y, const int* row_src, const int* total_rows,
@@ -803,24 +893,33 @@ static int grouped_gemm_impl(CamBuffer* b, const void* a_q, const float* a_scale
     p.topk = topk;
     int sms = 0;
     CAM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    // Switches: a Buffer reads UMDK_CAM_GEMM_* once when it is created; the stand-alone ops (no Buffer) read the
+    // environment per call.  -1 = not set.
+    auto env_now = [](const char* name) {
+        const char* v = getenv(name);
+        return (v == nullptr || v[0] == '\0') ? -1 : atoi(v);
+    };
+    const int sw_bulk = b ? b->env_bulk_push : env_now("UMDK_CAM_GEMM_BULK_PUSH");
+    const int sw_pair = b ? b->env_pair : env_now("UMDK_CAM_GEMM_PAIR");
+    const int sw_swap = b ? b->env_swap : env_now("UMDK_CAM_GEMM_SWAP");
+    const int sw_stg2 = b ? b->env_staging2 : env_now("UMDK_CAM_GEMM_STAGING2");
     // rows leave the GEMM2 epilogue as 256-byte bulk copies (measured a few percent ahead of vector stores at 2 and 4
     // GPUs); UMDK_CAM_GEMM_BULK_PUSH=0 selects the vector-store form
-    p.bulk_push = 1;
-    if (const char* env = getenv("UMDK_CAM_GEMM_BULK_PUSH")) p.bulk_push = env[0] == '1';
+    p.bulk_push = sw_bulk < 0 ? 1 : (sw_bulk == 1);
     // CTA pairs (256-row tiles, B tile shared inside the cluster) pay off once experts fill such tiles;
     // UMDK_CAM_GEMM_PAIR=0/1 forces the choice.
     bool pair = ue8m0 && rows_per_expert_hint >= 384;
-    if (const char* env = getenv("UMDK_CAM_GEMM_PAIR")) pair = ue8m0 && env[0] == '1';
+    if (sw_pair >= 0) pair = ue8m0 && sw_pair == 1;
     // Small experts (a tile of rows or less each) take the kernel with the operands exchanged, whose tensor-core
     // time follows the rows actually present instead of whole 128-row tiles; UMDK_CAM_GEMM_SWAP=0/1 forces the choice.
     bool swap = ue8m0 && !pair && rows_per_expert_hint < kSwapRowsPerExpert;
-    if (const char* env = getenv("UMDK_CAM_GEMM_SWAP")) swap = ue8m0 && !pair && env[0] == '1';
+    if (sw_swap >= 0) swap = ue8m0 && !pair && sw_swap == 1;
     // The combine-send epilogue of the block-scaled kernels overlaps converting a half tile with the copies of the previous
     // one (two staging buffers, paid for with pipeline stages); UMDK_CAM_GEMM_STAGING2=0 keeps the one-buffer form.
     // On by default in the CTA-pair kernel only: the one-CTA kernel, used for small experts, lives on streaming weights
     // and loses more from its fourth pipeline stage than the epilogue gains (measured on one GPU, 256 experts).
     bool two_staging = mode == 2 && p.bulk_push != 0 && pair;
-    if (const char* env = getenv("UMDK_CAM_GEMM_STAGING2")) two_staging = mode == 2 && p.bulk_push != 0 && env[0] == '1';
+    if (sw_stg2 >= 0) two_staging = mode == 2 && p.bulk_push != 0 && sw_stg2 == 1;
     const int rc = !ue8m0 ? cam_launch_grouped_gemm_fp8(&p, &ta, &tb, sms, stream)
                    : pair ? cam_launch_grouped_gemm_mxfp8_pair(&p, &ta, &tb, sms, two_staging ? 1 : 0, stream)
                           : cam_launch_grouped_gemm_mxfp8(&p, &ta, &tb, sms, swap ? 1 : 0, two_staging ? 1 : 0, stream);
@@ -978,6 +1077,110 @@ extern "C" int cam_fused_moe_w8a8(CamBuffer* b, const void* x, const void* exper
     return 0;
 }
 
+// Deep-fused route of the layer: launch 1 exchanges the counts, quantises the tokens locally and writes the
+// expert-ordered send list; launch 2 sends the rows, runs both grouped GEMMs as their inputs become complete and
+// pushes the outputs into the origins' combine slots; launch 3 is the weighted reduce.
+static int fused_moe_deep(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,
+                          const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
+                          const float* w2_s, void* out, int64_t* expert_token_nums, int T, int K, int h, int inter,
+                          int E, int El, int rows_hint, int phase_mask, cudaStream_t stream) {
+    const CamLayout& L = b->layout;
+    const bool prof = b->profile && phase_mask == 15;
+    auto stamp = [&](int i) { if (prof) cudaEventRecord(b->prof_ev[i], stream); };
+    stamp(0);
+    const int prep_mask = phase_mask & (CAM_PHASE_COUNT | CAM_PHASE_SEND);
+    if (prep_mask) {
+        if (dispatch_normal_impl(b, x, expert_ids, idx_is_i64, T, K, h, E, CAM_QUANT_FP8_1x128_UE8M0, prep_mask, true,
+                                 stream) != 0)
+            return -1;
+    }
+    stamp(1);
+    const int fmask = phase_mask & (CAM_PHASE_SEND | CAM_PHASE_RECV);
+    if (fmask) {
+        if (ensure_deep_workspace(b) != 0) return -1;
+        uint8_t* recv_x = b->base + L.off_recv_x;
+        CUtensorMap ta1, tb1, ta2, tb2;
+        if (make_tmap(b, &ta1, recv_x, static_cast<uint64_t>(h), static_cast<uint64_t>(L.capacity)) != 0) return -1;
+        if (make_tmap(b, &tb1, w1_q, static_cast<uint64_t>(h), static_cast<uint64_t>(El) * 2 * inter) != 0) return -1;
+        if (make_tmap(b, &ta2, b->act_q, static_cast<uint64_t>(inter), static_cast<uint64_t>(L.capacity)) != 0) return -1;
+        if (make_tmap(b, &tb2, w2_q, static_cast<uint64_t>(inter), static_cast<uint64_t>(El) * h) != 0) return -1;
+        const int fit = cam_fused_moe_max_pairs();
+        CAM_CHECK(fit > 0, "fused_moe: the fused kernel does not fit on this device");
+        cam::FusedMoeParams p{};
+        p.expert_offsets = b->expert_offsets;
+        p.num_experts = El;
+        p.h = h;
+        p.inter = inter;
+        p.a_rows = L.capacity;
+        p.max_tokens = L.max_tokens;
+        p.a1_scales = reinterpret_cast<const float*>(b->base + L.off_recv_scales);
+        p.b1_scales = w1_s;
+        p.b2_scales = w2_s;
+        p.act_q = b->act_q;
+        p.act_s = b->act_s;
+        p.row_src = reinterpret_cast<const int*>(b->base + L.off_recv_src);
+        p.peer_base = b->d_peer_table;
+        p.off_combine_buf = L.off_combine_buf;
+        p.off_combine_flag = L.off_combine_flag;
+        p.off_recv_x = L.off_recv_x;
+        p.off_recv_scales = L.off_recv_scales;
+        p.off_recv_src = L.off_recv_src;
+        p.off_arrival = L.off_arrival;
+        p.arrival_stride = E;
+        p.topk = K;
+        p.num_ranks = b->num_ranks;
+        p.rank = b->rank;
+        p.epoch_send = b->d_epochs + 3;
+        p.epoch_dispatch = b->d_epochs + 1;
+        p.dbg_drop_flags = b->dbg_drop_flags;
+        p.done_ctr = b->done_ctr + 2;
+        p.status = b->d_status;
+        p.g1_done = b->g1_done;
+        // The second GEMM of an expert is scheduled `lag` experts behind the first, far enough that the tiles it
+        // waits for were started a whole wave of CTA pairs earlier.
+        const int tiles1 = ((rows_hint + 255) / 256) * (inter / 128);
+        int lag = tiles1 > 0 ? (fit + tiles1 - 1) / tiles1 : 1;
+        if (b->env_fuse_lag >= 0) lag = b->env_fuse_lag;
+        if (lag < 1) lag = 1;
+        if (lag > El) lag = El;
+        p.lag = lag;
+        p.xq = b->xq;
+        p.xs = b->xs;
+        p.send_list = b->send_list;
+        p.send_list_len = b->send_list_len;
+        p.send_list_cap = L.max_tokens * L.topk;
+        p.phase_mask = fmask;
+        p.timeout_ns = b->timeout_ns;
+        p.trace = b->fused_trace;
+        if (b->fused_trace != nullptr && (fmask & CAM_PHASE_RECV))
+            CAM_CUDA(cudaMemsetAsync(b->fused_trace, 0, sizeof(unsigned long long) * (L.num_experts + 1), stream));
+        const int rc = cam_launch_fused_moe(&p, &ta1, &tb1, &ta2, &tb2, b->num_sms, stream);
+        CAM_CHECK(rc == 0, "fused_moe launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+        if ((fmask & CAM_PHASE_RECV) && expert_token_nums != nullptr)
+            CAM_CUDA(cudaMemcpyAsync(expert_token_nums, b->num_recv_per_expert, sizeof(int64_t) * El,
+                                     cudaMemcpyDeviceToDevice, stream));
+    }
+    stamp(2);
+    stamp(3);
+    if (phase_mask & 8) {
+        if (cam_combine(b, nullptr, nullptr, nullptr, expert_ids, idx_is_i64, topk_weights, out, T, K, h, E, 0, 0,
+                        CAM_PHASE_RECV, stream) != 0)
+            return -1;
+    }
+    stamp(4);
+    if (prof) b->profile_valid = true;
+    return 0;
+}
+
+// Whether the deep-fused route serves this call: block-scaled fp8 with power-of-two scales, experts large enough for
+// 256-row tiles (or UMDK_CAM_DEEP_FUSE=1), rows the copy warps can stage.  UMDK_CAM_DEEP_FUSE=0 keeps the four launches.
+static bool use_deep_fuse(const CamBuffer* b, bool ue8m0, int h, int inter, int rows_hint) {
+    if (!ue8m0 || b->env_deep_fuse == 0) return false;
+    if (h % 512 != 0 || h > 7168 || inter % 128 != 0) return false;
+    if (b->env_deep_fuse == 1) return true;
+    return rows_hint >= 384;
+}
+
 static int fused_moe_impl(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,
                           const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
                           const float* w2_s, void* out, int64_t* expert_token_nums, int T, int K, int h, int inter,
@@ -990,6 +1193,12 @@ static int fused_moe_impl(CamBuffer* b, const void* x, const void* expert_ids, i
     // local expert ever receives rows)
     const int El = (gemm_experts > 0 && gemm_experts <= E / b->num_ranks) ? gemm_experts : E / b->num_ranks;
     const CamLayout& L = b->layout;
+    // mean rows per local expert when routing is balanced: every rank sends T * K rows in total
+    const int rows_hint = static_cast<int>(static_cast<int64_t>(T) * K * b->num_ranks / E);
+    CAM_CUDA(cudaSetDevice(b->device));
+    if (use_deep_fuse(b, ue8m0, h, inter, rows_hint))
+        return fused_moe_deep(b, x, expert_ids, idx_is_i64, topk_weights, w1_q, w1_s, w2_q, w2_s, out, expert_token_nums, T,
+                              K, h, inter, E, El, rows_hint, phase_mask, stream);
     const int disp_mask = phase_mask & CAM_PHASE_ALL;
     const bool prof = b->profile && phase_mask == 15;
     auto stamp = [&](int i) { if (prof) cudaEventRecord(b->prof_ev[i], stream); };
@@ -1004,8 +1213,6 @@ static int fused_moe_impl(CamBuffer* b, const void* x, const void* expert_ids, i
         const uint8_t* recv_x = b->base + L.off_recv_x;
         const float* recv_s = reinterpret_cast<const float*>(b->base + L.off_recv_scales);
         const int* recv_src = reinterpret_cast<const int*>(b->base + L.off_recv_src);
-        // mean rows per local expert when routing is balanced: every rank sends T * K rows in total
-        const int rows_hint = static_cast<int>(static_cast<int64_t>(T) * K * b->num_ranks / E);
         if (grouped_gemm_impl(b, recv_x, recv_s, L.capacity, w1_q, w1_s, b->expert_offsets, El, 2 * inter, h, 1,
                               nullptr, b->act_q, b->act_s, nullptr, K, 0, ue8m0, rows_hint, stream) != 0)
             return -1;

@@ -205,6 +205,18 @@ class Buffer:
             return {n: (v - t0) / 1e3 for n, v in zip(names, vals) if v}
         return {"dispatch_ll": rel(t[:8], self.LL_DISPATCH_TRACE), "combine": rel(t[8:14], self.COMBINE_TRACE)}
 
+    def set_fused_trace(self, on: bool = True) -> None:
+        """Timeline of the deep-fused layer (off by default): the kernel notes when the first GEMM of every local
+        expert was released, i.e. when all rows of that expert had arrived."""
+        if self._native is not None:
+            self._native.set_fused_trace(on)
+
+    def read_fused_trace(self, num_local_experts: Optional[int] = None) -> List[Optional[float]]:
+        """Microseconds after the start of the last fused kernel at which each local expert's first GEMM was
+        released; ``None`` for an expert that never was (its rows did not all arrive).  Synchronises the device."""
+        n = num_local_experts or self.config.num_experts // self.num_ranks
+        return [None if v < 0 else v / 1e3 for v in self._native.read_fused_trace(n)]
+
     def set_profile(self, on: bool = True) -> None:
         """Per-stage device timing of ``fused_deep_moe`` (CUDA events around its four launches)."""
         if self._native is not None:
@@ -212,7 +224,9 @@ class Buffer:
 
     def read_profile(self) -> dict:
         """Milliseconds of the last profiled fused layer: dispatch, GEMM1 (+SwiGLU+requant), GEMM2
-        (+combine send), combine reduce.  Synchronises on the last event."""
+        (+combine send), combine reduce.  On the deep-fused route the first entry is the count exchange and local
+        quantisation, the second the one kernel that sends, runs both GEMMs and pushes the combine rows, the third
+        is zero.  Synchronises on the last event."""
         d, g1, g2, c = self._native.read_profile()
         return {"dispatch_ms": d, "gemm1_ms": g1, "gemm2_send_ms": g2, "combine_ms": c}
 

@@ -17,8 +17,10 @@ STATUS_TEXT = {
     6: "timeout waiting for a low-latency count cell",
     7: "timeout in the cross-rank barrier",
     8: "index out of range recorded by a device-side check",
+    9: "timeout waiting for the rows of one local expert to arrive (fused layer)",
+    10: "timeout waiting for the first GEMM of a row block (fused layer)",
 }
-TIMEOUT_CODES = {1, 2, 3, 5, 6, 7}
+TIMEOUT_CODES = {1, 2, 3, 5, 6, 7, 9, 10}
 
 
 class CamError(RuntimeError):

@@ -390,3 +390,86 @@ def test_low_latency_with_tensor_parallel_pair():
         assert (outs[v].cpu().float() - want.float()).abs().max() == 0.0
     for b in flat:
         b.destroy()
+
+
+def test_receive_overflow_publishes_no_rows_and_writes_nothing():
+    """More rows are routed to rank 0 than its buffer holds: the status word says so, every sender skips that
+    rank, the counts rank 0 publishes are zero (so the kernels that follow touch no row at or past the capacity)
+    and its receive region stays as it was.  The fused layer on the same routing returns the same status."""
+    world, t, h, e, k, cap = 2, 64, 256, 4, 2, 32
+    g = torch.Generator().manual_seed(5)
+    xs = [torch.randn(t, h, generator=g).to(torch.bfloat16) for _ in range(world)]
+    topk = [torch.stack([torch.randperm(2, generator=g)[:k] for _ in range(t)]) for _ in range(world)]  # experts 0, 1: rank 0
+    wts = [torch.rand(t, k, generator=g) for _ in range(world)]
+    cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, capacity=cap, timeout_ms=2000.0)
+    bufs = u.Buffer.virtual(world, cfg, _dev(), name="ovf_")
+    dx, dk, dw = ([v.to(_dev()) for v in part] for part in (xs, topk, wts))
+    region = bufs[0].native.recv_x(cap, h, 0)
+    region.fill_(7.0)
+    canary = region.clone()
+
+    def disp(r):
+        return ops.moe_dispatch_prefill_quant(dx[r], dk[r], dw[r], cap, bufs[r].name, r, world, 0)
+
+    res = run_virtual(disp, world, masks=(PHASE_COUNT, PHASE_SEND, PHASE_RECV))
+    with pytest.raises(u.RecvOverflow) as ei:
+        bufs[0].check()
+    assert ei.value.who == 0 and ei.value.detail == world * t * k
+    assert int(bufs[0].native.total_recv().item()) == 0
+    assert int(bufs[0].native.expert_offsets(e // world + 1).abs().sum().item()) == 0
+    assert int(res[0][3].sum().item()) == 0          # rows per local expert
+    assert torch.equal(region, canary)
+    for r in range(world):                            # no sender assigned a row on the overflowing rank
+        assert bool((bufs[r].native.send_row(t * k) == -1).all())
+    for b in bufs:
+        try:
+            b.check()
+        except u.CamError:
+            pass
+        b.reset()
+
+    from umdk_original_b200.models import random_fp8_experts
+    w = random_fp8_experts(e // world, h, 128, device=_dev(), seed=1)
+
+    def fused(r):
+        return ops.fused_deep_moe(dx[r], dk[r], [w.w1], [w.s1], [w.w2], [w.s2], dw[r], None, None, bufs[r].name, world, r,
+                                  e, 0, 0, 4, 0)
+
+    every = run_virtual(fused, world, return_all=True)
+    with pytest.raises(u.RecvOverflow):
+        bufs[0].check()
+    assert int(every[PHASE_RECV][0][1].sum().item()) == 0
+    assert torch.equal(region, canary)
+    for b in bufs:
+        try:
+            b.check()
+        except u.CamError:
+            pass
+        b.destroy()
+
+
+def test_dispatch_outputs_are_views_until_the_next_dispatch_or_copies_on_request():
+    """Default: the outputs of the prefill dispatch view the Buffer's receive region, so the next dispatch on the
+    same Buffer replaces their contents.  With set_copy_outputs(True) every call returns tensors of its own (what
+    the reference does, pybind/moe_dispatch_prefill.cpp:166-191)."""
+    t, h, e, k = 24, 256, 4, 2
+    g = torch.Generator().manual_seed(9)
+    x1 = torch.randn(t, h, generator=g).to(torch.bfloat16).to(_dev())
+    x2 = torch.randn(t, h, generator=g).to(torch.bfloat16).to(_dev())
+    idx = torch.stack([torch.randperm(e, generator=g)[:k] for _ in range(t)]).to(_dev())
+    w = torch.rand(t, k, generator=g).to(_dev())
+    cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, timeout_ms=2000.0)
+    buf = u.Buffer(None, cfg, name="life", device=_dev(), rank=0, num_ranks=1)
+    a = ops.moe_dispatch_prefill_quant(x1, idx, w, 0, "life", 0, 1, 0)
+    first = a[0].clone()
+    b = ops.moe_dispatch_prefill_quant(x2, idx, w, 0, "life", 0, 1, 0)
+    assert a[0].data_ptr() == b[0].data_ptr() and torch.equal(a[0], b[0]) and not torch.equal(a[0], first)
+    buf.set_copy_outputs(True)
+    c = ops.moe_dispatch_prefill_quant(x1, idx, w, 0, "life", 0, 1, 0)
+    d = ops.moe_dispatch_prefill_quant(x2, idx, w, 0, "life", 0, 1, 0)
+    assert c[0].data_ptr() != d[0].data_ptr()
+    assert torch.equal(c[0], first) and torch.equal(d[0], b[0]) and torch.equal(c[1], d[1])
+    buf.check()
+    # a view that outlives destroy() keeps the memory mapped: reading it afterwards is still defined
+    buf.destroy()
+    assert torch.equal(b[0], d[0])

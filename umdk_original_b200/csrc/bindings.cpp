@@ -42,6 +42,9 @@ public:
                                      static_cast<int>(capacity), static_cast<int>(ll_max_tokens), static_cast<int>(tp_rows)));
         buf_ = cam_buffer_create(static_cast<int>(device), static_cast<int>(rank), static_cast<int>(num_ranks), &layout_);
         TORCH_CHECK(buf_ != nullptr, "umdk_cam_op_lib: ", cam_last_error());
+        // Tensors that view the buffer's memory (the outputs of the dispatch ops) share ownership of it, so the
+        // memory is released when the Buffer has been destroyed AND the last such tensor is gone.
+        hold_ = std::shared_ptr<CamBuffer>(buf_, [](CamBuffer* b) { cam_buffer_destroy(b); });
         std::lock_guard<std::mutex> g(g_reg_mutex);
         id_ = g_next_id++;
         g_by_id[id_] = this;
@@ -56,9 +59,14 @@ public:
         }
         ll_src_ = at::Tensor();
         ll_total_ = at::Tensor();
-        cam_buffer_destroy(buf_);
+        tp_counts_ = tp_reduced_ = tp_rows_ = tp_scales_ = at::Tensor();
         buf_ = nullptr;
+        hold_.reset();  // frees now unless views of the memory are still alive
     }
+    // Outputs of the prefill dispatch: views of the symmetric memory (default; valid until the next dispatch on
+    // this Buffer, reset() or destroy()) or private copies that the caller may keep for as long as it likes.
+    void set_copy_outputs(bool on) { copy_outputs_ = on; }
+    bool copy_outputs() const { return copy_outputs_; }
     void register_name(const std::string& name) {
         std::lock_guard<std::mutex> g(g_reg_mutex);
         if (!name_.empty()) g_by_name.erase(name_);
@@ -137,7 +145,9 @@ public:
     cudaStream_t stream() const { return at::cuda::getCurrentCUDAStream(cam_buffer_device(buf_)).stream(); }
     c10::Device device() const { return c10::Device(c10::kCUDA, static_cast<c10::DeviceIndex>(cam_buffer_device(buf_))); }
     at::Tensor view(void* ptr, at::IntArrayRef sizes, at::ScalarType dt) const {
-        return at::from_blob(ptr, sizes, at::TensorOptions().dtype(dt).device(device()));
+        std::shared_ptr<CamBuffer> keep = hold_;
+        return at::from_blob(ptr, sizes, [keep](void*) mutable { keep.reset(); },
+                             at::TensorOptions().dtype(dt).device(device()));
     }
     at::Tensor recv_x(int64_t rows, int64_t h, int64_t quant_mode) const {
         auto* base = static_cast<uint8_t*>(cam_buffer_base(buf_));
@@ -217,6 +227,8 @@ private:
     StackCache stack_cache_[4];
     StackCache kmajor_cache_[2];
     CamBuffer* buf_ = nullptr;
+    std::shared_ptr<CamBuffer> hold_;
+    bool copy_outputs_ = false;
     CamLayout layout_{};
     int64_t id_ = 0;
     std::string name_;
@@ -343,7 +355,15 @@ std::vector<at::Tensor> dispatch_prefill_impl(const at::Tensor& x, const at::Ten
     CAM_ASSERT(rows <= b->capacity(), "num_worst_tokens exceeds the Buffer capacity");
     const int64_t nscale = (quant_mode == 3 || quant_mode == 4) ? h / 128 : (quant_mode == 2 ? 1 : 0);
     at::Tensor scales = nscale > 0 ? b->recv_scales(rows, nscale) : at::empty({0}, x.options().dtype(at::kFloat));
-    return {b->recv_x(rows, h, quant_mode), b->recv_src(rows), b->recv_count(E), per_expert, scales};
+    // The four device outputs are views of the Buffer's memory: the next dispatch on the same Buffer (from this rank
+    // or from a peer that has moved on), reset() and destroy() change or void them.  The reference returns fresh
+    // tensors (pybind/moe_dispatch_prefill.cpp:166-191); Buffer.set_copy_outputs(True) gives the same here at the
+    // cost of one device copy of the received rows.
+    std::vector<at::Tensor> outs = {b->recv_x(rows, h, quant_mode), b->recv_src(rows), b->recv_count(E), per_expert, scales};
+    if (b->copy_outputs())
+        for (at::Tensor& t : outs)
+            if (t.is_cuda()) t = t.clone();
+    return outs;
 }
 
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> moe_dispatch_prefill_cuda(
@@ -870,6 +890,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("reset", &Buffer::reset)
         .def("set_timeout_ms", &Buffer::set_timeout_ms)
         .def("set_debug_drop_flags", &Buffer::set_debug_drop_flags)
+        .def("set_copy_outputs", &Buffer::set_copy_outputs)
         .def("barrier", &Buffer::barrier)
         .def("p2p_write", &Buffer::p2p_write)
         .def("p2p_pingpong", &Buffer::p2p_pingpong)

@@ -154,7 +154,7 @@ grouped_gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         bool ok = true;
         for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
              tile += static_cast<int>(gridDim.x), ++tcount) {
-            const bool valid = r < rows;
+            const bool valid = r < rows && row0 + r < p.a_rows;  // never a row at or past the end of A
             const int grow = row0 + (valid ? r : 0);
             if (!mbar_wait_bounded(bar_tfull, tcount & 1u, abort_flag, 2000000000ull, 256u)) { ok = false; break; }
             tc_fence_after_sync();
@@ -232,7 +232,7 @@ grouped_gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         const int src = p.row_src[static_cast<size_t>(grow) * 3 + 0];
                         const int tok = p.row_src[static_cast<size_t>(grow) * 3 + 1];
                         const int kk = p.row_src[static_cast<size_t>(grow) * 3 + 2];
-                        if (src >= 0 && src < p.num_ranks && tok >= 0 && kk >= 0 && kk < p.topk)
+                        if (src >= 0 && src < p.num_ranks && tok >= 0 && tok < p.max_tokens && kk >= 0 && kk < p.topk)
                             orow = reinterpret_cast<__nv_bfloat16*>(p.peer_base[src] + p.off_combine_buf) +
                                    (static_cast<size_t>(tok) * p.topk + kk) * static_cast<size_t>(p.n_dim);
                     }

@@ -242,7 +242,7 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
         for (int tile = pair_id; ok && w.locate(tile, e, mt, nt, row0, rows); tile += num_pairs, ++tcount) {
             row0 += static_cast<int>(cta) * BM;            // this CTA's half of the 256-row tile
             rows = max(0, min(BM, rows - static_cast<int>(cta) * BM));
-            const bool valid = r < rows;
+            const bool valid = r < rows && row0 + r < p.a_rows;  // never a row at or past the end of A
             const int grow = row0 + (valid ? r : 0);
             if (!mbar_wait_bounded(bar_tfull, tcount & 1u, abort_flag, 2000000000ull, 256u)) { ok = false; break; }
             tc_fence_after_sync();
@@ -300,7 +300,7 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
                         const int src = p.row_src[static_cast<size_t>(grow) * 3 + 0];
                         const int tok = p.row_src[static_cast<size_t>(grow) * 3 + 1];
                         const int kk = p.row_src[static_cast<size_t>(grow) * 3 + 2];
-                        if (src >= 0 && src < p.num_ranks && tok >= 0 && kk >= 0 && kk < p.topk)
+                        if (src >= 0 && src < p.num_ranks && tok >= 0 && tok < p.max_tokens && kk >= 0 && kk < p.topk)
                             orow = reinterpret_cast<__nv_bfloat16*>(p.peer_base[src] + p.off_combine_buf) +
                                    (static_cast<size_t>(tok) * p.topk + kk) * static_cast<size_t>(p.n_dim);
                     }

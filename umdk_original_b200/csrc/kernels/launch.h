@@ -61,6 +61,7 @@ struct CombineParams {
     const float* topk_weights;  // [T, K]
     __nv_bfloat16* out;         // [T, h]
     int T, K, h, E, R, rank;
+    int max_tokens;  // tokens per rank the combine slots hold (SEND drops rows that name a later token)
     int comm_quant;  // 0: bf16 rows on the wire, 2: int8 rows + one fp32 scale per 128 elements
     uint32_t* epochs;        // device counters [send, recv]
     unsigned int* exit_ctr;
@@ -127,6 +128,7 @@ struct GroupedGemmParams {
     uint8_t* const* peer_base;
     uint64_t off_combine_buf, off_combine_flag;
     int topk, num_ranks, rank;
+    int max_tokens;             // mode 2: tokens per rank the combine slots hold (rows naming a later token are dropped)
     uint32_t* epoch_send;       // device counter of the combine send phase (mode 2 plays that phase)
     int bulk_push;              // modes 0/2 of the block-scaled kernels: rows leave as bulk copies instead of vector stores
     int dbg_drop_flags;

@@ -695,6 +695,7 @@ extern "C" int cam_combine(CamBuffer* b, const void* y, const int* row_src, cons
     p.out = static_cast<__nv_bfloat16*>(out);
     p.T = T; p.K = K; p.h = h; p.E = E; p.R = b->num_ranks; p.rank = b->rank;
     p.comm_quant = comm_quant;
+    p.max_tokens = maxT;
     p.epochs = b->d_epochs + (low_latency ? 7 : 3);
     p.exit_ctr = b->exit_ctr + 1;
     p.trace = b->d_trace ? b->d_trace + 8 : nullptr;
@@ -880,6 +881,7 @@ static int grouped_gemm_impl(CamBuffer* b, const void* a_q, const float* a_scale
         p.done_ctr = b->done_ctr + 2;
         p.status = b->d_status;
         p.epoch_send = b->d_epochs + (low_latency ? 7 : 3);
+        p.max_tokens = low_latency ? b->layout.ll_max_tokens : b->layout.max_tokens;
     } else {
         if (s_fallback_status == nullptr) {
             CAM_CUDA(cudaMalloc(&s_fallback_status, sizeof(CamStatus)));
@@ -999,6 +1001,7 @@ static int grouped_gemm_w8a8_impl(CamBuffer* b, const void* a_q, const float* a_
         p.done_ctr = b->done_ctr + 2;
         p.status = b->d_status;
         p.epoch_send = b->d_epochs + 3;
+        p.max_tokens = b->layout.max_tokens;
     } else {
         if (s_status == nullptr) {
             CAM_CUDA(cudaMalloc(&s_status, sizeof(CamStatus)));

@@ -73,6 +73,7 @@ class Buffer:
             self._native = C.Buffer(self.device.index or 0, self.rank, self.num_ranks, cfg.num_experts, cfg.max_tokens,
                                     cfg.hidden, cfg.topk, self.capacity, cfg.ll_max_tokens, tp_rows)
             self._native.set_timeout_ms(cfg.timeout_ms)
+            self._native.set_copy_outputs(bool(cfg.copy_outputs))
             self._native.register_name(self.name)
             self.handle = int(self._native.id)
             if _connect:
@@ -166,6 +167,15 @@ class Buffer:
         elif self._cpu is not None:
             self._cpu.ll_src = None
             self._cpu.last_src = None
+
+    def set_copy_outputs(self, on: bool = True) -> None:
+        """What ``moe_dispatch_prefill`` / ``moe_dispatch_prefill_quant`` return.  Off (default): views of this
+        Buffer's receive region, valid until the next dispatch on the Buffer (this rank's, or a peer's that has
+        moved on to its next call), ``reset()`` or ``destroy()``; the memory itself stays allocated for as long as
+        such a view is alive.  On: private copies, as the reference returns
+        (pybind/moe_dispatch_prefill.cpp:166-191), for callers that keep a layer's rows across the next dispatch."""
+        if self._native is not None:
+            self._native.set_copy_outputs(on)
 
     def set_timeout_ms(self, ms: float) -> None:
         if self._native is not None:

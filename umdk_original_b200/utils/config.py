@@ -20,6 +20,7 @@ class CamConfig:
     capacity_factor: float = 0.0    # >0: capacity = factor * T * K (mean load per rank is T*K)
     ll_max_tokens: int = 0          # tokens per rank, low-latency mode (0 = disabled)
     timeout_ms: float = 10000.0     # budget of every device-side wait
+    copy_outputs: bool = False      # prefill dispatch returns private copies instead of views of the buffer
 
     @classmethod
     def from_env(cls, **overrides) -> "CamConfig":
@@ -27,7 +28,8 @@ class CamConfig:
         for f in fields(cls):
             v = os.environ.get("UMDK_CAM_" + f.name.upper())
             if v is not None and f.name not in overrides:
-                setattr(cfg, f.name, type(getattr(cfg, f.name))(v))
+                kind = type(getattr(cfg, f.name))
+                setattr(cfg, f.name, v.strip().lower() in ("1", "true", "yes", "on") if kind is bool else kind(v))
         return cfg
 
     def resolve_capacity(self, num_ranks: int) -> int:

@@ -79,25 +79,25 @@ class BaselineMoE:
         if world > 1:
             recv_counts = torch.empty_like(counts)
             dist.all_to_all_single(recv_counts, counts)  # [src, le] for my experts
+            # one host sync: NCCL needs the split sizes on the host
+            both = torch.stack([recv_counts.view(world, el).sum(dim=1), counts.view(world, el).sum(dim=1)]).cpu()
+            recv_split, send_split = both[0].tolist(), both[1].tolist()
         else:
             recv_counts = counts
-        rc = recv_counts.view(world, el).cpu()           # host sync: NCCL needs split sizes on the host
-        sc = counts.view(world, el).sum(dim=1).cpu()
         send = x[order // k]
         if world > 1:
-            recv = send.new_empty((int(rc.sum()), cfg.hidden))
-            dist.all_to_all_single(recv, send, output_split_sizes=rc.sum(dim=1).tolist(), input_split_sizes=sc.tolist())
+            recv = send.new_empty((sum(recv_split), cfg.hidden))
+            dist.all_to_all_single(recv, send, output_split_sizes=recv_split, input_split_sizes=send_split)
+            # source-major -> expert-major
+            seg_expert = torch.arange(el, device=self.dev).repeat(world)
+            row_expert = torch.repeat_interleave(seg_expert, recv_counts.view(-1), output_size=recv.shape[0])
+            perm = torch.argsort(row_expert, stable=True)
+            rows = recv[perm]
         else:
-            recv = send
-        # source-major -> expert-major
-        seg_expert = torch.arange(el, device=self.dev).repeat(world)
-        seg_len = recv_counts.view(-1)
-        row_expert = torch.repeat_interleave(seg_expert, seg_len)
-        perm = torch.argsort(row_expert, stable=True)
-        rows = recv[perm]
-        per_e = rc.sum(dim=0)
+            rows, perm = send, None          # one rank: already expert-major, nothing reaches the host
+        per_e = recv_counts.view(world, el).sum(dim=0)
         if self.mode == "bf16_grouped_mm":
-            offs = per_e.cumsum(0).to(torch.int32).to(self.dev)
+            offs = per_e.cumsum(0).to(torch.int32)
             y = torch._grouped_mm(rows, self.w1t, offs=offs)
             i = cfg.intermediate
             act = torch.nn.functional.silu(y[:, :i]) * y[:, i:]
@@ -105,44 +105,56 @@ class BaselineMoE:
         else:
             z = torch.empty_like(rows)
             a = 0
+            per_e_host = per_e.tolist()
             for le in range(el):
-                n = int(per_e[le])
+                n = int(per_e_host[le])
                 if n:
                     z[a:a + n] = self._mlp_fp8(rows[a:a + n], le)
                 a += n
-        back = torch.empty_like(z)
-        back[perm] = z
         if world > 1:
+            back = torch.empty_like(z)
+            back[perm] = z
             ret = back.new_empty((t * k, cfg.hidden))
-            dist.all_to_all_single(ret, back, output_split_sizes=sc.tolist(), input_split_sizes=rc.sum(dim=1).tolist())
+            dist.all_to_all_single(ret, back, output_split_sizes=send_split, input_split_sizes=recv_split)
         else:
-            ret = back
+            ret = z
         pair_rows = torch.empty_like(ret)
         pair_rows[order] = ret
         out = (pair_rows.view(t, k, cfg.hidden).float() * w.unsqueeze(-1)).sum(dim=1)
         return out.to(torch.bfloat16)
 
 
-def run_baseline(args, cfg, rank, world, local, metric):
+def time_baseline(cfg, tokens, rank, world, local, steps, warmup, gemm="bf16_grouped", sets=None):
+    """Device time per step (ms, max over ranks) of the comparison layer on the given inputs, and the GEMM it used."""
     from bench import barrier, make_inputs, max_over_ranks
     dev = torch.device("cuda", local)
-    tokens = args.tokens or cfg.tokens_per_rank
-    layer = BaselineMoE(cfg, rank, world, dev, gemm=getattr(args, "baseline_gemm", "bf16_grouped"))
-    sets = make_inputs(cfg, tokens, rank, 4, dev)
-    for i in range(max(args.warmup, 3)):
-        layer.forward(*sets[i % 4])
+    layer = BaselineMoE(cfg, rank, world, dev, gemm=gemm)
+    if sets is None:
+        sets = make_inputs(cfg, tokens, rank, 4, dev)
+    for i in range(max(warmup, 3)):
+        layer.forward(*sets[i % len(sets)])
     barrier(world)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(args.steps):
-        layer.forward(*sets[i % 4])
+    for i in range(steps):
+        layer.forward(*sets[i % len(sets)])
     e1.record()
     barrier(world)
-    ms = max_over_ranks(e0.elapsed_time(e1), world) / args.steps
+    ms = max_over_ranks(e0.elapsed_time(e1), world) / steps
+    mode = layer.mode
+    del layer
+    torch.cuda.empty_cache()
+    return ms, mode
+
+
+def run_baseline(args, cfg, rank, world, local, metric):
+    tokens = args.tokens or cfg.tokens_per_rank
+    ms, mode = time_baseline(cfg, tokens, rank, world, local, args.steps, args.warmup,
+                             gemm=getattr(args, "baseline_gemm", "bf16_grouped"))
     if rank == 0:
         print(json.dumps({
             "metric": metric, "value": tokens * world / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "weak", "impl": "baseline", "dtype": layer.mode, "data": "synthetic",
+            "scaling": "weak", "impl": "baseline", "dtype": mode, "data": "synthetic",
             "config": {"model": cfg.name, "tokens_per_rank": tokens, "num_experts": cfg.num_experts,
-                       "parallelism": f"ep{world}", "comm": "nccl all_to_all_single", "gemm": layer.mode}}))
+                       "parallelism": f"ep{world}", "comm": "nccl all_to_all_single", "gemm": mode}}))

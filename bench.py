@@ -41,6 +41,10 @@ def parse_args():
     ap.add_argument("--tokens", type=int, default=0, help="tokens per rank (0 = the model's default)")
     ap.add_argument("--experts", type=int, default=0, help="override the number of routed experts (smaller smoke runs)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-baseline", action="store_true",
+                    help="skip the NCCL + cuBLAS comparison layer that fills vs_baseline (it runs after the timed regions)")
+    ap.add_argument("--no-verify", action="store_true",
+                    help="skip the check of one step's output against the unfused ops of this library")
     ap.add_argument("--baseline-gemm", default="bf16_grouped", choices=["fp8_per_expert", "bf16_grouped"],
                     help="--impl baseline: cuBLAS fp8 per expert, or the library's bf16 grouped GEMM")
     ap.add_argument("--fp32-scales", action="store_true",
@@ -105,6 +109,24 @@ def make_inputs(cfg, tokens: int, rank: int, nsets: int, dev):
     return sets
 
 
+def verify_against_unfused_ops(layer, buf, x, idx, w, rank, world):
+    """One step of the fused layer against the same layer built from the stand-alone ops of this library
+    (dispatch with fp8 quantisation -> grouped GEMM + SwiGLU + requantisation -> grouped GEMM -> combine).
+    Every rank calls it (the ops are collective).  Returns (max abs difference, max abs of the output)."""
+    ops = torch.ops.umdk_cam_op_lib
+    out, _ = layer(x, idx, w)
+    out = out.clone()
+    wts = layer.weights
+    el = layer.num_local
+    rx, src, cnt, per_e, rs = ops.moe_dispatch_prefill_quant(x, idx, w, 0, buf.name, rank, world, 4)
+    off = buf.native.expert_offsets(el + 1).clone()
+    q, s = ops.grouped_gemm_fp8_swiglu(rx, rs, wts.w1, wts.s1, off, True)
+    y = ops.grouped_gemm_fp8(q, s, wts.w2, wts.s2, off, True)
+    want = ops.moe_combine_prefill(y, idx, w, src, cnt, buf.name, rank, world)
+    torch.cuda.synchronize()
+    return float((out.float() - want.float()).abs().max()), float(want.float().abs().max())
+
+
 def run_ours(args, cfg, rank, world, local):
     import umdk_original_b200 as u
     from umdk_original_b200.models import FusedMoE, MoEStepRunner, make_buffer_for
@@ -131,6 +153,7 @@ def run_ours(args, cfg, rank, world, local):
     barrier(world)
     buf.check()
 
+    launches0 = buf.native.launch_count()
     with ClockSampler(local) as clocks:
         barrier(world)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -141,8 +164,15 @@ def run_ours(args, cfg, rank, world, local):
         barrier(world)
         ms = max_over_ranks(e0.elapsed_time(e1), world) / args.steps
         time.sleep(0.3)
+    launches = buf.native.launch_count() - launches0   # kernels of this library launched inside the timed region
     buf.check()
     clock_summary = clocks.summary()
+
+    max_err = None
+    if not args.no_verify and layer.quant_mode == 4:
+        err, scale = verify_against_unfused_ops(layer, buf, *sets[0], rank, world)
+        max_err = {"max_abs_err_vs_unfused_ops": max_over_ranks(err, world), "output_max_abs": max_over_ranks(scale, world)}
+        buf.check()
 
     # per-stage breakdown from a separate, untimed pass (events between the four launches)
     buf.set_profile(True)
@@ -179,14 +209,28 @@ def run_ours(args, cfg, rank, world, local):
         e2e_ms = max_over_ranks(t0.elapsed_time(t1), world) / args.steps
         buf.check()
         e2e = {"value": tokens * world / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": runner.h2d_bytes, "d2h_bytes_per_step": runner.d2h_bytes}
+               "h2d_bytes_per_step": runner.h2d_bytes, "d2h_bytes_per_step": runner.d2h_bytes,
+               "d2h": "the layer output [tokens, hidden] bf16 and a record of token counts + checksum, every step"}
+        del runner, host
+
+    # the comparison layer (NCCL all_to_all_single + library GEMMs) at the same N on the same inputs, after the timed regions
+    base = None
+    if not args.no_baseline:
+        from baseline.nccl_cublas import time_baseline
+        try:
+            base_ms, base_mode = time_baseline(cfg, tokens, rank, world, local, max(5, args.steps // 2), 3,
+                                               gemm=args.baseline_gemm, sets=sets)
+            base = {"ms_per_step": base_ms, "value": tokens * world / (base_ms * 1e-3), "gemm": base_mode,
+                    "comm": "nccl all_to_all_single" if world > 1 else "none (one rank)"}
+        except Exception as exc:  # noqa: BLE001 - the comparison must not take the product's number down with it
+            base = {"error": f"{type(exc).__name__}: {exc}"[:200]}
 
     if rank == 0:
         value = tokens * world / (ms * 1e-3)
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None,
+            "vs_baseline": (value / base["value"]) if base and "value" in base else None,
             "dtype": ("fp8_e4m3 block-scaled (fp32 accumulate, bf16 in/out)" if cfg.weight_format != "w8a8" else
                       "int8 W8A8 (per-token x per-channel scales, int32 accumulate, bf16 in/out)" if args.w8a8_exact else
                       "int8-range weights + per-channel scales computed as fp8_e4m3 block-scaled (fp32 accumulate, bf16 in/out)"),
@@ -200,12 +244,17 @@ def run_ours(args, cfg, rank, world, local):
                                   "power of two (tensor-core block scaling)"),
                        "cache": "expert weights per rank exceed the 126 MB L2 and 4 input sets rotate; no explicit flush"},
             "clocks": {k: clock_summary[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
-            "gpu_launches": 4 * args.steps,
+            "gpu_launches": int(launches),
+            "launches_per_step": launches / args.steps,
             "tflops_per_gpu": cfg.flops_per_token() * tokens / (ms * 1e-3) / 1e12,
             "stage_ms_max_over_ranks": breakdown,
         }
         if e2e is not None:
             line["e2e"] = e2e
+        if base is not None:
+            line["baseline"] = base
+        if max_err is not None:
+            line["verify"] = max_err
         print(json.dumps(line))
     barrier(world)
     buf.destroy()

@@ -17,16 +17,18 @@ def test_pipelined_steps_return_each_steps_own_record():
                                      timeout_ms=2000.0), name="runner", device=dev, rank=0, num_ranks=1)
     layer = FusedMoE(cfg, buf, seed=0)
     g = torch.Generator().manual_seed(5)
-    host, want = [], []
+    host, want, want_out = [], [], []
     for _ in range(5):
         x = torch.randn(t, cfg.hidden, generator=g).to(torch.bfloat16)
         idx, w = layer.route(x.to(dev))
         host.append((x.pin_memory(), idx.cpu().pin_memory(), w.float().cpu().pin_memory()))
         out, nums = layer(x.to(dev), idx, w)
         want.append(torch.cat([nums.float(), out.sum(dtype=torch.float32).reshape(1)]).cpu())
+        want_out.append(out.cpu())
     runner = MoEStepRunner(layer, t)
-    assert runner.h2d_bytes == t * (cfg.hidden * 2 + cfg.topk * 12) and runner.d2h_bytes == 4 * (layer.num_local + 1)
-    got = []
+    assert runner.h2d_bytes == t * (cfg.hidden * 2 + cfg.topk * 12)
+    assert runner.d2h_bytes == 4 * (layer.num_local + 1) + t * cfg.hidden * 2     # the record and the output itself
+    got, got_out = [], []
     runner.stage(*host[0])
     pending = None
     for i in range(len(host)):
@@ -35,13 +37,16 @@ def test_pipelined_steps_return_each_steps_own_record():
             runner.stage(*host[i + 1])
         if pending is not None:
             got.append(runner.result(pending).clone())
+            got_out.append(runner.output(pending).clone())
         pending = ticket
     got.append(runner.result(pending).clone())
+    got_out.append(runner.output(pending).clone())
     assert torch.equal(runner.finish(), got[-1])
     buf.check()
     for i, (a, b) in enumerate(zip(got, want)):
         assert torch.equal(a[:-1], b[:-1]), f"step {i}: token counts differ"
         assert abs(float(a[-1]) - float(b[-1])) <= 1e-3 * max(1.0, abs(float(b[-1]))), f"step {i}: checksum differs"
+        assert torch.equal(got_out[i], want_out[i]), f"step {i}: the output read back on the host differs"
     with pytest.raises(AssertionError):
         runner.result(0)  # long overwritten
     buf.destroy()

@@ -117,6 +117,7 @@ public:
                                        initiator ? 1 : 0, stream()));
     }
     void set_trace(bool on) { CAM_RT(cam_buffer_set_trace(buf_, on ? 1 : 0)); }
+    int64_t launch_count() const { return static_cast<int64_t>(cam_buffer_launch_count(buf_)); }
     void set_fused_trace(bool on) { CAM_RT(cam_buffer_set_fused_trace(buf_, on ? 1 : 0)); }
     std::vector<int64_t> read_fused_trace(int64_t num_local_experts) {
         std::vector<long long> t(static_cast<size_t>(num_local_experts));
@@ -896,6 +897,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("p2p_pingpong", &Buffer::p2p_pingpong)
         .def("set_trace", &Buffer::set_trace)
         .def("read_trace", &Buffer::read_trace)
+        .def("launch_count", &Buffer::launch_count)
         .def("set_fused_trace", &Buffer::set_fused_trace)
         .def("read_fused_trace", &Buffer::read_fused_trace)
         .def("set_profile", &Buffer::set_profile)

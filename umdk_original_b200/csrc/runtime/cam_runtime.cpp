@@ -97,6 +97,7 @@ struct CamBuffer {
     uint32_t* g1_done = nullptr;
     int g1_done_len = 0;
     unsigned long long* fused_trace = nullptr;  // [E + 1], null = off
+    unsigned long long launches = 0;            // kernels this buffer's ops have launched (host-side count)
     // switches read from the environment once, when the buffer is created (UMDK_CAM_GEMM_*, UMDK_CAM_DEEP_FUSE):
     // -1 = not set (the runtime decides), 0 / 1 = forced
     int env_bulk_push = -1, env_pair = -1, env_swap = -1, env_staging2 = -1, env_deep_fuse = -1, env_fuse_lag = -1;
@@ -430,6 +431,7 @@ extern "C" int cam_buffer_read_profile(CamBuffer* b, float* ms4) {
 extern "C" void cam_buffer_set_debug_drop_flags(CamBuffer* b, int on) {
     if (b != nullptr) b->dbg_drop_flags = on ? 1 : 0;
 }
+extern "C" unsigned long long cam_buffer_launch_count(CamBuffer* b) { return b ? b->launches : 0ull; }
 extern "C" int* cam_buffer_recv_count(CamBuffer* b) { return b->recv_count; }
 extern "C" int* cam_buffer_expert_offsets(CamBuffer* b) { return b->expert_offsets; }
 extern "C" int64_t* cam_buffer_num_recv_per_expert(CamBuffer* b) { return b->num_recv_per_expert; }
@@ -515,6 +517,7 @@ static int tp_exchange(CamBuffer* b, int reduce, const void* rows, const float* 
     p.status = b->d_status;
     const int rc = cam_launch_tp_exchange(&p, b->num_sms, stream);
     CAM_CHECK(rc == 0, "tp exchange launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    if (b != nullptr) ++b->launches;
     return 0;
 }
 
@@ -540,6 +543,7 @@ extern "C" int cam_buffer_barrier(CamBuffer* b, int phase_mask, cudaStream_t str
     const int rc = cam_launch_barrier(b->d_peer_table, b->layout.off_barrier_flag, b->d_epochs + 9, b->num_ranks, b->rank,
                                       phase_mask, b->dbg_drop_flags, b->timeout_ns, b->d_status, stream);
     CAM_CHECK(rc == 0, "barrier launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    if (b != nullptr) ++b->launches;
     return 0;
 }
 
@@ -669,6 +673,7 @@ static int dispatch_normal_impl(CamBuffer* b, const void* x, const void* topk_id
     int grid = b->num_sms;  // fixed per device so that the COUNT and SEND phases agree on token chunks
     const int rc = cam_launch_dispatch_normal(&p, grid, stream);
     CAM_CHECK(rc == 0, "dispatch_normal launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    if (b != nullptr) ++b->launches;
     return 0;
 }
 
@@ -709,6 +714,7 @@ extern "C" int cam_combine(CamBuffer* b, const void* y, const int* row_src, cons
     p.status = b->d_status;
     const int rc = cam_launch_combine(&p, b->num_sms, stream);
     CAM_CHECK(rc == 0, "combine launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    if (b != nullptr) ++b->launches;
     return 0;
 }
 
@@ -773,6 +779,7 @@ extern "C" int cam_dispatch_ll(CamBuffer* b, const void* x, const void* expert_i
     if (grid > want) grid = want;
     const int rc = cam_launch_dispatch_ll(&p, grid, stream);
     CAM_CHECK(rc == 0, "dispatch_ll launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    if (b != nullptr) ++b->launches;
     return 0;
 }
 
@@ -926,6 +933,7 @@ static int grouped_gemm_impl(CamBuffer* b, const void* a_q, const float* a_scale
                    : pair ? cam_launch_grouped_gemm_mxfp8_pair(&p, &ta, &tb, sms, two_staging ? 1 : 0, stream)
                           : cam_launch_grouped_gemm_mxfp8(&p, &ta, &tb, sms, swap ? 1 : 0, two_staging ? 1 : 0, stream);
     CAM_CHECK(rc == 0, "grouped_gemm launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    if (b != nullptr) ++b->launches;
     return 0;
 }
 
@@ -1016,6 +1024,7 @@ static int grouped_gemm_w8a8_impl(CamBuffer* b, const void* a_q, const float* a_
     CAM_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
     const int rc = cam_launch_grouped_gemm_w8a8(&p, &ta, &tb, sms, stream);
     CAM_CHECK(rc == 0, "grouped_gemm_w8a8 launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    if (b != nullptr) ++b->launches;
     return 0;
 }
 
@@ -1061,6 +1070,7 @@ extern "C" int cam_fused_moe_w8a8(CamBuffer* b, const void* x, const void* exper
         const int rc = cam_launch_rowquant_int8(b->act_f32, b->row_amax, b->expert_offsets, El, inter, b->act_q, b->act_s,
                                                 stream);
         CAM_CHECK(rc == 0, "rowquant launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    if (b != nullptr) ++b->launches;
         stamp(2);
         if (grouped_gemm_w8a8_impl(b, b->act_q, b->act_s, L.capacity, w2_q, w2_s, b->expert_offsets, El, h, inter, 2,
                                    nullptr, nullptr, nullptr, recv_src, K, stream) != 0)
@@ -1159,6 +1169,7 @@ static int fused_moe_deep(CamBuffer* b, const void* x, const void* expert_ids, i
             CAM_CUDA(cudaMemsetAsync(b->fused_trace, 0, sizeof(unsigned long long) * (L.num_experts + 1), stream));
         const int rc = cam_launch_fused_moe(&p, &ta1, &tb1, &ta2, &tb2, b->num_sms, stream);
         CAM_CHECK(rc == 0, "fused_moe launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
+    if (b != nullptr) ++b->launches;
         if ((fmask & CAM_PHASE_RECV) && expert_token_nums != nullptr)
             CAM_CUDA(cudaMemcpyAsync(expert_token_nums, b->num_recv_per_expert, sizeof(int64_t) * El,
                                      cudaMemcpyDeviceToDevice, stream));

@@ -86,19 +86,23 @@ class FusedMoE(torch.nn.Module):
 
 
 class MoEStepRunner:
-    """End-to-end step: pinned host inputs -> H2D -> FusedMoE -> D2H of a result record.
+    """End-to-end step: pinned host inputs -> H2D -> FusedMoE -> D2H of the step's result.
 
-    Two device input slots and two result records alternate; the copy of step i+1 runs on a side
-    stream while step i computes, and the host may launch step i+1 before it reads the record of step i
-    (``run`` returns a ticket, ``result(ticket)`` waits for that step only), so the device does not idle
-    while the host reads a result and prepares the next launch.  The record read back each step is the
-    per-expert token count plus the sum of the output in fp32 (a checksum a caller can log);
-    ``h2d_bytes`` / ``d2h_bytes`` are what moves."""
+    Two device input slots and two host result slots alternate; the copy of step i+1 runs on a side
+    stream while step i computes, the result of step i leaves on a third stream while step i+1 computes,
+    and the host may launch step i+1 before it reads the result of step i (``run`` returns a ticket,
+    ``result(ticket)`` waits for that step only), so the device does not idle while the host reads a
+    result and prepares the next launch.  What is read back each step is the layer's output ``[T, h]``
+    in bf16 (``copy_output=False``: nothing of it) plus a small record: the per-expert token counts and
+    the sum of the output in fp32 (a checksum a caller can log); ``h2d_bytes`` / ``d2h_bytes`` are what
+    moves per step."""
 
-    def __init__(self, layer: FusedMoE, tokens: int):
+    def __init__(self, layer: FusedMoE, tokens: int, copy_output: bool = True):
         self.layer = layer
         cfg, dev = layer.cfg, layer.buffer.device
         self.copy_stream = torch.cuda.Stream(device=dev)
+        self.d2h_stream = torch.cuda.Stream(device=dev)
+        self.copy_output = copy_output
         self.slots = []
         for _ in range(2):
             self.slots.append({
@@ -109,9 +113,12 @@ class MoEStepRunner:
             })
         self.result_dev = [torch.zeros(layer.num_local + 1, dtype=torch.float32, device=dev) for _ in range(2)]
         self.result_host = [torch.zeros(layer.num_local + 1, dtype=torch.float32).pin_memory() for _ in range(2)]
+        self.out_host = [torch.empty(tokens, cfg.hidden, dtype=torch.bfloat16).pin_memory() if copy_output else None
+                         for _ in range(2)]
+        self.computed = [torch.cuda.Event(), torch.cuda.Event()]
         self.result_done = [torch.cuda.Event(), torch.cuda.Event()]
         self.h2d_bytes = tokens * (cfg.hidden * 2 + cfg.topk * 8 + cfg.topk * 4)
-        self.d2h_bytes = (layer.num_local + 1) * 4
+        self.d2h_bytes = (layer.num_local + 1) * 4 + (tokens * cfg.hidden * 2 if copy_output else 0)
         self._step = 0
         self._staged = None
 
@@ -129,32 +136,43 @@ class MoEStepRunner:
     def run(self) -> int:
         """Launches the staged step (nothing here waits for the device) and returns its ticket.  At most
         two steps may be outstanding: collect ``result(ticket)`` of a step before launching the step after
-        the next one, whose record takes the same place."""
+        the next one, whose result takes the same place."""
         slot = self._staged
         cur = torch.cuda.current_stream()
         cur.wait_event(slot["ready"])
         out, nums = self.layer(slot["x"], slot["idx"], slot["w"])
         slot["free"].record(cur)
         r = self._step % 2
-        with nvtx_range("umdk_cam.step.result_d2h"):
-            self.result_dev[r][:-1] = nums.float()
-            self.result_dev[r][-1] = out.sum(dtype=torch.float32)
+        self.result_dev[r][:-1] = nums.float()
+        self.result_dev[r][-1] = out.sum(dtype=torch.float32)
+        self.computed[r].record(cur)
+        with nvtx_range("umdk_cam.step.result_d2h"), torch.cuda.stream(self.d2h_stream):
+            self.d2h_stream.wait_event(self.computed[r])
+            if self.copy_output:
+                self.out_host[r].copy_(out, non_blocking=True)
+                out.record_stream(self.d2h_stream)
             self.result_host[r].copy_(self.result_dev[r], non_blocking=True)
-            self.result_done[r].record(cur)
+            self.result_done[r].record(self.d2h_stream)
         ticket = self._step
         self._step += 1
         self.last_out = out
         return ticket
 
     def result(self, ticket: int) -> torch.Tensor:
-        """Host record of the step with this ticket (waits for that step only)."""
-        assert self._step - 2 <= ticket < self._step, "the record of this step has been overwritten or not produced"
+        """Host record of the step with this ticket (waits for that step only); the step's output is then
+        in ``output(ticket)``."""
+        assert self._step - 2 <= ticket < self._step, "the result of this step has been overwritten or not produced"
         self.result_done[ticket % 2].synchronize()
         return self.result_host[ticket % 2]
+
+    def output(self, ticket: int) -> Optional[torch.Tensor]:
+        """Pinned host copy of the step's output (valid after ``result(ticket)``, until two steps later)."""
+        return self.out_host[ticket % 2]
 
     def finish(self) -> torch.Tensor:
         """Waits for everything launched and returns the record of the last step."""
         torch.cuda.current_stream().synchronize()
+        self.d2h_stream.synchronize()
         return self.result_host[(self._step - 1) % 2]
 
 

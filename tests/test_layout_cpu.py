@@ -13,7 +13,7 @@ CAM_MAX_RANKS = 72  # flag arrays are sized for this many ranks (cam_types.h)
 OFFSETS = ["off_count_flag", "off_data_flag", "off_combine_flag", "off_barrier_flag", "off_ll_combine_flag",
            "off_count_matrix", "off_ll_cells", "off_recv_x", "off_recv_scales", "off_recv_src", "off_combine_buf",
            "off_ll_x", "off_ll_scales", "off_ll_meta", "off_ll_combine_buf", "off_tp_flag", "off_tp_cnt", "off_tp_x",
-           "off_tp_scales", "off_dup_cnt", "off_dup_list", "total_bytes"]
+           "off_tp_scales", "off_dup_cnt", "off_dup_list", "off_arrival", "total_bytes"]
 
 
 class CamLayout(ctypes.Structure):
@@ -54,6 +54,7 @@ def test_regions_are_aligned_ordered_and_big_enough(lib, r, e, t, h, k, ll, tp_r
         "off_tp_flag": 8, "off_tp_cnt": 8,
         "off_tp_x": tp_rows * h * 2, "off_tp_scales": 4 * tp_rows * (h // 128),
         "off_dup_cnt": 4 * 2 * CAM_MAX_RANKS, "off_dup_list": 8 * 2 * r * t * k,
+        "off_arrival": 4 * 2 * e,  # rows landed per local expert of the fused layer, two parities
     }
     # regions that this configuration does not have (no low-latency mode, no TP partner) keep offset 0
     offs = sorted((getattr(lay, n), n) for n in OFFSETS if n != "total_bytes" and need[n] > 0)

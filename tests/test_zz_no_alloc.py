@@ -75,6 +75,35 @@ def test_noalloc_dispatch_matches_buffer_dispatch_twice(quant_mode):
     buf.destroy()
 
 
+@pytest.mark.parametrize("quant_mode", [2, 3])
+def test_noalloc_dispatch_many_pairs_per_cta(quant_mode):
+    """8192 tokens x 16 pairs at hidden 128: every CTA makes several passes over its pairs (more pairs per CTA than
+    it has threads), with per-token int8 and with fp8 rows; compared with the Buffer dispatch row for row."""
+    lib = _lib()
+    t, h, e, k = 8192, 128, 64, 16
+    cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, timeout_ms=4000.0)
+    buf = u.Buffer(None, cfg, name=f"na_big{quant_mode}", device=DEV, rank=0, num_ranks=1)
+    g = torch.Generator().manual_seed(3 + quant_mode)
+    x = torch.randn(t, h, generator=g).to(torch.bfloat16).to(DEV)
+    idx = torch.stack([torch.randperm(e, generator=g)[:k] for _ in range(t)])
+    idx[::11, 5] = -1
+    idx[7, 0] = 2 ** 32 + 3          # must be skipped, not taken for expert 3
+    idx = idx.to(DEV)
+    w = torch.rand(t, k, generator=g).to(DEV)
+    rx0, src0, cnt0, per_e0, rs0 = torch.ops.umdk_cam_op_lib.moe_dispatch_prefill_quant(x, idx, w, 0, buf.name, 0, 1,
+                                                                                        quant_mode)
+    buf.check()
+    n = rx0.shape[0]
+    assert n == int(((idx >= 0) & (idx < e)).sum())
+    rx, rs, src, off, status = _call(lib, x, idx, e, quant_mode, capacity=t * k)
+    assert status == 0, lib.cam_dispatch_local_noalloc_error().decode()
+    assert int(off[-1]) == n and torch.equal(off.cpu(), buf.native.expert_offsets(e + 1).cpu())
+    assert torch.equal(src[:n].cpu().reshape(-1), src0.cpu())
+    assert torch.equal(rx[:n].cpu(), rx0.contiguous().view(torch.uint8).reshape(n, -1).cpu())
+    assert torch.equal(rs[:n].cpu().reshape(-1), rs0.cpu().reshape(-1))
+    buf.destroy()
+
+
 def test_noalloc_rejects_oversize_and_reports_overflow():
     lib = _lib()
     x = torch.zeros(8, 128, dtype=torch.bfloat16, device=DEV)
@@ -88,6 +117,13 @@ def test_noalloc_rejects_oversize_and_reports_overflow():
     rc = lib.cam_dispatch_local_noalloc(x.data_ptr(), idx.data_ptr(), 1, 8, 2, 128, 4096, 0, 16, out.data_ptr(), None,
                                         out.data_ptr(), out.data_ptr(), stream)
     assert rc == -1
+    # a pointer the 16-byte row accesses cannot use: refused with a message, nothing is launched
+    rc = lib.cam_dispatch_local_noalloc(x.data_ptr() + 2, idx.data_ptr(), 1, 4, 2, 128, 4, 0, 16, out.data_ptr(), None,
+                                        out.data_ptr(), out.data_ptr(), stream)
+    assert rc == -1 and b"aligned" in lib.cam_dispatch_local_noalloc_error()
+    rc = lib.cam_dispatch_local_noalloc(x.data_ptr(), idx.data_ptr(), 1, 4, 2, 128, 4, 0, 16, out.data_ptr() + 8, None,
+                                        out.data_ptr(), out.data_ptr(), stream)
+    assert rc == -1 and b"aligned" in lib.cam_dispatch_local_noalloc_error()
     # outputs too small for the rows: the kernel writes no row and the status says so
     rx, rs, src, off, status = _call(lib, x, idx, 4, 0, capacity=5)
     assert status == -3 and int(off[-1]) == 16

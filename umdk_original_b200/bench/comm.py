@@ -127,11 +127,18 @@ def _pct(v, q):
 
 
 def _remote_rows(idx: torch.Tensor, num_experts: int, world: int, rank: int):
+    """(pairs, pairs whose expert lives on another rank, distinct (token, other rank) combinations).  The last
+    number is what the normal dispatch of this library puts on NVLink: a token crosses once per destination rank
+    and is replicated there; the NCCL arm and both combines move one row per pair."""
     el = num_experts // world
     dst = torch.where(idx >= 0, idx // el, torch.full_like(idx, -1))
     total = int((dst >= 0).sum())
     remote = int(((dst >= 0) & (dst != rank)).sum())
-    return total, remote
+    hit = torch.zeros(idx.shape[0], world + 1, dtype=torch.bool, device=idx.device)
+    hit.scatter_(1, torch.where(dst >= 0, dst, torch.full_like(dst, world)), True)
+    hit[:, rank] = False
+    unique_remote = int(hit[:, :world].sum())
+    return total, remote, unique_remote
 
 
 def run(args):
@@ -156,7 +163,7 @@ def run(args):
         idx, w = route(logits, k, 8, 4)
     idx = idx.contiguous()
     w = w.float().contiguous()
-    total_rows, remote_rows = _remote_rows(idx, e, world, rank)
+    total_rows, remote_rows, unique_remote_rows = _remote_rows(idx, e, world, rank)
     nscale = h // 128
     disp_row_bytes = h + nscale * 4 + 12
     comb_row_bytes = h * 2
@@ -279,11 +286,15 @@ def run(args):
         p50 = _max(_pct(ts, 0.5), world) * 1e3
         p99 = _max(_pct(ts, 0.99), world) * 1e3
         mean = _max(statistics.fmean(ts), world) * 1e3
-        nv_bytes = remote_rows * row_bytes
+        # bytes that actually cross NVLink: this library's normal dispatch sends a token once per destination rank
+        # (12 bytes of source triple per pair still travel); everything else moves one row per remote pair
+        dedup = name == "dispatch" and args.impl == "ours" and not ll
+        wire_rows = unique_remote_rows if dedup else remote_rows
+        nv_bytes = wire_rows * row_bytes + (remote_rows - wire_rows) * 20
         all_bytes = total_rows * row_bytes
         result[name] = {
             "p50_us": p50, "p99_us": p99, "mean_us": mean,
-            "rows": total_rows, "remote_rows": remote_rows,
+            "rows": total_rows, "remote_rows": remote_rows, "rows_on_the_wire": wire_rows,
             "nvlink_bytes_per_gpu": nv_bytes, "payload_bytes_per_gpu": all_bytes,
             "nvlink_gbs_per_gpu": nv_bytes / (p50 * 1e-6) / 1e9 if world > 1 else 0.0,
             "payload_gbs_per_gpu": all_bytes / (p50 * 1e-6) / 1e9,

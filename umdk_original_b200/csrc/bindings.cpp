@@ -640,7 +640,12 @@ std::vector<at::Tensor> fused_deep_moe_cuda(const at::Tensor& x, const at::Tenso
                                             int64_t epRankSize, int64_t epRankId, int64_t moeExpertNum,
                                             int64_t sharedExpertNum, int64_t sharedExpertRankNum, int64_t quantMode,
                                             int64_t globalBs) {
-    (void)expertSmoothScales; (void)sharedExpertNum; (void)globalBs;
+    (void)sharedExpertNum; (void)globalBs;
+    // The reference multiplies every row by its expert's smooth vector before the per-token quantisation
+    // (fused_deep_moe.h:398, cam_moe_distribute_dispatch.h:704-714); the dispatch of the fused layer here quantises a
+    // token once for all of its experts, so the argument is refused rather than silently dropped.
+    CAM_ASSERT(!(expertSmoothScales.has_value() && expertSmoothScales->defined()),
+               "expertSmoothScales is not supported by fused_deep_moe (pass None; moe_dispatch_shmem applies smooth scales)");
     Buffer* b = buffer_by_name(groupEp);
     CAM_ASSERT(x.dim() == 2 && expertIds.dim() == 2, "x must be [bs, h] and expertIds [bs, k]");
     CAM_ASSERT(x.scalar_type() == at::kBFloat16, "x must be bfloat16");

@@ -38,6 +38,16 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// Expert id i of a [tokens, topk] tensor of int64 or int32.  A 64-bit value that does not fit an int
+// comes back as -1 (every caller skips ids outside [0, E)), so 2^32 + 3 is never taken for expert 3.
+__device__ __forceinline__ int load_expert_id(const void* idx, int is_i64, size_t i) {
+    if (is_i64) {
+        const long long v = reinterpret_cast<const long long*>(idx)[i];
+        return (v < 0 || v > 0x7FFFFFFFll) ? -1 : static_cast<int>(v);
+    }
+    return reinterpret_cast<const int*>(idx)[i];
+}
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

@@ -30,11 +30,6 @@ __device__ __forceinline__ void comb_record_status(CamStatus* st, int code, int 
     }
 }
 
-__device__ __forceinline__ int comb_expert_id(const void* idx, int is_i64, size_t i) {
-    return is_i64 ? static_cast<int>(reinterpret_cast<const long long*>(idx)[i])
-                  : reinterpret_cast<const int*>(idx)[i];
-}
-
 __device__ __forceinline__ void fma_bf16x8(float (&acc)[8], const uint4& v, float w) {
     acc[0] = fmaf(w, bf16_lo(v.x), acc[0]);
     acc[1] = fmaf(w, bf16_hi(v.x), acc[1]);
@@ -170,7 +165,7 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineP
                 const int e_end = min(p.h, e_begin + per_q * 512);
                 bool pair_ok = false;
                 if (lane < static_cast<uint32_t>(p.K)) {
-                    const int id = comb_expert_id(p.topk_idx, p.idx_is_i64, static_cast<size_t>(t) * p.K + lane);
+                    const int id = load_expert_id(p.topk_idx, p.idx_is_i64, static_cast<size_t>(t) * p.K + lane);
                     s_w[warp][lane] = p.topk_weights[static_cast<size_t>(t) * p.K + lane];
                     pair_ok = (id >= 0 && id < p.E);
                 }
@@ -217,7 +212,7 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineP
             const int o_end = min(row_bytes, o_begin + per * 512);
             bool pair_ok = false;
             if (lane < static_cast<uint32_t>(p.K)) {
-                const int id = comb_expert_id(p.topk_idx, p.idx_is_i64, static_cast<size_t>(t) * p.K + lane);
+                const int id = load_expert_id(p.topk_idx, p.idx_is_i64, static_cast<size_t>(t) * p.K + lane);
                 s_w[warp][lane] = p.topk_weights[static_cast<size_t>(t) * p.K + lane];
                 pair_ok = (id >= 0 && id < p.E);
             }

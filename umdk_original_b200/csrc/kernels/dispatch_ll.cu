@@ -37,11 +37,6 @@ __device__ __forceinline__ void ll_record_status(CamStatus* st, int code, int wh
     }
 }
 
-__device__ __forceinline__ int ll_expert_id(const void* idx, int is_i64, size_t i) {
-    return is_i64 ? static_cast<int>(reinterpret_cast<const long long*>(idx)[i])
-                  : reinterpret_cast<const int*>(idx)[i];
-}
-
 __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const DispatchLLParams p) {
     extern __shared__ __align__(16) uint8_t dyn_smem[];
     __shared__ int s_run[CAM_MAX_EXPERTS];   // SEND: pairs per expert / RECV: rows per cell (local expert, source)
@@ -76,7 +71,7 @@ __global__ void __launch_bounds__(kLLThreads, 1) dispatch_ll_kernel(const Dispat
     if (p.phase_mask & CAM_PHASE_SEND) {
         const int parity = static_cast<int>(ep_send & 1u);
         for (int i = tid; i < npairs; i += kLLThreads) {
-            int id = ll_expert_id(p.expert_ids, p.idx_is_i64, i);
+            int id = load_expert_id(p.expert_ids, p.idx_is_i64, i);
             if (id < 0 || id >= E || (i / K) >= p.active_tokens) id = -1;
             s_ids[i] = id;
         }

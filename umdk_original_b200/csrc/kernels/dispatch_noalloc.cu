@@ -38,10 +38,6 @@ struct LocalParams {
     int* status;    // [0] = 0 ok / CAM_NOALLOC_OVERFLOW, [1] = rows needed
 };
 
-__device__ __forceinline__ int load_id(const void* idx, int is_i64, size_t i) {
-    return is_i64 ? static_cast<int>(reinterpret_cast<const long long*>(idx)[i])
-                  : reinterpret_cast<const int*>(idx)[i];
-}
 
 __global__ void __launch_bounds__(kThreads, 1) dispatch_local_kernel(const LocalParams p) {
     extern __shared__ __align__(16) uint8_t dyn_smem[];
@@ -65,7 +61,7 @@ __global__ void __launch_bounds__(kThreads, 1) dispatch_local_kernel(const Local
         const int i = sub + tid;
         int id = -1;
         if (i < npairs) {
-            id = load_id(p.topk_idx, p.idx_is_i64, static_cast<size_t>(t0) * K + i);
+            id = cam::load_expert_id(p.topk_idx, p.idx_is_i64, static_cast<size_t>(t0) * K + i);
             if (id < 0 || id >= E) id = -1;
         }
         s_ids[tid] = id;
@@ -129,7 +125,7 @@ __global__ void __launch_bounds__(kThreads, 1) dispatch_local_kernel(const Local
         __syncwarp();
         for (int k = 0; k < K; ++k) {
             const size_t g = static_cast<size_t>(t) * K + k;
-            const int id = load_id(p.topk_idx, p.idx_is_i64, g);
+            const int id = cam::load_expert_id(p.topk_idx, p.idx_is_i64, g);
             if (id < 0 || id >= E) continue;
             const int row = s_base[id] + s_pre[id] + p.slot[g];
             uint8_t* dst = p.recv_x + static_cast<size_t>(row) * row_bytes;
@@ -197,6 +193,13 @@ extern "C" int cam_dispatch_local_noalloc(const void* x, const void* topk_idx, i
     if (quant_mode != CAM_QUANT_NONE && recv_scales == nullptr)
         return set_error(CAM_NOALLOC_BAD_ARGUMENT, "recv_scales is required for quant_mode %d", quant_mode);
     if (capacity < 1) return set_error(CAM_NOALLOC_BAD_ARGUMENT, "capacity must be positive");
+    // rows and scales move as 16-byte vectors
+    if ((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(recv_x) & 15u) ||
+        (recv_scales != nullptr && (reinterpret_cast<uintptr_t>(recv_scales) & 15u)))
+        return set_error(CAM_NOALLOC_BAD_ARGUMENT, "x, recv_x and recv_scales must be 16-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(topk_idx) & (idx_is_i64 ? 7u : 3u)) || (reinterpret_cast<uintptr_t>(recv_src) & 3u) ||
+        (reinterpret_cast<uintptr_t>(expert_offsets) & 3u))
+        return set_error(CAM_NOALLOC_BAD_ARGUMENT, "topk_idx, recv_src and expert_offsets must be aligned to their element size");
 
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);

@@ -20,8 +20,11 @@
 // Limits (a call outside them is rejected with a message, nothing is launched):
 //   tokens * topk <= CAM_NOALLOC_MAX_PAIRS, experts <= CAM_NOALLOC_MAX_EXPERTS,
 //   topk <= 16, hidden a multiple of 128 and <= 8192, quant_mode in {0, 2, 3},
+//   x, recv_x and recv_scales 16-byte aligned (rows move as 16-byte vectors), the integer arrays aligned to
+//   their element size,
 //   `capacity` (rows the caller's outputs can hold) >= the number of valid pairs, else the call
 //   returns CAM_NOALLOC_OVERFLOW after the kernel ran without writing any row.
+// Expert ids outside [0, experts) are skipped; a 64-bit id is compared as 64 bits (2^32 + 3 is not expert 3).
 //
 // Sharing: all calls on a device use the same scratch array.  The kernel rewrites every word it
 // later reads, so nothing has to be cleared between calls, but two calls that overlap on the GPU
@@ -30,7 +33,8 @@
 // First call on a device: it looks up the array's device address (cudaGetSymbolAddress with
 // that device current) and sizes the launch; make that first call outside any stream capture.
 // The call is asynchronous on `stream`; `cam_dispatch_local_noalloc_status` synchronises the
-// stream and returns the status the last call on the current device recorded.
+// stream it is given and returns the status the last call on the current device recorded.  Pass
+// it the stream of that call: on any other stream the read is not ordered after the kernel.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>

@@ -33,14 +33,6 @@ __device__ __forceinline__ void record_status(CamStatus* st, int code, int who, 
     }
 }
 
-__device__ __forceinline__ int load_expert_id(const void* idx, int is_i64, size_t i) {
-    if (is_i64) {
-        const long long v = reinterpret_cast<const long long*>(idx)[i];
-        return static_cast<int>(v);
-    }
-    return reinterpret_cast<const int*>(idx)[i];
-}
-
 __global__ void __launch_bounds__(kDispThreads, 1)
 dispatch_normal_kernel(const DispatchNormalParams p) {
     extern __shared__ __align__(16) uint8_t dyn_smem[];

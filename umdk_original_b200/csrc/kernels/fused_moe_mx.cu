@@ -48,7 +48,7 @@ static_assert(kFmSmem <= 232448, "exceeds the shared memory of one CTA");
 constexpr uint32_t kFmTmemCols = 512;
 constexpr uint32_t kFmSfCol0 = 256, kFmSfStride = 16;
 // Register re-partitioning, see grouped_gemm_mx2.cu: the launch count is what ptxas reports.
-constexpr uint32_t kFmLaunchRegs = 80, kFmCtrlRegs = 40, kFmSfRegs = 56, kFmEpiRegs = 96;
+constexpr uint32_t kFmLaunchRegs = 80, kFmCtrlRegs = 40, kFmSfRegs = 80, kFmEpiRegs = 88;
 static_assert(128 * kFmCtrlRegs + 128 * kFmSfRegs + kFmEpiThreads * kFmEpiRegs <= kFmLaunchRegs * kFmThreads,
               "setmaxnreg budget exceeds the registers the CTA owns: the kernel would hang");
 
@@ -58,6 +58,11 @@ __device__ __forceinline__ uint32_t fm_ue8m0_word(float scale) {
 __device__ __forceinline__ float ld_cg_f32(const float* p) {
     float v;
     asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 ld_cg_f32x4(const float* p) {
+    float4 v;
+    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
     return v;
 }
 
@@ -398,7 +403,11 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                     if (e != ready_e) {
                         uint32_t seen;
                         const bool got = fm_wait_counter<true>(my_arrival + e, static_cast<uint32_t>(cnt), wt, seen);
-                        if (!__all_sync(0xFFFFFFFFu, got)) { ok = false; break; }
+                        if (!__all_sync(0xFFFFFFFFu, got)) {
+                            if (lane == 0) gemm_record_status(p.status, CAM_ERR_TIMEOUT_ARRIVAL, e, static_cast<int>(seen));
+                            ok = false;
+                            break;
+                        }
                         ready_e = e;
                     }
                 } else {
@@ -406,7 +415,11 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                     if (blk != ready_blk) {
                         uint32_t seen;
                         const bool got = fm_wait_counter<false>(p.g1_done + blk, static_cast<uint32_t>(2 * nt1), wt, seen);
-                        if (!__all_sync(0xFFFFFFFFu, got)) { ok = false; break; }
+                        if (!__all_sync(0xFFFFFFFFu, got)) {
+                            if (lane == 0) gemm_record_status(p.status, CAM_ERR_TIMEOUT_GEMM1, e, static_cast<int>(seen));
+                            ok = false;
+                            break;
+                        }
                         ready_blk = blk;
                     }
                 }
@@ -422,29 +435,17 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                 else { nb_lo = 2 * nt; nb_hi = min(2 * nt + 1, nblk2 - 1); nblk = nblk2; b_scales = p.b2_scales; }
                 const float* bs_lo = b_scales + (static_cast<size_t>(e) * nblk + nb_lo) * kblocks;
                 const float* bs_hi = b_scales + (static_cast<size_t>(e) * nblk + nb_hi) * kblocks;
-                float c[6], n1[6];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) c[j] = ld_cg_f32(as[j]);
-                c[4] = __ldg(bs_lo); c[5] = __ldg(bs_hi);
-#pragma unroll
-                for (int j = 0; j < 6; ++j) n1[j] = c[j];
-                if (kblocks > 1) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) n1[j] = ld_cg_f32(as[j] + 1);
-                    n1[4] = __ldg(bs_lo + 1); n1[5] = __ldg(bs_hi + 1);
-                }
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    uint32_t wd[6];
-#pragma unroll
-                    for (int j = 0; j < 6; ++j) { wd[j] = fm_ue8m0_word(c[j]); c[j] = n1[j]; }
+                // One K-block: write the six scale words of stage s into TMEM and tell the MMA issuer.
+                auto put = [&](float a0, float a1, float a2, float a3, float b0, float b1) -> bool {
                     const uint32_t s = it % kFmStages, ph = (it / kFmStages) & 1u;
                     const bool got = fm_mbar_wait(&bar_empty[s], ph ^ 1u, wt);
-                    if (!__all_sync(0xFFFFFFFFu, got)) { ok = false; break; }
+                    if (!__all_sync(0xFFFFFFFFu, got)) return false;
                     tc_fence_after_sync();
                     const uint32_t col = tmem_base + lane_base + kFmSfCol0 + s * kFmSfStride;
-                    tmem_st_32x32b_x4(col, wd[0], wd[1], wd[2], wd[3]);
-                    tmem_st_32x32b_x4(col + 4u, wd[4], wd[4], wd[4], wd[4]);
-                    tmem_st_32x32b_x4(col + 8u, wd[5], wd[5], wd[5], wd[5]);
+                    const uint32_t w4 = fm_ue8m0_word(b0), w5 = fm_ue8m0_word(b1);
+                    tmem_st_32x32b_x4(col, fm_ue8m0_word(a0), fm_ue8m0_word(a1), fm_ue8m0_word(a2), fm_ue8m0_word(a3));
+                    tmem_st_32x32b_x4(col + 4u, w4, w4, w4, w4);
+                    tmem_st_32x32b_x4(col + 8u, w5, w5, w5, w5);
                     tc_wait_st();
                     tc_fence_before_sync();
                     __syncwarp();
@@ -452,11 +453,37 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                         if (cta == 0) mbar_arrive(&bar_sf[s]);
                         else mbar_arrive_cluster(map_to_cta(&bar_sf[s], 0));
                     }
-                    if (kb + 2 < kblocks) {
+                    ++it;
+                    return true;
+                };
+                // The activation scales come from L2 (no L1: they were written during this kernel), about a
+                // microsecond away, while a K-block takes half of that: a lane fetches the scales of FOUR K-blocks of
+                // each of its rows with one 16-byte load, one group of four ahead of their use.  The weight scales are
+                // constant and hit in L1.
+                if ((kblocks & 3) == 0) {
+                    float4 cur[4], nxt[4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) n1[j] = ld_cg_f32(as[j] + kb + 2);
-                        n1[4] = __ldg(bs_lo + kb + 2); n1[5] = __ldg(bs_hi + kb + 2);
+                    for (int j = 0; j < 4; ++j) cur[j] = ld_cg_f32x4(as[j]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) nxt[j] = (kblocks > 4) ? ld_cg_f32x4(as[j] + 4) : cur[j];
+                    for (int kb = 0; ok && kb < kblocks; kb += 4) {
+                        const float4 blo = __ldg(reinterpret_cast<const float4*>(bs_lo + kb));
+                        const float4 bhi = __ldg(reinterpret_cast<const float4*>(bs_hi + kb));
+                        ok = put(cur[0].x, cur[1].x, cur[2].x, cur[3].x, blo.x, bhi.x) &&
+                             put(cur[0].y, cur[1].y, cur[2].y, cur[3].y, blo.y, bhi.y) &&
+                             put(cur[0].z, cur[1].z, cur[2].z, cur[3].z, blo.z, bhi.z) &&
+                             put(cur[0].w, cur[1].w, cur[2].w, cur[3].w, blo.w, bhi.w);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) cur[j] = nxt[j];
+                        if (kb + 8 < kblocks) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) nxt[j] = ld_cg_f32x4(as[j] + kb + 8);
+                        }
                     }
+                } else {
+                    for (int kb = 0; ok && kb < kblocks; ++kb)
+                        ok = put(ld_cg_f32(as[0] + kb), ld_cg_f32(as[1] + kb), ld_cg_f32(as[2] + kb), ld_cg_f32(as[3] + kb),
+                                 __ldg(bs_lo + kb), __ldg(bs_hi + kb));
                 }
             }
             if (!ok && lane == 0) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 3, static_cast<int>(it));

@@ -876,8 +876,12 @@ static int grouped_gemm_impl(CamBuffer* b, const void* a_q, const float* a_scale
     p.act_q = static_cast<uint8_t*>(act_q);
     p.act_s = act_s;
     p.row_src = row_src;
-    static CamStatus* s_fallback_status = nullptr;
-    static unsigned int* s_fallback_ctr = nullptr;
+    // stand-alone calls (no Buffer): one status word and counter per device, allocated on that device's first call
+    static CamStatus* s_fallback_status_dev[64] = {nullptr};
+    static unsigned int* s_fallback_ctr_dev[64] = {nullptr};
+    if (b == nullptr) CAM_CHECK(device >= 0 && device < 64, "grouped_gemm: device index %d not supported", device);
+    CamStatus*& s_fallback_status = s_fallback_status_dev[b ? 0 : device];
+    unsigned int*& s_fallback_ctr = s_fallback_ctr_dev[b ? 0 : device];
     if (b != nullptr) {
         p.peer_base = b->d_peer_table;
         p.off_combine_buf = low_latency ? b->layout.off_ll_combine_buf : b->layout.off_combine_buf;
@@ -997,8 +1001,11 @@ static int grouped_gemm_w8a8_impl(CamBuffer* b, const void* a_q, const float* a_
     p.row_amax = row_amax;
     p.row_src = row_src;
     p.topk = topk;
-    static CamStatus* s_status = nullptr;
-    static unsigned int* s_ctr = nullptr;
+    static CamStatus* s_status_dev[64] = {nullptr};
+    static unsigned int* s_ctr_dev[64] = {nullptr};
+    if (b == nullptr) CAM_CHECK(device >= 0 && device < 64, "grouped_gemm_w8a8: device index %d not supported", device);
+    CamStatus*& s_status = s_status_dev[b ? 0 : device];
+    unsigned int*& s_ctr = s_ctr_dev[b ? 0 : device];
     if (b != nullptr) {
         p.peer_base = b->d_peer_table;
         p.off_combine_buf = b->layout.off_combine_buf;

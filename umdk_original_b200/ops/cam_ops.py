@@ -218,6 +218,9 @@ def _stack(ws) -> torch.Tensor:
 def _fused_deep_moe_cpu(x, expertIds, gmm1PermutedWeight, gmm1PermutedWeightScale, gmm2Weight, gmm2WeightScale,
                         expertScales, expertSmoothScales, xActiveMask, groupEp, epRankSize, epRankId, moeExpertNum,
                         sharedExpertNum, sharedExpertRankNum, quantMode, globalBs):
+    if expertSmoothScales is not None:
+        raise RuntimeError("expertSmoothScales is not supported by fused_deep_moe (pass None; moe_dispatch_shmem "
+                           "applies smooth scales)")
     g = _reg().by_name(groupEp)
     be = _backend()
     w1, s1 = _stack(gmm1PermutedWeight), _stack(gmm1PermutedWeightScale)

@@ -161,9 +161,13 @@ class Buffer:
 
     def reset(self) -> None:
         """Zeroes flags and epochs after an error (every surviving rank must call it).  Handles and
-        tensors returned by earlier dispatch calls are void afterwards."""
+        tensors returned by earlier dispatch calls are void afterwards.  With a process group the call ends with a
+        host-side barrier over the group, so that no rank's first flags of the next op can be wiped by a rank that
+        is still zeroing."""
         if self._native is not None:
             self._native.reset()
+            if self.num_ranks > 1 and self.group is not None and dist.is_available() and dist.is_initialized():
+                dist.barrier(group=self.group)
         elif self._cpu is not None:
             self._cpu.ll_src = None
             self._cpu.last_src = None

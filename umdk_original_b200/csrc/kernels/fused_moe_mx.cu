@@ -1,7 +1,8 @@
 // Deep-fused MoE layer for sm_100a: ONE persistent kernel of CTA pairs that
 //   * sends this rank's quantised tokens to their expert ranks, in the order of the destination's
 //     local experts, and counts every landed row on a per-expert arrival counter in the
-//     destination's memory (copy warps: bulk copies local memory -> shared memory -> peer memory);
+//     destination's memory (plain 16-byte loads and peer stores by the epilogue warps while they
+//     wait for accumulators);
 //   * runs the first grouped GEMM (+ SwiGLU + 1x128 fp8 requantisation) of a local expert as soon
 //     as that expert's counter says all of its rows are in, while later experts still arrive;
 //   * runs the second grouped GEMM of a row block as soon as the first one has finished that
@@ -21,7 +22,8 @@
 // Tensor-core pipeline, barriers and epilogues are those of the CTA-pair grouped GEMM
 // (grouped_gemm_mx2.cu): tcgen05.mma.cta_group::2 with UE8M0 block scaling, operands by plain TMA
 // loads (no multicast qualifier anywhere), accumulators in TMEM.  Warps: 0 TMA producer, 1 MMA
-// issuer (first CTA of the pair), 2-3 copy warps, 4-7 scale-factor writers, 8-23 epilogue.
+// issuer (first CTA of the pair), 4-7 scale-factor writers, 8-23 epilogue; the epilogue warps send the
+// dispatch rows while they wait for accumulators.
 //
 // Every wait is bounded.  A wait that runs out records a status word, raises the CTA's abort flag
 // (and the partner CTA's), and every role leaves its loop; both CTAs always reach the cluster
@@ -33,17 +35,17 @@ namespace cam {
 constexpr int kFmThreads = 768;
 constexpr int kFmEpiThreads = 512;
 constexpr int kFmSfWarp0 = 4, kFmEpiWarp0 = 8;
-constexpr int kFmStages = 4;
+constexpr int kFmStages = 6;
 constexpr int kFmATile = BM * BK;    // this CTA's 128 rows of A, 16 KiB
 constexpr int kFmBTile = 128 * BK;   // this CTA's half of the 256-row B tile, 16 KiB
 constexpr int kFmStageBytes = kFmATile + kFmBTile;
 constexpr int kFmStgPitch = 272;
-constexpr int kFmStgBytes = BM * kFmStgPitch;  // 34816, two of them (combine-send epilogue)
-constexpr int kFmCommWarps = 2, kFmCommBufs = 2;
-constexpr int kFmCommRow = 7168;               // largest hidden size the copy warps stage
-constexpr int kFmCommBuf = kFmCommRow + 256;   // row + up to 56 fp32 scales
+constexpr int kFmStgBytes = BM * kFmStgPitch;  // 34816: bf16 staging of half an output tile (combine-send epilogue)
+constexpr int kFmCommBatch = 4;                // rows a warp sends between two arrival signals
 constexpr int kFmSmemCtrl = 1024;
-constexpr int kFmSmem = kFmStages * kFmStageBytes + 2 * kFmStgBytes + kFmCommWarps * kFmCommBufs * kFmCommBuf + kFmSmemCtrl;
+// six pipeline stages | one staging buffer | barriers: 232448 bytes, all a CTA can have (dispatch rows move
+// through registers and need none of it)
+constexpr int kFmSmem = kFmStages * kFmStageBytes + kFmStgBytes + kFmSmemCtrl;
 static_assert(kFmSmem <= 232448, "exceeds the shared memory of one CTA");
 constexpr uint32_t kFmTmemCols = 512;
 constexpr uint32_t kFmSfCol0 = 256, kFmSfStride = 16;
@@ -155,6 +157,85 @@ __device__ __forceinline__ bool fm_wait_counter(const uint32_t* ctr, uint32_t wa
     }
 }
 
+// Dispatch send, run by the epilogue warps while they have nothing to drain.
+struct FmSendState { int ci, pend_d, pend_le, pend_n; };  // per warp, in shared memory: list cursor, rows not yet counted
+struct FmSendArgs {
+    uint8_t* const* peer_base;
+    const uint8_t* xq;
+    const float* xs;
+    const int4* send_list;
+    CamStatus* status;
+    uint64_t off_recv_x, off_recv_scales, off_recv_src, off_arrival;  // off_arrival already points at this call's parity
+    int h, rank, num_ranks, max_tokens, a_rows, drop, stride, nlist;
+};
+
+// One warp sends rows of the list (its cursor advances by `stride`) until the list is exhausted or, when `bar`
+// is given, until that mbarrier phase has completed.  A row moves through the warp's registers (eight 16-byte loads
+// in flight per lane) from this rank's quantised tokens straight into the destination rank's receive buffer.  After
+// kFmCommBatch rows, when the destination expert changes and before returning, one system-scope fence makes the rows
+// visible and they are counted on the arrival counter of their expert at the destination.  Kept out of line so that
+// its registers do not add to those of the epilogue around the call.
+__device__ __noinline__ void fm_send_rows(const FmSendArgs* args, FmSendState* st, uint64_t* bar, uint32_t bar_parity) {
+    const FmSendArgs& a = *args;  // shared memory
+    const uint32_t lane = lane_id();
+    int ci = st->ci, pend_d = st->pend_d, pend_le = st->pend_le, pend_n = st->pend_n;
+    auto flush = [&]() {
+        if (pend_n > 0 && !a.drop) {  // drop: host-side fault injection, the rows are never counted
+            __syncwarp();
+            if (lane == 0) {
+                fence_acq_rel_sys();
+                red_release_sys_add_u32(reinterpret_cast<uint32_t*>(a.peer_base[pend_d] + a.off_arrival) + pend_le,
+                                        static_cast<uint32_t>(pend_n));
+            }
+        }
+        pend_n = 0;
+    };
+    const int nsc16 = a.h >> 9;  // scales of a row in 16-byte pieces (h is a multiple of 512)
+    while (ci < a.nlist) {
+        if (bar != nullptr && __all_sync(0xFFFFFFFFu, mbar_try_wait(bar, bar_parity))) break;
+        const int4 ent = a.send_list[ci];
+        const int t = ent.x, d = ent.y, row = ent.z, le = ent.w & 0xFFFF, kk = ent.w >> 16;
+        if (t < 0 || t >= a.max_tokens || d < 0 || d >= a.num_ranks || row < 0 || row >= a.a_rows) {
+            if (lane == 0) gemm_record_status(a.status, CAM_ERR_BAD_INDEX, 5, ci);
+            ci = a.nlist;  // stop sending
+            break;
+        }
+        if (pend_n > 0 && (d != pend_d || le != pend_le || pend_n >= kFmCommBatch)) flush();
+        uint8_t* pb = a.peer_base[d];
+        const uint8_t* src = a.xq + static_cast<size_t>(t) * a.h;
+        uint8_t* dst = pb + a.off_recv_x + static_cast<size_t>(row) * a.h;
+        for (int o = static_cast<int>(lane) * 16; o < a.h; o += 8 * 512) {
+            uint4 v[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                if (o + q * 512 < a.h) v[q] = ld_nc_v4(src + o + q * 512);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                if (o + q * 512 < a.h) st_na_v4(dst + o + q * 512, v[q]);
+        }
+        if (static_cast<int>(lane) < nsc16)
+            st_na_v4(pb + a.off_recv_scales + (static_cast<size_t>(row) * nsc16 + lane) * 16,
+                     ld_nc_v4(reinterpret_cast<const uint8_t*>(a.xs) + (static_cast<size_t>(t) * nsc16 + lane) * 16));
+        if (lane < 3u) {
+            int* tri = reinterpret_cast<int*>(pb + a.off_recv_src) + static_cast<size_t>(row) * 3;
+            tri[lane] = lane == 0u ? a.rank : lane == 1u ? t : kk;
+        }
+        pend_d = d;
+        pend_le = le;
+        ++pend_n;
+        ci += a.stride;
+    }
+    flush();
+    __syncwarp();
+    if (lane == 0) {
+        st->ci = ci;
+        st->pend_d = pend_d;
+        st->pend_le = pend_le;
+        st->pend_n = 0;
+    }
+    __syncwarp();
+}
+
 // Unique counter index of the 256-row block that starts at `row0` of local expert `e` (experts own contiguous rows).
 __device__ __forceinline__ int fm_block_index(int row0, int e) { return (row0 >> 8) + e; }
 
@@ -168,16 +249,17 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
         return;
     }
     uint8_t* stg = smem + kFmStages * kFmStageBytes;
-    uint8_t* comm = stg + 2 * kFmStgBytes;
-    uint8_t* ctrl = comm + kFmCommWarps * kFmCommBufs * kFmCommBuf;
+    uint8_t* ctrl = stg + kFmStgBytes;
     uint64_t* bar_full = reinterpret_cast<uint64_t*>(ctrl);
     uint64_t* bar_sf = bar_full + kFmStages;
     uint64_t* bar_empty = bar_sf + kFmStages;
     uint64_t* bar_tfull = bar_empty + kFmStages;
     uint64_t* bar_tempty = bar_tfull + 1;
-    uint64_t* bar_comm = bar_tempty + 1;  // [copy warp][buffer]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_comm + kFmCommWarps * kFmCommBufs);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    FmSendState* send_state = reinterpret_cast<FmSendState*>(ctrl + 512);  // [16 epilogue warps]
+    FmSendArgs* send_args = reinterpret_cast<FmSendArgs*>(ctrl + 768);
+    static_assert(768 + sizeof(FmSendArgs) <= kFmSmemCtrl && 512 + 16 * sizeof(FmSendState) <= 768, "control area layout");
     float* s_amax = reinterpret_cast<float*>(stg);  // first-GEMM epilogue: [2 parities][4 column quarters][128 rows]
 
     const int warp = static_cast<int>(threadIdx.x) >> 5;
@@ -202,10 +284,27 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
         }
         mbar_init(bar_tfull, 1);
         mbar_init(bar_tempty, 2 * (kFmEpiThreads / 32));
-        for (int i = 0; i < kFmCommWarps * kFmCommBufs; ++i) mbar_init(&bar_comm[i], 1);
         *abort_flag = 0u;
         mbar_fence_init();
         if (blockIdx.x == 0 && p.trace != nullptr) p.trace[p.num_experts] = globaltimer_ns();
+        FmSendArgs& sa = *send_args;
+        sa.peer_base = p.peer_base;
+        sa.xq = p.xq;
+        sa.xs = p.xs;
+        sa.send_list = p.send_list;
+        sa.status = p.status;
+        sa.off_recv_x = p.off_recv_x;
+        sa.off_recv_scales = p.off_recv_scales;
+        sa.off_recv_src = p.off_recv_src;
+        sa.off_arrival = p.off_arrival + static_cast<uint64_t>(parity) * p.arrival_stride * sizeof(uint32_t);
+        sa.h = p.h;
+        sa.rank = p.rank;
+        sa.num_ranks = p.num_ranks;
+        sa.max_tokens = p.max_tokens;
+        sa.a_rows = p.a_rows;
+        sa.drop = p.dbg_drop_flags;
+        sa.stride = static_cast<int>(gridDim.x) * (kFmEpiThreads / 32);
+        sa.nlist = do_send ? min(p.send_list_len[0], p.send_list_cap) : 0;
     }
     if (do_gemm && warp == 1) {
         tmem_alloc_pair(tmem_slot, kFmTmemCols);
@@ -319,70 +418,6 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                 tc_commit_pair(tfull1);
             }
             if (!ok) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 1, static_cast<int>(it));
-        } else if (warp >= 2 && lane == 0 && do_send) {
-            // ------------------------------------------------------------ copy warps: dispatch send
-            // One thread per warp moves rows with the bulk-copy engine: local memory -> shared memory -> the
-            // destination rank's receive buffer, two rows in flight.  A row is counted on the destination's
-            // arrival counter of its local expert once its copy has completed.
-            const int cw = warp - 2;
-            const int gw = static_cast<int>(blockIdx.x) * kFmCommWarps + cw;
-            const int total_cw = static_cast<int>(gridDim.x) * kFmCommWarps;
-            const int nlist = min(p.send_list_len[0], p.send_list_cap);
-            const uint32_t row_bytes = static_cast<uint32_t>(p.h);
-            const uint32_t sc_bytes = static_cast<uint32_t>(p.h >> 7) * 4u;
-            uint8_t* buf0 = comm + cw * kFmCommBufs * kFmCommBuf;
-            uint64_t* cbar = bar_comm + cw * kFmCommBufs;
-            int pend_d[2] = {0, 0}, pend_le[2] = {0, 0};
-            auto signal = [&](int d, int le) {
-                if (p.dbg_drop_flags) return;  // host-side fault injection: this rank's rows are never counted
-                fence_acq_rel_sys();
-                red_release_sys_add_u32(reinterpret_cast<uint32_t*>(p.peer_base[d] + p.off_arrival) +
-                                            static_cast<size_t>(parity) * p.arrival_stride + le, 1u);
-            };
-            int n = 0;
-            bool ok = true;
-            for (int i = gw; i < nlist; i += total_cw, ++n) {
-                const int4 ent = p.send_list[i];
-                const int t = ent.x, d = ent.y, row = ent.z, le = ent.w & 0xFFFF, kk = ent.w >> 16;
-                const int bsel = n & 1;
-                if (n >= 2) {  // the copy that used this buffer two rows ago is complete: count that row
-                    bulk_wait_group<1>();
-                    signal(pend_d[bsel], pend_le[bsel]);
-                }
-                if (t < 0 || t >= p.max_tokens || d < 0 || d >= p.num_ranks || row < 0 || row >= p.a_rows) {
-                    gemm_record_status(p.status, CAM_ERR_BAD_INDEX, 5, i);
-                    ok = false;
-                    break;
-                }
-                uint8_t* buf = buf0 + bsel * kFmCommBuf;
-                mbar_arrive_expect_tx(&cbar[bsel], row_bytes + sc_bytes);
-                bulk_load_g2s(buf, p.xq + static_cast<size_t>(t) * row_bytes, row_bytes, &cbar[bsel]);
-                bulk_load_g2s(buf + kFmCommRow, p.xs + static_cast<size_t>(t) * (p.h >> 7), sc_bytes, &cbar[bsel]);
-                if (!fm_mbar_wait(&cbar[bsel], static_cast<uint32_t>(n >> 1) & 1u, wt)) { ok = false; break; }
-                uint8_t* pb = p.peer_base[d];
-                bulk_store_s2g(pb + p.off_recv_x + static_cast<size_t>(row) * row_bytes, buf, row_bytes);
-                bulk_store_s2g(pb + p.off_recv_scales + static_cast<size_t>(row) * sc_bytes, buf + kFmCommRow, sc_bytes);
-                bulk_commit_group();
-                int* tri = reinterpret_cast<int*>(pb + p.off_recv_src) + static_cast<size_t>(row) * 3;
-                tri[0] = p.rank;
-                tri[1] = t;
-                tri[2] = kk;
-                pend_d[bsel] = d;
-                pend_le[bsel] = le;
-            }
-            if (ok) {
-                if (n >= 2) {
-                    bulk_wait_group<1>();
-                    signal(pend_d[n & 1], pend_le[n & 1]);
-                }
-                if (n >= 1) {
-                    bulk_wait_group<0>();
-                    signal(pend_d[(n - 1) & 1], pend_le[(n - 1) & 1]);
-                }
-            } else {
-                bulk_wait_group<0>();  // nothing of this thread stays in flight
-                gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 4, n);
-            }
         }
     } else if (warp < kFmEpiWarp0) {
         reg_dealloc<kFmSfRegs>();
@@ -490,14 +525,28 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
         }
     } else {
         reg_alloc<kFmEpiRegs>();
-        // ---------------------------------------------------------------- epilogue warps
+        // ---------------------------------------------------------------- epilogue warps (and dispatch send)
+        // While an epilogue warp waits for an accumulator it sends rows of the dispatch: one row per turn, moved
+        // through its registers (eight 16-byte loads in flight per lane) from this rank's quantised tokens straight
+        // into the destination rank's receive buffer.  Rows are taken from the list in order, so the first local
+        // expert of every rank is complete first.  After a few rows (or when the destination expert changes) one
+        // system-scope fence makes them visible and they are counted on the arrival counter of their expert there.
+        const FmSendArgs& sa = *send_args;  // filled by thread 0 before the first barrier of the CTA
+        FmSendState* sst = send_state + (warp - kFmEpiWarp0);  // this warp's cursor, in shared memory
+        if (lane == 0) {
+            sst->ci = static_cast<int>(blockIdx.x) * (kFmEpiThreads / 32) + (warp - kFmEpiWarp0);
+            sst->pend_d = -1;
+            sst->pend_le = 0;
+            sst->pend_n = 0;
+        }
+        __syncwarp();
         if (do_gemm) {
             const int ew = warp - kFmEpiWarp0;
             const int q = warp & 3;   // TMEM lane quarter this warp may read
             const int cq = ew >> 2;   // which 32-column quarter of each 128-column half
             const int r = q * 32 + static_cast<int>(lane);
             FusedWalker w(p.expert_offsets, p.num_experts, nt1, nt2, p.lag);
-            uint32_t tcount = 0, halves = 0;
+            uint32_t tcount = 0;
             int kind, e, mt, nt, row0, rows, cnt;
             bool ok = true;
             for (int tile = pair_id; ok && w.locate(tile, kind, e, mt, nt, row0, rows, cnt); tile += num_pairs, ++tcount) {
@@ -506,6 +555,7 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                 rows = max(0, min(BM, rows - static_cast<int>(cta) * BM));
                 const bool valid = r < rows && row0 + r < p.a_rows;
                 const int grow = row0 + (valid ? r : 0);
+                if (sst->ci < sa.nlist) fm_send_rows(send_args, sst, bar_tfull, tcount & 1u);  // nothing to drain yet: send rows
                 // one decision for all epilogue threads: a thread that gave up must not leave the others at a
                 // named barrier further down
                 if (!named_bar_and(1, kFmEpiThreads, fm_mbar_wait(bar_tfull, tcount & 1u, wt, 256u))) { ok = false; break; }
@@ -563,7 +613,7 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                         red_release_gpu_add_u32(p.g1_done + blk, 1u);
                     }
                 } else {
-                    // bf16 rows straight to the origin rank's combine slots (bulk copies, two staging buffers)
+                    // bf16 rows straight to the origin rank's combine slots (256-byte bulk copies out of the staging buffer)
                     __nv_bfloat16* orow = nullptr;
                     if (valid) {
                         const int src = p.row_src[static_cast<size_t>(grow) * 3 + 0];
@@ -574,10 +624,8 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                                    (static_cast<size_t>(tok) * p.topk + kk) * static_cast<size_t>(p.h);
                     }
                     auto push_half = [&](const uint32_t (&v)[32], int c0) {
-                        uint8_t* sbuf = stg + (halves & 1u) * kFmStgBytes;
-                        uint8_t* srow = sbuf + r * kFmStgPitch;
-                        ++halves;
-                        if (cq == 0) bulk_wait_group_read<1>();  // the copies that read this buffer are done with it
+                        uint8_t* srow = stg + r * kFmStgPitch;
+                        if (cq == 0) bulk_wait_group_read<0>();  // the copies that read the staging buffer are done with it
                         named_bar_sync(1, kFmEpiThreads);
 #pragma unroll
                         for (int j = 0; j < 32; j += 8)
@@ -600,6 +648,7 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
             if (cq == 0) bulk_wait_group<0>();  // every row this thread sent has been written
             if (!ok) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 2, static_cast<int>(tcount));
         }
+        if (sst->ci < sa.nlist) fm_send_rows(send_args, sst, nullptr, 0u);  // rows left when the tiles ran out (or send-only launch)
     }
 
     // ------------------------------------------------------------------ teardown

@@ -13,7 +13,7 @@ CAM_MAX_RANKS = 72  # flag arrays are sized for this many ranks (cam_types.h)
 OFFSETS = ["off_count_flag", "off_data_flag", "off_combine_flag", "off_barrier_flag", "off_ll_combine_flag",
            "off_count_matrix", "off_ll_cells", "off_recv_x", "off_recv_scales", "off_recv_src", "off_combine_buf",
            "off_ll_x", "off_ll_scales", "off_ll_meta", "off_ll_combine_buf", "off_tp_flag", "off_tp_cnt", "off_tp_x",
-           "off_tp_scales", "off_dup_cnt", "off_dup_list", "off_arrival", "total_bytes"]
+           "off_tp_scales", "off_dup_cnt", "off_dup_list", "off_arrival", "off_guard0", "off_guard1", "off_guard2", "off_guard3", "total_bytes"]
 
 
 class CamLayout(ctypes.Structure):
@@ -55,6 +55,7 @@ def test_regions_are_aligned_ordered_and_big_enough(lib, r, e, t, h, k, ll, tp_r
         "off_tp_x": tp_rows * h * 2, "off_tp_scales": 4 * tp_rows * (h // 128),
         "off_dup_cnt": 4 * 2 * CAM_MAX_RANKS, "off_dup_list": 8 * 2 * r * t * k,
         "off_arrival": 4 * 2 * e,  # rows landed per local expert of the fused layer, two parities
+        "off_guard0": 64, "off_guard1": 64, "off_guard2": 64, "off_guard3": 64,
     }
     # regions that this configuration does not have (no low-latency mode, no TP partner) keep offset 0
     offs = sorted((getattr(lay, n), n) for n in OFFSETS if n != "total_bytes" and need[n] > 0)
@@ -115,6 +116,6 @@ def test_grouped_gemm_rejects_bad_shapes_before_any_launch(lib, over, word):
 
 def test_status_strings_cover_every_code(lib):
     lib.cam_status_string.restype = ctypes.c_char_p
-    texts = [lib.cam_status_string(c).decode() for c in range(0, 9)]
+    texts = [lib.cam_status_string(c).decode() for c in range(0, 11)]
     assert texts[0] == "ok" and len(set(texts)) == len(texts) and "unknown status" not in texts
     assert lib.cam_status_string(999).decode() == "unknown status"

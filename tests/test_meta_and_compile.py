@@ -50,7 +50,7 @@ def test_meta_layout_and_low_latency_shapes():
     assert outs[0].shape == (rows, h) and outs[0].dtype == torch.float8_e4m3fn
     assert outs[2].shape == (t * k,) and outs[3].shape == (el,) and outs[4].shape == (r * el,)
     y = ops.moe_combine_shmem(_m(rows, h, dtype=torch.bfloat16), _m(t, k, dtype=torch.int32), outs[2], outs[4], _m(t, k),
-                              None, None, None, None, None, None, r, 0, e, 1, 0, 0, 0, 0, 0, 0, 0, 0, 1)
+                              None, None, None, None, None, None, r, 0, e, 1, 0, 0, 0, 0, 0, 0, 1, 0, 0)
     assert y.shape == (t, h) and y.dtype == torch.bfloat16
 
 
@@ -77,7 +77,7 @@ def test_compiled_fused_layer_and_low_latency_ops_match_eager():
         d = ops.moe_dispatch_shmem(x, idx32, None, None, 1, 0, cfg.num_experts, 1, 0, 0, 0, 0, 0, 0, 1, buf.handle)
         lay = ops.get_dispatch_layout(idx32.long(), cfg.num_experts, 1)
         return ops.moe_combine_shmem(d[0], idx32, d[2], d[4], w, None, None, None, None, None, None, 1, 0, cfg.num_experts,
-                                     1, 0, 0, 0, 0, 0, 0, 0, 0, buf.handle), lay[1]
+                                     1, 0, 0, 0, 0, 0, 0, buf.handle, 0, 0), lay[1]
 
     want = fused(x, idx, w.float())
     got = torch.compile(fused, fullgraph=True, backend="aot_eager")(x, idx, w.float())

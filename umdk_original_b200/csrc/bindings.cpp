@@ -117,12 +117,27 @@ public:
                                        initiator ? 1 : 0, stream()));
     }
     void set_trace(bool on) { CAM_RT(cam_buffer_set_trace(buf_, on ? 1 : 0)); }
+    int64_t check_guards() {
+        int damaged = 0;
+        CAM_RT(cam_buffer_check_guards(buf_, stream(), &damaged));
+        return damaged;
+    }
+    at::Tensor guard(int64_t i) const {
+        const uint64_t offs[4] = {layout_.off_guard0, layout_.off_guard1, layout_.off_guard2, layout_.off_guard3};
+        CAM_ASSERT(i >= 0 && i < 4, "guard index must be 0..3");
+        return view(static_cast<uint8_t*>(cam_buffer_base(buf_)) + offs[i], {CAM_GUARD_BYTES}, at::kByte);
+    }
     int64_t launch_count() const { return static_cast<int64_t>(cam_buffer_launch_count(buf_)); }
     void set_fused_trace(bool on) { CAM_RT(cam_buffer_set_fused_trace(buf_, on ? 1 : 0)); }
     std::vector<int64_t> read_fused_trace(int64_t num_local_experts) {
         std::vector<long long> t(static_cast<size_t>(num_local_experts));
         CAM_RT(cam_buffer_read_fused_trace(buf_, t.data(), static_cast<int>(num_local_experts)));
         return std::vector<int64_t>(t.begin(), t.end());
+    }
+    std::vector<int64_t> read_fused_waits(int64_t num_local_experts) {
+        long long t[7];
+        CAM_RT(cam_buffer_read_fused_waits(buf_, t, static_cast<int>(num_local_experts)));
+        return std::vector<int64_t>(t, t + 7);
     }
     std::vector<int64_t> read_trace() {
         unsigned long long t[16];
@@ -253,6 +268,19 @@ int idx_kind(const at::Tensor& t, const char* what) {
     CAM_ASSERT(t.scalar_type() == at::kLong || t.scalar_type() == at::kInt, what, " must be int64 or int32");
     return t.scalar_type() == at::kLong ? 1 : 0;
 }
+// Activations may be bfloat16 or float16, as in the reference (fused_deep_moe/op_host/fused_deep_moe.cpp:17-19,
+// moe_dispatch_normal/op_host/moe_dispatch_normal.cpp:19).  The kernels read bfloat16.  A dispatch that moves rows
+// unchanged (quant mode 0) takes float16 rows as they are (two bytes per element either way); everything that computes
+// on the values (quantisation, weighted sums) converts float16 once on entry, and results go back to the input's dtype.
+bool is_half(const at::Tensor& t, const char* what) {
+    CAM_ASSERT(t.scalar_type() == at::kBFloat16 || t.scalar_type() == at::kHalf, what, " must be bfloat16 or float16");
+    return t.scalar_type() == at::kHalf;
+}
+at::Tensor rows_for_kernel(const at::Tensor& x, bool half, bool moved_unchanged) {
+    if (!half) return x;
+    return moved_unchanged ? x.view(at::kBFloat16) : x.to(at::kBFloat16);
+}
+
 void check_cuda_contig(const at::Tensor& t, const char* what) {
     CAM_ASSERT(t.is_cuda(), what, " must be a CUDA tensor");
     CAM_ASSERT(t.is_contiguous(), what, " must be contiguous");
@@ -332,7 +360,7 @@ std::vector<at::Tensor> dispatch_prefill_impl(const at::Tensor& x, const at::Ten
                                               int64_t quant_mode, int64_t num_experts) {
     Buffer* b = buffer_by_name(group_ep);
     CAM_ASSERT(x.dim() == 2 && topk_idx.dim() == 2, "x must be [tokens, hidden] and topk_idx [tokens, topk]");
-    CAM_ASSERT(x.scalar_type() == at::kBFloat16, "x must be bfloat16");
+    const bool half = is_half(x, "x");
     check_cuda_contig(x, "x");
     check_cuda_contig(topk_idx, "topk_idx");
     CAM_ASSERT(topk_weights.sizes() == topk_idx.sizes(), "topk_weights must match topk_idx");
@@ -343,7 +371,8 @@ std::vector<at::Tensor> dispatch_prefill_impl(const at::Tensor& x, const at::Ten
     c10::cuda::CUDAGuard guard(x.device());
     const int64_t T = x.size(0), h = x.size(1), K = topk_idx.size(1);
     const int64_t E = num_experts > 0 ? num_experts : b->layout().num_experts, El = E / num_ranks;
-    CAM_RT(cam_dispatch_normal(b->raw(), x.data_ptr(), topk_idx.data_ptr(), is64, static_cast<int>(T),
+    const at::Tensor xk = rows_for_kernel(x, half, quant_mode == 0);
+    CAM_RT(cam_dispatch_normal(b->raw(), xk.data_ptr(), topk_idx.data_ptr(), is64, static_cast<int>(T),
                                static_cast<int>(K), static_cast<int>(h), static_cast<int>(E),
                                static_cast<int>(quant_mode), g_phase_mask & 7, b->stream()));
     int64_t rows = num_worst_tokens;
@@ -361,6 +390,7 @@ std::vector<at::Tensor> dispatch_prefill_impl(const at::Tensor& x, const at::Ten
     // tensors (pybind/moe_dispatch_prefill.cpp:166-191); Buffer.set_copy_outputs(True) gives the same here at the
     // cost of one device copy of the received rows.
     std::vector<at::Tensor> outs = {b->recv_x(rows, h, quant_mode), b->recv_src(rows), b->recv_count(E), per_expert, scales};
+    if (half && quant_mode == 0) outs[0] = outs[0].view(at::kHalf);
     if (b->copy_outputs())
         for (at::Tensor& t : outs)
             if (t.is_cuda()) t = t.clone();
@@ -392,7 +422,8 @@ at::Tensor moe_combine_prefill_cuda(const at::Tensor& x, const at::Tensor& topk_
                                     const at::Tensor& src_idx, const at::Tensor& send_head,
                                     c10::string_view group_ep, int64_t rank, int64_t num_ranks) {
     Buffer* b = buffer_by_name(group_ep);
-    CAM_ASSERT(x.dim() == 2 && x.scalar_type() == at::kBFloat16, "x must be a 2-D bfloat16 tensor of expert outputs");
+    CAM_ASSERT(x.dim() == 2, "x must be a 2-D tensor of expert outputs");
+    const bool half = is_half(x, "x");
     check_cuda_contig(x, "x");
     check_cuda_contig(topk_idx, "topk_idx");
     check_cuda_contig(src_idx, "src_idx");
@@ -405,20 +436,21 @@ at::Tensor moe_combine_prefill_cuda(const at::Tensor& x, const at::Tensor& topk_
     const int64_t T = topk_idx.size(0), K = topk_idx.size(1), h = x.size(1);
     const int64_t E = send_head.numel();
     at::Tensor w = topk_weights.contiguous();
-    at::Tensor out = at::empty({T, h}, x.options());
+    const at::Tensor xk = rows_for_kernel(x, half, false);
+    at::Tensor out = at::empty({T, h}, xk.options());
     // rows actually present: the smaller of x's rows and the device-side count of the last dispatch
     at::Tensor total = at::minimum(b->total_recv(), at::full({1}, x.size(0), b->total_recv().options()));
-    CAM_RT(cam_combine(b->raw(), x.data_ptr(), src_idx.data_ptr<int>(), total.data_ptr<int>(), topk_idx.data_ptr(),
+    CAM_RT(cam_combine(b->raw(), xk.data_ptr(), src_idx.data_ptr<int>(), total.data_ptr<int>(), topk_idx.data_ptr(),
                        is64, w.data_ptr<float>(), out.data_ptr(), static_cast<int>(T), static_cast<int>(K),
                        static_cast<int>(h), static_cast<int>(E), 0, 0,
                        (g_phase_mask & 7) & (CAM_PHASE_SEND | CAM_PHASE_RECV), b->stream()));
-    return out;
+    return half ? out.to(at::kHalf) : out;
 }
 
 // --------------------------------------------------------------------------------------------
 // moe_dispatch_shmem / moe_combine_shmem  (pybind/moe_dispatch_shmem.cpp:27-153, moe_combine_shmem.cpp:27-85)
 // --------------------------------------------------------------------------------------------
-std::vector<at::Tensor> moe_dispatch_shmem_cuda(const at::Tensor& x, const at::Tensor& expertIds,
+std::vector<at::Tensor> moe_dispatch_shmem_bf16(const at::Tensor& x, const at::Tensor& expertIds,
                                                 const c10::optional<at::Tensor>& scales,
                                                 const c10::optional<at::Tensor>& xActiveMask, int64_t epWorldSize,
                                                 int64_t epRankId, int64_t moeExpertNum, int64_t tpWorldSize,
@@ -523,6 +555,21 @@ std::vector<at::Tensor> moe_dispatch_shmem_cuda(const at::Tensor& x, const at::T
     return {expandX, dynScales, expandIdx, tokenNums, epSend, tpSend};
 }
 
+std::vector<at::Tensor> moe_dispatch_shmem_cuda(const at::Tensor& x, const at::Tensor& expertIds,
+                                                const c10::optional<at::Tensor>& scales,
+                                                const c10::optional<at::Tensor>& xActiveMask, int64_t epWorldSize,
+                                                int64_t epRankId, int64_t moeExpertNum, int64_t tpWorldSize,
+                                                int64_t tpRankId, int64_t expertShardType, int64_t sharedExpertNum,
+                                                int64_t sharedExpertRankNum, int64_t quantMode, int64_t globalBS,
+                                                int64_t expertTokenNumsType, int64_t extInfo) {
+    const bool half = is_half(x, "x");
+    auto outs = moe_dispatch_shmem_bf16(rows_for_kernel(x, half, quantMode == 0), expertIds, scales, xActiveMask, epWorldSize,
+                                        epRankId, moeExpertNum, tpWorldSize, tpRankId, expertShardType, sharedExpertNum,
+                                        sharedExpertRankNum, quantMode, globalBS, expertTokenNumsType, extInfo);
+    if (half && quantMode == 0) outs[0] = outs[0].view(at::kHalf);  // rows travelled unchanged
+    return outs;
+}
+
 std::vector<at::Tensor> moe_dispatch_shmem_meta(const at::Tensor& x, const at::Tensor& expertIds,
                                                 const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&,
                                                 int64_t epWorldSize, int64_t epRankId, int64_t moeExpertNum,
@@ -551,7 +598,7 @@ std::vector<at::Tensor> moe_dispatch_shmem_meta(const at::Tensor& x, const at::T
             at::empty({std::max<int64_t>(tpWorldSize, 1)}, x.options().dtype(at::kInt))};
 }
 
-at::Tensor moe_combine_shmem_cuda(const at::Tensor& expandX, const at::Tensor& expertIds, const at::Tensor& expandIdx,
+at::Tensor moe_combine_shmem_bf16(const at::Tensor& expandX, const at::Tensor& expertIds, const at::Tensor& expandIdx,
                                   const at::Tensor& epSendCounts, const at::Tensor& expertScales,
                                   const c10::optional<at::Tensor>& tpSendCounts,
                                   const c10::optional<at::Tensor>& xActiveMask,
@@ -615,6 +662,22 @@ at::Tensor moe_combine_shmem_cuda(const at::Tensor& expandX, const at::Tensor& e
     return out;
 }
 
+at::Tensor moe_combine_shmem_cuda(const at::Tensor& expandX, const at::Tensor& expertIds, const at::Tensor& expandIdx,
+                                  const at::Tensor& epSendCounts, const at::Tensor& expertScales,
+                                  const c10::optional<at::Tensor>& tpSendCounts,
+                                  const c10::optional<at::Tensor>& xActiveMask,
+                                  const c10::optional<at::Tensor>& activationScale,
+                                  const c10::optional<at::Tensor>& weightScale,
+                                  const c10::optional<at::Tensor>& groupList,
+                                  const c10::optional<at::Tensor>& expandScales, int64_t epWorldSize, int64_t epRankId,
+                                  int64_t moeExpertNum, int64_t tpWorldSize, int64_t tpRankId, int64_t expertShardType,
+                                  int64_t sharedExpertNum, int64_t sharedExpertRankNum, int64_t globalBS,
+                                  int64_t commQuantMode, int64_t extInfo, int64_t outDtype, int64_t groupListType) {
+    const bool half = is_half(expandX, "expandX");
+    at::Tensor out = moe_combine_shmem_bf16(rows_for_kernel(expandX, half, false), expertIds, expandIdx, epSendCounts, expertScales, tpSendCounts, xActiveMask, activationScale, weightScale, groupList, expandScales, epWorldSize, epRankId, moeExpertNum, tpWorldSize, tpRankId, expertShardType, sharedExpertNum, sharedExpertRankNum, globalBS, commQuantMode, extInfo, outDtype, groupListType);
+    return half ? out.to(at::kHalf) : out;
+}
+
 at::Tensor moe_combine_shmem_meta(const at::Tensor& expandX, const at::Tensor& expertIds, const at::Tensor&,
                                   const at::Tensor&, const at::Tensor&, const c10::optional<at::Tensor>&,
                                   const c10::optional<at::Tensor>&, const c10::optional<at::Tensor>&,
@@ -631,7 +694,7 @@ at::Tensor moe_combine_shmem_meta(const at::Tensor& expandX, const at::Tensor& e
 // gmm2Weight [E_l, h, I] e4m3 with scales [E_l, h/128, I/128]; a list of E_l per-expert tensors
 // is stacked once and cached by the Python layer before it reaches this function.
 // --------------------------------------------------------------------------------------------
-std::vector<at::Tensor> fused_deep_moe_cuda(const at::Tensor& x, const at::Tensor& expertIds,
+std::vector<at::Tensor> fused_deep_moe_bf16(const at::Tensor& x, const at::Tensor& expertIds,
                                             at::TensorList gmm1PermutedWeight, at::TensorList gmm1PermutedWeightScale,
                                             at::TensorList gmm2Weight, at::TensorList gmm2WeightScale,
                                             const at::Tensor& expertScales,
@@ -719,6 +782,21 @@ std::vector<at::Tensor> fused_deep_moe_cuda(const at::Tensor& x, const at::Tenso
                  static_cast<int>(K), static_cast<int>(h), static_cast<int>(I), static_cast<int>(E),
                  static_cast<int>(El), g_phase_mask & 15, b->stream()));
     return {out, nums};
+}
+
+std::vector<at::Tensor> fused_deep_moe_cuda(const at::Tensor& x, const at::Tensor& expertIds,
+                                            at::TensorList gmm1PermutedWeight, at::TensorList gmm1PermutedWeightScale,
+                                            at::TensorList gmm2Weight, at::TensorList gmm2WeightScale,
+                                            const at::Tensor& expertScales,
+                                            const c10::optional<at::Tensor>& expertSmoothScales,
+                                            const c10::optional<at::Tensor>& xActiveMask, c10::string_view groupEp,
+                                            int64_t epRankSize, int64_t epRankId, int64_t moeExpertNum,
+                                            int64_t sharedExpertNum, int64_t sharedExpertRankNum, int64_t quantMode,
+                                            int64_t globalBs) {
+    const bool half = is_half(x, "x");
+    auto outs = fused_deep_moe_bf16(rows_for_kernel(x, half, false), expertIds, gmm1PermutedWeight, gmm1PermutedWeightScale, gmm2Weight, gmm2WeightScale, expertScales, expertSmoothScales, xActiveMask, groupEp, epRankSize, epRankId, moeExpertNum, sharedExpertNum, sharedExpertRankNum, quantMode, globalBs);
+    if (half) outs[0] = outs[0].to(at::kHalf);
+    return outs;
 }
 
 std::vector<at::Tensor> fused_deep_moe_meta(const at::Tensor& x, const at::Tensor&, at::TensorList, at::TensorList,
@@ -903,8 +981,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("set_trace", &Buffer::set_trace)
         .def("read_trace", &Buffer::read_trace)
         .def("launch_count", &Buffer::launch_count)
+        .def("check_guards", &Buffer::check_guards)
+        .def("guard", &Buffer::guard)
         .def("set_fused_trace", &Buffer::set_fused_trace)
         .def("read_fused_trace", &Buffer::read_fused_trace)
+        .def("read_fused_waits", &Buffer::read_fused_waits)
         .def("set_profile", &Buffer::set_profile)
         .def("read_profile", &Buffer::read_profile)
         .def("poll_status", &Buffer::poll_status)

@@ -51,6 +51,7 @@ enum CamPhase {
     CAM_PHASE_ALL = 7,
 };
 
+#define CAM_GUARD_BYTES 64
 #define CAM_MAX_RANKS 72
 #define CAM_MAX_EXPERTS 1024
 #define CAM_MAX_TOPK 16
@@ -87,6 +88,9 @@ typedef struct CamLayout {
     uint64_t off_dup_cnt;       // u32[2][CAM_MAX_RANKS]: replicate-list lengths per source (normal dispatch)
     uint64_t off_dup_list;      // i32[2][R][max_tokens*topk][2]: (row that arrived, row to copy it to)
     uint64_t off_arrival;       // u32[2][E]: rows that have landed per local expert (fused layer, parity of the epoch)
+    // Guard words (CAM_GUARD_BYTES of 0xA5 each) directly behind the four regions that peers write rows into: recv_x,
+    // recv_scales, recv_src, combine_buf.  Nothing ever writes them; cam_buffer_check_guards tells if something did.
+    uint64_t off_guard0, off_guard1, off_guard2, off_guard3;
     uint64_t total_bytes;
 } CamLayout;
 

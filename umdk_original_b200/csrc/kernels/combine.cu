@@ -68,7 +68,11 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineP
             const int src = p.row_src[static_cast<size_t>(i) * 3 + 0];
             const int t = p.row_src[static_cast<size_t>(i) * 3 + 1];
             const int k = p.row_src[static_cast<size_t>(i) * 3 + 2];
-            if (src < 0 || src >= p.R || t < 0 || t >= p.max_tokens || k < 0 || k >= p.K) continue;  // never store out of range
+            if (src < 0 || src >= p.R || t < 0 || t >= p.max_tokens || k < 0 || k >= p.K) {
+                // never store out of range: the row is dropped and the status word says which one it was
+                if (lane == 0) comb_record_status(p.status, CAM_ERR_BAD_INDEX, 1, i);
+                continue;
+            }
             const uint8_t* s = reinterpret_cast<const uint8_t*>(p.y) + static_cast<size_t>(i) * row_bytes;
             uint8_t* d = p.peer_base[src] + p.off_combine_buf +
                          (static_cast<size_t>(t) * p.K + k) * static_cast<size_t>(row_bytes);

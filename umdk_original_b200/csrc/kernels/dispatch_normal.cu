@@ -389,7 +389,10 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
             const int* ent = reinterpret_cast<const int*>(my_base + p.off_dup_list) +
                              ((static_cast<size_t>(parity) * R + s) * p.dup_cap + (i - s_dup_pre[s])) * 2;
             const int from = __ldcg(ent), to = __ldcg(ent + 1);
-            if (from < 0 || to < 0 || from >= p.capacity || to >= p.capacity) continue;  // never copy out of range
+            if (from < 0 || to < 0 || from >= p.capacity || to >= p.capacity) {  // never copy out of range
+                if (lane == 0) record_status(p.status, CAM_ERR_BAD_INDEX, 2, i);
+                continue;
+            }
             warp_copy_row<true>(rx + static_cast<size_t>(to) * row_bytes, rx + static_cast<size_t>(from) * row_bytes,
                                 row_bytes, lane);
             for (int o = static_cast<int>(lane); o < nscale; o += 32)

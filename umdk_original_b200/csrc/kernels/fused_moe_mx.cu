@@ -57,35 +57,33 @@ static_assert(128 * kFmCtrlRegs + 128 * kFmSfRegs + kFmEpiThreads * kFmEpiRegs <
 __device__ __forceinline__ uint32_t fm_ue8m0_word(float scale) {
     return ((__float_as_uint(scale) >> 23) & 0xFFu) * 0x01010101u;
 }
-__device__ __forceinline__ float ld_cg_f32(const float* p) {
+// Activation scales are read through L1 although other SMs or GPUs write them during this kernel.  That is safe here
+// because (1) a row of scales starts on a 128-byte line of its own (the row pitch is a multiple of 32 floats), (2) a row
+// is read only after the counter that says it is complete has been acquired, and never before (rows outside the tile's
+// valid range are not touched at all), and (3) L1 holds nothing from before the launch.  The asm is volatile so that
+// the compiler cannot move the load above the acquire.
+__device__ __forceinline__ float ld_ca_f32(const float* p) {
     float v;
-    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ float4 ld_cg_f32x4(const float* p) {
-    float4 v;
-    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    asm volatile("ld.global.ca.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
     return v;
 }
 
 // Order of the tiles of one launch.  Step j of the walk holds the first GEMM of expert j (while j < E_local) and
 // then the second GEMM of expert j - lag (once j >= lag).  `tile` must not decrease from call to call.
 struct FusedWalker {
-    const int* off;
-    int num_experts, nt1, nt2, lag;
-    int j, sub, base;
-    __device__ FusedWalker(const int* o, int ne, int n1, int n2, int lg)
-        : off(o), num_experts(ne), nt1(n1), nt2(n2), lag(lg), j(0), sub(0), base(0) {}
+    int j = 0, sub = 0, base = 0;  // everything else comes from the kernel parameters (constant bank, no registers)
     // kind 0 = first GEMM, 1 = second GEMM; cnt = rows of the expert.
-    __device__ bool locate(int tile, int& kind, int& e_out, int& mt, int& nt, int& row0, int& rows, int& cnt_out) {
+    __device__ __forceinline__ bool locate(const FusedMoeParams& p, int tile, int& kind, int& e_out, int& mt, int& nt,
+                                           int& row0, int& rows, int& cnt_out) {
+        const int num_experts = p.num_experts, lag = p.lag;
         while (j < num_experts + lag) {
             const int e = sub ? j - lag : j;
             const bool has = sub ? (j >= lag) : (j < num_experts);
             int first = 0, cnt = 0, tiles = 0;
-            const int per = sub ? nt2 : nt1;
+            const int per = sub ? (p.h + BN - 1) / BN : p.inter / 128;
             if (has) {
-                first = __ldg(off + e);
-                cnt = __ldg(off + e + 1) - first;
+                first = __ldg(p.expert_offsets + e);
+                cnt = __ldg(p.expert_offsets + e + 1) - first;
                 tiles = ((cnt + 2 * BM - 1) / (2 * BM)) * per;
             }
             if (tile < base + tiles) {
@@ -106,30 +104,31 @@ struct FusedWalker {
     }
 };
 
+// What a wait needs when it does not succeed at once.  One copy per CTA in shared memory, so that the roles (above all
+// the single threads that issue TMA loads and MMAs) hold one pointer instead of a dozen registers.
 struct FmWait {
-    volatile uint32_t* abort_flag;  // this CTA's
-    uint32_t partner_abort;         // cluster address of the partner's
+    volatile uint32_t abort_flag;   // raised by any role of this CTA (or of the partner CTA) that gave up
+    uint32_t partner_abort;         // cluster address of the partner's abort flag
     const volatile int* status_code;
     uint64_t timeout_ns;       // waits inside the pipeline (they sit behind waits for other GPUs: the longest budget)
     uint64_t arrival_ns;       // wait for another GPU's rows: the budget the caller set
     uint64_t gemm1_ns;         // wait for the first GEMM of a row block, which itself may wait for arrivals
 };
 
-__device__ __forceinline__ void fm_raise_abort(const FmWait& w) {
-    *w.abort_flag = 1u;
-    st_shared_cluster_u32(w.partner_abort, 1u);
+__device__ __forceinline__ void fm_raise_abort(FmWait* w) {
+    w->abort_flag = 1u;
+    st_shared_cluster_u32(w->partner_abort, 1u);
 }
 
 // mbarrier wait that also gives up when any CTA of the launch has recorded an error.
-__device__ __forceinline__ bool fm_mbar_wait(uint64_t* bar, uint32_t parity, const FmWait& w, uint32_t sleep_ns = 0u) {
-    if (mbar_try_wait(bar, parity)) return true;
+__device__ __forceinline__ bool fm_mbar_wait_slow(uint64_t* bar, uint32_t parity, FmWait* w, uint32_t sleep_ns) {
     const uint64_t t0 = globaltimer_ns();
     uint32_t polls = 0;
     while (!mbar_try_wait(bar, parity)) {
         if (sleep_ns) __nanosleep(sleep_ns);
         if ((++polls & 127u) == 0u) {
-            if (*w.abort_flag) return false;
-            if (*w.status_code != 0 || globaltimer_ns() - t0 > w.timeout_ns) {
+            if (w->abort_flag) return false;
+            if (*w->status_code != 0 || globaltimer_ns() - t0 > w->timeout_ns) {
                 fm_raise_abort(w);
                 return false;
             }
@@ -137,13 +136,18 @@ __device__ __forceinline__ bool fm_mbar_wait(uint64_t* bar, uint32_t parity, con
     }
     return true;
 }
+__device__ __forceinline__ bool fm_mbar_wait(uint64_t* bar, uint32_t parity, FmWait* w, uint32_t sleep_ns = 0u) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;  // try_wait itself blocks for a while: the common case ends here
+    return fm_mbar_wait_slow(bar, parity, w, sleep_ns);
+}
 
 // Spin until *ctr >= want.  SYS: the counter is written by other GPUs.  Called by single threads or whole warps.
 template <bool SYS>
-__device__ __forceinline__ bool fm_wait_counter(const uint32_t* ctr, uint32_t want, const FmWait& w, uint32_t& seen) {
-    const uint64_t budget = SYS ? w.arrival_ns : w.gemm1_ns;
+__device__ __forceinline__ bool fm_wait_counter(const uint32_t* ctr, uint32_t want, FmWait* w, uint32_t& seen) {
     seen = SYS ? ld_acquire_sys_u32(ctr) : ld_acquire_gpu_u32(ctr);
     if (seen >= want) return true;
+    const uint64_t budget = SYS ? w->arrival_ns : w->gemm1_ns;
     const uint64_t t0 = globaltimer_ns();
     uint32_t polls = 0;
     while (true) {
@@ -151,8 +155,8 @@ __device__ __forceinline__ bool fm_wait_counter(const uint32_t* ctr, uint32_t wa
         if (seen >= want) return true;
         __nanosleep(100);
         if ((++polls & 31u) == 0u) {
-            if (*w.abort_flag) return false;
-            if (*w.status_code != 0 || globaltimer_ns() - t0 > budget) return false;
+            if (w->abort_flag) return false;
+            if (*w->status_code != 0 || globaltimer_ns() - t0 > budget) return false;
         }
     }
 }
@@ -167,6 +171,7 @@ struct FmSendArgs {
     CamStatus* status;
     uint64_t off_recv_x, off_recv_scales, off_recv_src, off_arrival;  // off_arrival already points at this call's parity
     int h, rank, num_ranks, max_tokens, a_rows, drop, stride, nlist;
+    int scale_pitch;  // floats between the scale rows of the destination's receive buffer
 };
 
 // One warp sends rows of the list (its cursor advances by `stride`) until the list is exhausted or, when `bar`
@@ -214,7 +219,7 @@ __device__ __noinline__ void fm_send_rows(const FmSendArgs* args, FmSendState* s
                 if (o + q * 512 < a.h) st_na_v4(dst + o + q * 512, v[q]);
         }
         if (static_cast<int>(lane) < nsc16)
-            st_na_v4(pb + a.off_recv_scales + (static_cast<size_t>(row) * nsc16 + lane) * 16,
+            st_na_v4(pb + a.off_recv_scales + (static_cast<size_t>(row) * a.scale_pitch * 4) + lane * 16,
                      ld_nc_v4(reinterpret_cast<const uint8_t*>(a.xs) + (static_cast<size_t>(t) * nsc16 + lane) * 16));
         if (lane < 3u) {
             int* tri = reinterpret_cast<int*>(pb + a.off_recv_src) + static_cast<size_t>(row) * 3;
@@ -256,10 +261,11 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
     uint64_t* bar_tfull = bar_empty + kFmStages;
     uint64_t* bar_tempty = bar_tfull + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 1);
-    volatile uint32_t* abort_flag = tmem_slot + 1;
+    FmWait* wt = reinterpret_cast<FmWait*>(ctrl + 384);
     FmSendState* send_state = reinterpret_cast<FmSendState*>(ctrl + 512);  // [16 epilogue warps]
     FmSendArgs* send_args = reinterpret_cast<FmSendArgs*>(ctrl + 768);
-    static_assert(768 + sizeof(FmSendArgs) <= kFmSmemCtrl && 512 + 16 * sizeof(FmSendState) <= 768, "control area layout");
+    static_assert(768 + sizeof(FmSendArgs) <= kFmSmemCtrl && 512 + 16 * sizeof(FmSendState) <= 768 &&
+                      384 + sizeof(FmWait) <= 512 && (3 * kFmStages + 2) * 8 + 8 <= 384, "control area layout");
     float* s_amax = reinterpret_cast<float*>(stg);  // first-GEMM epilogue: [2 parities][4 column quarters][128 rows]
 
     const int warp = static_cast<int>(threadIdx.x) >> 5;
@@ -270,7 +276,7 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
     const bool do_send = (p.phase_mask & CAM_PHASE_SEND) != 0;
     const bool do_gemm = (p.phase_mask & CAM_PHASE_RECV) != 0;
     const int kb1 = p.h / BK, kb2 = p.inter / BK;
-    const int nt1 = p.inter / 128, nt2 = (p.h + BN - 1) / BN;
+    const int nt1 = p.inter / 128;
     const int nblk1 = 2 * p.inter / 128, nblk2 = p.h / 128;
     const uint32_t parity = *p.epoch_dispatch & 1u;  // the first launch of the layer has already advanced it
     const uint32_t* my_arrival = reinterpret_cast<const uint32_t*>(p.peer_base[p.rank] + p.off_arrival) +
@@ -284,7 +290,12 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
         }
         mbar_init(bar_tfull, 1);
         mbar_init(bar_tempty, 2 * (kFmEpiThreads / 32));
-        *abort_flag = 0u;
+        wt->abort_flag = 0u;
+        wt->partner_abort = map_to_cta(const_cast<uint32_t*>(&wt->abort_flag), cta ^ 1u);
+        wt->status_code = &p.status->code;
+        wt->arrival_ns = p.timeout_ns;
+        wt->gemm1_ns = p.timeout_ns + 1000000000ull;
+        wt->timeout_ns = p.timeout_ns + 2000000000ull;
         mbar_fence_init();
         if (blockIdx.x == 0 && p.trace != nullptr) p.trace[p.num_experts] = globaltimer_ns();
         FmSendArgs& sa = *send_args;
@@ -305,6 +316,7 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
         sa.drop = p.dbg_drop_flags;
         sa.stride = static_cast<int>(gridDim.x) * (kFmEpiThreads / 32);
         sa.nlist = do_send ? min(p.send_list_len[0], p.send_list_cap) : 0;
+        sa.scale_pitch = p.a1_scale_pitch;
     }
     if (do_gemm && warp == 1) {
         tmem_alloc_pair(tmem_slot, kFmTmemCols);
@@ -315,13 +327,6 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
     cluster_sync_all();  // both CTAs' barriers are initialised before anything signals them
     tc_fence_after_sync();
     const uint32_t tmem_base = do_gemm ? *tmem_slot : 0u;
-    FmWait wt;
-    wt.abort_flag = abort_flag;
-    wt.partner_abort = map_to_cta(const_cast<uint32_t*>(abort_flag), cta ^ 1u);
-    wt.status_code = &p.status->code;
-    wt.arrival_ns = p.timeout_ns;
-    wt.gemm1_ns = p.timeout_ns + 1000000000ull;
-    wt.timeout_ns = p.timeout_ns + 2000000000ull;
 
     if (warp < kFmSfWarp0) {
         reg_dealloc<kFmCtrlRegs>();
@@ -331,14 +336,12 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
             prefetch_tensormap(&tmap_b1);
             prefetch_tensormap(&tmap_a2);
             prefetch_tensormap(&tmap_b2);
-            FusedWalker w(p.expert_offsets, p.num_experts, nt1, nt2, p.lag);
+            FusedWalker w;
             uint32_t it = 0;
             int kind, e, mt, nt, row0, rows, cnt;
             int ready_e = -1, ready_blk = -1;
             bool ok = true;
-            for (int tile = pair_id; ok && w.locate(tile, kind, e, mt, nt, row0, rows, cnt); tile += num_pairs) {
-                const CUtensorMap* ta = kind ? &tmap_a2 : &tmap_a1;
-                const CUtensorMap* tb = kind ? &tmap_b2 : &tmap_b1;
+            for (int tile = pair_id; ok && w.locate(p, tile, kind, e, mt, nt, row0, rows, cnt); tile += num_pairs) {
                 const int kblocks = kind ? kb2 : kb1;
                 int brow_lo, brow_hi;
                 if (kind == 0) {
@@ -374,33 +377,47 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                 fence_proxy_async_all();  // rows written by other SMs / GPUs are read by TMA below
                 const int my_arow = row0 + static_cast<int>(cta) * BM;
                 const int my_brow = cta ? brow_hi : brow_lo;
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const uint32_t s = it % kFmStages, ph = (it / kFmStages) & 1u;
-                    if (!fm_mbar_wait(&bar_empty[s], ph ^ 1u, wt)) { ok = false; break; }
-                    uint8_t* sa = smem + s * kFmStageBytes;
-                    if (cta == 0) mbar_arrive_expect_tx(&bar_full[s], 2 * kFmStageBytes);
-                    const uint32_t full0 = map_to_cta(&bar_full[s], 0);
-                    tma_load_2d_pair(sa, ta, full0, kb * BK, my_arow);
-                    tma_load_2d_pair(sa + kFmATile, tb, full0, kb * BK, my_brow);
-                }
+                // the two GEMMs get their own copy of the loop, so that each TMA instruction names its descriptor by
+                // its fixed place among the kernel parameters instead of through a pointer chosen at run time
+                auto load_tile = [&](const CUtensorMap& ma, const CUtensorMap& mb) {
+                    for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                        const uint32_t s = it % kFmStages, ph = (it / kFmStages) & 1u;
+                        if (!fm_mbar_wait(&bar_empty[s], ph ^ 1u, wt)) { ok = false; break; }
+                        uint8_t* sa = smem + s * kFmStageBytes;
+                        if (cta == 0) mbar_arrive_expect_tx(&bar_full[s], 2 * kFmStageBytes);
+                        const uint32_t full0 = map_to_cta(&bar_full[s], 0);
+                        tma_load_2d_pair(sa, &ma, full0, kb * BK, my_arow);
+                        tma_load_2d_pair(sa + kFmATile, &mb, full0, kb * BK, my_brow);
+                    }
+                };
+                if (kind == 0) load_tile(tmap_a1, tmap_b1);
+                else load_tile(tmap_a2, tmap_b2);
             }
             if (!ok) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 0, static_cast<int>(it));
         } else if (warp == 1 && lane == 0 && cta == 0 && do_gemm) {
             // ------------------------------------------------------------ MMA issuer (first CTA only)
             constexpr uint32_t idesc = umma_idesc_mxf8(2 * BM, BN);
-            FusedWalker w(p.expert_offsets, p.num_experts, nt1, nt2, p.lag);
+            FusedWalker w;
             uint32_t it = 0, tcount = 0;
             int kind, e, mt, nt, row0, rows, cnt;
             bool ok = true;
             const uint32_t tfull0 = map_to_cta(bar_tfull, 0), tfull1 = map_to_cta(bar_tfull, 1);
-            for (int tile = pair_id; ok && w.locate(tile, kind, e, mt, nt, row0, rows, cnt); tile += num_pairs, ++tcount) {
+            // with tracing on, the first pair adds up what its MMA issuer waited for (clock cycles)
+            const bool prof = p.trace != nullptr && blockIdx.x == 0;
+            long long w_acc = 0, w_sf = 0, w_full = 0, w_issue = 0, t_begin = clock64();
+            for (int tile = pair_id; ok && w.locate(p, tile, kind, e, mt, nt, row0, rows, cnt); tile += num_pairs, ++tcount) {
                 const int kblocks = kind ? kb2 : kb1;
+                long long c0 = prof ? clock64() : 0;
                 if (!fm_mbar_wait(bar_tempty, (tcount & 1u) ^ 1u, wt)) { ok = false; break; }
+                if (prof) w_acc += clock64() - c0;
                 tc_fence_after_sync();
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const uint32_t s = it % kFmStages, ph = (it / kFmStages) & 1u;
+                    if (prof) c0 = clock64();
                     if (!fm_mbar_wait(&bar_sf[s], ph, wt)) { ok = false; break; }
+                    if (prof) { const long long c1 = clock64(); w_sf += c1 - c0; c0 = c1; }
                     if (!fm_mbar_wait(&bar_full[s], ph, wt)) { ok = false; break; }
+                    if (prof) { const long long c1 = clock64(); w_full += c1 - c0; c0 = c1; }
                     tc_fence_after_sync();
                     const uint32_t sa = smem_u32(smem + s * kFmStageBytes);
                     const uint64_t adesc = umma_desc_k_sw128(sa);
@@ -412,24 +429,35 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                         tc_mma_mxf8_pair(tmem_base, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) ? 1u : 0u, sfa, sfb);
                     tc_commit_pair(map_to_cta(&bar_empty[s], 0));
                     tc_commit_pair(map_to_cta(&bar_empty[s], 1));
+                    if (prof) w_issue += clock64() - c0;
                 }
                 if (!ok) break;
                 tc_commit_pair(tfull0);
                 tc_commit_pair(tfull1);
             }
             if (!ok) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 1, static_cast<int>(it));
+            if (prof) p.trace[p.num_experts + 7] = static_cast<unsigned long long>(w_issue);
+            if (prof) {
+                unsigned long long* t = p.trace + p.num_experts + 1;
+                t[0] = static_cast<unsigned long long>(clock64() - t_begin);  // the issuer's whole loop
+                t[1] = static_cast<unsigned long long>(w_acc);                // ... waiting for the accumulator to be drained
+                t[2] = static_cast<unsigned long long>(w_sf);                 // ... for scale factors
+                t[3] = static_cast<unsigned long long>(w_full);               // ... for operand tiles
+                t[4] = it;                                                    // K-blocks issued
+                t[5] = tcount;                                                // tiles
+            }
         }
     } else if (warp < kFmEpiWarp0) {
         reg_dealloc<kFmSfRegs>();
         // ---------------------------------------------------------------- scale-factor writers
         if (do_gemm) {
             const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-            FusedWalker w(p.expert_offsets, p.num_experts, nt1, nt2, p.lag);
+            FusedWalker w;
             uint32_t it = 0;
             int kind, e, mt, nt, row0, rows, cnt;
             int ready_e = -1, ready_blk = -1;
             bool ok = true;
-            for (int tile = pair_id; ok && w.locate(tile, kind, e, mt, nt, row0, rows, cnt); tile += num_pairs) {
+            for (int tile = pair_id; ok && w.locate(p, tile, kind, e, mt, nt, row0, rows, cnt); tile += num_pairs) {
                 const int kblocks = kind ? kb2 : kb1;
                 const float* a_scales = kind ? p.act_s : p.a1_scales;
                 // activation scales arrive during this kernel (from peers or from the first GEMM): wait like the
@@ -458,12 +486,14 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                         ready_blk = blk;
                     }
                 }
-                const float* as[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int r = min(row0 + static_cast<int>(cta) * BM + 32 * j + static_cast<int>(lane), p.a_rows - 1);
-                    as[j] = a_scales + static_cast<size_t>(r) * kblocks;
-                }
+                // row 32 j + lane of this CTA's half of the tile, clamped to the tile's last valid row: rows behind it
+                // may belong to an expert or row block that is not complete yet and must not be read (nor cached)
+                const int rbase = row0 + static_cast<int>(cta) * BM + static_cast<int>(lane);
+                const int rlast = min(row0 + rows, p.a_rows) - 1;
+                const int pitch = kind ? p.act_scale_pitch : p.a1_scale_pitch;
+                auto a_ptr = [&](int j, int kb) {
+                    return a_scales + static_cast<size_t>(min(rbase + 32 * j, rlast)) * pitch + kb;
+                };
                 int nb_lo, nb_hi, nblk;
                 const float* b_scales;
                 if (kind == 0) { nb_lo = nt; nb_hi = nblk1 / 2 + nt; nblk = nblk1; b_scales = p.b1_scales; }
@@ -491,34 +521,17 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                     ++it;
                     return true;
                 };
-                // The activation scales come from L2 (no L1: they were written during this kernel), about a
-                // microsecond away, while a K-block takes half of that: a lane fetches the scales of FOUR K-blocks of
-                // each of its rows with one 16-byte load, one group of four ahead of their use.  The weight scales are
-                // constant and hit in L1.
-                if ((kblocks & 3) == 0) {
-                    float4 cur[4], nxt[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) cur[j] = ld_cg_f32x4(as[j]);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) nxt[j] = (kblocks > 4) ? ld_cg_f32x4(as[j] + 4) : cur[j];
-                    for (int kb = 0; ok && kb < kblocks; kb += 4) {
-                        const float4 blo = __ldg(reinterpret_cast<const float4*>(bs_lo + kb));
-                        const float4 bhi = __ldg(reinterpret_cast<const float4*>(bs_hi + kb));
-                        ok = put(cur[0].x, cur[1].x, cur[2].x, cur[3].x, blo.x, bhi.x) &&
-                             put(cur[0].y, cur[1].y, cur[2].y, cur[3].y, blo.y, bhi.y) &&
-                             put(cur[0].z, cur[1].z, cur[2].z, cur[3].z, blo.z, bhi.z) &&
-                             put(cur[0].w, cur[1].w, cur[2].w, cur[3].w, blo.w, bhi.w);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) cur[j] = nxt[j];
-                        if (kb + 8 < kblocks) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) nxt[j] = ld_cg_f32x4(as[j] + kb + 8);
-                        }
-                    }
-                } else {
-                    for (int kb = 0; ok && kb < kblocks; ++kb)
-                        ok = put(ld_cg_f32(as[0] + kb), ld_cg_f32(as[1] + kb), ld_cg_f32(as[2] + kb), ld_cg_f32(as[3] + kb),
-                                 __ldg(bs_lo + kb), __ldg(bs_hi + kb));
+                // scales of K-block kb + 1 are requested while those of kb are written: they hit in L1 except once per
+                // 32 K-blocks and row, and the pipeline stages ahead of the MMA absorb that miss
+                float c0 = ld_ca_f32(a_ptr(0, 0)), c1 = ld_ca_f32(a_ptr(1, 0)), c2 = ld_ca_f32(a_ptr(2, 0)), c3 = ld_ca_f32(a_ptr(3, 0));
+                float c4 = __ldg(bs_lo), c5 = __ldg(bs_hi);
+                for (int kb = 0; ok && kb < kblocks; ++kb) {
+                    const int kn = min(kb + 1, kblocks - 1);
+                    const float n0 = ld_ca_f32(a_ptr(0, kn)), n1 = ld_ca_f32(a_ptr(1, kn)), n2 = ld_ca_f32(a_ptr(2, kn)),
+                                n3 = ld_ca_f32(a_ptr(3, kn));
+                    const float n4 = __ldg(bs_lo + kn), n5 = __ldg(bs_hi + kn);
+                    ok = put(c0, c1, c2, c3, c4, c5);
+                    c0 = n0; c1 = n1; c2 = n2; c3 = n3; c4 = n4; c5 = n5;
                 }
             }
             if (!ok && lane == 0) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 3, static_cast<int>(it));
@@ -545,11 +558,11 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
             const int q = warp & 3;   // TMEM lane quarter this warp may read
             const int cq = ew >> 2;   // which 32-column quarter of each 128-column half
             const int r = q * 32 + static_cast<int>(lane);
-            FusedWalker w(p.expert_offsets, p.num_experts, nt1, nt2, p.lag);
+            FusedWalker w;
             uint32_t tcount = 0;
             int kind, e, mt, nt, row0, rows, cnt;
             bool ok = true;
-            for (int tile = pair_id; ok && w.locate(tile, kind, e, mt, nt, row0, rows, cnt); tile += num_pairs, ++tcount) {
+            for (int tile = pair_id; ok && w.locate(p, tile, kind, e, mt, nt, row0, rows, cnt); tile += num_pairs, ++tcount) {
                 const int blk = fm_block_index(row0, e);
                 row0 += static_cast<int>(cta) * BM;            // this CTA's half of the 256-row tile
                 rows = max(0, min(BM, rows - static_cast<int>(cta) * BM));
@@ -604,7 +617,7 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                             o.w = pack_e4m3x4(act[j + 12] * inv, act[j + 13] * inv, act[j + 14] * inv, act[j + 15] * inv);
                             *reinterpret_cast<uint4*>(dst + j) = o;
                         }
-                        if (cq == 0) p.act_s[static_cast<size_t>(grow) * (p.inter / 128) + nt] = scale;
+                        if (cq == 0) p.act_s[static_cast<size_t>(grow) * p.act_scale_pitch + nt] = scale;
                     }
                     // this CTA's half of the tile is in memory: tell the second GEMM of this row block
                     named_bar_sync(1, kFmEpiThreads);

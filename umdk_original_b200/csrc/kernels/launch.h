@@ -145,11 +145,13 @@ struct FusedMoeParams {
     int h, inter;               // hidden size, intermediate size
     int a_rows;                 // rows of the receive buffer (capacity)
     int max_tokens;             // tokens per rank the combine slots are sized for
-    const float* a1_scales;     // [a_rows, h/128] scales of the received rows (arrive during the kernel)
+    const float* a1_scales;     // [a_rows, a1_scale_pitch] scales of the received rows (arrive during the kernel)
+    int a1_scale_pitch;         // floats per scale row: h/128 rounded up to 32, so that a row owns whole 128-byte lines
+    int act_scale_pitch;        // the same for act_s (I/128 rounded up to 32)
     const float* b1_scales;     // [E_local, 2I/128, h/128]
     const float* b2_scales;     // [E_local, h/128, I/128]
     uint8_t* act_q;             // [a_rows, I] e4m3, between the two GEMMs
-    float* act_s;               // [a_rows, I/128]
+    float* act_s;               // [a_rows, act_scale_pitch]
     const int* row_src;         // [a_rows, 3] (src rank, src token, src k) of every received row
     uint8_t* const* peer_base;
     uint64_t off_combine_buf, off_combine_flag, off_recv_x, off_recv_scales, off_recv_src, off_arrival;

@@ -169,10 +169,18 @@ extern "C" int cam_layout_compute_tp(CamLayout* L, int R, int E, int max_tokens,
     L->off_arrival = take(sizeof(uint32_t) * 2ull * E);
     const uint64_t ctrl_end = off;
     (void)ctrl_end;
-    L->off_recv_x = take(static_cast<uint64_t>(capacity) * hidden * 2);
-    L->off_recv_scales = take(static_cast<uint64_t>(capacity) * (hidden / 128) * 4);
-    L->off_recv_src = take(static_cast<uint64_t>(capacity) * 3 * 4);
-    L->off_combine_buf = take(static_cast<uint64_t>(max_tokens) * topk * hidden * 2);
+    // every region peers push rows into is followed, byte for byte, by a guard block
+    auto take_guarded = [&](uint64_t bytes, uint64_t* guard) {
+        uint64_t o = off;
+        *guard = align_up(off + bytes, 16);
+        off = align_up(*guard + CAM_GUARD_BYTES, 1024);
+        return o;
+    };
+    L->off_recv_x = take_guarded(static_cast<uint64_t>(capacity) * hidden * 2, &L->off_guard0);
+    // sized for scale rows padded to whole 128-byte lines (the fused layer's layout); the stand-alone ops pack them
+    L->off_recv_scales = take_guarded(static_cast<uint64_t>(capacity) * align_up(hidden / 128, 32) * 4, &L->off_guard1);
+    L->off_recv_src = take_guarded(static_cast<uint64_t>(capacity) * 3 * 4, &L->off_guard2);
+    L->off_combine_buf = take_guarded(static_cast<uint64_t>(max_tokens) * topk * hidden * 2, &L->off_guard3);
     L->off_dup_list = take(2ull * R * static_cast<uint64_t>(max_tokens) * topk * 8);
     if (tp_rows > 0) {
         L->off_tp_x = take(static_cast<uint64_t>(tp_rows) * hidden * 2);
@@ -226,6 +234,8 @@ extern "C" CamBuffer* cam_buffer_create(int device, int rank, int num_ranks, con
     }
     // control words (everything before recv_x) start at zero
     cudaMemset(b->base, 0, layout->off_recv_x);
+    for (uint64_t g : {layout->off_guard0, layout->off_guard1, layout->off_guard2, layout->off_guard3})
+        cudaMemset(b->base + g, 0xA5, CAM_GUARD_BYTES);
     b->peer_ptr.assign(R, nullptr);
     b->peer_is_ipc.assign(R, false);
     b->peer_ptr[rank] = b->base;
@@ -249,7 +259,7 @@ extern "C" CamBuffer* cam_buffer_create(int device, int rank, int num_ranks, con
     ok &= cudaMalloc(&b->d_status, sizeof(CamStatus)) == cudaSuccess;
     ok &= cudaMallocHost(&b->h_status, sizeof(CamStatus)) == cudaSuccess;
     ok &= cudaMalloc(&b->act_q, static_cast<size_t>(layout->capacity) * layout->hidden) == cudaSuccess;
-    ok &= cudaMalloc(&b->act_s, static_cast<size_t>(layout->capacity) * (layout->hidden / 128) * 4) == cudaSuccess;
+    ok &= cudaMalloc(&b->act_s, static_cast<size_t>(layout->capacity) * align_up(layout->hidden / 128, 32) * 4) == cudaSuccess;
     if (!ok) {
         fail("buffer_create: workspace allocation failed: %s", cudaGetErrorString(cudaGetLastError()));
         cam_buffer_destroy(b);
@@ -388,7 +398,7 @@ extern "C" int cam_buffer_read_trace(CamBuffer* b, unsigned long long* out16) {
 extern "C" int cam_buffer_set_fused_trace(CamBuffer* b, int on) {
     CAM_CHECK(b != nullptr, "set_fused_trace: null buffer");
     CAM_CUDA(cudaSetDevice(b->device));
-    const size_t bytes = sizeof(unsigned long long) * (b->layout.num_experts + 1);
+    const size_t bytes = sizeof(unsigned long long) * (b->layout.num_experts + 8);
     if (on && b->fused_trace == nullptr) {
         CAM_CUDA(cudaMalloc(&b->fused_trace, bytes));
         CAM_CUDA(cudaMemset(b->fused_trace, 0, bytes));
@@ -411,6 +421,15 @@ extern "C" int cam_buffer_read_fused_trace(CamBuffer* b, long long* out, int num
         out[e] = t[e] == 0ull ? -1ll : static_cast<long long>(t[e] - t0);
     return 0;
 }
+// What the MMA issuer of the first CTA pair waited for during the last traced fused kernel, in clock cycles:
+// {whole loop, accumulator drained, scale factors, operand tiles, K-blocks issued, tiles}.
+extern "C" int cam_buffer_read_fused_waits(CamBuffer* b, long long* out6, int num_local_experts) {
+    CAM_CHECK(b != nullptr && out6 != nullptr && b->fused_trace != nullptr, "read_fused_waits: tracing is off");
+    CAM_CUDA(cudaSetDevice(b->device));
+    CAM_CUDA(cudaDeviceSynchronize());
+    CAM_CUDA(cudaMemcpy(out6, b->fused_trace + num_local_experts + 1, sizeof(long long) * 7, cudaMemcpyDeviceToHost));
+    return 0;
+}
 extern "C" int cam_buffer_set_profile(CamBuffer* b, int on) {
     CAM_CHECK(b != nullptr, "set_profile: null buffer");
     CAM_CUDA(cudaSetDevice(b->device));
@@ -431,6 +450,29 @@ extern "C" int cam_buffer_read_profile(CamBuffer* b, float* ms4) {
 extern "C" void cam_buffer_set_debug_drop_flags(CamBuffer* b, int on) {
     if (b != nullptr) b->dbg_drop_flags = on ? 1 : 0;
 }
+// Guard blocks behind the receive regions: *damaged gets one bit per guard (0: recv_x, 1: recv_scales, 2: recv_src,
+// 3: combine_buf) whose bytes are no longer 0xA5, i.e. something wrote past the end of that region.  Synchronises
+// `stream`.  Damaged guards are restored, so one overrun is reported once.
+extern "C" int cam_buffer_check_guards(CamBuffer* b, cudaStream_t stream, int* damaged) {
+    CAM_CHECK(b != nullptr && damaged != nullptr, "check_guards: null argument");
+    CAM_CUDA(cudaSetDevice(b->device));
+    const uint64_t offs[4] = {b->layout.off_guard0, b->layout.off_guard1, b->layout.off_guard2, b->layout.off_guard3};
+    unsigned char host[4][CAM_GUARD_BYTES];
+    for (int i = 0; i < 4; ++i)
+        CAM_CUDA(cudaMemcpyAsync(host[i], b->base + offs[i], CAM_GUARD_BYTES, cudaMemcpyDeviceToHost, stream));
+    CAM_CUDA(cudaStreamSynchronize(stream));
+    *damaged = 0;
+    for (int i = 0; i < 4; ++i)
+        for (int j = 0; j < CAM_GUARD_BYTES; ++j)
+            if (host[i][j] != 0xA5) {
+                *damaged |= 1 << i;
+                break;
+            }
+    for (int i = 0; i < 4; ++i)
+        if (*damaged & (1 << i)) CAM_CUDA(cudaMemsetAsync(b->base + offs[i], 0xA5, CAM_GUARD_BYTES, stream));
+    return 0;
+}
+
 extern "C" unsigned long long cam_buffer_launch_count(CamBuffer* b) { return b ? b->launches : 0ull; }
 extern "C" int* cam_buffer_recv_count(CamBuffer* b) { return b->recv_count; }
 extern "C" int* cam_buffer_expert_offsets(CamBuffer* b) { return b->expert_offsets; }
@@ -1134,6 +1176,8 @@ static int fused_moe_deep(CamBuffer* b, const void* x, const void* expert_ids, i
         p.a_rows = L.capacity;
         p.max_tokens = L.max_tokens;
         p.a1_scales = reinterpret_cast<const float*>(b->base + L.off_recv_scales);
+        p.a1_scale_pitch = static_cast<int>(align_up(h / 128, 32));
+        p.act_scale_pitch = static_cast<int>(align_up(inter / 128, 32));
         p.b1_scales = w1_s;
         p.b2_scales = w2_s;
         p.act_q = b->act_q;
@@ -1173,7 +1217,7 @@ static int fused_moe_deep(CamBuffer* b, const void* x, const void* expert_ids, i
         p.timeout_ns = b->timeout_ns;
         p.trace = b->fused_trace;
         if (b->fused_trace != nullptr && (fmask & CAM_PHASE_RECV))
-            CAM_CUDA(cudaMemsetAsync(b->fused_trace, 0, sizeof(unsigned long long) * (L.num_experts + 1), stream));
+            CAM_CUDA(cudaMemsetAsync(b->fused_trace, 0, sizeof(unsigned long long) * (L.num_experts + 8), stream));
         const int rc = cam_launch_fused_moe(&p, &ta1, &tb1, &ta2, &tb2, b->num_sms, stream);
         CAM_CHECK(rc == 0, "fused_moe launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
     if (b != nullptr) ++b->launches;

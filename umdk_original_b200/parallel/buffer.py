@@ -152,12 +152,21 @@ class Buffer:
     def cpu_group(self) -> Optional[CpuGroup]:
         return self._cpu
 
-    def check(self) -> None:
-        """Synchronises the current stream, reads the device status word and raises on an error."""
+    GUARDED_REGIONS = ("recv_x", "recv_scales", "recv_src", "combine_buf")
+
+    def check(self, guards: bool = False) -> None:
+        """Synchronises the current stream, reads the device status word and raises on an error.  With ``guards``
+        it also reads the guard words that sit directly behind the four regions peers write rows into and raises
+        ``CamError`` (code 8) naming every region something has written past."""
         if self._native is None:
             return
         code, who, detail, block, text = self._native.poll_status()
         raise_for_status(code, who, detail, block, text)
+        if guards:
+            damaged = int(self._native.check_guards())
+            if damaged:
+                names = [n for i, n in enumerate(self.GUARDED_REGIONS) if damaged & (1 << i)]
+                raise_for_status(8, -1, damaged, -1, "guard words overwritten behind " + ", ".join(names))
 
     def reset(self) -> None:
         """Zeroes flags and epochs after an error (every surviving rank must call it).  Handles and
@@ -230,6 +239,14 @@ class Buffer:
         released; ``None`` for an expert that never was (its rows did not all arrive).  Synchronises the device."""
         n = num_local_experts or self.config.num_experts // self.num_ranks
         return [None if v < 0 else v / 1e3 for v in self._native.read_fused_trace(n)]
+
+    def read_fused_waits(self, num_local_experts: Optional[int] = None) -> dict:
+        """What the MMA-issuing thread of the first CTA pair waited for in the last traced fused kernel (clock
+        cycles): the whole loop, and inside it the waits for a drained accumulator, for scale factors and for
+        operand tiles; also the K-blocks and tiles it issued.  Tells which producer limits the tensor cores."""
+        n = num_local_experts or self.config.num_experts // self.num_ranks
+        v = self._native.read_fused_waits(n)
+        return dict(zip(("loop_cycles", "wait_accumulator", "wait_scale_factors", "wait_operands", "k_blocks", "tiles", "issue_cycles"), v))
 
     def set_profile(self, on: bool = True) -> None:
         """Per-stage device timing of ``fused_deep_moe`` (CUDA events around its four launches)."""

@@ -110,9 +110,10 @@ struct FmWait {
     volatile uint32_t abort_flag;   // raised by any role of this CTA (or of the partner CTA) that gave up
     uint32_t partner_abort;         // cluster address of the partner's abort flag
     const volatile int* status_code;
-    uint64_t timeout_ns;       // waits inside the pipeline (they sit behind waits for other GPUs: the longest budget)
-    uint64_t arrival_ns;       // wait for another GPU's rows: the budget the caller set
-    uint64_t gemm1_ns;         // wait for the first GEMM of a row block, which itself may wait for arrivals
+    // absolute times (globaltimer) at which the waits of this launch give up
+    uint64_t deadline_arrival;  // for another GPU's rows: launch + the budget the caller set
+    uint64_t deadline_gemm1;    // for the first GEMM of a row block, which itself may wait for arrivals: a second later
+    uint64_t deadline_pipe;     // inside the pipeline, behind both: another second later
 };
 
 __device__ __forceinline__ void fm_raise_abort(FmWait* w) {
@@ -121,25 +122,33 @@ __device__ __forceinline__ void fm_raise_abort(FmWait* w) {
 }
 
 // mbarrier wait that also gives up when any CTA of the launch has recorded an error.
-__device__ __forceinline__ bool fm_mbar_wait_slow(uint64_t* bar, uint32_t parity, FmWait* w, uint32_t sleep_ns) {
-    const uint64_t t0 = globaltimer_ns();
-    uint32_t polls = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if (sleep_ns) __nanosleep(sleep_ns);
-        if ((++polls & 127u) == 0u) {
-            if (w->abort_flag) return false;
-            if (*w->status_code != 0 || globaltimer_ns() - t0 > w->timeout_ns) {
-                fm_raise_abort(w);
-                return false;
-            }
-        }
+// A wait first tries once.  The loop behind it is kept to a handful of instructions (the loop bodies of the producer,
+// the MMA issuer and the scale-factor writers share a scheduler's instruction cache): every 4096 unsuccessful tries it
+// looks at the abort flag, at the status word of the launch and at the deadline.
+__device__ __forceinline__ bool fm_give_up(FmWait* w, uint64_t deadline) {
+    if (w->abort_flag) return true;
+    if (*w->status_code != 0 || globaltimer_ns() > deadline) {
+        fm_raise_abort(w);
+        return true;
     }
+    return false;
+}
+__device__ __forceinline__ bool fm_mbar_wait(uint64_t* bar, uint32_t parity, FmWait* w) {
+    if (mbar_try_wait(bar, parity)) return true;
+    uint32_t polls = 0;
+    while (!mbar_try_wait(bar, parity))
+        if ((++polls & 4095u) == 0u && fm_give_up(w, w->deadline_pipe)) return false;
     return true;
 }
-__device__ __forceinline__ bool fm_mbar_wait(uint64_t* bar, uint32_t parity, FmWait* w, uint32_t sleep_ns = 0u) {
+// for the epilogue warps, which wait a whole tile: sleeps between tries
+__device__ __forceinline__ bool fm_mbar_wait_sleep(uint64_t* bar, uint32_t parity, FmWait* w) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (mbar_try_wait(bar, parity)) return true;  // try_wait itself blocks for a while: the common case ends here
-    return fm_mbar_wait_slow(bar, parity, w, sleep_ns);
+    uint32_t polls = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(256);
+        if ((++polls & 255u) == 0u && fm_give_up(w, w->deadline_pipe)) return false;
+    }
+    return true;
 }
 
 // Spin until *ctr >= want.  SYS: the counter is written by other GPUs.  Called by single threads or whole warps.
@@ -147,8 +156,7 @@ template <bool SYS>
 __device__ __forceinline__ bool fm_wait_counter(const uint32_t* ctr, uint32_t want, FmWait* w, uint32_t& seen) {
     seen = SYS ? ld_acquire_sys_u32(ctr) : ld_acquire_gpu_u32(ctr);
     if (seen >= want) return true;
-    const uint64_t budget = SYS ? w->arrival_ns : w->gemm1_ns;
-    const uint64_t t0 = globaltimer_ns();
+    const uint64_t deadline = SYS ? w->deadline_arrival : w->deadline_gemm1;
     uint32_t polls = 0;
     while (true) {
         seen = SYS ? ld_acquire_sys_u32(ctr) : ld_acquire_gpu_u32(ctr);
@@ -156,7 +164,7 @@ __device__ __forceinline__ bool fm_wait_counter(const uint32_t* ctr, uint32_t wa
         __nanosleep(100);
         if ((++polls & 31u) == 0u) {
             if (w->abort_flag) return false;
-            if (*w->status_code != 0 || globaltimer_ns() - t0 > budget) return false;
+            if (*w->status_code != 0 || globaltimer_ns() > deadline) return false;
         }
     }
 }
@@ -293,9 +301,9 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
         wt->abort_flag = 0u;
         wt->partner_abort = map_to_cta(const_cast<uint32_t*>(&wt->abort_flag), cta ^ 1u);
         wt->status_code = &p.status->code;
-        wt->arrival_ns = p.timeout_ns;
-        wt->gemm1_ns = p.timeout_ns + 1000000000ull;
-        wt->timeout_ns = p.timeout_ns + 2000000000ull;
+        wt->deadline_arrival = globaltimer_ns() + p.timeout_ns;
+        wt->deadline_gemm1 = wt->deadline_arrival + 1000000000ull;
+        wt->deadline_pipe = wt->deadline_arrival + 2000000000ull;
         mbar_fence_init();
         if (blockIdx.x == 0 && p.trace != nullptr) p.trace[p.num_experts] = globaltimer_ns();
         FmSendArgs& sa = *send_args;
@@ -491,9 +499,10 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                 const int rbase = row0 + static_cast<int>(cta) * BM + static_cast<int>(lane);
                 const int rlast = min(row0 + rows, p.a_rows) - 1;
                 const int pitch = kind ? p.act_scale_pitch : p.a1_scale_pitch;
-                auto a_ptr = [&](int j, int kb) {
-                    return a_scales + static_cast<size_t>(min(rbase + 32 * j, rlast)) * pitch + kb;
-                };
+                const float* ap0 = a_scales + static_cast<size_t>(min(rbase, rlast)) * pitch;
+                const float* ap1 = a_scales + static_cast<size_t>(min(rbase + 32, rlast)) * pitch;
+                const float* ap2 = a_scales + static_cast<size_t>(min(rbase + 64, rlast)) * pitch;
+                const float* ap3 = a_scales + static_cast<size_t>(min(rbase + 96, rlast)) * pitch;
                 int nb_lo, nb_hi, nblk;
                 const float* b_scales;
                 if (kind == 0) { nb_lo = nt; nb_hi = nblk1 / 2 + nt; nblk = nblk1; b_scales = p.b1_scales; }
@@ -523,12 +532,11 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                 };
                 // scales of K-block kb + 1 are requested while those of kb are written: they hit in L1 except once per
                 // 32 K-blocks and row, and the pipeline stages ahead of the MMA absorb that miss
-                float c0 = ld_ca_f32(a_ptr(0, 0)), c1 = ld_ca_f32(a_ptr(1, 0)), c2 = ld_ca_f32(a_ptr(2, 0)), c3 = ld_ca_f32(a_ptr(3, 0));
+                float c0 = ld_ca_f32(ap0), c1 = ld_ca_f32(ap1), c2 = ld_ca_f32(ap2), c3 = ld_ca_f32(ap3);
                 float c4 = __ldg(bs_lo), c5 = __ldg(bs_hi);
                 for (int kb = 0; ok && kb < kblocks; ++kb) {
                     const int kn = min(kb + 1, kblocks - 1);
-                    const float n0 = ld_ca_f32(a_ptr(0, kn)), n1 = ld_ca_f32(a_ptr(1, kn)), n2 = ld_ca_f32(a_ptr(2, kn)),
-                                n3 = ld_ca_f32(a_ptr(3, kn));
+                    const float n0 = ld_ca_f32(ap0 + kn), n1 = ld_ca_f32(ap1 + kn), n2 = ld_ca_f32(ap2 + kn), n3 = ld_ca_f32(ap3 + kn);
                     const float n4 = __ldg(bs_lo + kn), n5 = __ldg(bs_hi + kn);
                     ok = put(c0, c1, c2, c3, c4, c5);
                     c0 = n0; c1 = n1; c2 = n2; c3 = n3; c4 = n4; c5 = n5;
@@ -571,7 +579,7 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                 if (sst->ci < sa.nlist) fm_send_rows(send_args, sst, bar_tfull, tcount & 1u);  // nothing to drain yet: send rows
                 // one decision for all epilogue threads: a thread that gave up must not leave the others at a
                 // named barrier further down
-                if (!named_bar_and(1, kFmEpiThreads, fm_mbar_wait(bar_tfull, tcount & 1u, wt, 256u))) { ok = false; break; }
+                if (!named_bar_and(1, kFmEpiThreads, fm_mbar_wait_sleep(bar_tfull, tcount & 1u, wt))) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t t0 = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + cq * 32;
                 uint32_t v0[32], v1[32];

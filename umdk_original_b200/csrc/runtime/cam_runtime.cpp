@@ -1237,13 +1237,14 @@ static int fused_moe_deep(CamBuffer* b, const void* x, const void* expert_ids, i
     return 0;
 }
 
-// Whether the deep-fused route serves this call: block-scaled fp8 with power-of-two scales, experts large enough for
-// 256-row tiles (or UMDK_CAM_DEEP_FUSE=1), rows the copy warps can stage.  UMDK_CAM_DEEP_FUSE=0 keeps the four launches.
+// Whether the deep-fused route serves this call.  It is opt-in (UMDK_CAM_DEEP_FUSE=1, read when the Buffer is created):
+// measured on one and two B200s the single kernel is slower than the four launches, because its tensor-core pipeline
+// runs at a lower duty than the stand-alone CTA-pair GEMMs (see the fused kernel's wait breakdown, Buffer.read_fused_waits).
+// Needs block-scaled fp8 with power-of-two scales and hidden sizes whose scale rows are whole 16-byte pieces.
 static bool use_deep_fuse(const CamBuffer* b, bool ue8m0, int h, int inter, int rows_hint) {
-    if (!ue8m0 || b->env_deep_fuse == 0) return false;
-    if (h % 512 != 0 || h > 7168 || inter % 128 != 0) return false;
-    if (b->env_deep_fuse == 1) return true;
-    return rows_hint >= 384;
+    (void)rows_hint;
+    if (!ue8m0 || b->env_deep_fuse != 1) return false;
+    return h % 512 == 0 && h <= 7168 && inter % 128 == 0;
 }
 
 static int fused_moe_impl(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,

@@ -4,8 +4,9 @@
 the C runtime into ``umdk_original_b200/lib/libumdk_cam.so`` and the PyTorch bindings into
 ``umdk_original_b200/_C*.so`` with ``umdk_original_b200._build`` (nvcc, sm_100a only) and packs both
 next to the Python sources.  The role of the reference's ``pybind/setup.py:55-106`` and its custom
-``bdist_wheel`` (``pybind/pytorch_extension/bdist_wheel_build.py``); ``UMDK_CAM_DEBUG=1`` builds
-with ``-O0 -g`` and the device-side index checks, like the reference's ``BUILD_TYPE=Debug``.
+``bdist_wheel`` (``pybind/pytorch_extension/bdist_wheel_build.py``); ``UMDK_CAM_DEBUG=1`` builds the
+host code with ``-O0 -g``, like the reference's ``BUILD_TYPE=Debug`` (the device-side range checks are in
+every build).
 """
 import importlib.util
 import os

@@ -473,3 +473,40 @@ def test_dispatch_outputs_are_views_until_the_next_dispatch_or_copies_on_request
     # a view that outlives destroy() keeps the memory mapped: reading it afterwards is still defined
     buf.destroy()
     assert torch.equal(b[0], d[0])
+
+
+def test_stats_name_rows_per_peer_and_waits_and_guards_catch_an_overrun():
+    """Buffer.stats(): pairs routed to every peer and the longest wait per peer; Buffer.check(guards=True): the guard
+    words behind the receive regions are intact after normal use and an overwritten one is reported by name."""
+    world, t, h, e, k = 2, 40, 256, 8, 2
+    xs, topk, wts = _inputs(world, t, h, e, k, seed=123, lo=0)
+    cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, timeout_ms=2000.0)
+    bufs = u.Buffer.virtual(world, cfg, _dev(), name="stats_")
+    dx, dk, dw = ([v.to(_dev()) for v in part] for part in (xs, topk, wts))
+
+    def disp(r):
+        return ops.moe_dispatch_prefill_quant(dx[r], dk[r], dw[r], 0, bufs[r].name, r, world, 0)
+
+    res = run_virtual(disp, world, masks=(PHASE_COUNT, PHASE_SEND, PHASE_RECV))
+
+    def comb(r):
+        rx, src, cnt, per_e, rs = res[r]
+        return ops.moe_combine_prefill(rx.clone(), dk[r], dw[r], src, cnt, bufs[r].name, r, world)
+
+    run_virtual(comb, world, masks=(PHASE_SEND, PHASE_RECV))
+    el = e // world
+    for r in range(world):
+        bufs[r].check(guards=True)
+        st = bufs[r].stats()
+        want = [int(((topk[r] // el) == d).sum()) for d in range(world)]
+        assert st["rows_routed_to_peer"] == want and st["dispatch_calls"] == 1 and st["combine_calls"] == 1
+        assert all(len(v) == world for v in st["max_wait_us"].values())
+        assert st["kernel_launches"] >= 5          # three dispatch phases, two combine phases
+        assert bufs[r].stats(reset=True)["dispatch_calls"] == 1 and bufs[r].stats()["dispatch_calls"] == 0
+    bufs[0].native.guard(2).zero_()                # as if something had written past the end of recv_src
+    with pytest.raises(u.CamError) as ei:
+        bufs[0].check(guards=True)
+    assert ei.value.code == 8 and "recv_src" in str(ei.value)
+    bufs[0].check(guards=True)                     # reported once, then restored
+    for b in bufs:
+        b.destroy()

@@ -117,6 +117,13 @@ public:
                                        initiator ? 1 : 0, stream()));
     }
     void set_trace(bool on) { CAM_RT(cam_buffer_set_trace(buf_, on ? 1 : 0)); }
+    std::tuple<std::vector<int64_t>, std::vector<int64_t>, std::vector<int64_t>> read_stats(bool reset) {
+        const int R = cam_buffer_num_ranks(buf_);
+        std::vector<unsigned long long> w(3 * R), rows(R), calls(2);
+        CAM_RT(cam_buffer_read_stats(buf_, w.data(), rows.data(), calls.data(), reset ? 1 : 0));
+        return {std::vector<int64_t>(w.begin(), w.end()), std::vector<int64_t>(rows.begin(), rows.end()),
+                std::vector<int64_t>(calls.begin(), calls.end())};
+    }
     int64_t check_guards() {
         int damaged = 0;
         CAM_RT(cam_buffer_check_guards(buf_, stream(), &damaged));
@@ -981,6 +988,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("set_trace", &Buffer::set_trace)
         .def("read_trace", &Buffer::read_trace)
         .def("launch_count", &Buffer::launch_count)
+        .def("read_stats", &Buffer::read_stats)
         .def("check_guards", &Buffer::check_guards)
         .def("guard", &Buffer::guard)
         .def("set_fused_trace", &Buffer::set_fused_trace)

@@ -147,10 +147,16 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineP
         uint8_t* const my_base = p.peer_base[p.rank];
         if (tid < p.R) {
             const uint32_t* f = reinterpret_cast<const uint32_t*>(my_base + p.off_combine_flag) + tid;
+            const bool keep = blockIdx.x == 0 && p.stats != nullptr;
+            const uint64_t t_wait = keep ? globaltimer_ns() : 0ull;
             if (!wait_flag_eq_sys(f, ep_recv, p.timeout_ns)) {
                 comb_record_status(p.status, CAM_ERR_TIMEOUT_COMBINE_FLAG, tid,
                                    static_cast<int>(ld_acquire_sys_u32(f)));
                 s_abort = 1u;
+            }
+            if (keep) {
+                atomicMax(&p.stats->max_wait_ns[2][tid], globaltimer_ns() - t_wait);
+                if (tid == 0) atomicAdd(&p.stats->calls[1], 1ull);
             }
         }
         __syncthreads();

@@ -136,10 +136,12 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
         const int parity = static_cast<int>(ep_send & 1u);
         if (tid < R) {
             const uint32_t* f = reinterpret_cast<const uint32_t*>(my_base + p.off_count_flag) + tid;
+            const uint64_t t_wait = (b == 0 && p.stats != nullptr) ? globaltimer_ns() : 0ull;
             if (!wait_flag_eq_sys(f, ep_send, p.timeout_ns)) {
                 record_status(p.status, CAM_ERR_TIMEOUT_COUNT_FLAG, tid, static_cast<int>(ld_acquire_sys_u32(f)));
                 s_abort = 1u;
             }
+            if (b == 0 && p.stats != nullptr) atomicMax(&p.stats->max_wait_ns[0][tid], globaltimer_ns() - t_wait);
         }
         __syncthreads();
         if (s_abort) goto done;  // no grid-wide sync follows, so leaving here cannot strand another CTA
@@ -165,6 +167,12 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
             for (int l = 0; l < El; ++l) tot += s_tot[d * El + l];
             s_rank_ok[d] = (tot <= p.capacity) ? 1 : 0;
             if (tot > p.capacity) record_status(p.status, CAM_ERR_RECV_OVERFLOW, d, tot);
+            if (b == 0 && p.stats != nullptr) {
+                int mine = 0;
+                for (int l = 0; l < El; ++l) mine += __ldcg(&cm[static_cast<size_t>(p.rank) * E + d * El + l]);
+                atomicAdd(&p.stats->rows_routed[d], static_cast<unsigned long long>(mine));
+                if (d == 0) atomicAdd(&p.stats->calls[0], 1ull);
+            }
         }
         __syncthreads();
         // Receiver-side bookkeeping for this rank's own experts (one CTA is enough).  When more rows are routed
@@ -358,10 +366,12 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
         const int parity = static_cast<int>(ep_recv & 1u);
         if (tid < R) {
             const uint32_t* f = reinterpret_cast<const uint32_t*>(my_base + p.off_data_flag) + tid;
+            const uint64_t t_wait = (b == 0 && p.stats != nullptr) ? globaltimer_ns() : 0ull;
             if (!wait_flag_eq_sys(f, ep_recv, p.timeout_ns)) {
                 record_status(p.status, CAM_ERR_TIMEOUT_DATA_FLAG, tid, static_cast<int>(ld_acquire_sys_u32(f)));
                 s_abort = 1u;
             }
+            if (b == 0 && p.stats != nullptr) atomicMax(&p.stats->max_wait_ns[1][tid], globaltimer_ns() - t_wait);
         }
         __syncthreads();
         if (s_abort) goto done;

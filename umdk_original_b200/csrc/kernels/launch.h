@@ -10,6 +10,14 @@
 
 namespace cam {
 
+// Per-buffer statistics kept on the device (Buffer.stats()): which peer this rank waited for longest, and how many rows
+// it routed to every peer.  Written by CTA 0 of the comm kernels; never reset by the kernels.
+struct CamStatsDev {
+    unsigned long long max_wait_ns[3][CAM_MAX_RANKS];  // [0] dispatch counts, [1] dispatch rows, [2] combine rows; per peer
+    unsigned long long rows_routed[CAM_MAX_RANKS];     // (token, k) pairs routed to every rank since the last reset
+    unsigned long long calls[3];                       // dispatches, combines (reduce side), spare
+};
+
 struct DispatchNormalParams {
     const __nv_bfloat16* x;  // [T, h]
     const void* topk_idx;    // [T, K] int64 or int32, ids outside [0, E) are skipped
@@ -42,6 +50,7 @@ struct DispatchNormalParams {
     // Deferred push (the fused layer's first launch): the SEND phase pushes nothing.  It quantises every token once
     // into local memory and writes the list of rows to send, ordered by (local expert at the destination, destination
     // rank, scan order), so that the fused kernel's copy warps complete expert 0 of every rank first, then expert 1, ...
+    CamStatsDev* stats;             // optional
     int defer_push;
     uint8_t* xq;                    // [T, h] e4m3
     float* xs;                      // [T, h/128]
@@ -73,6 +82,7 @@ struct CombineParams {
     uint64_t off_combine_buf, off_combine_flag;
     unsigned int* done_ctr;
     CamStatus* status;
+    CamStatsDev* stats;  // optional
 };
 
 struct DispatchLLParams {

@@ -98,6 +98,7 @@ struct CamBuffer {
     int g1_done_len = 0;
     unsigned long long* fused_trace = nullptr;  // [E + 1], null = off
     unsigned long long launches = 0;            // kernels this buffer's ops have launched (host-side count)
+    cam::CamStatsDev* d_stats = nullptr;        // per-peer waits and routed rows (normal-mode ops)
     // switches read from the environment once, when the buffer is created (UMDK_CAM_GEMM_*, UMDK_CAM_DEEP_FUSE):
     // -1 = not set (the runtime decides), 0 / 1 = forced
     int env_bulk_push = -1, env_pair = -1, env_swap = -1, env_staging2 = -1, env_deep_fuse = -1, env_fuse_lag = -1;
@@ -258,6 +259,7 @@ extern "C" CamBuffer* cam_buffer_create(int device, int rank, int num_ranks, con
     ok &= cudaMalloc(&b->exit_ctr, sizeof(unsigned int) * 4) == cudaSuccess;
     ok &= cudaMalloc(&b->d_status, sizeof(CamStatus)) == cudaSuccess;
     ok &= cudaMallocHost(&b->h_status, sizeof(CamStatus)) == cudaSuccess;
+    ok &= cudaMalloc(&b->d_stats, sizeof(cam::CamStatsDev)) == cudaSuccess;
     ok &= cudaMalloc(&b->act_q, static_cast<size_t>(layout->capacity) * layout->hidden) == cudaSuccess;
     ok &= cudaMalloc(&b->act_s, static_cast<size_t>(layout->capacity) * align_up(layout->hidden / 128, 32) * 4) == cudaSuccess;
     if (!ok) {
@@ -265,6 +267,7 @@ extern "C" CamBuffer* cam_buffer_create(int device, int rank, int num_ranks, con
         cam_buffer_destroy(b);
         return nullptr;
     }
+    cudaMemset(b->d_stats, 0, sizeof(cam::CamStatsDev));
     cudaMemset(b->done_ctr, 0, sizeof(unsigned int) * 4);
     cudaMemset(b->dup_ctr, 0, sizeof(unsigned int) * CAM_MAX_RANKS);
     cudaMemset(b->d_epochs, 0, sizeof(uint32_t) * 16);
@@ -291,6 +294,7 @@ extern "C" int cam_buffer_destroy(CamBuffer* b) {
     for (void* p : frees)
         if (p != nullptr) cudaFree(p);
     if (b->h_status != nullptr) cudaFreeHost(b->h_status);
+    if (b->d_stats != nullptr) cudaFree(b->d_stats);
     if (b->d_trace != nullptr) cudaFree(b->d_trace);
     if (b->act_f32 != nullptr) cudaFree(b->act_f32);
     if (b->row_amax != nullptr) cudaFree(b->row_amax);
@@ -470,6 +474,25 @@ extern "C" int cam_buffer_check_guards(CamBuffer* b, cudaStream_t stream, int* d
             }
     for (int i = 0; i < 4; ++i)
         if (*damaged & (1 << i)) CAM_CUDA(cudaMemsetAsync(b->base + offs[i], 0xA5, CAM_GUARD_BYTES, stream));
+    return 0;
+}
+
+// Statistics of the normal-mode ops since the buffer was created or since the last call with reset = 1 (synchronises the
+// device).  out_wait_ns: [3][num_ranks] longest wait for every peer's dispatch counts / dispatch rows / combine rows (ns);
+// out_rows: [num_ranks] (token, k) pairs routed to every rank; out_calls: [2] dispatches, combines.
+extern "C" int cam_buffer_read_stats(CamBuffer* b, unsigned long long* out_wait_ns, unsigned long long* out_rows,
+                                     unsigned long long* out_calls, int reset) {
+    CAM_CHECK(b != nullptr && out_wait_ns && out_rows && out_calls, "read_stats: null argument");
+    CAM_CUDA(cudaSetDevice(b->device));
+    CAM_CUDA(cudaDeviceSynchronize());
+    cam::CamStatsDev h;
+    CAM_CUDA(cudaMemcpy(&h, b->d_stats, sizeof(h), cudaMemcpyDeviceToHost));
+    for (int k = 0; k < 3; ++k)
+        for (int r = 0; r < b->num_ranks; ++r) out_wait_ns[k * b->num_ranks + r] = h.max_wait_ns[k][r];
+    for (int r = 0; r < b->num_ranks; ++r) out_rows[r] = h.rows_routed[r];
+    out_calls[0] = h.calls[0];
+    out_calls[1] = h.calls[1];
+    if (reset) CAM_CUDA(cudaMemset(b->d_stats, 0, sizeof(h)));
     return 0;
 }
 
@@ -699,6 +722,7 @@ static int dispatch_normal_impl(CamBuffer* b, const void* x, const void* topk_id
     p.done_ctr = b->done_ctr + 0;
     p.status = b->d_status;
     p.off_arrival = b->layout.off_arrival;
+    p.stats = b->d_stats;
     if (defer_push) {
         CAM_CHECK(CAM_QUANT_IS_FP8(quant_mode), "dispatch_normal: the deferred push carries fp8 rows only");
         if (ensure_deep_workspace(b) != 0) return -1;
@@ -754,6 +778,7 @@ extern "C" int cam_combine(CamBuffer* b, const void* y, const int* row_src, cons
     p.off_combine_flag = low_latency ? b->layout.off_ll_combine_flag : b->layout.off_combine_flag;
     p.done_ctr = b->done_ctr + 1;
     p.status = b->d_status;
+    p.stats = low_latency ? nullptr : b->d_stats;
     const int rc = cam_launch_combine(&p, b->num_sms, stream);
     CAM_CHECK(rc == 0, "combine launch failed: %s", cudaGetErrorString(static_cast<cudaError_t>(rc)));
     if (b != nullptr) ++b->launches;

@@ -62,7 +62,9 @@ void cam_buffer_set_debug_drop_flags(CamBuffer* b, int on);
 int cam_buffer_set_trace(CamBuffer* b, int on);
 int cam_buffer_read_trace(CamBuffer* b, unsigned long long* out16);
 int cam_buffer_check_guards(CamBuffer* b, cudaStream_t stream, int* damaged);  // bit i: guard behind region i was overwritten
-unsigned long long cam_buffer_launch_count(CamBuffer* b);  // kernels launched by this buffer's ops so far
+unsigned long long cam_buffer_launch_count(CamBuffer* b);
+int cam_buffer_read_stats(CamBuffer* b, unsigned long long* out_wait_ns, unsigned long long* out_rows,
+                          unsigned long long* out_calls, int reset);  // kernels launched by this buffer's ops so far
 int cam_buffer_set_fused_trace(CamBuffer* b, int on);
 int cam_buffer_read_fused_trace(CamBuffer* b, long long* out, int num_local_experts);
 int cam_buffer_read_fused_waits(CamBuffer* b, long long* out6, int num_local_experts);

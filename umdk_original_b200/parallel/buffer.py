@@ -261,13 +261,25 @@ class Buffer:
         d, g1, g2, c = self._native.read_profile()
         return {"dispatch_ms": d, "gemm1_ms": g1, "gemm2_send_ms": g2, "combine_ms": c}
 
-    def stats(self) -> dict:
+    def stats(self, reset: bool = False) -> dict:
+        """Counters of this rank since the Buffer was created (or since the last ``stats(reset=True)``); synchronises
+        the device.  Besides the row counts of the last dispatch: per peer, the (token, k) pairs routed to it by the
+        normal-mode dispatches and the longest time this rank waited for that peer's dispatch counts, dispatch rows
+        and combine rows (microseconds) -- the peer with the largest wait is the one that was late."""
         if self._cpu is not None:
             return dict(self._cpu.stats)
         el = self.config.num_experts // self.num_ranks
+        waits, rows, calls = self._native.read_stats(reset)
+        r = self.num_ranks
         return {"total_recv": int(self._native.total_recv().item()),
                 "recv_per_expert": self._native.num_recv_per_expert(el).tolist(),
-                "symmetric_bytes": self.total_bytes}
+                "symmetric_bytes": self.total_bytes,
+                "dispatch_calls": calls[0], "combine_calls": calls[1],
+                "rows_routed_to_peer": list(rows),
+                "max_wait_us": {"dispatch_counts": [w / 1e3 for w in waits[0:r]],
+                                "dispatch_rows": [w / 1e3 for w in waits[r:2 * r]],
+                                "combine_rows": [w / 1e3 for w in waits[2 * r:3 * r]]},
+                "kernel_launches": int(self._native.launch_count())}
 
     def destroy(self) -> None:
         if self._native is not None:

@@ -156,8 +156,8 @@ struct FusedMoeParams {
     int a_rows;                 // rows of the receive buffer (capacity)
     int max_tokens;             // tokens per rank the combine slots are sized for
     const float* a1_scales;     // [a_rows, a1_scale_pitch] scales of the received rows (arrive during the kernel)
-    int a1_scale_pitch;         // floats per scale row: h/128 rounded up to 32, so that a row owns whole 128-byte lines
-    int act_scale_pitch;        // the same for act_s (I/128 rounded up to 32)
+    int a1_scale_pitch;         // floats per scale row: h/128 rounded up to 4 (rows are read 16 bytes at a time)
+    int act_scale_pitch;        // the same for act_s (I/128 rounded up to 4)
     const float* b1_scales;     // [E_local, 2I/128, h/128]
     const float* b2_scales;     // [E_local, h/128, I/128]
     uint8_t* act_q;             // [a_rows, I] e4m3, between the two GEMMs

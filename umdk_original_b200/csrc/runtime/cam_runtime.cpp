@@ -45,6 +45,9 @@ int fail(const char* fmt, ...) {
     } while (0)
 
 uint64_t align_up(uint64_t v, uint64_t a) { return (v + a - 1) / a * a; }
+// Floats between two rows of activation scales on the deep-fused route: the fused kernel reads a row four K-blocks
+// (16 bytes) at a time.
+uint64_t scale_row_pitch(uint64_t blocks) { return align_up(blocks, 4); }
 
 }  // namespace
 
@@ -179,7 +182,7 @@ extern "C" int cam_layout_compute_tp(CamLayout* L, int R, int E, int max_tokens,
     };
     L->off_recv_x = take_guarded(static_cast<uint64_t>(capacity) * hidden * 2, &L->off_guard0);
     // sized for scale rows padded to whole 128-byte lines (the fused layer's layout); the stand-alone ops pack them
-    L->off_recv_scales = take_guarded(static_cast<uint64_t>(capacity) * align_up(hidden / 128, 32) * 4, &L->off_guard1);
+    L->off_recv_scales = take_guarded(static_cast<uint64_t>(capacity) * scale_row_pitch(hidden / 128) * 4, &L->off_guard1);
     L->off_recv_src = take_guarded(static_cast<uint64_t>(capacity) * 3 * 4, &L->off_guard2);
     L->off_combine_buf = take_guarded(static_cast<uint64_t>(max_tokens) * topk * hidden * 2, &L->off_guard3);
     L->off_dup_list = take(2ull * R * static_cast<uint64_t>(max_tokens) * topk * 8);
@@ -261,7 +264,7 @@ extern "C" CamBuffer* cam_buffer_create(int device, int rank, int num_ranks, con
     ok &= cudaMallocHost(&b->h_status, sizeof(CamStatus)) == cudaSuccess;
     ok &= cudaMalloc(&b->d_stats, sizeof(cam::CamStatsDev)) == cudaSuccess;
     ok &= cudaMalloc(&b->act_q, static_cast<size_t>(layout->capacity) * layout->hidden) == cudaSuccess;
-    ok &= cudaMalloc(&b->act_s, static_cast<size_t>(layout->capacity) * align_up(layout->hidden / 128, 32) * 4) == cudaSuccess;
+    ok &= cudaMalloc(&b->act_s, static_cast<size_t>(layout->capacity) * scale_row_pitch(layout->hidden / 128) * 4) == cudaSuccess;
     if (!ok) {
         fail("buffer_create: workspace allocation failed: %s", cudaGetErrorString(cudaGetLastError()));
         cam_buffer_destroy(b);
@@ -1201,8 +1204,8 @@ static int fused_moe_deep(CamBuffer* b, const void* x, const void* expert_ids, i
         p.a_rows = L.capacity;
         p.max_tokens = L.max_tokens;
         p.a1_scales = reinterpret_cast<const float*>(b->base + L.off_recv_scales);
-        p.a1_scale_pitch = static_cast<int>(align_up(h / 128, 32));
-        p.act_scale_pitch = static_cast<int>(align_up(inter / 128, 32));
+        p.a1_scale_pitch = static_cast<int>(scale_row_pitch(h / 128));
+        p.act_scale_pitch = static_cast<int>(scale_row_pitch(inter / 128));
         p.b1_scales = w1_s;
         p.b2_scales = w2_s;
         p.act_q = b->act_q;

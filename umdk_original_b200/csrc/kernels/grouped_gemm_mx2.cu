@@ -52,6 +52,11 @@ constexpr uint32_t kP2LaunchRegs = 80, kP2CtrlRegs = 32, kP2SfRegs = 56, kP2EpiR
 static_assert(128 * kP2CtrlRegs + 128 * kP2SfRegs + kP2EpiThreads * kP2EpiRegs <= kP2LaunchRegs * kP2Threads,
               "setmaxnreg budget exceeds the registers the CTA owns: the kernel would hang");
 
+// the biased exponents (UE8M0 codes) of four power-of-two scales, one byte each
+__device__ __forceinline__ uint32_t pack_exp4(const float4& v) {
+    return ((__float_as_uint(v.x) >> 23) & 0xFFu) | (((__float_as_uint(v.y) >> 23) & 0xFFu) << 8) |
+           (((__float_as_uint(v.z) >> 23) & 0xFFu) << 16) | (((__float_as_uint(v.w) >> 23) & 0xFFu) << 24);
+}
 __device__ __forceinline__ uint32_t ue8m0_word2(float scale) {
     return ((__float_as_uint(scale) >> 23) & 0xFFu) * 0x01010101u;
 }
@@ -175,6 +180,9 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
         uint32_t it = 0;
         int e, mt, nt, row0, rows;
         bool ok = true;
+        // rows of scales can be read 16 bytes at a time when K is a multiple of 512 and the arrays are aligned
+        const bool vec_scales = (kblocks & 3) == 0 &&
+                                ((reinterpret_cast<uintptr_t>(p.a_scales) | reinterpret_cast<uintptr_t>(p.b_scales)) & 15u) == 0u;
         for (int tile = pair_id; ok && w.locate(tile, e, mt, nt, row0, rows); tile += num_pairs) {
             const float* as[4];
 #pragma unroll
@@ -187,7 +195,64 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
             else { nb_lo = 2 * nt; nb_hi = min(2 * nt + 1, nblk - 1); }
             const float* bs_lo = p.b_scales + (static_cast<size_t>(e) * nblk + nb_lo) * kblocks;
             const float* bs_hi = p.b_scales + (static_cast<size_t>(e) * nblk + nb_hi) * kblocks;
-            // scales are fetched two K-blocks ahead of their use
+            // One K-block: write the six scale words of stage s into TMEM and tell the MMA issuer.
+            auto put = [&](uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, uint32_t w4, uint32_t w5) -> bool {
+                const uint32_t s = it % NS, ph = (it / NS) & 1u;
+                const bool got = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, abort_flag);
+                if (!__all_sync(0xFFFFFFFFu, got)) return false;
+                tc_fence_after_sync();
+                const uint32_t col = tmem_base + lane_base + kP2SfCol0 + s * kP2SfStride;
+                tmem_st_32x32b_x4(col, w0, w1, w2, w3);
+                tmem_st_32x32b_x4(col + 4u, w4, w4, w4, w4);
+                tmem_st_32x32b_x4(col + 8u, w5, w5, w5, w5);
+                tc_wait_st();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {  // the first CTA's barrier counts the warps of both CTAs
+                    if (cta == 0) mbar_arrive(&bar_sf[s]);
+                    else mbar_arrive_cluster(map_to_cta(&bar_sf[s], 0));
+                }
+                ++it;
+                return true;
+            };
+            if (vec_scales) {
+                // Scales move in groups of four K-blocks: one 16-byte load per row and group, issued a whole group
+                // before its first use, so that a load that misses L1 still arrives in time (a load that is only one
+                // K-block ahead makes these warps, and with them the MMA issuer, run at one K-block per L2 latency
+                // whenever it misses).  A group is packed to one exponent byte per K-block as soon as it is there.
+                const int ngroups = kblocks >> 2;
+                float4 na[4], nbl, nbh;
+                auto load_group = [&](int g) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) na[j] = __ldg(reinterpret_cast<const float4*>(as[j]) + g);
+                    nbl = __ldg(reinterpret_cast<const float4*>(bs_lo) + g);
+                    nbh = __ldg(reinterpret_cast<const float4*>(bs_hi) + g);
+                };
+                load_group(0);
+                for (int g = 0; ok && g < ngroups; ++g) {
+                    uint32_t pk[6];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) pk[j] = pack_exp4(na[j]);
+                    pk[4] = pack_exp4(nbl);
+                    pk[5] = pack_exp4(nbh);
+                    ok = put(__byte_perm(pk[0], 0, 0x0000), __byte_perm(pk[1], 0, 0x0000), __byte_perm(pk[2], 0, 0x0000),
+                             __byte_perm(pk[3], 0, 0x0000), __byte_perm(pk[4], 0, 0x0000), __byte_perm(pk[5], 0, 0x0000));
+                    // the next group's loads go out only after the arrive above, which has release semantics and
+                    // would otherwise wait for them
+                    if (g + 1 < ngroups) load_group(g + 1);
+                    if (ok)
+                        ok = put(__byte_perm(pk[0], 0, 0x1111), __byte_perm(pk[1], 0, 0x1111), __byte_perm(pk[2], 0, 0x1111),
+                                 __byte_perm(pk[3], 0, 0x1111), __byte_perm(pk[4], 0, 0x1111), __byte_perm(pk[5], 0, 0x1111));
+                    if (ok)
+                        ok = put(__byte_perm(pk[0], 0, 0x2222), __byte_perm(pk[1], 0, 0x2222), __byte_perm(pk[2], 0, 0x2222),
+                                 __byte_perm(pk[3], 0, 0x2222), __byte_perm(pk[4], 0, 0x2222), __byte_perm(pk[5], 0, 0x2222));
+                    if (ok)
+                        ok = put(__byte_perm(pk[0], 0, 0x3333), __byte_perm(pk[1], 0, 0x3333), __byte_perm(pk[2], 0, 0x3333),
+                                 __byte_perm(pk[3], 0, 0x3333), __byte_perm(pk[4], 0, 0x3333), __byte_perm(pk[5], 0, 0x3333));
+                }
+                continue;
+            }
+            // any other K: scalar loads, fetched two K-blocks ahead of their use
             float c[6], n1[6];
 #pragma unroll
             for (int j = 0; j < 4; ++j) c[j] = __ldg(as[j]);
@@ -199,27 +264,11 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
                 for (int j = 0; j < 4; ++j) n1[j] = __ldg(as[j] + 1);
                 n1[4] = __ldg(bs_lo + 1); n1[5] = __ldg(bs_hi + 1);
             }
-            for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                uint32_t wd[6];
+            for (int kb = 0; ok && kb < kblocks; ++kb) {
+                ok = put(ue8m0_word2(c[0]), ue8m0_word2(c[1]), ue8m0_word2(c[2]), ue8m0_word2(c[3]), ue8m0_word2(c[4]),
+                         ue8m0_word2(c[5]));
 #pragma unroll
-                for (int j = 0; j < 6; ++j) { wd[j] = ue8m0_word2(c[j]); c[j] = n1[j]; }
-                const uint32_t s = it % NS, ph = (it / NS) & 1u;
-                const bool got = mbar_wait_bounded(&bar_empty[s], ph ^ 1u, abort_flag);
-                if (!__all_sync(0xFFFFFFFFu, got)) { ok = false; break; }
-                tc_fence_after_sync();
-                const uint32_t col = tmem_base + lane_base + kP2SfCol0 + s * kP2SfStride;
-                tmem_st_32x32b_x4(col, wd[0], wd[1], wd[2], wd[3]);
-                tmem_st_32x32b_x4(col + 4u, wd[4], wd[4], wd[4], wd[4]);
-                tmem_st_32x32b_x4(col + 8u, wd[5], wd[5], wd[5], wd[5]);
-                tc_wait_st();
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) {  // the first CTA's barrier counts the warps of both CTAs
-                    if (cta == 0) mbar_arrive(&bar_sf[s]);
-                    else mbar_arrive_cluster(map_to_cta(&bar_sf[s], 0));
-                }
-                // prefetch for K-block kb + 2 only now: the arrive above has release semantics and would
-                // otherwise wait for these loads
+                for (int j = 0; j < 6; ++j) c[j] = n1[j];
                 if (kb + 2 < kblocks) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) n1[j] = __ldg(as[j] + kb + 2);

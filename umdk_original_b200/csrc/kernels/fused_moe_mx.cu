@@ -1,8 +1,8 @@
 // Deep-fused MoE layer for sm_100a: ONE persistent kernel of CTA pairs that
 //   * sends this rank's quantised tokens to their expert ranks, in the order of the destination's
 //     local experts, and counts every landed row on a per-expert arrival counter in the
-//     destination's memory (plain 16-byte loads and peer stores by the epilogue warps while they
-//     wait for accumulators);
+//     destination's memory (bulk copies through a small ring in shared memory, driven by one thread
+//     per CTA, beside the tensor-core pipeline);
 //   * runs the first grouped GEMM (+ SwiGLU + 1x128 fp8 requantisation) of a local expert as soon
 //     as that expert's counter says all of its rows are in, while later experts still arrive;
 //   * runs the second grouped GEMM of a row block as soon as the first one has finished that
@@ -22,8 +22,10 @@
 // Tensor-core pipeline, barriers and epilogues are those of the CTA-pair grouped GEMM
 // (grouped_gemm_mx2.cu): tcgen05.mma.cta_group::2 with UE8M0 block scaling, operands by plain TMA
 // loads (no multicast qualifier anywhere), accumulators in TMEM.  Warps: 0 TMA producer, 1 MMA
-// issuer (first CTA of the pair), 4-7 scale-factor writers, 8-23 epilogue; the epilogue warps send the
-// dispatch rows while they wait for accumulators.
+// issuer (first CTA of the pair), 2 dispatch sender, 4-7 scale-factor writers, 8-23 epilogue.  The sender is one
+// thread that moves the dispatch rows with the bulk-copy engine (this rank's quantised token -> a ring in shared
+// memory -> the destination rank's receive buffer), so that the rows cost the other warps neither issue slots nor
+// load/store bandwidth.
 //
 // Every wait is bounded.  A wait that runs out records a status word, raises the CTA's abort flag
 // (and the partner CTA's), and every role leaves its loop; both CTAs always reach the cluster
@@ -35,7 +37,7 @@ namespace cam {
 constexpr int kFmThreads = 768;
 constexpr int kFmEpiThreads = 512;
 constexpr int kFmSfWarp0 = 4, kFmEpiWarp0 = 8;
-constexpr int kFmStages = 6;
+constexpr int kFmStages = 5;
 constexpr int kFmATile = BM * BK;    // this CTA's 128 rows of A, 16 KiB
 constexpr int kFmBTile = 128 * BK;   // this CTA's half of the 256-row B tile, 16 KiB
 constexpr int kFmStageBytes = kFmATile + kFmBTile;
@@ -43,15 +45,15 @@ constexpr int kFmStgPitch = 272;
 constexpr int kFmStgBytes = BM * kFmStgPitch;  // 34816: bf16 staging of half an output tile (combine-send epilogue)
 // arrivals on a g1_done counter per 128-column tile of the first GEMM: every epilogue warp of both CTAs
 constexpr int kFmG1Signals = 2 * (kFmEpiThreads / 32);
-// A 128 x 256 x 128 fp8 MMA per CTA keeps the tensor cores busy for at least this many SM clocks (just under the 542 of
-// the nominal rate), whatever the clock frequency; a row of the dispatch plus its fence takes about kFmSendMarginClocks.
-constexpr int kFmMinKBlockClocks = 520;
-constexpr int kFmSendMarginClocks = 10000;
-constexpr int kFmCommBatch = 4;                // rows a warp sends between two arrival signals
+// The sender's ring: kFmSendSlots rows in flight (a row of at most 7168 e4m3 values followed by its scales).
+constexpr int kFmSendSlots = 4;
+constexpr int kFmSendRowMax = 7168;
+constexpr int kFmSendSlotBytes = kFmSendRowMax + 256;
+constexpr int kFmSendAhead = 1;                // rows whose load is issued before the previous row's stores
+constexpr int kFmCommBatch = 4;                // rows between two arrival signals at most
 constexpr int kFmSmemCtrl = 1024;
-// six pipeline stages | one staging buffer | barriers: 232448 bytes, all a CTA can have (dispatch rows move
-// through registers and need none of it)
-constexpr int kFmSmem = kFmStages * kFmStageBytes + kFmStgBytes + kFmSmemCtrl;
+// five pipeline stages | one staging buffer | the sender's ring | barriers
+constexpr int kFmSmem = kFmStages * kFmStageBytes + kFmStgBytes + kFmSendSlots * kFmSendSlotBytes + kFmSmemCtrl;
 static_assert(kFmSmem <= 232448, "exceeds the shared memory of one CTA");
 constexpr uint32_t kFmTmemCols = 512;
 constexpr uint32_t kFmSfCol0 = 256, kFmSfStride = 16;
@@ -180,85 +182,95 @@ __device__ __forceinline__ bool fm_wait_counter(const uint32_t* ctr, uint32_t wa
     }
 }
 
-// Dispatch send, run by the epilogue warps while they have nothing to drain.
-struct FmSendState { int ci, pend_d, pend_le, pend_n; };  // per warp, in shared memory: list cursor, rows not yet counted
-struct FmSendArgs {
-    uint8_t* const* peer_base;
-    const uint8_t* xq;
-    const float* xs;
-    const int4* send_list;
-    CamStatus* status;
-    uint64_t off_recv_x, off_recv_scales, off_recv_src, off_arrival;  // off_arrival already points at this call's parity
-    int h, rank, num_ranks, max_tokens, a_rows, drop, stride, nlist;
-    int scale_pitch;  // floats between the scale rows of the destination's receive buffer
-};
+// Dispatch send.  One thread per CTA walks the expert-ordered send list (entries blockIdx.x, blockIdx.x + gridDim.x,
+// ...) and moves every row with three bulk copies: token and scales from this rank's quantised copy into a ring slot in
+// shared memory (counted on the slot's mbarrier), then both out of the slot into the destination rank's receive buffer.
+// The (rank, token, k) triple of the row goes by plain stores.  Up to kFmSendSlots rows are in flight.  A row is counted
+// on the arrival counter of its expert at the destination once its stores are complete (cp.async.bulk.wait_group
+// leaves only the newest groups pending), with a system-scope release; rows of one (rank, expert) are counted together,
+// kFmCommBatch at most.
+struct FmSender {
+    const FusedMoeParams& p;
+    FmWait* wt;
+    uint8_t* ring;       // kFmSendSlots x kFmSendSlotBytes
+    uint64_t* bar;       // [kFmSendSlots]
+    int4* meta;          // [kFmSendSlots] list entries of the rows in the slots
+    uint64_t off_arrival;  // of this call's parity
+    int pend_d = -1, pend_le = 0, pend_n = 0;
 
-// One warp sends rows of the list (its cursor advances by `stride`) until the list is exhausted or, when `bar`
-// is given, until that mbarrier phase has completed or the SM's clock has passed `stop_clock`.  A row moves through the warp's registers (eight 16-byte loads
-// in flight per lane) from this rank's quantised tokens straight into the destination rank's receive buffer.  After
-// kFmCommBatch rows, when the destination expert changes and before returning, one system-scope fence makes the rows
-// visible and they are counted on the arrival counter of their expert at the destination.  Kept out of line so that
-// its registers do not add to those of the epilogue around the call.
-__device__ __noinline__ void fm_send_rows(const FmSendArgs* args, FmSendState* st, uint64_t* bar, uint32_t bar_parity,
-                                          long long stop_clock) {
-    const FmSendArgs& a = *args;  // shared memory
-    const uint32_t lane = lane_id();
-    int ci = st->ci, pend_d = st->pend_d, pend_le = st->pend_le, pend_n = st->pend_n;
-    auto flush = [&]() {
-        if (pend_n > 0 && !a.drop) {  // drop: host-side fault injection, the rows are never counted
-            __syncwarp();
-            if (lane == 0) {
-                red_release_sys_add_u32(reinterpret_cast<uint32_t*>(a.peer_base[pend_d] + a.off_arrival) + pend_le,
-                                        static_cast<uint32_t>(pend_n));
-            }
-        }
+    __device__ void flush() {
+        if (pend_n > 0 && p.dbg_drop_flags == 0)  // drop: host-side fault injection, the rows are never counted
+            red_release_sys_add_u32(reinterpret_cast<uint32_t*>(p.peer_base[pend_d] + off_arrival) + pend_le,
+                                    static_cast<uint32_t>(pend_n));
         pend_n = 0;
-    };
-    const int nsc16 = a.h >> 9;  // scales of a row in 16-byte pieces (h is a multiple of 512)
-    while (ci < a.nlist) {
-        if (bar != nullptr && __any_sync(0xFFFFFFFFu, mbar_try_wait(bar, bar_parity) || clock64() - stop_clock > 0)) break;
-        const int4 ent = a.send_list[ci];
-        const int t = ent.x, d = ent.y, row = ent.z, le = ent.w & 0xFFFF, kk = ent.w >> 16;
-        if (t < 0 || t >= a.max_tokens || d < 0 || d >= a.num_ranks || row < 0 || row >= a.a_rows) {
-            if (lane == 0) gemm_record_status(a.status, CAM_ERR_BAD_INDEX, 5, ci);
-            ci = a.nlist;  // stop sending
-            break;
-        }
+    }
+    __device__ void count(const int4& ent) {
+        const int d = ent.y, le = ent.w & 0xFFFF;
         if (pend_n > 0 && (d != pend_d || le != pend_le || pend_n >= kFmCommBatch)) flush();
-        uint8_t* pb = a.peer_base[d];
-        const uint8_t* src = a.xq + static_cast<size_t>(t) * a.h;
-        uint8_t* dst = pb + a.off_recv_x + static_cast<size_t>(row) * a.h;
-        for (int o = static_cast<int>(lane) * 16; o < a.h; o += 8 * 512) {
-            uint4 v[8];
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-                if (o + q * 512 < a.h) v[q] = ld_nc_v4(src + o + q * 512);
-#pragma unroll
-            for (int q = 0; q < 8; ++q)
-                if (o + q * 512 < a.h) st_na_v4(dst + o + q * 512, v[q]);
-        }
-        if (static_cast<int>(lane) < nsc16)
-            st_na_v4(pb + a.off_recv_scales + (static_cast<size_t>(row) * a.scale_pitch * 4) + lane * 16,
-                     ld_nc_v4(reinterpret_cast<const uint8_t*>(a.xs) + (static_cast<size_t>(t) * nsc16 + lane) * 16));
-        if (lane < 3u) {
-            int* tri = reinterpret_cast<int*>(pb + a.off_recv_src) + static_cast<size_t>(row) * 3;
-            tri[lane] = lane == 0u ? a.rank : lane == 1u ? t : kk;
-        }
         pend_d = d;
         pend_le = le;
         ++pend_n;
-        ci += a.stride;
     }
-    flush();
-    __syncwarp();
-    if (lane == 0) {
-        st->ci = ci;
-        st->pend_d = pend_d;
-        st->pend_le = pend_le;
-        st->pend_n = 0;
+    __device__ void run() {
+        constexpr int kPend = kFmSendSlots - 1 - kFmSendAhead;  // store groups that may stay pending when a slot is reused
+        const int nlist = min(p.send_list_len[0], p.send_list_cap);
+        const int first = static_cast<int>(blockIdx.x), stride = static_cast<int>(gridDim.x);
+        const int n = first < nlist ? (nlist - first + stride - 1) / stride : 0;  // rows of this CTA
+        const uint32_t row_bytes = static_cast<uint32_t>(p.h);
+        const uint32_t sc_bytes = static_cast<uint32_t>(p.h >> 7) * 4u;  // a multiple of 16: h is a multiple of 512
+        bool ok = true;
+        int stored = 0, counted = 0;  // rows whose stores were committed / that were counted at their destination
+        for (int i = 0; ok && i < n + kFmSendAhead; ++i) {
+            if (i < n) {
+                // Row i takes the slot of row i - kFmSendSlots.  Rows [0, stored) have their stores committed, and
+                // stored = i - kFmSendAhead here, so with kPend groups pending rows up to i - kFmSendSlots are complete:
+                // count them (their list entries still sit in `meta`) before the slot is overwritten.
+                bulk_wait_group<kPend>();
+                for (; counted < stored - kPend; ++counted) count(meta[counted % kFmSendSlots]);
+                const int4 ent = p.send_list[first + i * stride];
+                const int t = ent.x, d = ent.y, row = ent.z;
+                if (t < 0 || t >= p.max_tokens || d < 0 || d >= p.num_ranks || row < 0 || row >= p.a_rows) {
+                    gemm_record_status(p.status, CAM_ERR_BAD_INDEX, 5, first + i * stride);
+                    ok = false;
+                    break;
+                }
+                const int slot = i % kFmSendSlots;
+                meta[slot] = ent;
+                uint8_t* sl = ring + slot * kFmSendSlotBytes;
+                mbar_arrive_expect_tx(&bar[slot], row_bytes + sc_bytes);
+                bulk_load_g2s(sl, p.xq + static_cast<size_t>(t) * p.h, row_bytes, &bar[slot]);
+                bulk_load_g2s(sl + kFmSendRowMax, reinterpret_cast<const uint8_t*>(p.xs) + static_cast<size_t>(t) * sc_bytes,
+                              sc_bytes, &bar[slot]);
+            }
+            const int j = i - kFmSendAhead;
+            if (j >= 0) {
+                const int slot = j % kFmSendSlots;
+                if (!fm_mbar_wait_sleep(&bar[slot], static_cast<uint32_t>(j / kFmSendSlots) & 1u, wt)) {
+                    gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 4, j);
+                    ok = false;
+                    break;
+                }
+                const int4 ent = meta[slot];
+                const int t = ent.x, d = ent.y, row = ent.z, kk = ent.w >> 16;
+                uint8_t* pb = p.peer_base[d];
+                const uint8_t* sl = ring + slot * kFmSendSlotBytes;
+                bulk_store_s2g(pb + p.off_recv_x + static_cast<size_t>(row) * p.h, sl, row_bytes);
+                bulk_store_s2g(pb + p.off_recv_scales + static_cast<size_t>(row) * p.a1_scale_pitch * 4, sl + kFmSendRowMax,
+                               sc_bytes);
+                bulk_commit_group();
+                int* tri = reinterpret_cast<int*>(pb + p.off_recv_src) + static_cast<size_t>(row) * 3;
+                tri[0] = p.rank;
+                tri[1] = t;
+                tri[2] = kk;
+                ++stored;
+            }
+        }
+        // whatever happened, nothing may still read the ring or be in flight when the CTA leaves
+        bulk_wait_group<0>();
+        for (; counted < stored; ++counted) count(meta[counted % kFmSendSlots]);
+        flush();
     }
-    __syncwarp();
-}
+};
 
 // Unique counter index of the 256-row block that starts at `row0` of local expert `e` (experts own contiguous rows).
 __device__ __forceinline__ int fm_block_index(int row0, int e) { return (row0 >> 8) + e; }
@@ -273,7 +285,8 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
         return;
     }
     uint8_t* stg = smem + kFmStages * kFmStageBytes;
-    uint8_t* ctrl = stg + kFmStgBytes;
+    uint8_t* send_ring = stg + kFmStgBytes;
+    uint8_t* ctrl = send_ring + kFmSendSlots * kFmSendSlotBytes;
     uint64_t* bar_full = reinterpret_cast<uint64_t*>(ctrl);
     uint64_t* bar_sf = bar_full + kFmStages;
     uint64_t* bar_empty = bar_sf + kFmStages;
@@ -281,10 +294,10 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
     uint64_t* bar_tempty = bar_tfull + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 1);
     FmWait* wt = reinterpret_cast<FmWait*>(ctrl + 384);
-    FmSendState* send_state = reinterpret_cast<FmSendState*>(ctrl + 512);  // [16 epilogue warps]
-    FmSendArgs* send_args = reinterpret_cast<FmSendArgs*>(ctrl + 768);
-    static_assert(768 + sizeof(FmSendArgs) <= kFmSmemCtrl && 512 + 16 * sizeof(FmSendState) <= 768 &&
-                      384 + sizeof(FmWait) <= 512 && (3 * kFmStages + 2) * 8 + 8 <= 384, "control area layout");
+    uint64_t* bar_send = reinterpret_cast<uint64_t*>(ctrl + 512);   // [kFmSendSlots]
+    int4* send_meta = reinterpret_cast<int4*>(ctrl + 576);          // [kFmSendSlots]
+    static_assert(576 + kFmSendSlots * 16 <= kFmSmemCtrl && 512 + kFmSendSlots * 8 <= 576 && 384 + sizeof(FmWait) <= 512 &&
+                      (3 * kFmStages + 2) * 8 + 8 <= 384, "control area layout");
     float* s_amax = reinterpret_cast<float*>(stg);  // first-GEMM epilogue: [2 parities][4 column quarters][128 rows]
 
     const int warp = static_cast<int>(threadIdx.x) >> 5;
@@ -307,6 +320,7 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
             mbar_init(&bar_sf[s], 8);
             mbar_init(&bar_empty[s], 1);
         }
+        for (int s = 0; s < kFmSendSlots; ++s) mbar_init(&bar_send[s], 1);
         mbar_init(bar_tfull, 1);
         mbar_init(bar_tempty, 2 * (kFmEpiThreads / 32));
         wt->abort_flag = 0u;
@@ -317,25 +331,6 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
         wt->deadline_pipe = wt->deadline_arrival + 2000000000ull;
         mbar_fence_init();
         if (blockIdx.x == 0 && p.trace != nullptr) p.trace[p.num_experts] = globaltimer_ns();
-        FmSendArgs& sa = *send_args;
-        sa.peer_base = p.peer_base;
-        sa.xq = p.xq;
-        sa.xs = p.xs;
-        sa.send_list = p.send_list;
-        sa.status = p.status;
-        sa.off_recv_x = p.off_recv_x;
-        sa.off_recv_scales = p.off_recv_scales;
-        sa.off_recv_src = p.off_recv_src;
-        sa.off_arrival = p.off_arrival + static_cast<uint64_t>(parity) * p.arrival_stride * sizeof(uint32_t);
-        sa.h = p.h;
-        sa.rank = p.rank;
-        sa.num_ranks = p.num_ranks;
-        sa.max_tokens = p.max_tokens;
-        sa.a_rows = p.a_rows;
-        sa.drop = p.dbg_drop_flags;
-        sa.stride = static_cast<int>(gridDim.x) * (kFmEpiThreads / 32);
-        sa.nlist = do_send ? min(p.send_list_len[0], p.send_list_cap) : 0;
-        sa.scale_pitch = p.a1_scale_pitch;
     }
     if (do_gemm && warp == 1) {
         tmem_alloc_pair(tmem_slot, kFmTmemCols);
@@ -465,6 +460,11 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                 t[4] = it;                                                    // K-blocks issued
                 t[5] = tcount;                                                // tiles
             }
+        } else if (warp == 2 && lane == 0 && do_send) {
+            // ------------------------------------------------------------ dispatch sender
+            FmSender sender{p, wt, send_ring, bar_send, send_meta,
+                            p.off_arrival + static_cast<uint64_t>(parity) * p.arrival_stride * sizeof(uint32_t)};
+            sender.run();
         }
     } else if (warp < kFmEpiWarp0) {
         reg_dealloc<kFmSfRegs>();
@@ -582,21 +582,7 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
         }
     } else {
         reg_alloc<kFmEpiRegs>();
-        // ---------------------------------------------------------------- epilogue warps (and dispatch send)
-        // While an epilogue warp waits for an accumulator it sends rows of the dispatch: one row per turn, moved
-        // through its registers (eight 16-byte loads in flight per lane) from this rank's quantised tokens straight
-        // into the destination rank's receive buffer.  Rows are taken from the list in order, so the first local
-        // expert of every rank is complete first.  After a few rows (or when the destination expert changes) one
-        // system-scope fence makes them visible and they are counted on the arrival counter of their expert there.
-        const FmSendArgs& sa = *send_args;  // filled by thread 0 before the first barrier of the CTA
-        FmSendState* sst = send_state + (warp - kFmEpiWarp0);  // this warp's cursor, in shared memory
-        if (lane == 0) {
-            sst->ci = static_cast<int>(blockIdx.x) * (kFmEpiThreads / 32) + (warp - kFmEpiWarp0);
-            sst->pend_d = -1;
-            sst->pend_le = 0;
-            sst->pend_n = 0;
-        }
-        __syncwarp();
+        // ---------------------------------------------------------------- epilogue warps
         if (do_gemm) {
             const int ew = warp - kFmEpiWarp0;
             const int q = warp & 3;   // TMEM lane quarter this warp may read
@@ -604,7 +590,6 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
             const int r = q * 32 + static_cast<int>(lane);
             FusedWalker w;
             uint32_t tcount = 0;
-            long long t_free = 0;  // SM clock when this warp last handed the accumulator back
             int kind, e, mt, nt, row0, rows, cnt;
             bool ok = true;
             for (int tile = pair_id; ok && w.locate(p, tile, kind, e, mt, nt, row0, rows, cnt); tile += num_pairs, ++tcount) {
@@ -613,39 +598,6 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                 rows = max(0, min(BM, rows - static_cast<int>(cta) * BM));
                 const bool valid = r < rows && row0 + r < p.a_rows;
                 const int grow = row0 + (valid ? r : 0);
-                // Nothing to drain yet: send rows of the dispatch.  A tile whose inputs are not complete yet has not
-                // started; the rows it waits for may be among those this warp still has to send, so keep sending until
-                // the accumulator shows up.  A tile that is running keeps the tensor cores busy for at least
-                // kFmMinKBlockClocks per K-block, and it cannot have started before this warp released the accumulator:
-                // send until then minus the time of one row and its fence, then wait quietly, so that the accumulator is
-                // taken the moment it is complete (the MMA issuer cannot start the next tile before that).  Should the
-                // tile be late all the same (something else holds it up), go back to sending.
-                if (sst->ci < sa.nlist) {
-                    const uint32_t par = tcount & 1u;
-                    bool held = tcount == 0;
-                    if (!held) {
-                        uint32_t have = 0;
-                        if (lane == 0)
-                            have = kind ? (ld_volatile_u32(p.g1_done + blk) >= static_cast<uint32_t>(kFmG1Signals * nt1))
-                                        : (ld_volatile_u32(my_arrival + e) >= static_cast<uint32_t>(cnt));
-                        held = __shfl_sync(0xFFFFFFFFu, have, 0) == 0u;
-                    }
-                    if (held) {
-                        fm_send_rows(send_args, sst, bar_tfull, par, 0x7FFFFFFFFFFFFFFFll);
-                    } else {
-                        const long long busy = static_cast<long long>(kind ? kb2 : kb1) * kFmMinKBlockClocks;
-                        if (clock64() - (t_free + busy - kFmSendMarginClocks) < 0)
-                            fm_send_rows(send_args, sst, bar_tfull, par, t_free + busy - kFmSendMarginClocks);
-                        const long long late = t_free + 3 * busy;
-                        bool fired = mbar_try_wait(bar_tfull, par);
-                        while (!__any_sync(0xFFFFFFFFu, fired) && !__any_sync(0xFFFFFFFFu, clock64() - late > 0)) {
-                            __nanosleep(128);
-                            fired = mbar_try_wait(bar_tfull, par);
-                        }
-                        if (!__any_sync(0xFFFFFFFFu, fired) && sst->ci < sa.nlist)
-                            fm_send_rows(send_args, sst, bar_tfull, par, 0x7FFFFFFFFFFFFFFFll);
-                    }
-                }
                 // one decision for all epilogue threads: a thread that gave up must not leave the others at a
                 // named barrier further down
                 if (!named_bar_and(1, kFmEpiThreads, fm_mbar_wait_sleep(bar_tfull, tcount & 1u, wt))) { ok = false; break; }
@@ -662,7 +614,6 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                     if (cta == 0) mbar_arrive(bar_tempty);
                     else mbar_arrive_cluster(map_to_cta(bar_tempty, 0));
                 }
-                t_free = clock64();
 
                 if (kind == 0) {
                     // SwiGLU on matching gate/up columns, then 1x128 fp8 requantisation (power-of-two scale).
@@ -738,7 +689,6 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
             if (cq == 0) bulk_wait_group<0>();  // every row this thread sent has been written
             if (!ok) gemm_record_status(p.status, CAM_ERR_TIMEOUT_PIPELINE, 2, static_cast<int>(tcount));
         }
-        if (sst->ci < sa.nlist) fm_send_rows(send_args, sst, nullptr, 0u, 0ll);  // rows left when the tiles ran out (or send-only launch)
     }
 
     // ------------------------------------------------------------------ teardown

@@ -43,7 +43,7 @@ def _local_weights(w, world, e):
 
 
 def _run_layer(monkeypatch, deep, world, cfg, name, dx, dk, dw, local, e):
-    monkeypatch.setenv("UMDK_CAM_DEEP_FUSE", "1" if deep else "0")
+    monkeypatch.setenv("UMDK_CAM_DEEP_FUSE", str(int(deep)))  # 0: four launches, 1: deep-fused, 2: fused GEMMs only
     bufs = u.Buffer.virtual(world, cfg, DEV, name=name)
 
     def step(r):
@@ -59,24 +59,25 @@ def _run_layer(monkeypatch, deep, world, cfg, name, dx, dk, dw, local, e):
     return bufs, step, outs, nums
 
 
-@pytest.mark.parametrize("world,holes", [(1, False), (2, True), (4, False)])
-def test_deep_fused_layer_matches_oracle_and_unfused(world, holes, monkeypatch):
+@pytest.mark.parametrize("world,holes,route", [(1, False, 1), (2, True, 1), (4, False, 1), (1, False, 2), (2, True, 2)])
+def test_deep_fused_layer_matches_oracle_and_unfused(world, holes, route, monkeypatch):
     """Virtual ranks on one GPU: every expert spans more than one 256-row tile on some rank and the
     tile walk interleaves the two GEMMs; results against the fp32 oracle (row-relative) and against
-    the four-launch route."""
+    the four-launch route.  Route 1 sends the dispatch rows from inside the fused kernel, route 2 runs the
+    normal dispatch first and the fused kernel for the two GEMMs only."""
     t, h, inter, e, k = 384, 1024, 512, 8, 4
     xs, topk, wts, w = _case(world, t, h, inter, e, k, seed=300 + world, holes=holes)
     cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, timeout_ms=3000.0)
     local = _local_weights(w, world, e)
     dx, dk, dw = ([v.to(DEV) for v in part] for part in (xs, topk, wts))
-    bufs, step, outs, nums = _run_layer(monkeypatch, True, world, cfg, f"deep{world}_", dx, dk, dw, local, e)
+    bufs, step, outs, nums = _run_layer(monkeypatch, route, world, cfg, f"deep{world}_{route}_", dx, dk, dw, local, e)
     # a second call on the same buffers: epochs, counters and parities roll over
     every2 = run_virtual(step, world, return_all=True)
     outs2 = [every2[PHASE_FINAL][r][0].cpu().float() for r in range(world)]
     for b in bufs:
         b.check()
         b.destroy()
-    bufs_u, _, outs_u, nums_u = _run_layer(monkeypatch, False, world, cfg, f"flat{world}_", dx, dk, dw, local, e)
+    bufs_u, _, outs_u, nums_u = _run_layer(monkeypatch, 0, world, cfg, f"flat{world}_{route}_", dx, dk, dw, local, e)
     for b in bufs_u:
         b.destroy()
     el = e // world

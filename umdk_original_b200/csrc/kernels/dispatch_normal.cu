@@ -85,11 +85,13 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
             __syncthreads();
         }
         for (int e = tid; e < E; e += kDispThreads) p.cta_hist[static_cast<size_t>(b) * E + e] = s_hist[e];
-        if (p.defer_push && b == nb - 1) {
+        if (p.g1_done != nullptr && b == nb - 1) {
             // Counters of the fused kernel start at zero.  Peers add to this call's arrival counters only after they
             // have seen this rank's count flag, which is raised after the grid-wide barrier below.
-            uint32_t* arr = reinterpret_cast<uint32_t*>(my_base + p.off_arrival) + static_cast<size_t>(parity) * E;
-            for (int e = tid; e < E; e += kDispThreads) arr[e] = 0u;
+            if (p.defer_push) {
+                uint32_t* arr = reinterpret_cast<uint32_t*>(my_base + p.off_arrival) + static_cast<size_t>(parity) * E;
+                for (int e = tid; e < E; e += kDispThreads) arr[e] = 0u;
+            }
             for (int i = tid; i < p.g1_done_len; i += kDispThreads) p.g1_done[i] = 0u;
             __threadfence_system();
         }

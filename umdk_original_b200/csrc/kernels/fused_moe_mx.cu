@@ -361,7 +361,7 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                 if (kind == 0) {
                     brow_lo = e * 2 * p.inter + nt * 128;
                     brow_hi = brow_lo + p.inter;
-                    if (e != ready_e) {  // the expert's rows (from every rank) must have landed
+                    if (!p.skip_arrival && e != ready_e) {  // the expert's rows (from every rank) must have landed
                         uint32_t seen;
                         if (!fm_wait_counter<true>(my_arrival + e, static_cast<uint32_t>(cnt), wt, seen)) {
                             gemm_record_status(p.status, CAM_ERR_TIMEOUT_ARRIVAL, e, static_cast<int>(seen));
@@ -482,7 +482,7 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                 // activation scales arrive during this kernel (from peers or from the first GEMM): wait like the
                 // producer does, and read them with L2-coherent loads only
                 if (kind == 0) {
-                    if (e != ready_e) {
+                    if (!p.skip_arrival && e != ready_e) {
                         uint32_t seen;
                         const bool got = fm_wait_counter<true>(my_arrival + e, static_cast<uint32_t>(cnt), wt, seen);
                         if (!__all_sync(0xFFFFFFFFu, got)) {

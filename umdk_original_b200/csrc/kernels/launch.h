@@ -173,6 +173,7 @@ struct FusedMoeParams {
     unsigned int* done_ctr;
     CamStatus* status;
     uint32_t* g1_done;          // per 256-row block: column tiles of GEMM1 written (zeroed by the first launch)
+    int skip_arrival;           // the rows were brought by a dispatch that finished before this launch: no arrival counters
     int lag;                    // GEMM2 of expert e is scheduled after GEMM1 of expert e + lag
     // dispatch send
     const uint8_t* xq;          // [T, h] this rank's quantised tokens

@@ -736,6 +736,10 @@ static int dispatch_normal_impl(CamBuffer* b, const void* x, const void* topk_id
         p.send_list_len = b->send_list_len;
         p.g1_done = b->g1_done;
         p.g1_done_len = b->g1_done_len;
+    } else if (b->g1_done != nullptr) {
+        // the fused kernel may follow this dispatch as a GEMM-only launch: its row-block counters start at zero
+        p.g1_done = b->g1_done;
+        p.g1_done_len = b->g1_done_len;
     }
     // The count matrix is laid out for layout.num_experts; a call with fewer experts still uses
     // stride E because every rank of the call passes the same E.
@@ -1173,19 +1177,22 @@ extern "C" int cam_fused_moe_w8a8(CamBuffer* b, const void* x, const void* exper
 static int fused_moe_deep(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,
                           const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
                           const float* w2_s, void* out, int64_t* expert_token_nums, int T, int K, int h, int inter,
-                          int E, int El, int rows_hint, int phase_mask, cudaStream_t stream) {
+                          int E, int El, int rows_hint, int phase_mask, bool own_dispatch, cudaStream_t stream) {
     const CamLayout& L = b->layout;
     const bool prof = b->profile && phase_mask == 15;
     auto stamp = [&](int i) { if (prof) cudaEventRecord(b->prof_ev[i], stream); };
     stamp(0);
-    const int prep_mask = phase_mask & (CAM_PHASE_COUNT | CAM_PHASE_SEND);
+    // own_dispatch: the fused kernel sends the rows itself, launch 1 only prepares them.  Otherwise launch 1 is the
+    // whole normal dispatch and the fused kernel is just the two GEMMs with their tiles interleaved.
+    const int prep_mask = own_dispatch ? phase_mask & (CAM_PHASE_COUNT | CAM_PHASE_SEND) : phase_mask & CAM_PHASE_ALL;
     if (prep_mask) {
-        if (dispatch_normal_impl(b, x, expert_ids, idx_is_i64, T, K, h, E, CAM_QUANT_FP8_1x128_UE8M0, prep_mask, true,
-                                 stream) != 0)
+        if (ensure_deep_workspace(b) != 0) return -1;
+        if (dispatch_normal_impl(b, x, expert_ids, idx_is_i64, T, K, h, E, CAM_QUANT_FP8_1x128_UE8M0, prep_mask,
+                                 own_dispatch, stream) != 0)
             return -1;
     }
     stamp(1);
-    const int fmask = phase_mask & (CAM_PHASE_SEND | CAM_PHASE_RECV);
+    const int fmask = own_dispatch ? phase_mask & (CAM_PHASE_SEND | CAM_PHASE_RECV) : phase_mask & CAM_PHASE_RECV;
     if (fmask) {
         if (ensure_deep_workspace(b) != 0) return -1;
         uint8_t* recv_x = b->base + L.off_recv_x;
@@ -1228,6 +1235,7 @@ static int fused_moe_deep(CamBuffer* b, const void* x, const void* expert_ids, i
         p.done_ctr = b->done_ctr + 2;
         p.status = b->d_status;
         p.g1_done = b->g1_done;
+        p.skip_arrival = own_dispatch ? 0 : 1;
         // The second GEMM of an expert is scheduled `lag` experts behind the first, far enough that the tiles it
         // waits for were started a whole wave of CTA pairs earlier.
         const int tiles1 = ((rows_hint + 255) / 256) * (inter / 128);
@@ -1269,10 +1277,12 @@ static int fused_moe_deep(CamBuffer* b, const void* x, const void* expert_ids, i
 // measured on one and two B200s the single kernel is slower than the four launches, because its tensor-core pipeline
 // runs at a lower duty than the stand-alone CTA-pair GEMMs (see the fused kernel's wait breakdown, Buffer.read_fused_waits).
 // Needs block-scaled fp8 with power-of-two scales and hidden sizes whose scale rows are whole 16-byte pieces.
-static bool use_deep_fuse(const CamBuffer* b, bool ue8m0, int h, int inter, int rows_hint) {
+// UMDK_CAM_DEEP_FUSE=2 keeps the normal dispatch as launch 1 and uses the fused kernel for the two GEMMs only (their
+// tiles interleaved, so that the combine rows leave during the whole compute time instead of during the second GEMM).
+static int use_deep_fuse(const CamBuffer* b, bool ue8m0, int h, int inter, int rows_hint) {
     (void)rows_hint;
-    if (!ue8m0 || b->env_deep_fuse != 1) return false;
-    return h % 512 == 0 && h <= 7168 && inter % 128 == 0;
+    if (!ue8m0 || (b->env_deep_fuse != 1 && b->env_deep_fuse != 2)) return 0;
+    return (h % 512 == 0 && h <= 7168 && inter % 128 == 0) ? b->env_deep_fuse : 0;
 }
 
 static int fused_moe_impl(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,
@@ -1290,9 +1300,9 @@ static int fused_moe_impl(CamBuffer* b, const void* x, const void* expert_ids, i
     // mean rows per local expert when routing is balanced: every rank sends T * K rows in total
     const int rows_hint = static_cast<int>(static_cast<int64_t>(T) * K * b->num_ranks / E);
     CAM_CUDA(cudaSetDevice(b->device));
-    if (use_deep_fuse(b, ue8m0, h, inter, rows_hint))
+    if (const int deep = use_deep_fuse(b, ue8m0, h, inter, rows_hint))
         return fused_moe_deep(b, x, expert_ids, idx_is_i64, topk_weights, w1_q, w1_s, w2_q, w2_s, out, expert_token_nums, T,
-                              K, h, inter, E, El, rows_hint, phase_mask, stream);
+                              K, h, inter, E, El, rows_hint, phase_mask, deep == 1, stream);
     const int disp_mask = phase_mask & CAM_PHASE_ALL;
     const bool prof = b->profile && phase_mask == 15;
     auto stamp = [&](int i) { if (prof) cudaEventRecord(b->prof_ev[i], stream); };

@@ -37,7 +37,7 @@ namespace cam {
 constexpr int kFmThreads = 768;
 constexpr int kFmEpiThreads = 512;
 constexpr int kFmSfWarp0 = 4, kFmEpiWarp0 = 8;
-constexpr int kFmStages = 5;
+constexpr int kFmStagesSend = 5, kFmStagesGemm = 6;
 constexpr int kFmATile = BM * BK;    // this CTA's 128 rows of A, 16 KiB
 constexpr int kFmBTile = 128 * BK;   // this CTA's half of the 256-row B tile, 16 KiB
 constexpr int kFmStageBytes = kFmATile + kFmBTile;
@@ -53,8 +53,12 @@ constexpr int kFmSendAhead = 1;                // rows whose load is issued befo
 constexpr int kFmCommBatch = 4;                // rows between two arrival signals at most
 constexpr int kFmSmemCtrl = 1024;
 // five pipeline stages | one staging buffer | the sender's ring | barriers
-constexpr int kFmSmem = kFmStages * kFmStageBytes + kFmStgBytes + kFmSendSlots * kFmSendSlotBytes + kFmSmemCtrl;
-static_assert(kFmSmem <= 232448, "exceeds the shared memory of one CTA");
+template <int NS>
+constexpr int fm_smem() {
+    return NS * kFmStageBytes + kFmStgBytes + (NS == kFmStagesSend ? kFmSendSlots * kFmSendSlotBytes : 0) + kFmSmemCtrl;
+}
+constexpr int kFmSmem = fm_smem<kFmStagesGemm>();  // the larger of the two
+static_assert(fm_smem<kFmStagesSend>() <= kFmSmem && kFmSmem <= 232448, "exceeds the shared memory of one CTA");
 constexpr uint32_t kFmTmemCols = 512;
 constexpr uint32_t kFmSfCol0 = 256, kFmSfStride = 16;
 // Register re-partitioning, see grouped_gemm_mx2.cu: the launch count is what ptxas reports.
@@ -182,8 +186,7 @@ __device__ __forceinline__ bool fm_wait_counter(const uint32_t* ctr, uint32_t wa
     }
 }
 
-// Dispatch send.  One thread per CTA walks the expert-ordered send list (entries blockIdx.x, blockIdx.x + gridDim.x,
-// ...) and moves every row with three bulk copies: token and scales from this rank's quantised copy into a ring slot in
+// Dispatch send.  One thread per CTA walks its share of the expert-ordered send list and moves every row with three bulk copies: token and scales from this rank's quantised copy into a ring slot in
 // shared memory (counted on the slot's mbarrier), then both out of the slot into the destination rank's receive buffer.
 // The (rank, token, k) triple of the row goes by plain stores.  Up to kFmSendSlots rows are in flight.  A row is counted
 // on the arrival counter of its expert at the destination once its stores are complete (cp.async.bulk.wait_group
@@ -214,8 +217,15 @@ struct FmSender {
     __device__ void run() {
         constexpr int kPend = kFmSendSlots - 1 - kFmSendAhead;  // store groups that may stay pending when a slot is reused
         const int nlist = min(p.send_list_len[0], p.send_list_cap);
+        // The list is dealt out in runs of kFmCommBatch consecutive entries (run q of this CTA is run q * gridDim.x +
+        // blockIdx.x of the list): consecutive entries nearly always go to the same (rank, expert), so that one
+        // system-scope release counts a whole run.
         const int first = static_cast<int>(blockIdx.x), stride = static_cast<int>(gridDim.x);
-        const int n = first < nlist ? (nlist - first + stride - 1) / stride : 0;  // rows of this CTA
+        const int runs = (nlist + kFmCommBatch - 1) / kFmCommBatch;
+        const int my_runs = first < runs ? (runs - first + stride - 1) / stride : 0;
+        int n = my_runs * kFmCommBatch;  // rows of this CTA
+        if (my_runs > 0 && (my_runs - 1) * stride + first == runs - 1) n -= runs * kFmCommBatch - nlist;  // the list's last run may be short
+        auto entry = [&](int i) { return ((i / kFmCommBatch) * stride + first) * kFmCommBatch + (i % kFmCommBatch); };
         const uint32_t row_bytes = static_cast<uint32_t>(p.h);
         const uint32_t sc_bytes = static_cast<uint32_t>(p.h >> 7) * 4u;  // a multiple of 16: h is a multiple of 512
         bool ok = true;
@@ -227,10 +237,10 @@ struct FmSender {
                 // count them (their list entries still sit in `meta`) before the slot is overwritten.
                 bulk_wait_group<kPend>();
                 for (; counted < stored - kPend; ++counted) count(meta[counted % kFmSendSlots]);
-                const int4 ent = p.send_list[first + i * stride];
+                const int4 ent = p.send_list[entry(i)];
                 const int t = ent.x, d = ent.y, row = ent.z;
                 if (t < 0 || t >= p.max_tokens || d < 0 || d >= p.num_ranks || row < 0 || row >= p.a_rows) {
-                    gemm_record_status(p.status, CAM_ERR_BAD_INDEX, 5, first + i * stride);
+                    gemm_record_status(p.status, CAM_ERR_BAD_INDEX, 5, entry(i));
                     ok = false;
                     break;
                 }
@@ -275,29 +285,33 @@ struct FmSender {
 // Unique counter index of the 256-row block that starts at `row0` of local expert `e` (experts own contiguous rows).
 __device__ __forceinline__ int fm_block_index(int row0, int e) { return (row0 >> 8) + e; }
 
+// NS pipeline stages.  The form that sends the dispatch rows itself has five and the sender's ring; a launch that only
+// runs the GEMMs (the rows were sent before it) has six and no ring.
+template <int NS>
 __global__ void __launch_bounds__(kFmThreads, 1)
 fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_constant__ CUtensorMap tmap_b1,
                       const __grid_constant__ CUtensorMap tmap_a2, const __grid_constant__ CUtensorMap tmap_b2,
                       const FusedMoeParams p) {
+    constexpr int kSlots = NS == kFmStagesSend ? kFmSendSlots : 0;
     extern __shared__ __align__(1024) uint8_t smem[];
     if (smem_u32(smem) & 1023u) {  // swizzled TMA tiles need it; nothing has been set up yet, so just leave
         if (threadIdx.x == 0) gemm_record_status(p.status, CAM_ERR_BAD_INDEX, 4, static_cast<int>(smem_u32(smem) & 1023u));
         return;
     }
-    uint8_t* stg = smem + kFmStages * kFmStageBytes;
+    uint8_t* stg = smem + NS * kFmStageBytes;
     uint8_t* send_ring = stg + kFmStgBytes;
-    uint8_t* ctrl = send_ring + kFmSendSlots * kFmSendSlotBytes;
+    uint8_t* ctrl = send_ring + kSlots * kFmSendSlotBytes;
     uint64_t* bar_full = reinterpret_cast<uint64_t*>(ctrl);
-    uint64_t* bar_sf = bar_full + kFmStages;
-    uint64_t* bar_empty = bar_sf + kFmStages;
-    uint64_t* bar_tfull = bar_empty + kFmStages;
+    uint64_t* bar_sf = bar_full + NS;
+    uint64_t* bar_empty = bar_sf + NS;
+    uint64_t* bar_tfull = bar_empty + NS;
     uint64_t* bar_tempty = bar_tfull + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 1);
     FmWait* wt = reinterpret_cast<FmWait*>(ctrl + 384);
-    uint64_t* bar_send = reinterpret_cast<uint64_t*>(ctrl + 512);   // [kFmSendSlots]
-    int4* send_meta = reinterpret_cast<int4*>(ctrl + 576);          // [kFmSendSlots]
-    static_assert(576 + kFmSendSlots * 16 <= kFmSmemCtrl && 512 + kFmSendSlots * 8 <= 576 && 384 + sizeof(FmWait) <= 512 &&
-                      (3 * kFmStages + 2) * 8 + 8 <= 384, "control area layout");
+    uint64_t* bar_send = reinterpret_cast<uint64_t*>(ctrl + 512);   // [kSlots]
+    int4* send_meta = reinterpret_cast<int4*>(ctrl + 576);          // [kSlots]
+    static_assert(576 + kSlots * 16 <= kFmSmemCtrl && 512 + kSlots * 8 <= 576 && 384 + sizeof(FmWait) <= 512 &&
+                      (3 * NS + 2) * 8 + 8 <= 384, "control area layout");
     float* s_amax = reinterpret_cast<float*>(stg);  // first-GEMM epilogue: [2 parities][4 column quarters][128 rows]
 
     const int warp = static_cast<int>(threadIdx.x) >> 5;
@@ -315,12 +329,12 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                                  static_cast<size_t>(parity) * p.arrival_stride;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kFmStages; ++s) {
+        for (int s = 0; s < NS; ++s) {
             mbar_init(&bar_full[s], 1);
             mbar_init(&bar_sf[s], 8);
             mbar_init(&bar_empty[s], 1);
         }
-        for (int s = 0; s < kFmSendSlots; ++s) mbar_init(&bar_send[s], 1);
+        for (int s = 0; s < kSlots; ++s) mbar_init(&bar_send[s], 1);
         mbar_init(bar_tfull, 1);
         mbar_init(bar_tempty, 2 * (kFmEpiThreads / 32));
         wt->abort_flag = 0u;
@@ -395,7 +409,7 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                 // its fixed place among the kernel parameters instead of through a pointer chosen at run time
                 auto load_tile = [&](const CUtensorMap& ma, const CUtensorMap& mb) {
                     for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                        const uint32_t s = it % kFmStages, ph = (it / kFmStages) & 1u;
+                        const uint32_t s = it % NS, ph = (it / NS) & 1u;
                         if (!fm_mbar_wait(&bar_empty[s], ph ^ 1u, wt)) { ok = false; break; }
                         uint8_t* sa = smem + s * kFmStageBytes;
                         if (cta == 0) mbar_arrive_expect_tx(&bar_full[s], 2 * kFmStageBytes);
@@ -426,7 +440,7 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                 if (prof) w_acc += clock64() - c0;
                 tc_fence_after_sync();
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const uint32_t s = it % kFmStages, ph = (it / kFmStages) & 1u;
+                    const uint32_t s = it % NS, ph = (it / NS) & 1u;
                     if (prof) c0 = clock64();
                     if (!fm_mbar_wait(&bar_sf[s], ph, wt)) { ok = false; break; }
                     if (prof) { const long long c1 = clock64(); w_sf += c1 - c0; c0 = c1; }
@@ -460,7 +474,7 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                 t[4] = it;                                                    // K-blocks issued
                 t[5] = tcount;                                                // tiles
             }
-        } else if (warp == 2 && lane == 0 && do_send) {
+        } else if (kSlots > 0 && warp == 2 && lane == 0 && do_send) {
             // ------------------------------------------------------------ dispatch sender
             FmSender sender{p, wt, send_ring, bar_send, send_meta,
                             p.off_arrival + static_cast<uint64_t>(parity) * p.arrival_stride * sizeof(uint32_t)};
@@ -522,7 +536,7 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                 const float* bs_hi = b_scales + (static_cast<size_t>(e) * nblk + nb_hi) * kblocks;
                 // One K-block: write the six scale words of stage s into TMEM and tell the MMA issuer.
                 auto put = [&](uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) -> bool {
-                    const uint32_t s = it % kFmStages, ph = (it / kFmStages) & 1u;
+                    const uint32_t s = it % NS, ph = (it / NS) & 1u;
                     const bool got = fm_mbar_wait(&bar_empty[s], ph ^ 1u, wt);
                     if (!__all_sync(0xFFFFFFFFu, got)) return false;
                     tc_fence_after_sync();
@@ -721,11 +735,11 @@ extern "C" int cam_fused_moe_smem_bytes(void) { return cam::kFmSmem; }
 
 namespace {
 
-void fm_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int grid, cudaStream_t stream) {
+void fm_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int grid, int smem, cudaStream_t stream) {
     cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid & ~1));
     cfg.blockDim = dim3(cam::kFmThreads);
-    cfg.dynamicSmemBytes = cam::kFmSmem;
+    cfg.dynamicSmemBytes = static_cast<size_t>(smem);
     cfg.stream = stream;
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
@@ -739,17 +753,20 @@ void fm_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int grid, cud
 
 // CTA pairs of the fused kernel that can be resident at once on the current device (cached per device; -1 on error).
 extern "C" int cam_fused_moe_max_pairs(void) {
-    static cam::SmemLimitCache limit;
-    if (limit.ensure(cam::fused_moe_pair_kernel, cam::kFmSmem) != cudaSuccess) return -1;
+    static cam::SmemLimitCache limit_send, limit_gemm;
+    if (limit_send.ensure(cam::fused_moe_pair_kernel<cam::kFmStagesSend>, cam::fm_smem<cam::kFmStagesSend>()) != cudaSuccess) return -1;
+    if (limit_gemm.ensure(cam::fused_moe_pair_kernel<cam::kFmStagesGemm>, cam::fm_smem<cam::kFmStagesGemm>()) != cudaSuccess) return -1;
     static int max_pairs[64] = {0};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
     if (max_pairs[dev] == 0) {
         cudaLaunchConfig_t cfg;
         cudaLaunchAttribute attr[1];
-        fm_config(cfg, attr, 2, nullptr);
+        // both forms take (nearly) all the shared memory of an SM and the same threads and registers: one answer
+        fm_config(cfg, attr, 2, cam::kFmSmem, nullptr);
         int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, cam::fused_moe_pair_kernel, &cfg) == cudaSuccess && n > 0) max_pairs[dev] = n;
+        if (cudaOccupancyMaxActiveClusters(&n, cam::fused_moe_pair_kernel<cam::kFmStagesGemm>, &cfg) == cudaSuccess && n > 0)
+            max_pairs[dev] = n;
         else max_pairs[dev] = -1;
     }
     return max_pairs[dev];
@@ -763,7 +780,12 @@ extern "C" int cam_launch_fused_moe(const cam::FusedMoeParams* p, const CUtensor
     if (fit <= 0) return static_cast<int>(cudaErrorLaunchOutOfResources);
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[1];
-    fm_config(cfg, attr, grid, stream);
+    const bool sends = (p->phase_mask & CAM_PHASE_SEND) != 0;
+    fm_config(cfg, attr, grid, sends ? cam::fm_smem<cam::kFmStagesSend>() : cam::fm_smem<cam::kFmStagesGemm>(), stream);
     if (2 * fit < static_cast<int>(cfg.gridDim.x)) cfg.gridDim = dim3(static_cast<unsigned>(2 * fit));
-    return static_cast<int>(cudaLaunchKernelEx(&cfg, cam::fused_moe_pair_kernel, *tmap_a1, *tmap_b1, *tmap_a2, *tmap_b2, *p));
+    if (sends)
+        return static_cast<int>(cudaLaunchKernelEx(&cfg, cam::fused_moe_pair_kernel<cam::kFmStagesSend>, *tmap_a1, *tmap_b1,
+                                                   *tmap_a2, *tmap_b2, *p));
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, cam::fused_moe_pair_kernel<cam::kFmStagesGemm>, *tmap_a1, *tmap_b1, *tmap_a2,
+                                               *tmap_b2, *p));
 }

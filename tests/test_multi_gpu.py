@@ -77,6 +77,23 @@ def _case(rank, world):
     assert err <= 0.06 * want.float().abs().max().item() + 1e-3, err
     assert torch.equal(nums.cpu(), plan.per_expert)
     report["fused_mx_err"] = err
+    # the same layer through the fused kernels (route 1: the kernel sends the dispatch rows itself over NVLink and starts
+    # an expert when its arrival counter is complete; route 2: normal dispatch, then the two GEMMs in one kernel).  The
+    # route is chosen when a Buffer is created, so each gets a Buffer of its own.
+    for route in (1, 2):
+        os.environ["UMDK_CAM_DEEP_FUSE"] = str(route)
+        bd = u.Buffer(None, cfg, name=f"mgd{route}", device=dev)
+        os.environ["UMDK_CAM_DEEP_FUSE"] = "0"
+        for _ in range(3):
+            out_d, nums_d = ops.fused_deep_moe(x, idx, [pw.w1], [pw.s1], [pw.w2], [pw.s2], w, None, None, f"mgd{route}",
+                                               world, rank, e, 0, 0, 4, 0)
+            bd.check()
+        assert torch.equal(nums_d.cpu(), plan.per_expert)
+        diff = (out_d.float() - out.float()).abs().max().item()
+        assert diff <= 0.01 * want.float().abs().max().item() + 1e-3, (route, diff)
+        report[f"fused_route{route}_diff"] = diff
+        dist.barrier()
+        bd.destroy()
     # low-latency pair
     idx32 = idx.to(torch.int32)
     for _ in range(3):

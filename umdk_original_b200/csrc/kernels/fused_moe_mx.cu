@@ -50,7 +50,7 @@ constexpr int kFmSendSlots = 4;
 constexpr int kFmSendRowMax = 7168;
 constexpr int kFmSendSlotBytes = kFmSendRowMax + 256;
 constexpr int kFmSendAhead = 1;                // rows whose load is issued before the previous row's stores
-constexpr int kFmCommBatch = 4;                // rows between two arrival signals at most
+constexpr int kFmCommBatch = 16;               // rows of one run of the send list, counted with one release
 constexpr int kFmSmemCtrl = 1024;
 // five pipeline stages | one staging buffer | the sender's ring | barriers
 template <int NS>
@@ -202,9 +202,13 @@ struct FmSender {
     int pend_d = -1, pend_le = 0, pend_n = 0;
 
     __device__ void flush() {
-        if (pend_n > 0 && p.dbg_drop_flags == 0)  // drop: host-side fault injection, the rows are never counted
-            red_release_sys_add_u32(reinterpret_cast<uint32_t*>(p.peer_base[pend_d] + off_arrival) + pend_le,
-                                    static_cast<uint32_t>(pend_n));
+        if (pend_n > 0 && p.dbg_drop_flags == 0) {  // drop: host-side fault injection, the rows are never counted
+            uint32_t* ctr = reinterpret_cast<uint32_t*>(p.peer_base[pend_d] + off_arrival) + pend_le;
+            // Rows that stay on this GPU are released at GPU scope: a system-scope release also waits for the path to
+            // the host, which is slow while copies between host and device are running.
+            if (pend_d == p.rank) red_release_gpu_add_u32(ctr, static_cast<uint32_t>(pend_n));
+            else red_release_sys_add_u32(ctr, static_cast<uint32_t>(pend_n));
+        }
         pend_n = 0;
     }
     __device__ void count(const int4& ent) {

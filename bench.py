@@ -34,8 +34,8 @@ METRIC = "moe_layer_tokens_per_s"
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "baseline"])
     ap.add_argument("--model", default="deepseek-v3-moe")
     ap.add_argument("--tokens", type=int, default=0, help="tokens per rank (0 = the model's default)")

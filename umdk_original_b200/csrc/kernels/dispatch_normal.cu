@@ -431,6 +431,7 @@ done:
 __global__ void layout_kernel(const void* topk_idx, int idx_is_i64, int T, int K, int E, int R,
                               int* num_tokens_per_rank, int* num_tokens_per_expert,
                               uint8_t* is_token_in_rank) {
+    static_assert(CAM_MAX_RANKS <= 128, "the ranks a token goes to are tracked in two 64-bit masks");
     __shared__ int s_rank[CAM_MAX_RANKS];
     __shared__ int s_exp[CAM_MAX_EXPERTS];
     for (int i = threadIdx.x; i < R; i += blockDim.x) s_rank[i] = 0;
@@ -496,7 +497,8 @@ extern "C" int cam_launch_layout(const void* topk_idx, int idx_is_i64, int T, in
     if (T <= 0) return 0;
     const int threads = 256;
     int blocks = (T + threads - 1) / threads;
-    if (blocks > 148 * 4) blocks = 148 * 4;
+    const int cap = 4 * cam::sm_count_of_current_device();  // the kernel strides over the tokens
+    if (blocks > cap) blocks = cap;
     cam::layout_kernel<<<blocks, threads, 0, stream>>>(topk_idx, idx_is_i64, T, K, E, R, num_tokens_per_rank,
                                                        num_tokens_per_expert, is_token_in_rank);
     return static_cast<int>(cudaGetLastError());

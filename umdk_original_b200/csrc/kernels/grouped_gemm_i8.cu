@@ -322,7 +322,7 @@ __global__ void rowquant_int8_kernel(const float* __restrict__ act, float* row_a
 
 extern "C" int cam_launch_rowquant_int8(const float* act, float* row_amax, const int* expert_offsets, int num_experts,
                                         int inter, void* out_q, float* out_s, cudaStream_t stream) {
-    cam::rowquant_int8_kernel<<<148 * 4, 256, 0, stream>>>(act, row_amax, expert_offsets, num_experts, inter,
+    cam::rowquant_int8_kernel<<<4 * cam::sm_count_of_current_device(), 256, 0, stream>>>(act, row_amax, expert_offsets, num_experts, inter,
                                                            static_cast<int8_t*>(out_q), out_s);
     return static_cast<int>(cudaGetLastError());
 }

@@ -229,6 +229,18 @@ struct SmemLimitCache {
     }
 };
 
+// SMs of the current device (cached per device; 148 on a B200, which is also the answer if the query fails).
+inline int sm_count_of_current_device() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        cached[dev] = (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) ? n : 148;
+    }
+    return cached[dev];
+}
+
 }  // namespace cam
 
 extern "C" {

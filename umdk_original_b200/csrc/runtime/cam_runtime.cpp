@@ -105,7 +105,8 @@ struct CamBuffer {
     // switches read from the environment once, when the buffer is created (UMDK_CAM_GEMM_*, UMDK_CAM_DEEP_FUSE):
     // -1 = not set (the runtime decides), 0 / 1 = forced
     int env_bulk_push = -1, env_pair = -1, env_swap = -1, env_staging2 = -1, env_deep_fuse = -1, env_fuse_lag = -1;
-    std::map<std::tuple<const void*, uint64_t, uint64_t>, CUtensorMap> tmap_cache;
+    std::map<std::tuple<const void*, uint64_t, uint64_t>, std::pair<CUtensorMap, uint64_t>> tmap_cache;  // map, last use
+    uint64_t tmap_clock = 0;
     std::map<std::tuple<int, int, int, int>, int> ll_grid_cache;  // (h, quant, T, K) -> co-resident grid
 };
 
@@ -877,12 +878,15 @@ static EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
+constexpr size_t kTmapCacheEntries = 64;
+
 // 2-D byte tensor [rows, inner] with row pitch == inner, boxes of 128 bytes x 128 rows, 128-byte swizzle.
 static int make_tmap(CamBuffer* cache_owner, CUtensorMap* out, const void* base, uint64_t inner, uint64_t rows) {
     if (cache_owner != nullptr) {
         auto it = cache_owner->tmap_cache.find(std::make_tuple(base, inner, rows));
         if (it != cache_owner->tmap_cache.end()) {
-            *out = it->second;
+            *out = it->second.first;
+            it->second.second = ++cache_owner->tmap_clock;
             return 0;
         }
     }
@@ -901,8 +905,14 @@ static int make_tmap(CamBuffer* cache_owner, CUtensorMap* out, const void* base,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     CAM_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
     if (cache_owner != nullptr) {
-        if (cache_owner->tmap_cache.size() > 64) cache_owner->tmap_cache.clear();
-        cache_owner->tmap_cache[std::make_tuple(base, inner, rows)] = *out;
+        // bounded: when full, the entry used longest ago makes room (a layer uses four to six maps per call)
+        if (cache_owner->tmap_cache.size() >= kTmapCacheEntries) {
+            auto oldest = cache_owner->tmap_cache.begin();
+            for (auto c = cache_owner->tmap_cache.begin(); c != cache_owner->tmap_cache.end(); ++c)
+                if (c->second.second < oldest->second.second) oldest = c;
+            cache_owner->tmap_cache.erase(oldest);
+        }
+        cache_owner->tmap_cache[std::make_tuple(base, inner, rows)] = std::make_pair(*out, ++cache_owner->tmap_clock);
     }
     return 0;
 }

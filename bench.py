@@ -186,13 +186,14 @@ def run_ours(args, cfg, rank, world, local):
 
     e2e = None
     if not args.no_e2e:
-        runner = MoEStepRunner(layer, tokens)
+        runner = MoEStepRunner(layer, tokens, time_copies=True)
         host = [(x.cpu().pin_memory(), idx.cpu().pin_memory(), w.cpu().pin_memory()) for x, idx, w in sets]
         runner.stage(*host[0])
         for i in range(3):  # warm-up of the pipelined path
             runner.run()
             runner.stage(*host[(i + 1) % len(host)])
             runner.finish()
+        runner.copy_times()  # forget the warm-up copies
         barrier(world)
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
@@ -207,10 +208,15 @@ def run_ours(args, cfg, rank, world, local):
         t1.record()
         barrier(world)
         e2e_ms = max_over_ranks(t0.elapsed_time(t1), world) / args.steps
+        copies = runner.copy_times()
+        copies = {k: max_over_ranks(v, world) for k, v in copies.items()}
         buf.check()
         e2e = {"value": tokens * world / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": runner.h2d_bytes, "d2h_bytes_per_step": runner.d2h_bytes,
-               "d2h": "the layer output [tokens, hidden] bf16 and a record of token counts + checksum, every step"}
+               "d2h": "the layer output [tokens, hidden] bf16 and a record of token counts + checksum, every step",
+               # how long the slowest rank's copies of one step take by themselves (they overlap the compute of
+               # the neighbouring steps; a value near ms_per_step means the host link, not the GPU, sets the pace)
+               "h2d_ms_max_over_ranks": copies["h2d_ms"], "d2h_ms_max_over_ranks": copies["d2h_ms"]}
         del runner, host
 
     # the comparison layer (NCCL all_to_all_single + library GEMMs) at the same N on the same inputs, after the timed regions

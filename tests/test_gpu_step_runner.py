@@ -25,7 +25,7 @@ def test_pipelined_steps_return_each_steps_own_record():
         out, nums = layer(x.to(dev), idx, w)
         want.append(torch.cat([nums.float(), out.sum(dtype=torch.float32).reshape(1)]).cpu())
         want_out.append(out.cpu())
-    runner = MoEStepRunner(layer, t)
+    runner = MoEStepRunner(layer, t, time_copies=True)
     assert runner.h2d_bytes == t * (cfg.hidden * 2 + cfg.topk * 12)
     assert runner.d2h_bytes == 4 * (layer.num_local + 1) + t * cfg.hidden * 2     # the record and the output itself
     got, got_out = [], []
@@ -43,6 +43,8 @@ def test_pipelined_steps_return_each_steps_own_record():
     got_out.append(runner.output(pending).clone())
     assert torch.equal(runner.finish(), got[-1])
     buf.check()
+    times = runner.copy_times()
+    assert times["h2d_ms"] > 0.0 and times["d2h_ms"] > 0.0 and runner.copy_times() == {"h2d_ms": 0.0, "d2h_ms": 0.0}
     for i, (a, b) in enumerate(zip(got, want)):
         assert torch.equal(a[:-1], b[:-1]), f"step {i}: token counts differ"
         assert abs(float(a[-1]) - float(b[-1])) <= 1e-3 * max(1.0, abs(float(b[-1]))), f"step {i}: checksum differs"

@@ -97,8 +97,12 @@ class MoEStepRunner:
     the sum of the output in fp32 (a checksum a caller can log); ``h2d_bytes`` / ``d2h_bytes`` are what
     moves per step."""
 
-    def __init__(self, layer: FusedMoE, tokens: int, copy_output: bool = True):
+    def __init__(self, layer: FusedMoE, tokens: int, copy_output: bool = True, time_copies: bool = False):
         self.layer = layer
+        # time_copies: CUDA events round every host<->device copy (on the copy streams, so they cost the
+        # pipeline nothing); ``copy_times()`` then says how long this rank's copies took per step
+        self.time_copies = time_copies
+        self._copy_events = {"h2d": [], "d2h": []}
         cfg, dev = layer.cfg, layer.buffer.device
         self.copy_stream = torch.cuda.Stream(device=dev)
         self.d2h_stream = torch.cuda.Stream(device=dev)
@@ -127,9 +131,12 @@ class MoEStepRunner:
         slot = self.slots[self._step % 2]
         with nvtx_range("umdk_cam.step.h2d"), torch.cuda.stream(self.copy_stream):
             self.copy_stream.wait_event(slot["free"])
+            ev = self._timed("h2d", self.copy_stream)
             slot["x"].copy_(x_host, non_blocking=True)
             slot["idx"].copy_(idx_host, non_blocking=True)
             slot["w"].copy_(w_host, non_blocking=True)
+            if ev is not None:
+                ev[1].record(self.copy_stream)
             slot["ready"].record(self.copy_stream)
         self._staged = slot
 
@@ -148,15 +155,38 @@ class MoEStepRunner:
         self.computed[r].record(cur)
         with nvtx_range("umdk_cam.step.result_d2h"), torch.cuda.stream(self.d2h_stream):
             self.d2h_stream.wait_event(self.computed[r])
+            ev = self._timed("d2h", self.d2h_stream)
             if self.copy_output:
                 self.out_host[r].copy_(out, non_blocking=True)
                 out.record_stream(self.d2h_stream)
             self.result_host[r].copy_(self.result_dev[r], non_blocking=True)
+            if ev is not None:
+                ev[1].record(self.d2h_stream)
             self.result_done[r].record(self.d2h_stream)
         ticket = self._step
         self._step += 1
         self.last_out = out
         return ticket
+
+    def _timed(self, kind: str, stream):
+        if not self.time_copies:
+            return None
+        pair = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        pair[0].record(stream)
+        self._copy_events[kind].append(pair)
+        return pair
+
+    def copy_times(self, reset: bool = True) -> dict:
+        """Mean milliseconds per step of this rank's host->device and device->host copies since the last call
+        (``time_copies=True``); synchronises both copy streams."""
+        self.copy_stream.synchronize()
+        self.d2h_stream.synchronize()
+        out = {}
+        for kind, pairs in self._copy_events.items():
+            out[kind + "_ms"] = sum(a.elapsed_time(b) for a, b in pairs) / len(pairs) if pairs else 0.0
+        if reset:
+            self._copy_events = {"h2d": [], "d2h": []}
+        return out
 
     def result(self, ticket: int) -> torch.Tensor:
         """Host record of the step with this ticket (waits for that step only); the step's output is then

@@ -34,7 +34,7 @@ def _call(lib, x, idx, e, quant_mode, capacity):
     t, h = x.shape
     k = idx.shape[1]
     esize = 2 if quant_mode == 0 else 1
-    nscale = h // 128 if quant_mode == 3 else 1
+    nscale = h // 128 if quant_mode in (3, 4) else 1
     rx = torch.zeros(capacity, h * esize, dtype=torch.uint8, device=DEV)
     rs = torch.zeros(capacity, nscale, dtype=torch.float32, device=DEV)
     src = torch.full((capacity, 3), -7, dtype=torch.int32, device=DEV)
@@ -47,7 +47,7 @@ def _call(lib, x, idx, e, quant_mode, capacity):
     return rx, rs, src, off, lib.cam_dispatch_local_noalloc_status(stream)
 
 
-@pytest.mark.parametrize("quant_mode", [3, 0])
+@pytest.mark.parametrize("quant_mode", [3, 0, 4])
 def test_noalloc_dispatch_matches_buffer_dispatch_twice(quant_mode):
     lib = _lib()
     t, h, e, k = 150, 512, 24, 4
@@ -69,7 +69,7 @@ def test_noalloc_dispatch_matches_buffer_dispatch_twice(quant_mode):
         assert torch.equal(off.cpu(), want_off) and int(off[-1]) == n
         assert torch.equal(src[:n].cpu().reshape(-1), src0.cpu())
         assert torch.equal(rx[:n].cpu(), rx0.contiguous().view(torch.uint8).reshape(n, -1).cpu())
-        if quant_mode == 3:
+        if quant_mode in (3, 4):
             assert torch.equal(rs[:n].cpu(), rs0.cpu())
         assert (src[n:] == -7).all()  # nothing beyond the last row was touched
     buf.destroy()

@@ -113,14 +113,15 @@ __global__ void __launch_bounds__(kThreads, 1) dispatch_local_kernel(const Local
 
     const int warp = tid >> 5;
     const uint32_t lane = cam::lane_id();
-    const int nscale = (p.quant_mode == CAM_QUANT_FP8_1x128) ? (p.h >> 7) : (p.quant_mode == CAM_QUANT_INT8_TOKEN) ? 1 : 0;
+    const int nscale = CAM_QUANT_IS_FP8(p.quant_mode) ? (p.h >> 7) : (p.quant_mode == CAM_QUANT_INT8_TOKEN) ? 1 : 0;
     const int row_bytes = (p.quant_mode == CAM_QUANT_NONE) ? p.h * 2 : p.h;
     const int stage_bytes = (p.quant_mode == CAM_QUANT_NONE) ? 0 : ((p.h + nscale * 4 + 15) & ~15);
     uint8_t* stage_q = dyn_smem + static_cast<size_t>(warp) * stage_bytes;
     float* stage_s = reinterpret_cast<float*>(stage_q + p.h);
     for (int t = t0 + warp; t < t1; t += kWarps) {
         const __nv_bfloat16* xrow = p.x + static_cast<size_t>(t) * p.h;
-        if (p.quant_mode == CAM_QUANT_FP8_1x128) cam::warp_quant_fp8_1x128(xrow, p.h, stage_q, stage_s);
+        if (p.quant_mode == CAM_QUANT_FP8_1x128) cam::warp_quant_fp8_1x128<false>(xrow, p.h, stage_q, stage_s);
+        else if (p.quant_mode == CAM_QUANT_FP8_1x128_UE8M0) cam::warp_quant_fp8_1x128<true>(xrow, p.h, stage_q, stage_s);
         else if (p.quant_mode == CAM_QUANT_INT8_TOKEN) cam::warp_quant_int8_token(xrow, p.h, stage_q, stage_s);
         __syncwarp();
         for (int k = 0; k < K; ++k) {
@@ -165,7 +166,7 @@ int set_error(int code, const char* fmt, ...) {
 
 int smem_bytes(int h, int quant_mode) {
     if (quant_mode == CAM_QUANT_NONE) return 0;
-    const int nscale = (quant_mode == CAM_QUANT_FP8_1x128) ? h / 128 : 1;
+    const int nscale = CAM_QUANT_IS_FP8(quant_mode) ? h / 128 : 1;
     return kWarps * ((h + nscale * 4 + 15) & ~15);
 }
 
@@ -188,8 +189,8 @@ extern "C" int cam_dispatch_local_noalloc(const void* x, const void* topk_idx, i
         return set_error(CAM_NOALLOC_BAD_ARGUMENT, "experts %d outside [1, %d]", experts, CAM_NOALLOC_MAX_EXPERTS);
     if (hidden < 128 || hidden % 128 != 0 || hidden > 8192)
         return set_error(CAM_NOALLOC_BAD_ARGUMENT, "hidden %d must be a multiple of 128 in [128, 8192]", hidden);
-    if (quant_mode != CAM_QUANT_NONE && quant_mode != CAM_QUANT_INT8_TOKEN && quant_mode != CAM_QUANT_FP8_1x128)
-        return set_error(CAM_NOALLOC_BAD_ARGUMENT, "quant_mode %d is not one of 0, 2, 3", quant_mode);
+    if (quant_mode != CAM_QUANT_NONE && quant_mode != CAM_QUANT_INT8_TOKEN && !CAM_QUANT_IS_FP8(quant_mode))
+        return set_error(CAM_NOALLOC_BAD_ARGUMENT, "quant_mode %d is not one of 0, 2, 3, 4", quant_mode);
     if (quant_mode != CAM_QUANT_NONE && recv_scales == nullptr)
         return set_error(CAM_NOALLOC_BAD_ARGUMENT, "recv_scales is required for quant_mode %d", quant_mode);
     if (capacity < 1) return set_error(CAM_NOALLOC_BAD_ARGUMENT, "capacity must be positive");

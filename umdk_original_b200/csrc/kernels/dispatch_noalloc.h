@@ -19,7 +19,7 @@
 //
 // Limits (a call outside them is rejected with a message, nothing is launched):
 //   tokens * topk <= CAM_NOALLOC_MAX_PAIRS, experts <= CAM_NOALLOC_MAX_EXPERTS,
-//   topk <= 16, hidden a multiple of 128 and <= 8192, quant_mode in {0, 2, 3},
+//   topk <= 16, hidden a multiple of 128 and <= 8192, quant_mode in {0, 2, 3, 4} (4: e4m3 with power-of-two scales),
 //   x, recv_x and recv_scales 16-byte aligned (rows move as 16-byte vectors), the integer arrays aligned to
 //   their element size,
 //   `capacity` (rows the caller's outputs can hold) >= the number of valid pairs, else the call
@@ -56,8 +56,8 @@ extern "C" {
 #define CAM_NOALLOC_OVERFLOW (-3)
 
 // x          [tokens, hidden] bf16 (device)          topk_idx [tokens, topk] int64 or int32 (device)
-// recv_x     [capacity, hidden] bf16 (quant 0) or 1-byte elements (quant 2: int8, 3: e4m3)
-// recv_scales[capacity, hidden/128] (quant 3) or [capacity] (quant 2); may be NULL for quant 0
+// recv_x     [capacity, hidden] bf16 (quant 0) or 1-byte elements (quant 2: int8, 3 and 4: e4m3)
+// recv_scales[capacity, hidden/128] (quant 3, 4) or [capacity] (quant 2); may be NULL for quant 0
 // recv_src   [capacity, 3] int32: (0, token, k) of every row
 // expert_offsets [experts + 1] int32: first row of every expert, last entry = number of rows
 // Returns CAM_NOALLOC_OK or a negative code; cam_dispatch_local_noalloc_error() has the text.

@@ -185,39 +185,46 @@ def run_ours(args, cfg, rank, world, local):
     breakdown = {k: max_over_ranks(sorted(p[k] for p in parts)[len(parts) // 2], world) for k in parts[0]}
 
     e2e = None
+    e2e_record = None
     if not args.no_e2e:
-        runner = MoEStepRunner(layer, tokens, time_copies=True)
         host = [(x.cpu().pin_memory(), idx.cpu().pin_memory(), w.cpu().pin_memory()) for x, idx, w in sets]
-        runner.stage(*host[0])
-        for i in range(3):  # warm-up of the pipelined path
-            runner.run()
-            runner.stage(*host[(i + 1) % len(host)])
-            runner.finish()
-        runner.copy_times()  # forget the warm-up copies
-        barrier(world)
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record()
-        pending = None
-        for i in range(args.steps):
-            ticket = runner.run()                         # step i is launched ...
-            runner.stage(*host[(i + 1) % len(host)])      # ... step i+1's inputs are copied in meanwhile ...
-            if pending is not None:
-                runner.result(pending)                    # ... and the record of step i-1 is read on the host
-            pending = ticket
-        runner.result(pending)                            # every step's record has reached the host
-        t1.record()
-        barrier(world)
-        e2e_ms = max_over_ranks(t0.elapsed_time(t1), world) / args.steps
-        copies = runner.copy_times()
-        copies = {k: max_over_ranks(v, world) for k, v in copies.items()}
-        buf.check()
-        e2e = {"value": tokens * world / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": runner.h2d_bytes, "d2h_bytes_per_step": runner.d2h_bytes,
-               "d2h": "the layer output [tokens, hidden] bf16 and a record of token counts + checksum, every step",
-               # how long the slowest rank's copies of one step take by themselves (they overlap the compute of
-               # the neighbouring steps; a value near ms_per_step means the host link, not the GPU, sets the pace)
-               "h2d_ms_max_over_ranks": copies["h2d_ms"], "d2h_ms_max_over_ranks": copies["d2h_ms"]}
-        del runner, host
+
+        def run_e2e(copy_output: bool):
+            runner = MoEStepRunner(layer, tokens, copy_output=copy_output, time_copies=True)
+            runner.stage(*host[0])
+            for i in range(3):  # warm-up of the pipelined path
+                runner.run()
+                runner.stage(*host[(i + 1) % len(host)])
+                runner.finish()
+            runner.copy_times()  # forget the warm-up copies
+            barrier(world)
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            pending = None
+            for i in range(args.steps):
+                ticket = runner.run()                         # step i is launched ...
+                runner.stage(*host[(i + 1) % len(host)])      # ... step i+1's inputs are copied in meanwhile ...
+                if pending is not None:
+                    runner.result(pending)                    # ... and the record of step i-1 is read on the host
+                pending = ticket
+            runner.result(pending)                            # every step's record has reached the host
+            t1.record()
+            barrier(world)
+            ms = max_over_ranks(t0.elapsed_time(t1), world) / args.steps
+            copies = {k: max_over_ranks(v, world) for k, v in runner.copy_times().items()}
+            buf.check()
+            return {"value": tokens * world / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+                    "h2d_bytes_per_step": runner.h2d_bytes, "d2h_bytes_per_step": runner.d2h_bytes,
+                    # how long the slowest rank's copies of one step take by themselves (they overlap the compute of
+                    # the neighbouring steps; a value near ms_per_step means the host link, not the GPU, sets the pace)
+                    "h2d_ms_max_over_ranks": copies["h2d_ms"], "d2h_ms_max_over_ranks": copies["d2h_ms"]}
+
+        e2e = run_e2e(True)
+        e2e["d2h"] = "the layer output [tokens, hidden] bf16 and a record of token counts + checksum, every step"
+        # the same with only the record read back (what a training step that keeps its activations on the device reads)
+        e2e_record = run_e2e(False)
+        e2e_record["d2h"] = "a record of token counts + checksum, every step; the output stays on the device"
+        del host
 
     # the comparison layer (NCCL all_to_all_single + library GEMMs) at the same N on the same inputs, after the timed regions
     base = None
@@ -255,8 +262,12 @@ def run_ours(args, cfg, rank, world, local):
             "tflops_per_gpu": cfg.flops_per_token() * tokens / (ms * 1e-3) / 1e12,
             "stage_ms_max_over_ranks": breakdown,
         }
+        # three launches per step = a fused route: "gemm1_ms" is then the one kernel that runs both GEMMs and the combine
+        # send (and, when "dispatch_ms" is only the count exchange and quantisation, the dispatch rows too)
+        line["route"] = "fused kernel (3 launches)" if round(launches / args.steps) == 3 else "four launches"
         if e2e is not None:
             line["e2e"] = e2e
+            line["e2e_record_only"] = e2e_record
         if base is not None:
             line["baseline"] = base
         if max_err is not None:

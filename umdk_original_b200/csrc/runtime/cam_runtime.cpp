@@ -1283,16 +1283,19 @@ static int fused_moe_deep(CamBuffer* b, const void* x, const void* expert_ids, i
     return 0;
 }
 
-// Whether the deep-fused route serves this call.  It is opt-in (UMDK_CAM_DEEP_FUSE=1, read when the Buffer is created):
-// measured on one and two B200s the single kernel is slower than the four launches, because its tensor-core pipeline
-// runs at a lower duty than the stand-alone CTA-pair GEMMs (see the fused kernel's wait breakdown, Buffer.read_fused_waits).
-// Needs block-scaled fp8 with power-of-two scales and hidden sizes whose scale rows are whole 16-byte pieces.
-// UMDK_CAM_DEEP_FUSE=2 keeps the normal dispatch as launch 1 and uses the fused kernel for the two GEMMs only (their
-// tiles interleaved, so that the combine rows leave during the whole compute time instead of during the second GEMM).
+// Which route serves the block-scaled fused layer: 0 = four launches, 1 = deep-fused (the fused kernel sends the
+// dispatch rows itself), 2 = normal dispatch, then the fused kernel for the two GEMMs.  UMDK_CAM_DEEP_FUSE=0/1/2 (read
+// when the Buffer is created) forces one.  Unset, the deep-fused route is taken where it measured faster: on 8 GPUs with
+// experts of about a thousand rows (DeepSeek-V3 shapes, 4096 tokens per rank: 1.85 ms against 2.07 ms per layer),
+// because seven eighths of the combine rows then cross NVLink and the second GEMM alone cannot hide them, while the
+// fused kernel spreads them over both GEMMs.  On 1, 2 and 4 GPUs the four launches measured faster (the two GEMMs inside
+// the fused kernel run 7 - 18 % slower than the stand-alone kernels, most on small experts).
+// The fused kernel needs power-of-two scales and hidden sizes whose scale rows are whole 16-byte pieces.
 static int use_deep_fuse(const CamBuffer* b, bool ue8m0, int h, int inter, int rows_hint) {
-    (void)rows_hint;
-    if (!ue8m0 || (b->env_deep_fuse != 1 && b->env_deep_fuse != 2)) return 0;
-    return (h % 512 == 0 && h <= 7168 && inter % 128 == 0) ? b->env_deep_fuse : 0;
+    if (!ue8m0 || b->env_deep_fuse == 0) return 0;
+    if (!(h % 512 == 0 && h <= 7168 && inter % 128 == 0)) return 0;
+    if (b->env_deep_fuse == 1 || b->env_deep_fuse == 2) return b->env_deep_fuse;
+    return (b->num_ranks >= 8 && rows_hint >= 768) ? 1 : 0;
 }
 
 static int fused_moe_impl(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,

@@ -223,20 +223,22 @@ dispatch_normal_kernel(const DispatchNormalParams p) {
         const bool bulk_scales = bulk_rows && ((nscale * 4) % 16 == 0);
         if (p.defer_push) {
             // Nothing is pushed here.  Position of every pair in the send list: pairs are ordered by (local expert
-            // at the destination, destination rank, scan order), so expert 0 of every rank is served first.
+            // at the destination, destination rank counted from this rank on, scan order), so expert 0 of every rank is
+            // served first and, at any one time, the ranks of the group send to different destinations.
             int* s_mine = reinterpret_cast<int*>(dyn_smem);  // the staging area is unused in this mode
             for (int e = tid; e < E; e += kDispThreads)
                 s_mine[e] = s_rank_ok[e / El] ? __ldcg(&cm[static_cast<size_t>(p.rank) * E + e]) : 0;
             __syncthreads();
             for (int e = tid; e < E; e += kDispThreads) {
                 const int d = e / El, le = e - d * El;
+                const int turn = (d - p.rank + R) % R;  // place of destination d in this rank's order
                 int pre = 0;
-                for (int l2 = 0; l2 <= le; ++l2) {
-                    const int dmax = (l2 < le) ? R : d;
-                    for (int d2 = 0; d2 < dmax; ++d2) pre += s_mine[d2 * El + l2];
-                }
+                for (int l2 = 0; l2 < le; ++l2)
+                    for (int d2 = 0; d2 < R; ++d2) pre += s_mine[d2 * El + l2];
+                for (int t2 = 0; t2 < turn; ++t2) pre += s_mine[((p.rank + t2) % R) * El + le];
                 s_hist[e] = pre;
-                if (b == 0 && e == E - 1) p.send_list_len[0] = pre + s_mine[e];  // expert E - 1 has the last key
+                // the last key: the last local expert of the destination this rank serves last
+                if (b == 0 && le == El - 1 && turn == R - 1) p.send_list_len[0] = pre + s_mine[e];
             }
             __syncthreads();
             for (int t = t0 + warp; t < t1; t += kDispWarps) {

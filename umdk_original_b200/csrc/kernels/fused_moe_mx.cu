@@ -107,6 +107,13 @@ struct FusedWalker {
                 const int local = tile - base;
                 mt = local / per;
                 nt = local - mt * per;
+                if (sub && p.num_ranks > 1) {
+                    // second GEMM: this rank starts the expert's row blocks (ordered by origin rank) at its own offset, so
+                    // that the ranks of the group push their combine rows to different origins at any one time
+                    const int blocks = (cnt + 2 * BM - 1) / (2 * BM);
+                    mt += p.rank * blocks / p.num_ranks;
+                    if (mt >= blocks) mt -= blocks;
+                }
                 row0 = first + mt * 2 * BM;
                 rows = min(2 * BM, cnt - mt * 2 * BM);
                 e_out = e;

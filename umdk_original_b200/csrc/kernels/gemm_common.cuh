@@ -21,7 +21,11 @@ struct TileWalkerT {
     int e, base;
     __device__ TileWalkerT(const int* o, int ne, int nt) : off(o), num_experts(ne), n_tiles(nt), e(0), base(0) {}
     // Maps a linear tile index (monotonically increasing across calls) to its expert and tile.
-    __device__ bool locate(int tile, int& e_out, int& mt, int& nt, int& row0, int& rows) {
+    // rot_den > 0: the row blocks of every expert are visited starting at block rot_num * blocks / rot_den (and wrapping
+    // round).  The kernels whose epilogue pushes rows to the tokens' origin ranks pass (rank, ranks): an expert's rows are
+    // ordered by origin rank, so without this every rank of the group would push to the same origin at the same time and
+    // share that one GPU's ingress, one eighth of the link each on 8 GPUs.
+    __device__ bool locate(int tile, int& e_out, int& mt, int& nt, int& row0, int& rows, int rot_num = 0, int rot_den = 0) {
         while (e < num_experts) {
             const int first = __ldg(off + e);
             const int cnt = __ldg(off + e + 1) - first;
@@ -30,6 +34,11 @@ struct TileWalkerT {
                 const int local = tile - base;
                 mt = local / n_tiles;
                 nt = local - mt * n_tiles;
+                if (rot_den > 0) {
+                    const int blocks = (cnt + TM - 1) / TM;
+                    mt += rot_num * blocks / rot_den;
+                    if (mt >= blocks) mt -= blocks;
+                }
                 row0 = first + mt * TM;
                 rows = min(TM, cnt - mt * TM);
                 e_out = e;

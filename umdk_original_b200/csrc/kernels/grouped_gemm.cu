@@ -72,6 +72,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     const int warp = static_cast<int>(threadIdx.x) >> 5;
     const uint32_t lane = lane_id();
     const int kblocks = p.k_dim / BK;
+    // combine-send form: this rank starts every expert's row blocks at its own offset (see TileWalkerT::locate)
+    const int rot_num = (p.mode == 2 && p.num_ranks > 1) ? p.rank : 0, rot_den = (p.mode == 2 && p.num_ranks > 1) ? p.num_ranks : 0;
     const int n_tiles = (p.mode == 1) ? (p.n_dim / 2) / 128 : (p.n_dim + BN - 1) / BN;
 
     if (threadIdx.x == 0) {
@@ -105,7 +107,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             uint32_t it = 0;
             int e, mt, nt, row0, rows;
             bool ok = true;
-            for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
+            for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows, rot_num, rot_den);
                  tile += static_cast<int>(gridDim.x)) {
                 const int brow_lo = e * p.n_dim + ((p.mode == 1) ? nt * 128 : nt * BN);
                 const int brow_hi = (p.mode == 1) ? (e * p.n_dim + p.n_dim / 2 + nt * 128) : (brow_lo + 128);
@@ -127,7 +129,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             uint32_t it = 0;
             int e, mt, nt, row0, rows;
             bool ok = true;
-            for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
+            for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows, rot_num, rot_den);
                  tile += static_cast<int>(gridDim.x)) {
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
@@ -162,7 +164,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         uint32_t tile_parity = 0;
         int e, mt, nt, row0, rows;
         bool ok = true;
-        for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
+        for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows, rot_num, rot_den);
              tile += static_cast<int>(gridDim.x), tile_parity ^= 1u) {
             const bool valid = r < rows && row0 + r < p.a_rows;  // never a row at or past the end of A
             const int grow = row0 + (valid ? r : 0);

@@ -62,6 +62,8 @@ grouped_gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const int warp = static_cast<int>(threadIdx.x) >> 5;
     const uint32_t lane = lane_id();
     const int kblocks = p.k_dim / BK;
+    // combine-send form: this rank starts every expert's row blocks at its own offset (see TileWalkerT::locate)
+    const int rot_num = (p.mode == 2 && p.num_ranks > 1) ? p.rank : 0, rot_den = (p.mode == 2 && p.num_ranks > 1) ? p.num_ranks : 0;
     const int n_tiles = (p.mode == 1) ? (p.n_dim / 2) / 128 : (p.n_dim + BN - 1) / BN;
 
     if (threadIdx.x == 0) {
@@ -94,7 +96,7 @@ grouped_gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             uint32_t it = 0;
             int e, mt, nt, row0, rows;
             bool ok = true;
-            for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
+            for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows, rot_num, rot_den);
                  tile += static_cast<int>(gridDim.x)) {
                 const int brow_lo = e * p.n_dim + ((p.mode == 1) ? nt * 128 : nt * BN);
                 const int brow_hi = (p.mode == 1) ? (e * p.n_dim + p.n_dim / 2 + nt * 128) : (brow_lo + 128);
@@ -116,7 +118,7 @@ grouped_gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             uint32_t it = 0, tcount = 0;
             int e, mt, nt, row0, rows;
             bool ok = true;
-            for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
+            for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows, rot_num, rot_den);
                  tile += static_cast<int>(gridDim.x), ++tcount) {
                 // the epilogue must have drained the previous tile before its columns are overwritten
                 if (!mbar_wait_bounded(bar_tempty, (tcount & 1u) ^ 1u, abort_flag)) { ok = false; break; }
@@ -152,7 +154,7 @@ grouped_gemm_w8a8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         uint32_t tcount = 0;
         int e, mt, nt, row0, rows;
         bool ok = true;
-        for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
+        for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows, rot_num, rot_den);
              tile += static_cast<int>(gridDim.x), ++tcount) {
             const bool valid = r < rows && row0 + r < p.a_rows;  // never a row at or past the end of A
             const int grow = row0 + (valid ? r : 0);

@@ -104,6 +104,8 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     const int warp = static_cast<int>(threadIdx.x) >> 5;
     const uint32_t lane = lane_id();
     const int kblocks = p.k_dim / BK;
+    // combine-send form: this rank starts every expert's row blocks at its own offset (see TileWalkerT::locate)
+    const int rot_num = (p.mode == 2 && p.num_ranks > 1) ? p.rank : 0, rot_den = (p.mode == 2 && p.num_ranks > 1) ? p.num_ranks : 0;
     const int n_tiles = (p.mode == 1) ? (p.n_dim / 2) / 128 : (p.n_dim + BN - 1) / BN;
     const int nblk = p.n_dim / 128;
 
@@ -137,7 +139,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             uint32_t it = 0;
             int e, mt, nt, row0, rows;
             bool ok = true;
-            for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
+            for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows, rot_num, rot_den);
                  tile += static_cast<int>(gridDim.x)) {
                 const int brow_lo = e * p.n_dim + ((p.mode == 1) ? nt * 128 : nt * BN);
                 const int brow_hi = (p.mode == 1) ? (e * p.n_dim + p.n_dim / 2 + nt * 128) : (brow_lo + 128);
@@ -159,7 +161,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
             uint32_t it = 0, tcount = 0;
             int e, mt, nt, row0, rows;
             bool ok = true;
-            for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
+            for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows, rot_num, rot_den);
                  tile += static_cast<int>(gridDim.x), ++tcount) {
                 // the epilogue must have drained the previous tile before its columns are overwritten
                 if (!mbar_wait_bounded(bar_tempty, (tcount & 1u) ^ 1u, abort_flag)) { ok = false; break; }
@@ -207,7 +209,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         // rows of scales can be read 16 bytes at a time when K is a multiple of 512 and the arrays are aligned
         const bool vec_scales = (kblocks & 3) == 0 &&
                                 ((reinterpret_cast<uintptr_t>(p.a_scales) | reinterpret_cast<uintptr_t>(p.b_scales)) & 15u) == 0u;
-        for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
+        for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows, rot_num, rot_den);
              tile += static_cast<int>(gridDim.x)) {
             const float* as[4];
 #pragma unroll
@@ -310,7 +312,7 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         uint32_t tcount = 0, halves = 0;
         int e, mt, nt, row0, rows;
         bool ok = true;
-        for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows);
+        for (int tile = static_cast<int>(blockIdx.x); ok && w.locate(tile, e, mt, nt, row0, rows, rot_num, rot_den);
              tile += static_cast<int>(gridDim.x), ++tcount) {
             const bool valid = r < rows && row0 + r < p.a_rows;  // never a row at or past the end of A
             const int grow = row0 + (valid ? r : 0);

@@ -87,6 +87,8 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
     const int pair_id = static_cast<int>(blockIdx.x) >> 1;
     const int num_pairs = static_cast<int>(gridDim.x) >> 1;
     const int kblocks = p.k_dim / BK;
+    // combine-send form: this rank starts every expert's row blocks at its own offset (see TileWalkerT::locate)
+    const int rot_num = (p.mode == 2 && p.num_ranks > 1) ? p.rank : 0, rot_den = (p.mode == 2 && p.num_ranks > 1) ? p.num_ranks : 0;
     const int n_tiles = (p.mode == 1) ? (p.n_dim / 2) / 128 : (p.n_dim + BN - 1) / BN;
     const int nblk = p.n_dim / 128;
 
@@ -121,7 +123,7 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
             uint32_t it = 0;
             int e, mt, nt, row0, rows;
             bool ok = true;
-            for (int tile = pair_id; ok && w.locate(tile, e, mt, nt, row0, rows); tile += num_pairs) {
+            for (int tile = pair_id; ok && w.locate(tile, e, mt, nt, row0, rows, rot_num, rot_den); tile += num_pairs) {
                 const int brow_lo = e * p.n_dim + ((p.mode == 1) ? nt * 128 : nt * BN);
                 const int brow_hi = (p.mode == 1) ? (e * p.n_dim + p.n_dim / 2 + nt * 128) : (brow_lo + 128);
                 const int my_arow = row0 + static_cast<int>(cta) * BM;
@@ -145,7 +147,7 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
             int e, mt, nt, row0, rows;
             bool ok = true;
             const uint32_t tfull0 = map_to_cta(bar_tfull, 0), tfull1 = map_to_cta(bar_tfull, 1);
-            for (int tile = pair_id; ok && w.locate(tile, e, mt, nt, row0, rows); tile += num_pairs, ++tcount) {
+            for (int tile = pair_id; ok && w.locate(tile, e, mt, nt, row0, rows, rot_num, rot_den); tile += num_pairs, ++tcount) {
                 // both epilogues must have drained the previous tile before its columns are overwritten
                 if (!mbar_wait_bounded(bar_tempty, (tcount & 1u) ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
@@ -183,7 +185,7 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
         // rows of scales can be read 16 bytes at a time when K is a multiple of 512 and the arrays are aligned
         const bool vec_scales = (kblocks & 3) == 0 &&
                                 ((reinterpret_cast<uintptr_t>(p.a_scales) | reinterpret_cast<uintptr_t>(p.b_scales)) & 15u) == 0u;
-        for (int tile = pair_id; ok && w.locate(tile, e, mt, nt, row0, rows); tile += num_pairs) {
+        for (int tile = pair_id; ok && w.locate(tile, e, mt, nt, row0, rows, rot_num, rot_den); tile += num_pairs) {
             const float* as[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {  // this CTA's 128 rows of the 256-row tile
@@ -288,7 +290,7 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
         uint32_t tcount = 0, halves = 0;
         int e, mt, nt, row0, rows;
         bool ok = true;
-        for (int tile = pair_id; ok && w.locate(tile, e, mt, nt, row0, rows); tile += num_pairs, ++tcount) {
+        for (int tile = pair_id; ok && w.locate(tile, e, mt, nt, row0, rows, rot_num, rot_den); tile += num_pairs, ++tcount) {
             row0 += static_cast<int>(cta) * BM;            // this CTA's half of the 256-row tile
             rows = max(0, min(BM, rows - static_cast<int>(cta) * BM));
             const bool valid = r < rows && row0 + r < p.a_rows;  // never a row at or past the end of A

@@ -64,7 +64,12 @@ __global__ void __launch_bounds__(kCombThreads, 1) combine_kernel(const CombineP
     // ------------------------------------------------------------------ SEND
     if (p.phase_mask & CAM_PHASE_SEND) {
         const int n = p.total_rows[0];
-        for (int i = gwarp; i < n; i += nwarps) {
+        // Rows are ordered by expert and, inside an expert, by origin rank.  Every rank starts its walk somewhere else
+        // (its share of the rows plus one grid-wide step per rank further on), so that at any one time the ranks of the
+        // group push to different origins instead of all filling the same GPU's ingress.
+        const int shift = (p.R > 1 && n > 0) ? static_cast<int>((static_cast<long long>(p.rank) * (n / p.R + nwarps)) % n) : 0;
+        for (int i0 = gwarp; i0 < n; i0 += nwarps) {
+            const int i = (i0 + shift < n) ? i0 + shift : i0 + shift - n;
             const int src = p.row_src[static_cast<size_t>(i) * 3 + 0];
             const int t = p.row_src[static_cast<size_t>(i) * 3 + 1];
             const int k = p.row_src[static_cast<size_t>(i) * 3 + 2];

@@ -181,3 +181,40 @@ def test_deep_fused_layer_runs_complete_experts_and_reports_a_held_back_rank(mon
         assert ((every[PHASE_FINAL][r][0].cpu().float() - wf).abs() / row_scale).max().item() <= 0.04
     for b in bufs:
         b.destroy()
+
+
+def test_route_follows_rank_count_expert_size_and_the_switch(monkeypatch):
+    """Unset, the deep-fused route is taken on 8 ranks or more when experts get 768 rows or more on average; the switch
+    forces any route.  The layer gives the same answer on every route (8 virtual ranks on one GPU)."""
+    world, t, h, inter, e, k = 8, 192, 512, 256, 8, 4   # 192 * 4 * 8 / 8 = 768 rows per expert
+    xs, topk, wts, w = _case(world, t, h, inter, e, k, seed=77, holes=False)
+    cfg = u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, timeout_ms=3000.0)
+    local = _local_weights(w, world, e)
+    dx, dk, dw = ([v.to(DEV) for v in part] for part in (xs, topk, wts))
+    monkeypatch.delenv("UMDK_CAM_DEEP_FUSE", raising=False)
+    bufs = u.Buffer.virtual(world, cfg, DEV, name="route_auto_")
+    assert bufs[0].fused_route(t, inter) == "deep-fused"
+    assert bufs[0].fused_route(t // 2, inter) == "four launches"          # 384 rows per expert
+    assert bufs[0].fused_route(t, inter, hidden=640) == "four launches"    # scale rows not whole 16-byte pieces
+
+    def step(r):
+        wl = local[r]
+        return ops.fused_deep_moe(dx[r], dk[r], [wl.w1], [wl.s1], [wl.w2], [wl.s2], dw[r], None, None, bufs[r].name, world,
+                                  r, e, 0, 0, 4, 0)
+
+    every = run_virtual(step, world, return_all=True)
+    outs = [every[PHASE_FINAL][r][0].cpu().float() for r in range(world)]
+    for b in bufs:
+        b.check()
+        b.destroy()
+    small = u.Buffer.virtual(2, cfg, DEV, name="route_two_")
+    assert small[0].fused_route(t * 4, inter) == "four launches"           # two ranks: never by default
+    for b in small:
+        b.destroy()
+    bufs_u, _, outs_u, _ = _run_layer(monkeypatch, 0, world, cfg, "route_flat_", dx, dk, dw, local, e)
+    assert bufs_u[0].fused_route(t, inter) == "four launches"
+    for b in bufs_u:
+        b.destroy()
+    for r in range(world):
+        scale = outs_u[r].abs().amax(dim=1, keepdim=True) + 1e-6
+        assert ((outs[r] - outs_u[r]).abs() / scale).max().item() <= 0.02

@@ -135,6 +135,10 @@ public:
         return view(static_cast<uint8_t*>(cam_buffer_base(buf_)) + offs[i], {CAM_GUARD_BYTES}, at::kByte);
     }
     int64_t launch_count() const { return static_cast<int64_t>(cam_buffer_launch_count(buf_)); }
+    int64_t fused_route(int64_t tokens, int64_t topk, int64_t hidden, int64_t inter, int64_t experts) const {
+        return cam_buffer_fused_route(buf_, static_cast<int>(tokens), static_cast<int>(topk), static_cast<int>(hidden),
+                                      static_cast<int>(inter), static_cast<int>(experts));
+    }
     void set_fused_trace(bool on) { CAM_RT(cam_buffer_set_fused_trace(buf_, on ? 1 : 0)); }
     std::vector<int64_t> read_fused_trace(int64_t num_local_experts) {
         std::vector<long long> t(static_cast<size_t>(num_local_experts));
@@ -988,6 +992,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("set_trace", &Buffer::set_trace)
         .def("read_trace", &Buffer::read_trace)
         .def("launch_count", &Buffer::launch_count)
+        .def("fused_route", &Buffer::fused_route)
         .def("read_stats", &Buffer::read_stats)
         .def("check_guards", &Buffer::check_guards)
         .def("guard", &Buffer::guard)

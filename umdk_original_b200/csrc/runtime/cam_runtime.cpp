@@ -1298,6 +1298,12 @@ static int use_deep_fuse(const CamBuffer* b, bool ue8m0, int h, int inter, int r
     return (b->num_ranks >= 8 && rows_hint >= 768) ? 1 : 0;
 }
 
+extern "C" int cam_buffer_fused_route(CamBuffer* b, int T, int K, int h, int inter, int E) {
+    if (b == nullptr || E <= 0) return 0;
+    const int rows_hint = static_cast<int>(static_cast<int64_t>(T) * K * b->num_ranks / E);
+    return use_deep_fuse(b, true, h, inter, rows_hint);
+}
+
 static int fused_moe_impl(CamBuffer* b, const void* x, const void* expert_ids, int idx_is_i64,
                           const float* topk_weights, const void* w1_q, const float* w1_s, const void* w2_q,
                           const float* w2_s, void* out, int64_t* expert_token_nums, int T, int K, int h, int inter,

@@ -63,6 +63,9 @@ int cam_buffer_set_trace(CamBuffer* b, int on);
 int cam_buffer_read_trace(CamBuffer* b, unsigned long long* out16);
 int cam_buffer_check_guards(CamBuffer* b, cudaStream_t stream, int* damaged);  // bit i: guard behind region i was overwritten
 unsigned long long cam_buffer_launch_count(CamBuffer* b);
+// Route the block-scaled fused layer (power-of-two scales) takes for these shapes on this Buffer: 0 = four launches,
+// 1 = deep-fused kernel, 2 = normal dispatch + fused GEMMs.  T = tokens of this rank, K = top-k, E = all experts.
+int cam_buffer_fused_route(CamBuffer* b, int T, int K, int h, int inter, int E);
 int cam_buffer_read_stats(CamBuffer* b, unsigned long long* out_wait_ns, unsigned long long* out_rows,
                           unsigned long long* out_calls, int reset);  // kernels launched by this buffer's ops so far
 int cam_buffer_set_fused_trace(CamBuffer* b, int on);

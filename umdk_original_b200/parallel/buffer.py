@@ -248,6 +248,17 @@ class Buffer:
         v = self._native.read_fused_waits(n)
         return dict(zip(("loop_cycles", "wait_accumulator", "wait_scale_factors", "wait_operands", "k_blocks", "tiles", "issue_cycles"), v))
 
+    def fused_route(self, tokens: int, intermediate: int, hidden: Optional[int] = None, topk: Optional[int] = None,
+                    num_experts: Optional[int] = None) -> str:
+        """Which route ``fused_deep_moe`` takes on this Buffer for block-scaled fp8 weights with power-of-two scales
+        and these shapes: ``"four launches"``, ``"deep-fused"`` (one kernel sends the dispatch rows, runs both GEMMs
+        and pushes the combine rows) or ``"dispatch + fused GEMMs"``.  The choice follows ``UMDK_CAM_DEEP_FUSE`` as it
+        was when the Buffer was created, else the rank count and the mean rows per expert."""
+        cfg = self.config
+        r = self._native.fused_route(tokens, topk or cfg.topk, hidden or cfg.hidden, intermediate,
+                                     num_experts or cfg.num_experts) if self._native is not None else 0
+        return ("four launches", "deep-fused", "dispatch + fused GEMMs")[int(r)]
+
     def set_profile(self, on: bool = True) -> None:
         """Per-stage device timing of ``fused_deep_moe`` (CUDA events around its four launches)."""
         if self._native is not None:

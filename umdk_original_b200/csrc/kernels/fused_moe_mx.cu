@@ -66,9 +66,6 @@ constexpr uint32_t kFmLaunchRegs = 80, kFmCtrlRegs = 40, kFmSfRegs = 80, kFmEpiR
 static_assert(128 * kFmCtrlRegs + 128 * kFmSfRegs + kFmEpiThreads * kFmEpiRegs <= kFmLaunchRegs * kFmThreads,
               "setmaxnreg budget exceeds the registers the CTA owns: the kernel would hang");
 
-__device__ __forceinline__ uint32_t fm_ue8m0_word(float scale) {
-    return ((__float_as_uint(scale) >> 23) & 0xFFu) * 0x01010101u;
-}
 // Activation scales are read through L1 although other SMs or GPUs write them during this kernel.  Every warp that
 // reads a row has itself acquired the counter that says the row is complete (a system- or GPU-scope acquire load, after
 // which its ordinary loads must observe the released stores, whichever cache operator they carry), and rows outside
@@ -78,11 +75,6 @@ __device__ __forceinline__ float4 ld_ca_v4f32(const float4* p) {
     float4 v;
     asm volatile("ld.global.ca.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
     return v;
-}
-// the biased exponents (UE8M0 codes) of four power-of-two scales, one byte each
-__device__ __forceinline__ uint32_t fm_pack_exp4(float a, float b, float c, float d) {
-    return ((__float_as_uint(a) >> 23) & 0xFFu) | (((__float_as_uint(b) >> 23) & 0xFFu) << 8) |
-           (((__float_as_uint(c) >> 23) & 0xFFu) << 16) | (((__float_as_uint(d) >> 23) & 0xFFu) << 24);
 }
 
 // Order of the tiles of one launch.  Step j of the walk holds the first GEMM of expert j (while j < E_local) and
@@ -583,9 +575,9 @@ fused_moe_pair_kernel(const __grid_constant__ CUtensorMap tmap_a1, const __grid_
                 };
                 load_group(0);
                 for (int g = 0; ok && g < ngroups; ++g) {
-                    const uint32_t pa0 = fm_pack_exp4(na0.x, na0.y, na0.z, na0.w), pa1 = fm_pack_exp4(na1.x, na1.y, na1.z, na1.w);
-                    const uint32_t pa2 = fm_pack_exp4(na2.x, na2.y, na2.z, na2.w), pa3 = fm_pack_exp4(na3.x, na3.y, na3.z, na3.w);
-                    const uint32_t pbl = fm_pack_exp4(nbl[0], nbl[1], nbl[2], nbl[3]), pbh = fm_pack_exp4(nbh[0], nbh[1], nbh[2], nbh[3]);
+                    const uint32_t pa0 = ue8m0_pack4(na0.x, na0.y, na0.z, na0.w), pa1 = ue8m0_pack4(na1.x, na1.y, na1.z, na1.w);
+                    const uint32_t pa2 = ue8m0_pack4(na2.x, na2.y, na2.z, na2.w), pa3 = ue8m0_pack4(na3.x, na3.y, na3.z, na3.w);
+                    const uint32_t pbl = ue8m0_pack4(nbl[0], nbl[1], nbl[2], nbl[3]), pbh = ue8m0_pack4(nbh[0], nbh[1], nbh[2], nbh[3]);
                     const int left = kblocks - 4 * g;
                     ok = put(__byte_perm(pa0, 0, 0x0000), __byte_perm(pa1, 0, 0x0000), __byte_perm(pa2, 0, 0x0000),
                              __byte_perm(pa3, 0, 0x0000), __byte_perm(pbl, 0, 0x0000), __byte_perm(pbh, 0, 0x0000));

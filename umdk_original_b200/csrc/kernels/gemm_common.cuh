@@ -53,6 +53,19 @@ struct TileWalkerT {
 
 using TileWalker = TileWalkerT<BM>;
 
+// A power-of-two scale as the word tcgen05 block scaling reads: its biased exponent (UE8M0 code) in all four bytes.
+__device__ __forceinline__ uint32_t ue8m0_word(float scale) {
+    return ((__float_as_uint(scale) >> 23) & 0xFFu) * 0x01010101u;
+}
+// The biased exponents (UE8M0 codes) of four power-of-two scales, one byte each: what the scale-factor warps of the
+// block-scaled kernels make of a 16-byte load of four K-blocks' scales.  Byte i, replicated by __byte_perm(w, 0, 0x1111 * i),
+// is the scale word of K-block i.
+__device__ __forceinline__ uint32_t ue8m0_pack4(float a, float b, float c, float d) {
+    return ((__float_as_uint(a) >> 23) & 0xFFu) | (((__float_as_uint(b) >> 23) & 0xFFu) << 8) |
+           (((__float_as_uint(c) >> 23) & 0xFFu) << 16) | (((__float_as_uint(d) >> 23) & 0xFFu) << 24);
+}
+__device__ __forceinline__ uint32_t ue8m0_pack4(const float4& v) { return ue8m0_pack4(v.x, v.y, v.z, v.w); }
+
 __device__ __forceinline__ void gemm_record_status(CamStatus* st, int code, int who, int detail) {
     if (atomicCAS(&st->code, 0, code) == 0) {
         st->who = who;

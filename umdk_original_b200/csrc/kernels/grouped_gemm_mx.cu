@@ -72,15 +72,6 @@ constexpr uint32_t kMxLaunchRegs = 80, kMxCtrlRegs = 32, kMxSfRegs = 56, kMxEpiR
 static_assert(128 * kMxCtrlRegs + 128 * kMxSfRegs + kMxEpiThreads * kMxEpiRegs <= kMxLaunchRegs * kMxThreads,
               "setmaxnreg budget exceeds the registers the CTA owns: the kernel would hang");
 
-// the biased exponents (UE8M0 codes) of four power-of-two scales, one byte each
-__device__ __forceinline__ uint32_t mx_pack_exp4(const float4& v) {
-    return ((__float_as_uint(v.x) >> 23) & 0xFFu) | (((__float_as_uint(v.y) >> 23) & 0xFFu) << 8) |
-           (((__float_as_uint(v.z) >> 23) & 0xFFu) << 16) | (((__float_as_uint(v.w) >> 23) & 0xFFu) << 24);
-}
-__device__ __forceinline__ uint32_t ue8m0_word(float scale) {
-    return ((__float_as_uint(scale) >> 23) & 0xFFu) * 0x01010101u;
-}
-
 template <bool SWAP, int NS, int NSTG>
 __global__ void __launch_bounds__(kMxThreads, 1)
 grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -256,9 +247,9 @@ grouped_gemm_mxfp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
                 for (int g = 0; ok && g < ngroups; ++g) {
                     uint32_t pk[6];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) pk[j] = mx_pack_exp4(na[j]);
-                    pk[4] = mx_pack_exp4(nbl);
-                    pk[5] = mx_pack_exp4(nbh);
+                    for (int j = 0; j < 4; ++j) pk[j] = ue8m0_pack4(na[j]);
+                    pk[4] = ue8m0_pack4(nbl);
+                    pk[5] = ue8m0_pack4(nbh);
                     ok = put(__byte_perm(pk[0], 0, 0x0000), __byte_perm(pk[1], 0, 0x0000), __byte_perm(pk[2], 0, 0x0000),
                              __byte_perm(pk[3], 0, 0x0000), __byte_perm(pk[4], 0, 0x0000), __byte_perm(pk[5], 0, 0x0000));
                     // the next group's loads go out only after the arrive above, which has release semantics and

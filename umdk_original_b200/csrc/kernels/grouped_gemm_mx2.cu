@@ -52,15 +52,6 @@ constexpr uint32_t kP2LaunchRegs = 80, kP2CtrlRegs = 32, kP2SfRegs = 56, kP2EpiR
 static_assert(128 * kP2CtrlRegs + 128 * kP2SfRegs + kP2EpiThreads * kP2EpiRegs <= kP2LaunchRegs * kP2Threads,
               "setmaxnreg budget exceeds the registers the CTA owns: the kernel would hang");
 
-// the biased exponents (UE8M0 codes) of four power-of-two scales, one byte each
-__device__ __forceinline__ uint32_t pack_exp4(const float4& v) {
-    return ((__float_as_uint(v.x) >> 23) & 0xFFu) | (((__float_as_uint(v.y) >> 23) & 0xFFu) << 8) |
-           (((__float_as_uint(v.z) >> 23) & 0xFFu) << 16) | (((__float_as_uint(v.w) >> 23) & 0xFFu) << 24);
-}
-__device__ __forceinline__ uint32_t ue8m0_word2(float scale) {
-    return ((__float_as_uint(scale) >> 23) & 0xFFu) * 0x01010101u;
-}
-
 template <int NS, int NSTG>
 __global__ void __launch_bounds__(kP2Threads, 1)
 grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -234,9 +225,9 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
                 for (int g = 0; ok && g < ngroups; ++g) {
                     uint32_t pk[6];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) pk[j] = pack_exp4(na[j]);
-                    pk[4] = pack_exp4(nbl);
-                    pk[5] = pack_exp4(nbh);
+                    for (int j = 0; j < 4; ++j) pk[j] = ue8m0_pack4(na[j]);
+                    pk[4] = ue8m0_pack4(nbl);
+                    pk[5] = ue8m0_pack4(nbh);
                     ok = put(__byte_perm(pk[0], 0, 0x0000), __byte_perm(pk[1], 0, 0x0000), __byte_perm(pk[2], 0, 0x0000),
                              __byte_perm(pk[3], 0, 0x0000), __byte_perm(pk[4], 0, 0x0000), __byte_perm(pk[5], 0, 0x0000));
                     // the next group's loads go out only after the arrive above, which has release semantics and
@@ -267,8 +258,8 @@ grouped_gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const
                 n1[4] = __ldg(bs_lo + 1); n1[5] = __ldg(bs_hi + 1);
             }
             for (int kb = 0; ok && kb < kblocks; ++kb) {
-                ok = put(ue8m0_word2(c[0]), ue8m0_word2(c[1]), ue8m0_word2(c[2]), ue8m0_word2(c[3]), ue8m0_word2(c[4]),
-                         ue8m0_word2(c[5]));
+                ok = put(ue8m0_word(c[0]), ue8m0_word(c[1]), ue8m0_word(c[2]), ue8m0_word(c[3]), ue8m0_word(c[4]),
+                         ue8m0_word(c[5]));
 #pragma unroll
                 for (int j = 0; j < 6; ++j) c[j] = n1[j];
                 if (kb + 2 < kblocks) {

@@ -248,3 +248,36 @@ def test_low_latency_ops_with_tensor_parallel_pair():
     for r, (st, val) in res.items():
         assert st == "ok", val
         assert val == 0.0
+
+
+def test_fp16_activations_are_accepted_and_returned_as_fp16():
+    """The reference's fused op and low-latency ops take bf16 or fp16 rows (fused_deep_moe.cpp:17-19).  One rank on
+    the CPU: fp16 input gives fp16 output equal to the bf16 path's result (the layer computes on bf16 rows)."""
+    import torch
+    import umdk_original_b200 as u
+    from umdk_original_b200.ops import reference as ref
+    ops = torch.ops.umdk_cam_op_lib
+    t, h, e, k, inter = 16, 256, 4, 2, 128
+    g = torch.Generator().manual_seed(0)
+    buf = u.Buffer(None, u.CamConfig(num_experts=e, max_tokens=t, hidden=h, topk=k, ll_max_tokens=t), name="h16",
+                   device=torch.device("cpu"))
+    x = torch.randn(t, h, generator=g).to(torch.bfloat16)   # values both 16-bit formats hold exactly after this cast
+    x = (x.float() * 0.5).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(e, generator=g)[:k] for _ in range(t)])
+    w = torch.softmax(torch.randn(t, k, generator=g), -1)
+    w1q, s1 = ref.quant_fp8_128x128(torch.randn(e, 2 * inter, h, generator=g) * 0.05, True)
+    w2q, s2 = ref.quant_fp8_128x128(torch.randn(e, h, inter, generator=g) * 0.05, True)
+    outs = {}
+    for dt in (torch.bfloat16, torch.float16):
+        out, nums = ops.fused_deep_moe(x.to(dt), idx, [w1q], [s1], [w2q], [s2], w, None, None, "h16", 1, 0, e, 0, 0, 4, 0)
+        assert out.dtype == dt and out.shape == (t, h)
+        outs[dt] = out.float()
+        idx32 = idx.to(torch.int32)
+        r = ops.moe_dispatch_shmem(x.to(dt), idx32, None, None, 1, 0, e, 1, 0, 0, 0, 0, 0, 0, 1, buf.handle)
+        o = ops.moe_combine_shmem(r[0], idx32, r[2], r[4], w, None, None, None, None, None, None, 1, 0, e, 1, 0, 0, 0, 0,
+                                  0, 0, buf.handle, 0, 0)
+        assert r[0].dtype == dt and o.dtype == dt
+    # bf16 rows survive the trip through fp16 here (|x| < 4, 8 mantissa bits fit in fp16's 11), so both runs saw the
+    # same rows; the fp16 result is the bf16 result rounded once more
+    assert (outs[torch.float16] - outs[torch.bfloat16]).abs().max() <= 1e-2 * outs[torch.bfloat16].abs().max()
+    buf.destroy()

@@ -223,6 +223,11 @@ def _fused_deep_moe_cpu(x, expertIds, gmm1PermutedWeight, gmm1PermutedWeightScal
                            "applies smooth scales)")
     g = _reg().by_name(groupEp)
     be = _backend()
+    # fp16 activations are accepted like bf16 ones (fused_deep_moe.cpp:17-19 of the reference): the layer computes on
+    # bf16 rows, as the CUDA implementation does, and the result comes back in the caller's dtype
+    in_dtype = x.dtype
+    if x.dtype == torch.float16:
+        x = x.to(torch.bfloat16)
     w1, s1 = _stack(gmm1PermutedWeight), _stack(gmm1PermutedWeightScale)
     w2, s2 = _stack(gmm2Weight), _stack(gmm2WeightScale)
     el = moeExpertNum // epRankSize
@@ -262,7 +267,7 @@ def _fused_deep_moe_cpu(x, expertIds, gmm1PermutedWeight, gmm1PermutedWeightScal
             if b > a:
                 y[a:b] = ref.swiglu_mlp_fp32(rx[a:b], w1[le], w2[le]).to(x.dtype)
     out = be.combine(g, y, src, ids, expertScales, out_dtype=x.dtype)
-    return [out, per_e[:el].to(torch.int64)]
+    return [out.to(in_dtype), per_e[:el].to(torch.int64)]
 
 
 def _grouped_gemm_fp8_cpu(a_q, a_s, w_q, w_s, expert_offsets, ue8m0=False):
